@@ -1,0 +1,70 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Conventions used by every kernel file:
+//  * launchers are extern "C", take raw device pointers plus a cudaStream_t, allocate
+//    nothing and return a cudaError_t value as int (0 = launched);
+//  * the residual stream and all statistics (norms, softmax, rotation angles) are fp32;
+//    `T` is the activation / weight / cache element type (float or __nv_bfloat16);
+//  * sizes are runtime arguments unless a file says otherwise; a launcher that cannot
+//    handle a size returns ODI_ERR_UNSUPPORTED instead of computing something else.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define ODI_ERR_UNSUPPORTED 10001  // size or alignment the kernel refuses
+#define ODI_ERR_ARGUMENT 10002     // inconsistent arguments
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// Round a float to the precision of T and back: marks the places where an activation
+// is materialised in the model dtype.
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f<T>(from_f<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` is
+// 33 floats of shared memory.  The order of additions is fixed by the thread layout.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Position of key `pos` inside a sequence's page list.  A group that keeps every key
+// has ring_pages == 0; a windowed group keeps a ring of ring_pages pages per sequence.
+__device__ __forceinline__ int page_slot_of(int pos, int page_size, int ring_pages) {
+  int p = pos / page_size;
+  return ring_pages > 0 ? p % ring_pages : p;
+}

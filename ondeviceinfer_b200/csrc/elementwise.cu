@@ -1,0 +1,252 @@
+// Memory-bound kernels of a decoder step: embedding gather, RMSNorm, the fused
+// per-head Q/K norm + rotary embedding + key/value cache write, the gated activation
+// and the residual add.  Each is written for both element types (dtype 0 = float,
+// 1 = bf16); statistics, angles and the residual stream are fp32 in both.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------
+// Embedding: hidden[t, :] = table[ids[t], :], widened to the fp32 residual stream.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ hidden, int H) {
+  const int t = blockIdx.x;
+  const T* row = table + (size_t)ids[t] * H;
+  float* out = hidden + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_f<T>(row[i]);
+}
+
+extern "C" int odi_embed(const void* table, const int* ids, float* hidden, int n, int H, int dtype,
+                         cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (dtype == 0) embed_kernel<float><<<n, threads, 0, stream>>>((const float*)table, ids, hidden, H);
+  else embed_kernel<bf16><<<n, threads, 0, stream>>>((const bf16*)table, ids, hidden, H);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// RMSNorm over fp32 rows: y = x * rsqrt(mean(x^2) + eps) rounded to T, then
+// out = weight * y rounded to T (the order of the reference: normalise in fp32, cast,
+// scale).  `rows` (optional) gathers input rows, so the final norm runs only on the
+// positions whose logits are wanted.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  T* o = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float y = round_to<T>(xr[i] * inv);
+    o[i] = from_f<T>(w[i] * y);
+  }
+}
+
+extern "C" int odi_rmsnorm(const float* x, const float* w, void* out, const int* rows, int n, int H,
+                           float eps, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (dtype == 0) rmsnorm_kernel<float><<<n, threads, 0, stream>>>(x, w, (float*)out, rows, H, eps);
+  else rmsnorm_kernel<bf16><<<n, threads, 0, stream>>>(x, w, (bf16*)out, rows, H, eps);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Fused head preparation.  Input: packed projections qkv[t, (nq + 2 nkv) * d] (query
+// heads, then key heads, then value heads).  One warp per (token, head):
+//   query / key heads: optional RMSNorm over d with one [d] weight for all heads,
+//                      optional half-split rotary embedding with the step's fp32
+//                      cos/sin tables [token, rot_dim / 2];
+//   query heads go to q_out[t, h, :]; key and value heads go to the cache page that
+//   holds the token's position (value heads are copied as they are).
+// Cache layout: pool[page][kv_head][row][d], row = position % page_size.
+// write_kv == 0 skips the key/value heads (a layer that reads another layer's cache).
+// ---------------------------------------------------------------------------------
+struct HeadPrepArgs {
+  const void* qkv;
+  void* q_out;
+  void* k_pool;
+  void* v_pool;
+  const float* q_norm_w;  // null: no norm
+  const float* k_norm_w;
+  const float* cos_t;     // null: no rotation; [n_tokens, rot_dim / 2]
+  const float* sin_t;
+  const int* tok_seq;
+  const int* tok_pos;
+  const int* page_start;
+  const int* page_ids;
+  int n_tokens, nq, nkv, d, rot_dim, page_size, ring_pages, write_kv;
+  float eps;
+};
+
+template <typename T, int MAXP>
+__global__ void head_prep_kernel(HeadPrepArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long)a.n_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item % heads);
+  const int d = a.d, half = a.rot_dim >> 1;
+  const T* src = (const T*)a.qkv + (size_t)t * (a.nq + 2 * a.nkv) * d + (size_t)h * d;
+  const int kind = h < a.nq ? 0 : (h < a.nq + a.nkv ? 1 : 2);  // 0 q, 1 k, 2 v
+  const int pos = a.tok_pos[t];
+
+  T* dst;
+  if (kind == 0) {
+    dst = (T*)a.q_out + ((size_t)t * a.nq + h) * d;
+  } else {
+    const int hk = kind == 1 ? h - a.nq : h - a.nq - a.nkv;
+    const int s = a.tok_seq[t];
+    const int page = a.page_ids[a.page_start[s] + page_slot_of(pos, a.page_size, a.ring_pages)];
+    T* pool = (T*)(kind == 1 ? a.k_pool : a.v_pool);
+    dst = pool + (((size_t)page * a.nkv + hk) * a.page_size + (pos % a.page_size)) * d;
+  }
+  if (kind == 2) {
+    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    return;
+  }
+  // Element i of the head lives in lane i % 32, register i / 32.
+  float x[MAXP];
+  float ss = 0.f;
+#pragma unroll
+  for (int r = 0; r < MAXP; ++r) {
+    const int i = lane + 32 * r;
+    x[r] = i < d ? to_f<T>(src[i]) : 0.f;
+    ss += x[r] * x[r];
+  }
+  const float* w = kind == 0 ? a.q_norm_w : a.k_norm_w;
+  if (w != nullptr) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)d + a.eps);
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) {
+      const int i = lane + 32 * r;
+      if (i < d) x[r] = round_to<T>(w[i] * round_to<T>(x[r] * inv));
+    }
+  }
+  if (a.cos_t != nullptr) {
+    // Pair (i, i + half) for i < half.  The partner of element i sits in another lane
+    // and register unless half is a multiple of 32, so go through shared memory.
+    __shared__ float stage[4][32 * MAXP];
+    float* st = stage[threadIdx.x >> 5];
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) st[lane + 32 * r] = x[r];
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) {
+      const int i = lane + 32 * r;
+      if (i < a.rot_dim) {
+        const int f = i < half ? i : i - half;
+        const float cs = a.cos_t[(size_t)t * half + f], sn = a.sin_t[(size_t)t * half + f];
+        const float other = i < half ? -st[i + half] : st[i - half];
+        x[r] = x[r] * cs + other * sn;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < MAXP; ++r) {
+    const int i = lane + 32 * r;
+    if (i < d) dst[i] = from_f<T>(x[r]);
+  }
+}
+
+extern "C" int odi_head_prep(const HeadPrepArgs* args, int dtype, cudaStream_t stream) {
+  HeadPrepArgs a = *args;
+  if (a.n_tokens <= 0) return 0;
+  if (a.d > 512 || a.d <= 0 || (a.rot_dim & 1) || a.rot_dim > a.d) return ODI_ERR_UNSUPPORTED;
+  const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
+  const long items = (long)a.n_tokens * heads;
+  const int blocks = (int)((items + 3) / 4);
+#define ODI_LAUNCH(T, P) head_prep_kernel<T, P><<<blocks, 128, 0, stream>>>(a)
+  if (dtype == 0) {
+    if (a.d <= 128) ODI_LAUNCH(float, 4); else if (a.d <= 256) ODI_LAUNCH(float, 8); else ODI_LAUNCH(float, 16);
+  } else {
+    if (a.d <= 128) ODI_LAUNCH(bf16, 4); else if (a.d <= 256) ODI_LAUNCH(bf16, 8); else ODI_LAUNCH(bf16, 16);
+  }
+#undef ODI_LAUNCH
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Gated activation on concatenated projections gu[t, 0:I] = gate, gu[t, I:2I] = up:
+// out[t, i] = silu(gate) * up, computed in fp32 and rounded once.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long n, int I) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * I) return;
+  const long t = idx / I;
+  const int i = (int)(idx % I);
+  const float g = to_f<T>(gu[t * 2 * I + i]);
+  const float u = to_f<T>(gu[t * 2 * I + I + i]);
+  out[idx] = from_f<T>(g / (1.f + expf(-g)) * u);
+}
+
+extern "C" int odi_silu_mul(const void* gu, void* out, int n, int I, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long total = (long)n * I;
+  const int blocks = (int)((total + 255) / 256);
+  if (dtype == 0) silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, n, I);
+  else silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, n, I);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Residual add into the fp32 stream: hidden += y.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ hidden, const T* __restrict__ y, long n) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < n) hidden[idx] += to_f<T>(y[idx]);
+}
+
+extern "C" int odi_residual_add(float* hidden, const void* y, long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256);
+  if (dtype == 0) residual_add_kernel<float><<<blocks, 256, 0, stream>>>(hidden, (const float*)y, n);
+  else residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(hidden, (const bf16*)y, n);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Widen rows to fp32 (logits of a bf16 matrix product returned as fp32).
+// ---------------------------------------------------------------------------------
+__global__ void widen_kernel(const bf16* __restrict__ x, float* __restrict__ out, long n) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < n) out[idx] = __bfloat162float(x[idx]);
+}
+
+extern "C" int odi_widen(const void* x, float* out, long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  widen_kernel<<<(int)((n + 255) / 256), 256, 0, stream>>>((const bf16*)x, out, n);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Rotary tables of a step: cos/sin[t, i] of position[t] * inv_freq[i], evaluated in
+// fp32 with the full-range sincosf.  One table serves every layer of the step.
+// ---------------------------------------------------------------------------------
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)n * half) return;
+  const int t = (int)(idx / half), i = (int)(idx % half);
+  float sn, cs;
+  sincosf((float)tok_pos[t] * inv_freq[i], &sn, &cs);
+  cos_t[idx] = cs;
+  sin_t[idx] = sn;
+}
+
+extern "C" int odi_rope_table(const float* inv_freq, const int* tok_pos, float* cos_t, float* sin_t, int n,
+                              int half, cudaStream_t stream) {
+  if (n <= 0 || half <= 0) return 0;
+  const long total = (long)n * half;
+  rope_table_kernel<<<(int)((total + 255) / 256), 256, 0, stream>>>(inv_freq, tok_pos, cos_t, sin_t, n, half);
+  return launch_status();
+}

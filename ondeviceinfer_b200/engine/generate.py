@@ -1,0 +1,127 @@
+"""The generation loop above the step function.
+
+Requests are lists of token ids.  They are served in batches: the prompts of a batch
+run in one step, then every live sequence advances by one token per step; a sequence
+ends when it produces a stop token (which is kept) or reaches ``max_new_tokens`` (which
+counts the token the prompt produces, as ondeviceinfer/generation.py:46-59 does); its
+slot is given back at once and the batch goes on without it.  When a batch is finished
+the next one starts, on the same cache, until every request is served.  The reference's
+loop is batch 1 and greedy only (ondeviceinfer/generation.py:39-40,47); batching, stop
+per sequence and temperature sampling are this library's.
+
+The loop talks to the model through four callables (``alloc``, ``free``, ``step``,
+``sample``), so its decisions can be tested without a GPU.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+
+@dataclass
+class GenerationResult:
+    """``generated_ids[r]`` are the new tokens of request ``r``; ``token_ids[r]`` is its
+    prompt followed by them.  Times are wall-clock seconds with the device synchronised;
+    ``decode_tokens_per_second`` counts the tokens produced by decode steps only, as
+    ondeviceinfer/generation.py:22-25 does."""
+
+    token_ids: List[List[int]]
+    generated_ids: List[List[int]]
+    finish_reasons: List[str]
+    prefill_seconds: float
+    decode_seconds: float
+    decode_steps: int = 0
+    batches: List[List[int]] = field(default_factory=list)
+
+    @property
+    def decode_tokens(self) -> int:
+        return sum(max(0, len(g) - 1) for g in self.generated_ids)
+
+    @property
+    def decode_tokens_per_second(self) -> float:
+        return self.decode_tokens / self.decode_seconds if self.decode_seconds > 0 else 0.0
+
+
+def plan_batches(prompt_lengths: Sequence[int], max_new_tokens: int, *, max_seqs: int, max_tokens: int,
+                 page_size: int) -> List[List[int]]:
+    """Cut the requests, in order, into batches that fit the cache: at most ``max_seqs``
+    sequences, and room for every sequence at its longest (prompt + max_new_tokens - 1
+    cached positions, rounded up to whole pages)."""
+    def footprint(n: int) -> int:
+        longest = n + max(max_new_tokens - 1, 0)
+        return -(-longest // page_size) * page_size
+
+    batches: List[List[int]] = []
+    current: List[int] = []
+    used = 0
+    for r, n in enumerate(prompt_lengths):
+        if n <= 0:
+            raise ValueError(f"request {r} has an empty prompt")
+        need = footprint(n)
+        if need > max_tokens:
+            raise ValueError(f"request {r} needs room for {need} tokens, the cache holds {max_tokens}")
+        if current and (len(current) >= max_seqs or used + need > max_tokens):
+            batches.append(current)
+            current, used = [], 0
+        current.append(r)
+        used += need
+    if current:
+        batches.append(current)
+    return batches
+
+
+def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
+                      alloc: Callable[[], int], free: Callable[[int], None],
+                      step: Callable[[List[int], List[List[int]]], object],
+                      sample: Callable[[object, List[int], List[int]], List[int]],
+                      batches: Sequence[Sequence[int]], stop_token_ids: Sequence[int] = (),
+                      synchronize: Callable[[], None] = lambda: None) -> GenerationResult:
+    """``step(slots, token_runs)`` returns the logits at each run's last token;
+    ``sample(logits, request_indices, step_numbers)`` returns one token per row."""
+    if max_new_tokens <= 0:
+        raise ValueError("max_new_tokens must be positive")
+    stop = set(int(t) for t in stop_token_ids)
+    generated: List[List[int]] = [[] for _ in prompts]
+    reasons = ["" for _ in prompts]
+    prefill_seconds = decode_seconds = 0.0
+    decode_steps = 0
+    for batch in batches:
+        live = list(batch)
+        slots = {r: alloc() for r in live}
+        try:
+            synchronize()
+            start = time.perf_counter()
+            logits = step([slots[r] for r in live], [list(prompts[r]) for r in live])
+            tokens = sample(logits, live, [0] * len(live))
+            synchronize()
+            prefill_seconds += time.perf_counter() - start
+            start = time.perf_counter()
+            while True:
+                still = []
+                for r, tok in zip(live, tokens):
+                    generated[r].append(int(tok))
+                    if int(tok) in stop:
+                        reasons[r] = "stop"
+                    elif len(generated[r]) >= max_new_tokens:
+                        reasons[r] = "length"
+                    else:
+                        still.append(r)
+                        continue
+                    free(slots.pop(r))
+                live = still
+                if not live:
+                    break
+                logits = step([slots[r] for r in live], [[generated[r][-1]] for r in live])
+                tokens = sample(logits, live, [len(generated[r]) for r in live])
+                decode_steps += 1
+            synchronize()
+            decode_seconds += time.perf_counter() - start
+        finally:
+            for slot in slots.values():
+                free(slot)
+    return GenerationResult(
+        token_ids=[list(p) + g for p, g in zip(prompts, generated)], generated_ids=generated,
+        finish_reasons=reasons, prefill_seconds=prefill_seconds, decode_seconds=decode_seconds,
+        decode_steps=decode_steps, batches=[list(b) for b in batches])

@@ -1,0 +1,265 @@
+"""Python launchers of the CUDA kernels: thin, checked, allocation-free where the caller gives the output.
+
+Every function takes CUDA tensors, checks what the kernel assumes (device, dtype,
+contiguity, sizes), launches on the current stream and raises :class:`KernelError`
+with the CUDA error text if the launch failed.  There is no CPU path: on a machine
+without a GPU, or without the compiled libraries, these functions raise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_float, c_int, c_long, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+ODI_ERR_UNSUPPORTED = 10001
+ODI_ERR_ARGUMENT = 10002
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _cuda_error_text(code: int) -> str:
+    if code == ODI_ERR_UNSUPPORTED:
+        return "the kernel does not take these sizes or this alignment"
+    if code == ODI_ERR_ARGUMENT:
+        return "inconsistent arguments"
+    try:
+        rt = ctypes.CDLL("libcudart.so.12")
+        rt.cudaGetErrorString.restype = ctypes.c_char_p
+        return rt.cudaGetErrorString(code).decode()
+    except OSError:
+        return f"CUDA error {code}"
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_cuda_error_text(code)} (code {code})")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+
+
+# ------------------------------------------------------------------------------ elementwise
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, hidden: torch.Tensor) -> None:
+    """hidden[t, :] = table[ids[t], :] into the fp32 residual stream."""
+    _require(table, "table", ndim=2)
+    _require(ids, "ids", torch.int32, 1)
+    _require(hidden, "hidden", torch.float32, 2)
+    if hidden.shape != (ids.numel(), table.shape[1]):
+        raise KernelError(f"hidden is {tuple(hidden.shape)}, expected {(ids.numel(), table.shape[1])}")
+    lib = load_library("elementwise")
+    _check(lib.odi_embed(_ptr(table), _ptr(ids), _ptr(hidden), c_int(ids.numel()), c_int(table.shape[1]),
+                         c_int(dtype_code(table.dtype)), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[i] = weight * cast(x[r_i] * rsqrt(mean(x[r_i]^2) + eps)), r_i = rows[i] or i."""
+    _require(x, "x", torch.float32, 2)
+    _require(weight, "weight", torch.float32, 1)
+    _require(out, "out", ndim=2)
+    n = out.shape[0]
+    H = x.shape[1]
+    if weight.numel() != H or out.shape[1] != H:
+        raise KernelError(f"rmsnorm sizes disagree: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if rows is not None:
+        _require(rows, "rows", torch.int32, 1)
+        if rows.numel() != n:
+            raise KernelError("rows and out disagree")
+    elif x.shape[0] != n:
+        raise KernelError("x and out disagree")
+    lib = load_library("elementwise")
+    _check(lib.odi_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), _ptr(rows), c_int(n), c_int(H), c_float(eps),
+                           c_int(dtype_code(out.dtype)), _stream()), "rmsnorm")
+
+
+class _HeadPrepArgs(Structure):
+    _fields_ = [("qkv", c_void_p), ("q_out", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p),
+                ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("cos_t", c_void_p), ("sin_t", c_void_p),
+                ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("page_start", c_void_p), ("page_ids", c_void_p),
+                ("n_tokens", c_int), ("nq", c_int), ("nkv", c_int), ("d", c_int), ("rot_dim", c_int),
+                ("page_size", c_int), ("ring_pages", c_int), ("write_kv", c_int), ("eps", c_float)]
+
+
+def rope_table(inv_freq: torch.Tensor, tok_pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor) -> None:
+    """cos_t/sin_t[t, i] = cos/sin(tok_pos[t] * inv_freq[i]) in fp32."""
+    _require(inv_freq, "inv_freq", torch.float32, 1)
+    _require(tok_pos, "tok_pos", torch.int32, 1)
+    _require(cos_t, "cos_t", torch.float32, 2)
+    _require(sin_t, "sin_t", torch.float32, 2)
+    n, half = tok_pos.numel(), inv_freq.numel()
+    if cos_t.shape != (n, half) or sin_t.shape != (n, half):
+        raise KernelError("rope tables must be [tokens, rot_dim / 2]")
+    lib = load_library("elementwise")
+    _check(lib.odi_rope_table(_ptr(inv_freq), _ptr(tok_pos), _ptr(cos_t), _ptr(sin_t), c_int(n), c_int(half),
+                              _stream()), "rope_table")
+
+
+def head_prep(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, cos_t, sin_t, tok_seq, tok_pos, page_start,
+              page_ids, *, nq: int, nkv: int, d: int, rot_dim: int, page_size: int, ring_pages: int,
+              write_kv: bool, eps: float) -> None:
+    """Per-head Q/K RMSNorm (optional), rotary embedding (optional) and cache write, fused."""
+    n = qkv.shape[0]
+    _require(qkv, "qkv", ndim=2)
+    _require(q_out, "q_out", qkv.dtype)
+    if qkv.shape[1] != (nq + 2 * nkv) * d or q_out.numel() != n * nq * d:
+        raise KernelError(f"head_prep sizes disagree: qkv {tuple(qkv.shape)}, nq={nq}, nkv={nkv}, d={d}")
+    if write_kv:
+        _require(k_pool, "k_pool", qkv.dtype)
+        _require(v_pool, "v_pool", qkv.dtype)
+    for name, w in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w)):
+        if w is not None:
+            _require(w, name, torch.float32, 1)
+            if w.numel() != d:
+                raise KernelError(f"{name} has {w.numel()} entries, head_dim is {d}")
+    if cos_t is not None:
+        _require(cos_t, "cos_t", torch.float32, 2)
+        _require(sin_t, "sin_t", torch.float32, 2)
+        if cos_t.shape != (n, rot_dim // 2) or sin_t.shape != cos_t.shape:
+            raise KernelError("rope tables must be [tokens, rot_dim / 2]")
+    args = _HeadPrepArgs(_ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w), _ptr(k_norm_w),
+                         _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq), _ptr(tok_pos), _ptr(page_start), _ptr(page_ids),
+                         n, nq, nkv, d, rot_dim, page_size, ring_pages, 1 if write_kv else 0, eps)
+    lib = load_library("elementwise")
+    _check(lib.odi_head_prep(byref(args), c_int(dtype_code(qkv.dtype)), _stream()), "head_prep")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _require(gate_up, "gate_up", ndim=2)
+    _require(out, "out", gate_up.dtype, 2)
+    n, I = out.shape
+    if gate_up.shape != (n, 2 * I):
+        raise KernelError(f"silu_mul sizes disagree: {tuple(gate_up.shape)} -> {tuple(out.shape)}")
+    lib = load_library("elementwise")
+    _check(lib.odi_silu_mul(_ptr(gate_up), _ptr(out), c_int(n), c_int(I), c_int(dtype_code(out.dtype)), _stream()),
+           "silu_mul")
+
+
+def residual_add(hidden: torch.Tensor, y: torch.Tensor) -> None:
+    """hidden (fp32) += y."""
+    _require(hidden, "hidden", torch.float32)
+    _require(y, "y")
+    if hidden.numel() != y.numel():
+        raise KernelError("residual_add sizes disagree")
+    lib = load_library("elementwise")
+    _check(lib.odi_residual_add(_ptr(hidden), _ptr(y), c_long(hidden.numel()), c_int(dtype_code(y.dtype)), _stream()),
+           "residual_add")
+
+
+def widen(x: torch.Tensor, out: torch.Tensor) -> None:
+    _require(x, "x", torch.bfloat16)
+    _require(out, "out", torch.float32)
+    lib = load_library("elementwise")
+    _check(lib.odi_widen(_ptr(x), _ptr(out), c_long(x.numel()), _stream()), "widen")
+
+
+# ------------------------------------------------------------------------------ matrix products
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> None:
+    """out[M,N] = a[M,K] w[N,K]^T (+ residual) in true fp32; residual may be ``out`` itself."""
+    _require(a, "a", torch.float32, 2)
+    _require(w, "w", torch.float32, 2)
+    _require(out, "out", torch.float32, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm sizes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if residual is not None:
+        _require(residual, "residual", torch.float32, 2)
+        if residual.shape != out.shape:
+            raise KernelError("residual and out disagree")
+    lib = load_library("gemm_f32")
+    _check(lib.odi_gemm_f32(_ptr(a), _ptr(w), _ptr(out), _ptr(residual), c_int(M), c_int(N), c_int(K),
+                            c_int(K), c_int(K), c_int(N), c_int(N), _stream()), "gemm_f32")
+
+
+# ------------------------------------------------------------------------------ attention
+
+
+class _AttnArgs(Structure):
+    _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p),
+                ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
+                ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("page_size", c_int),
+                ("ring_pages", c_int), ("window", c_int), ("splits", c_int), ("bq", c_int),
+                ("head_chunks", c_int), ("scale", c_float)]
+
+
+SIMT_HEAD_DIMS = tuple(range(16, 513, 16))
+
+
+def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
+                   nq: int, nkv: int, d: int, page_size: int, ring_pages: int, window: int, scale: float,
+                   splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+    """Causal GQA over the paged cache for any mixture of prompt and decode sequences."""
+    if d not in SIMT_HEAD_DIMS:
+        raise KernelError(f"attention takes head sizes in steps of 16 up to 512, not {d}")
+    _require(q, "q")
+    _require(out, "out", q.dtype)
+    _require(k_pool, "k_pool", q.dtype)
+    _require(v_pool, "v_pool", q.dtype)
+    n_tokens = q.numel() // (nq * d)
+    if out.numel() != q.numel():
+        raise KernelError("q and out disagree")
+    if splits > 1:
+        need = n_tokens * nq * splits * (d + 2)
+        if partial is None or partial.numel() < need or partial.dtype != torch.float32:
+            raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
+    args = _AttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
+                     _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, page_size, ring_pages, window, splits,
+                     0, 0, scale)
+    lib = load_library("attention_simt", {"ODI_HEAD_DIM": d})
+    _check(lib.odi_attention_simt(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(dtype_code(q.dtype)),
+                                  _stream()), "attention_simt")
+
+
+# ------------------------------------------------------------------------------ sampling
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, seed: int = 0,
+           streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> None:
+    """out[i] = argmax(logits[i]) if temperature == 0 else a draw from softmax(logits[i] / temperature)."""
+    _require(logits, "logits", torch.float32, 2)
+    _require(out, "out", torch.int32, 1)
+    n, V = logits.shape
+    if out.numel() < n:
+        raise KernelError("out is shorter than the number of rows")
+    if temperature > 0:
+        _require(streams, "streams", torch.int32, 1)
+        _require(steps, "steps", torch.int32, 1)
+    lib = load_library("sampling")
+    _check(lib.odi_sample(_ptr(logits), _ptr(out), c_int(n), c_int(V), c_int(V), c_float(temperature),
+                          c_ulonglong(seed & ((1 << 64) - 1)), _ptr(streams), _ptr(steps), _stream()), "sample")

@@ -1,0 +1,11 @@
+from .base import Part, Runtime, build_part, register_part
+from .linear import linear
+from . import norm, position, attention, mlp, block  # noqa: F401  (registers the built-in parts)
+from .attention import Attention
+from .block import PreNormBlock
+from .mlp import GatedMLP
+from .norm import RMSNorm
+from .position import NoPosition, Rotary
+
+__all__ = ["Part", "Runtime", "build_part", "register_part", "linear", "Attention", "PreNormBlock",
+           "GatedMLP", "RMSNorm", "NoPosition", "Rotary"]

@@ -1,0 +1,98 @@
+"""Grouped-query causal attention over the paged cache
+(ondeviceinfer/attention.py:88-177 of UESlubei/ondeviceinfer).
+
+Steps of ``forward``: one matrix product for the concatenated q, k, v projections; one
+fused kernel for the per-head Q/K RMSNorm, the rotary embedding and the cache write;
+attention over the cache pages of each sequence; the output projection with the
+residual add.  Head counts, head size, eps, window, scale and the position encoding are
+all fields of the spec.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache import PAGE_SIZE, KVNeed
+from ..config.specs import AttentionSpec
+from ..kernels import ops
+from ..weights.tensors import TensorDecl
+from .base import Part, build_part, register_part
+from .linear import linear
+
+
+class Attention(Part):
+    def __init__(self, spec: AttentionSpec) -> None:
+        super().__init__(spec)
+        if spec.num_heads % spec.num_kv_heads != 0:
+            raise ValueError("Q heads must be divisible by KV heads for GQA")
+        if spec.head_dim % 16 != 0 or not 16 <= spec.head_dim <= 512:
+            raise ValueError(f"head_dim={spec.head_dim}: the attention kernels take multiples of 16 up to 512")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError("window must be positive")
+        self.position = build_part(spec.position)
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
+
+    # ------------------------------------------------------------------ tensors
+
+    def tensor_decls(self):
+        s = self.spec
+        q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        decls = [TensorDecl(s.name("q"), (q, s.hidden_size)), TensorDecl(s.name("k"), (kv, s.hidden_size)),
+                 TensorDecl(s.name("v"), (kv, s.hidden_size)), TensorDecl(s.name("o"), (s.hidden_size, q))]
+        if s.qk_norm_eps is not None:
+            decls += [TensorDecl(s.name("q_norm"), (s.head_dim,), "one_plus_normal"),
+                      TensorDecl(s.name("k_norm"), (s.head_dim,), "one_plus_normal")]
+        return decls + self.position.tensor_decls()
+
+    def load(self, fetch, runtime) -> None:
+        s = self.spec
+        self.runtime = runtime
+        # q, k and v rows concatenated: one product yields [tokens, (nq + 2 nkv) * d]
+        self.w_qkv = torch.cat([fetch.matrix(s.name("q")), fetch.matrix(s.name("k")), fetch.matrix(s.name("v"))], 0)
+        self.w_o = fetch.matrix(s.name("o"))
+        self.q_norm = fetch.vector(s.name("q_norm")) if s.qk_norm_eps is not None else None
+        self.k_norm = fetch.vector(s.name("k_norm")) if s.qk_norm_eps is not None else None
+        self.position.load(fetch, runtime)
+
+    def cache_needs(self):
+        return (KVNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window),)
+
+    # ------------------------------------------------------------------ step
+
+    def forward(self, x, ctx, view, residual) -> None:
+        s = self.spec
+        n = x.shape[0]
+        group = view.kv_group
+        page_start, page_ids = ctx.page_table(group.index)
+        qkv = linear(x, self.w_qkv)
+        q = torch.empty((n, s.num_heads * s.head_dim), dtype=x.dtype, device=x.device)
+        tables = self.position.rotary_tables(ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        ops.head_prep(qkv, q, view.keys, view.values, self.q_norm, self.k_norm, cos, sin,
+                      ctx.tok_seq, ctx.tok_pos, page_start, page_ids,
+                      nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, rot_dim=self.position.rot_dim,
+                      page_size=PAGE_SIZE, ring_pages=group.ring_pages, write_kv=view.writes_kv,
+                      eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0)
+        o = torch.empty_like(q)
+        self.attend(q, o, ctx, view, page_start, page_ids)
+        linear(o, self.w_o, residual=residual)
+
+    def attend(self, q, o, ctx, view, page_start, page_ids) -> None:
+        s = self.spec
+        splits, partial = 1, None
+        if ctx.max_q_len == 1:
+            # decode: cut long key ranges so that enough blocks run side by side
+            work = ctx.n_seqs * s.num_kv_heads
+            splits = max(1, min(16, 296 // max(work, 1), (ctx.max_kv_len + 255) // 256))
+            if splits > 1:
+                partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.head_dim + 2),),
+                                      dtype=torch.float32, device=q.device)
+        ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
+                           n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
+                           d=s.head_dim, page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages,
+                           window=s.window or 0, scale=self.scale, splits=splits, partial=partial)
+
+
+register_part(AttentionSpec, Attention)

@@ -1,0 +1,38 @@
+"""Arrangement of norms, mixer and feed-forward in a layer."""
+
+from __future__ import annotations
+
+from ..config.specs import PreNormBlockSpec
+from .base import Part, build_part, register_part
+
+
+class PreNormBlock(Part):
+    """h += mixer(norm(h)); h += feed_forward(norm(h))  (ondeviceinfer/model.py:49-63)."""
+
+    def __init__(self, spec: PreNormBlockSpec) -> None:
+        super().__init__(spec)
+        self.mixer_norm = build_part(spec.mixer_norm)
+        self.mixer = build_part(spec.mixer)
+        self.ffn_norm = build_part(spec.ffn_norm)
+        self.ffn = build_part(spec.ffn)
+
+    def _children(self):
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+
+    def tensor_decls(self):
+        return [d for part in self._children() for d in part.tensor_decls()]
+
+    def load(self, fetch, runtime) -> None:
+        self.runtime = runtime
+        for part in self._children():
+            part.load(fetch, runtime)
+
+    def cache_needs(self):
+        return tuple(self.mixer.cache_needs())
+
+    def forward(self, hidden, ctx, view) -> None:
+        self.mixer.forward(self.mixer_norm(hidden), ctx, view, hidden)
+        self.ffn.forward(self.ffn_norm(hidden), ctx, hidden)
+
+
+register_part(PreNormBlockSpec, PreNormBlock)

@@ -1,0 +1,31 @@
+"""RMSNorm part (ondeviceinfer/layers.py:9-33 of UESlubei/ondeviceinfer)."""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import RMSNormSpec
+from ..kernels import ops
+from ..weights.tensors import TensorDecl
+from .base import Part, register_part
+
+
+class RMSNorm(Part):
+    """weight * cast(x * rsqrt(mean(x^2) + eps)): statistics in fp32, cast to the compute
+    dtype before the multiplication by the weight."""
+
+    def tensor_decls(self):
+        return [TensorDecl(self.spec.weight_name, (self.spec.size,), "one_plus_normal")]
+
+    def load(self, fetch, runtime) -> None:
+        self.runtime = runtime
+        self.weight = fetch.vector(self.spec.weight_name)
+
+    def __call__(self, x: torch.Tensor, rows=None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=x.device)
+        ops.rmsnorm(x, self.weight, self.spec.eps, out, rows)
+        return out
+
+
+register_part(RMSNormSpec, RMSNorm)
