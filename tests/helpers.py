@@ -1,0 +1,76 @@
+"""Shared helpers of the tests: tolerances, model folders in temporary directories."""
+
+import json
+from pathlib import Path
+
+import torch
+from safetensors.torch import save_file
+
+import plain_qwen3 as plain
+
+# Stated once, used everywhere.  fp32: the engine and the plain implementation follow the
+# same formulas in the same precision and differ by summation order only (observed
+# ~5e-7 on the tiny models).  bf16: the engine keeps fp32 accumulators and rounds once
+# per operation, the plain bf16 arithmetic rounds after every elementary operation
+# (observed ~5e-3 at |logit| ~ 1).
+F32_ATOL, F32_RTOL = 2e-5, 2e-5
+BF16_REL = 3e-2  # |d| <= BF16_REL * max(1, max |reference logit|)
+
+
+def assert_logits_close(actual: torch.Tensor, expected: torch.Tensor, dtype: str, what: str = "") -> None:
+    actual, expected = actual.float().cpu(), expected.float().cpu()
+    assert actual.shape == expected.shape, (what, actual.shape, expected.shape)
+    assert torch.isfinite(actual).all(), f"{what}: non-finite logits"
+    gap = (actual - expected).abs()
+    if dtype == "float32":
+        bad = gap > F32_ATOL + F32_RTOL * expected.abs()
+        assert not bad.any(), f"{what}: fp32 max |d| = {float(gap.max()):.3e} at {int(gap.argmax())}"
+    else:
+        limit = BF16_REL * max(1.0, float(expected.abs().max()))
+        assert float(gap.max()) <= limit, f"{what}: bf16 max |d| = {float(gap.max()):.3e} > {limit:.3e}"
+
+
+def write_model_folder(folder, cfg: dict, weights: dict) -> Path:
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    save_file({k: v.contiguous() for k, v in weights.items()}, str(folder / "model.safetensors"))
+    (folder / "config.json").write_text(json.dumps(cfg))
+    return folder
+
+
+CASES = {
+    "A": (plain.TINY_A, 0),
+    "B": (plain.TINY_B, 1),
+    "C": (plain.TINY_C, 2),
+}
+
+
+_MODELS = {}
+
+
+def engine_model(case: str, dtype: str, tmp_root):
+    """The engine's model for a tiny case, loaded once per test session from a folder
+    written into a temporary directory; returns (model, weights, config dictionary)."""
+    import ondeviceinfer_b200 as odi
+
+    key = (case, dtype)
+    if key not in _MODELS:
+        cfg, seed = CASES[case]
+        weights = plain.random_weights(cfg, seed)
+        folder = write_model_folder(Path(tmp_root) / f"model_{case}", cfg, weights)
+        _MODELS[key] = (odi.load_resident_model(folder, device="cuda:0", dtype=dtype), weights, cfg)
+    return _MODELS[key]
+
+
+_PLAIN = {}
+
+
+def plain_logits(case: str, tokens, dtype: str = "float32"):
+    """Whole-sequence logits of the plain implementation (memoised)."""
+    cfg, seed = CASES[case]
+    key = (case, tuple(tokens), dtype)
+    if key not in _PLAIN:
+        weights = plain.random_weights(cfg, seed)
+        _PLAIN[key] = plain.forward_logits(weights, cfg, list(tokens),
+                                           torch.float32 if dtype == "float32" else torch.bfloat16)
+    return _PLAIN[key]

@@ -1,0 +1,196 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16, under every
+way of cutting and batching the same requests."""
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import CASES, assert_logits_close, engine_model, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+# request lengths: one token, a page minus / exactly / plus one, several pages, odd sizes
+LENGTHS = {"A": [5, 11, 17, 64, 33, 100], "B": [1, 7, 30, 64, 65, 130, 63, 2], "C": [3, 200, 77, 129, 64, 31]}
+
+
+@pytest.fixture(scope="session")
+def tmp_root(tmp_path_factory):
+    return tmp_path_factory.mktemp("models")
+
+
+def requests_of(case):
+    cfg, seed = CASES[case]
+    return plain.random_prompts(cfg, LENGTHS[case], seed + 100)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "B", "C"])
+def test_each_request_alone_and_whole(case, dtype, tmp_root):
+    model, _, _ = engine_model(case, dtype, tmp_root)
+    cache = model.make_cache(max_tokens=256, max_seqs=1)
+    for r, tokens in enumerate(requests_of(case)):
+        slot = cache.alloc()
+        logits = model.step(cache, [slot], [tokens], "all")
+        assert logits.dtype == torch.float32 and logits.shape == (len(tokens), model.vocab_size)
+        assert_logits_close(logits, plain_logits(case, tokens), dtype, f"{case} request {r} whole")
+        assert cache.length(slot) == len(tokens)
+        cache.free(slot)
+    cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(case, dtype, tmp_root):
+    model, _, _ = engine_model(case, dtype, tmp_root)
+    cache = model.make_cache(max_tokens=256, max_seqs=1)
+    for r, tokens in enumerate(requests_of(case)):
+        expected = plain_logits(case, tokens)
+        cut = max(1, len(tokens) - 32)
+        slot = cache.alloc()
+        rows = [model.step(cache, [slot], [tokens[:cut]], "all")]
+        for t in range(cut, len(tokens)):
+            rows.append(model.step(cache, [slot], [[tokens[t]]], "last"))
+        assert_logits_close(torch.cat(rows), expected, dtype, f"{case} request {r} tail one by one")
+        cache.free(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "B", "C"])
+def test_batches_of_unequal_lengths_reuse_slots(case, dtype, tmp_root):
+    """Batches of three requests on a cache with three slots, one batch after another: the
+    prompts (all but the last d_i tokens, d_i unequal) in one step, then one token per live
+    request per step; shorter requests end earlier and give their slot back at once."""
+    model, _, _ = engine_model(case, dtype, tmp_root)
+    requests = requests_of(case)
+    cache = model.make_cache(max_tokens=3 * 256, max_seqs=3)
+    got = {r: [] for r in range(len(requests))}
+    seen_slots = []
+    for first in range(0, len(requests), 3):
+        batch = list(range(first, min(first + 3, len(requests))))
+        tails = {r: min(len(requests[r]) - 1, 3 + 7 * (r % 3)) for r in batch}
+        slots = {r: cache.alloc() for r in batch}
+        seen_slots.append(sorted(slots.values()))
+        prompts = [requests[r][:len(requests[r]) - tails[r]] for r in batch]
+        logits = model.step(cache, [slots[r] for r in batch], prompts, "all")
+        offset = 0
+        for r, p in zip(batch, prompts):
+            got[r].append(logits[offset:offset + len(p)])
+            offset += len(p)
+        fed = {r: len(p) for r, p in zip(batch, prompts)}
+        live = list(batch)
+        while True:
+            for r in [r for r in live if fed[r] == len(requests[r])]:
+                cache.free(slots.pop(r))
+                live.remove(r)
+            if not live:
+                break
+            logits = model.step(cache, [slots[r] for r in live], [[requests[r][fed[r]]] for r in live], "last")
+            for i, r in enumerate(live):
+                got[r].append(logits[i:i + 1])
+                fed[r] += 1
+        cache.check()
+    assert seen_slots[0] == seen_slots[1], "the second batch must run in the slots of the first"
+    for r, tokens in enumerate(requests):
+        assert_logits_close(torch.cat(got[r]), plain_logits(case, tokens), dtype, f"{case} request {r} batched")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_what_else_is_in_the_batch_changes_nothing(dtype, tmp_root):
+    """The same request alone, first of a batch, last of a batch, and in another slot:
+    bit-equal in 32-bit (each row's arithmetic does not depend on the batch)."""
+    model, _, _ = engine_model("B", dtype, tmp_root)
+    requests = requests_of("B")
+    target = requests[5]
+    cache = model.make_cache(max_tokens=1024, max_seqs=4)
+
+    def run(batch, which):
+        slots = [cache.alloc() for _ in batch]
+        logits = model.step(cache, slots, batch, "all")
+        start = sum(len(b) for b in batch[:which])
+        out = logits[start:start + len(batch[which])].clone()
+        for s in slots:
+            cache.free(s)
+        return out
+
+    alone = run([target], 0)
+    first = run([target, requests[3], requests[0]], 0)
+    last = run([requests[4], requests[6], requests[1], target], 3)
+    if dtype == "float32":
+        assert torch.equal(alone, first) and torch.equal(alone, last)
+    else:
+        expected = plain_logits("B", target)
+        assert_logits_close(first, expected, dtype, "first of a batch")
+        assert_logits_close(last, expected, dtype, "last of a batch")
+        assert_logits_close(first, alone, dtype, "batch against alone")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_across_pages(dtype, tmp_root):
+    """A 40-token prompt, then 300 tokens one by one: positions cross pages 64, 128, 192,
+    256, 320 and the decode kernels split their key range."""
+    model, _, cfg = engine_model("C", dtype, tmp_root)
+    tokens = plain.random_prompts(cfg, [340], 77)[0]
+    expected = plain_logits("C", tokens)
+    cache = model.make_cache(max_tokens=384, max_seqs=1)
+    slot = cache.alloc()
+    rows = [model.step(cache, [slot], [tokens[:40]], "all")]
+    for t in range(40, len(tokens)):
+        rows.append(model.step(cache, [slot], [[tokens[t]]], "last"))
+    assert_logits_close(torch.cat(rows), expected, dtype, "long decoding")
+    assert cache.length(slot) == 340 and cache.tokens_held == 384
+    cache.free(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "B"])
+def test_first_tokens_of_a_sequence(case, dtype, tmp_root):
+    """A sequence fed one token at a time from its very first token: positions 0, 1, 2, ..."""
+    model, _, cfg = engine_model(case, dtype, tmp_root)
+    tokens = plain.random_prompts(cfg, [6], 5)[0]
+    expected = plain_logits(case, tokens)
+    cache = model.make_cache(max_tokens=64, max_seqs=1)
+    slot = cache.alloc()
+    rows = [model.step(cache, [slot], [[t]], "last") for t in tokens]
+    assert_logits_close(torch.cat(rows), expected, dtype, "first tokens")
+    cache.free(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_chunks_of_a_few_tokens_and_chosen_places(dtype, tmp_root):
+    """Steps of several tokens on top of a cache (neither prompt nor single token), with
+    logits wanted at chosen places only, in a batch whose members bring unequal chunks."""
+    model, _, _ = engine_model("B", dtype, tmp_root)
+    requests = requests_of("B")
+    a, b = requests[5], requests[2]          # 130 and 30 tokens
+    cache = model.make_cache(max_tokens=512, max_seqs=2)
+    sa, sb = cache.alloc(), cache.alloc()
+    none = model.step(cache, [sa, sb], [a[:50], b[:10]], "none")
+    assert none.shape == (0, model.vocab_size)
+    logits = model.step(cache, [sa, sb], [a[50:90], b[10:13]], [[0, 39], [1]])
+    ea, eb = plain_logits("B", a), plain_logits("B", b)
+    assert_logits_close(logits, torch.stack([ea[50], ea[89], eb[11]]), dtype, "chunk on a cache")
+    logits = model.step(cache, [sb, sa], [b[13:], a[90:]], "last")
+    assert_logits_close(logits, torch.stack([eb[-1], ea[-1]]), dtype, "swapped order")
+    cache.free(sa)
+    cache.free(sb)
+
+
+def test_capacity_and_misuse_are_host_errors(tmp_root):
+    from ondeviceinfer_b200 import CacheCapacityError
+
+    model, _, _ = engine_model("A", "float32", tmp_root)
+    cache = model.make_cache(max_tokens=128, max_seqs=2)
+    slot = cache.alloc()
+    with pytest.raises(CacheCapacityError):
+        model.step(cache, [slot], [[1] * 129], "last")
+    assert cache.length(slot) == 0
+    with pytest.raises(ValueError):
+        model.step(cache, [slot], [[256]], "last")           # token id outside the vocabulary
+    with pytest.raises(ValueError):
+        model.step(cache, [slot + 1], [[1]], "last")         # slot not held
+    model.step(cache, [slot], [[1] * 128], "none")
+    with pytest.raises(CacheCapacityError):
+        model.step(cache, [slot], [[1]], "last")
+    cache.free(slot)
+    cache.check()

@@ -1,0 +1,320 @@
+"""Each CUDA kernel alone against a plain torch reference of the same operation, at sizes
+other than the tiny models': widths and vocabularies that are no power of two, head sizes
+16..256, any number of heads and groups, ragged batches."""
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from ondeviceinfer_b200.kernels import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def close(actual, expected, dtype, scale=1.0):
+    actual, expected = actual.float().cpu(), expected.float().cpu()
+    if dtype == "float32":
+        assert torch.allclose(actual, expected, atol=2e-5 * scale, rtol=2e-5), float((actual - expected).abs().max())
+    else:
+        limit = 2e-2 * max(1.0, float(expected.abs().max()))
+        assert float((actual - expected).abs().max()) <= limit, float((actual - expected).abs().max())
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("V,H,n", [(389, 80, 7), (1000, 4096, 3)])
+def test_embed(dtype, V, H, n):
+    torch.manual_seed(0)
+    table = torch.randn(V, H).to(DT[dtype]).to(DEV)
+    ids = torch.randint(0, V, (n,), dtype=torch.int32, device=DEV)
+    ids[0], ids[-1] = V - 1, 0
+    out = torch.empty(n, H, dtype=torch.float32, device=DEV)
+    ops.embed(table, ids, out)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.cpu().long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("H,eps", [(80, 1e-5), (1000, 1e-6), (4096, 3e-6), (5120, 1e-6)])
+def test_rmsnorm_and_row_gather(dtype, H, eps):
+    torch.manual_seed(1)
+    x = (torch.randn(9, H) * 3).to(DEV)
+    w = (1 + 0.1 * torch.randn(H)).to(DEV)
+    out = torch.empty(9, H, dtype=DT[dtype], device=DEV)
+    ops.rmsnorm(x, w, eps, out)
+    expected = plain.rms_norm(x.cpu().to(DT[dtype]), w.cpu().to(DT[dtype]), eps)
+    close(out, expected, dtype)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    picked = torch.empty(3, H, dtype=DT[dtype], device=DEV)
+    ops.rmsnorm(x, w, eps, picked, rows)
+    assert torch.equal(picked, out[rows.long()])
+
+
+def test_rope_table_matches_host_angles():
+    theta, dim = 1e6, 128
+    inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    pos = torch.tensor([0, 1, 63, 64, 4095, 40959], dtype=torch.int32)
+    cos = torch.empty(len(pos), dim // 2, dtype=torch.float32, device=DEV)
+    sin = torch.empty_like(cos)
+    ops.rope_table(inv_freq.to(DEV), pos.to(DEV), cos, sin)
+    ec, es = plain.rope_tables(pos, dim, theta, torch.float32)
+    assert torch.allclose(cos.cpu(), ec[:, :dim // 2], atol=2e-7, rtol=0)
+    assert torch.allclose(sin.cpu(), es[:, :dim // 2], atol=2e-7, rtol=0)
+
+
+def paged_setup(lengths, past, nkv, d, dtype, ring_pages=0, page=64, seed=0):
+    """Random keys/values for sequences with `past` cached and `lengths` new positions, laid
+    into shuffled pages.  Returns pools, index tensors and the dense per-sequence K/V."""
+    g = torch.Generator().manual_seed(seed)
+    n_seqs = len(lengths)
+    total = [p + t for p, t in zip(past, lengths)]
+    per_seq = [min(-(-n // page), ring_pages) if ring_pages else -(-n // page) for n in total]
+    n_pages = sum(per_seq) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    k_pool = torch.zeros(n_pages, nkv, page, d)
+    v_pool = torch.zeros(n_pages, nkv, page, d)
+    page_lists, dense = [], []
+    for s in range(n_seqs):
+        pages = [order.pop() for _ in range(per_seq[s])]
+        page_lists.append(pages)
+        k = torch.randn(nkv, total[s], d, generator=g)
+        v = torch.randn(nkv, total[s], d, generator=g)
+        dense.append((k, v))
+        for pos in range(total[s]):
+            slot = (pos // page) % ring_pages if ring_pages else pos // page
+            k_pool[pages[slot], :, pos % page] = k[:, pos]
+            v_pool[pages[slot], :, pos % page] = v[:, pos]
+    start = [0]
+    for pages in page_lists:
+        start.append(start[-1] + len(pages))
+    cu = [0]
+    for t in lengths:
+        cu.append(cu[-1] + t)
+    to = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return dict(k_pool=k_pool.to(DT[dtype]).to(DEV), v_pool=v_pool.to(DT[dtype]).to(DEV), dense=dense,
+                page_start=to(start), page_ids=to([p for l in page_lists for p in l]), cu_q=to(cu), past=to(past),
+                tok_seq=to([s for s, t in enumerate(lengths) for _ in range(t)]),
+                tok_pos=to([past[s] + i for s, t in enumerate(lengths) for i in range(t)]))
+
+
+def plain_attention(q, dense, lengths, past, nq, nkv, d, window, scale, dtype):
+    """softmax(q k^T * scale + mask) v per sequence; q [tokens, nq, d]."""
+    outs, offset, g = [], 0, nq // nkv
+    for s, t in enumerate(lengths):
+        k, v = dense[s]
+        k, v = k.to(DT[dtype]).float(), v.to(DT[dtype]).float()
+        qs = q[offset:offset + t].to(DT[dtype]).float().transpose(0, 1)          # [nq, t, d]
+        scores = qs @ k.repeat_interleave(g, 0).transpose(-1, -2) * scale
+        qpos = torch.arange(past[s], past[s] + t).unsqueeze(1)
+        kpos = torch.arange(past[s] + t).unsqueeze(0)
+        visible = kpos <= qpos
+        if window:
+            visible &= kpos > qpos - window
+        scores = scores.masked_fill(~visible, float("-inf"))
+        outs.append((torch.softmax(scores, -1) @ v.repeat_interleave(g, 0)).transpose(0, 1))
+        offset += t
+    return torch.cat(outs).reshape(-1, nq * d)
+
+
+ATTN_CASES = [
+    # d, nq, nkv, lengths, past, window, splits
+    (16, 4, 2, [5, 11, 17], [0, 0, 0], 0, 1),
+    (48, 6, 2, [1, 70, 33], [0, 0, 0], 0, 1),
+    (128, 5, 1, [1, 1, 1, 1], [300, 64, 63, 0], 0, 1),          # decode, ragged pasts
+    (128, 5, 1, [1, 1, 1, 1], [300, 64, 63, 0], 0, 4),          # the same with split keys
+    (128, 32, 1, [9], [120], 0, 1),                              # 32 query heads on one kv head
+    (64, 8, 8, [40, 3], [100, 200], 0, 1),                       # chunks on a cache, no grouping
+    (256, 2, 1, [20, 1], [0, 77], 0, 1),
+    (32, 3, 3, [130, 2], [0, 190], 50, 1),                       # window
+    (32, 6, 2, [1, 1], [400, 70], 50, 3),                        # window, decode, splits
+]
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("d,nq,nkv,lengths,past,window,splits", ATTN_CASES)
+def test_attention_simt(dtype, d, nq, nkv, lengths, past, window, splits):
+    torch.manual_seed(2)
+    setup = paged_setup(lengths, past, nkv, d, dtype)
+    n = sum(lengths)
+    q = torch.randn(n, nq, d)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.empty(n, nq * d, dtype=DT[dtype], device=DEV)
+    partial = torch.empty(n * nq * splits * (d + 2), dtype=torch.float32, device=DEV) if splits > 1 else None
+    ops.attention_simt(q.to(DT[dtype]).to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"],
+                       setup["past"], setup["page_start"], setup["page_ids"], n_seqs=len(lengths),
+                       max_q_len=max(lengths), nq=nq, nkv=nkv, d=d, page_size=64, ring_pages=0, window=window,
+                       scale=scale, splits=splits, partial=partial)
+    expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, window, scale, dtype)
+    close(out, expected, dtype, scale=4.0)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """Random data would hide a key that is skipped: make one far key the only one that
+    matters (its score stands out by a large margin) and ask for its value back."""
+    d, nq, nkv = 128, 4, 2
+    lengths, past = [1, 1, 300], [700, 64, 0]
+    setup = paged_setup(lengths, past, nkv, d, dtype, seed=3)
+    n = sum(lengths)
+    q = torch.randn(n, nq, d) * 0.1
+    targets = {0: 5, 1: 63, 2 + 299: 1}            # packed token -> the key position to find
+    for tok, key in targets.items():
+        seq = 0 if tok == 0 else (1 if tok == 1 else 2)
+        k, v = setup["dense"][seq]
+        direction = torch.nn.functional.normalize(k[:, key], dim=-1)       # [nkv, d]
+        q[tok] = direction.repeat_interleave(nq // nkv, 0) * 40.0
+    scale = 1.0 / math.sqrt(d)
+    out = torch.empty(n, nq * d, dtype=DT[dtype], device=DEV)
+    # the pools hold the rounded keys; keep the crafted queries as they are
+    for splits in (1, 5):
+        partial = torch.empty(n * nq * splits * (d + 2), dtype=torch.float32, device=DEV) if splits > 1 else None
+        ops.attention_simt(q.to(DT[dtype]).to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"],
+                           setup["past"], setup["page_start"], setup["page_ids"], n_seqs=3, max_q_len=300,
+                           nq=nq, nkv=nkv, d=d, page_size=64, ring_pages=0, window=0, scale=scale,
+                           splits=splits if max(lengths) == 1 else 1, partial=partial)
+        expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, 0, scale, dtype)
+        close(out, expected, dtype, scale=4.0)
+        for tok, key in targets.items():
+            seq = 0 if tok == 0 else (1 if tok == 1 else 2)
+            value = setup["dense"][seq][1][:, key].to(DT[dtype]).float().repeat_interleave(nq // nkv, 0).reshape(-1)
+            assert float((out[tok].float().cpu() - value).abs().max()) < 0.05, (tok, key)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("d,rot,nq,nkv,norm,ring", [(16, 16, 4, 2, True, 0), (128, 128, 8, 2, True, 0),
+                                                    (48, 32, 3, 1, False, 0), (256, 64, 2, 2, True, 0),
+                                                    (32, 32, 2, 1, True, 3), (64, 0, 2, 2, True, 0)])
+def test_head_prep(dtype, d, rot, nq, nkv, norm, ring):
+    """Per-head norm (or none), rotation of the first `rot` lanes (or none), cache write
+    into shuffled pages (or a ring of pages), against plain torch."""
+    torch.manual_seed(4)
+    lengths, past = [3, 1, 70], [0, 200, 10]
+    if ring:
+        lengths, past = [3, 1, 20], [0, 200, 100]
+    setup = paged_setup(lengths, past, nkv, d, dtype, ring_pages=ring, seed=5)
+    n = sum(lengths)
+    tdt = DT[dtype]
+    qkv = torch.randn(n, (nq + 2 * nkv) * d).to(tdt)
+    qw, kw = (1 + 0.1 * torch.randn(d)), (1 + 0.1 * torch.randn(d))
+    eps, theta = 1e-5, 10000.0
+    k_pool, v_pool = torch.zeros_like(setup["k_pool"]), torch.zeros_like(setup["v_pool"])
+    cos = sin = None
+    if rot:
+        inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+        cos = torch.empty(n, rot // 2, dtype=torch.float32, device=DEV)
+        sin = torch.empty_like(cos)
+        ops.rope_table(inv_freq.to(DEV), setup["tok_pos"], cos, sin)
+    q_out = torch.empty(n, nq * d, dtype=tdt, device=DEV)
+    ops.head_prep(qkv.to(DEV), q_out, k_pool, v_pool, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None,
+                  cos, sin, setup["tok_seq"], setup["tok_pos"], setup["page_start"], setup["page_ids"],
+                  nq=nq, nkv=nkv, d=d, rot_dim=rot, page_size=64, ring_pages=ring, write_kv=True, eps=eps)
+    # plain: norm in the model dtype's rounding, rotation on the first `rot` lanes
+    pos = setup["tok_pos"].cpu()
+    x = qkv.view(n, nq + 2 * nkv, d)
+    q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
+    if norm:
+        q, k = plain.rms_norm(q, qw.to(tdt), eps), plain.rms_norm(k, kw.to(tdt), eps)
+    if rot:
+        c, s = plain.rope_tables(pos, rot, theta, torch.float32)
+
+        def rotate(t):
+            t = t.float()
+            head = plain.apply_rope(t[..., :rot].transpose(0, 1), c, s).transpose(0, 1)
+            return torch.cat((head, t[..., rot:]), -1)
+
+        q, k = rotate(q), rotate(k)
+    close(q_out.view(n, nq, d), q, dtype)
+    page_start, page_ids = setup["page_start"].cpu(), setup["page_ids"].cpu()
+    seqs = setup["tok_seq"].cpu()
+    for t in range(n):
+        slot = int(pos[t]) // 64
+        slot = slot % ring if ring else slot
+        page = int(page_ids[int(page_start[int(seqs[t])]) + slot])
+        close(k_pool[page, :, int(pos[t]) % 64], k[t], dtype)
+        assert torch.equal(v_pool[page, :, int(pos[t]) % 64].cpu(), v[t])
+    written = (k_pool.float().abs().sum(-1) > 0).sum().item()
+    assert written == n * nkv, "keys were written to rows that no token owns"
+    # write_kv off: queries only, the cache is not touched
+    k2, v2 = torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+    q2 = torch.empty_like(q_out)
+    ops.head_prep(qkv.to(DEV), q2, k2, v2, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None,
+                  cos, sin, setup["tok_seq"], setup["tok_pos"], setup["page_start"], setup["page_ids"],
+                  nq=nq, nkv=nkv, d=d, rot_dim=rot, page_size=64, ring_pages=ring, write_kv=False, eps=eps)
+    assert torch.equal(q2, q_out) and float(k2.float().abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_silu_mul_and_residual_add(dtype):
+    torch.manual_seed(6)
+    n, I = 5, 208
+    gu = (torch.randn(n, 2 * I) * 3).to(DT[dtype])
+    out = torch.empty(n, I, dtype=DT[dtype], device=DEV)
+    ops.silu_mul(gu.to(DEV), out)
+    g, u = gu[:, :I].float(), gu[:, I:].float()
+    close(out, torch.nn.functional.silu(g) * u, dtype)
+    hidden = torch.randn(n, I)
+    y = torch.randn(n, I).to(DT[dtype])
+    h = hidden.clone().to(DEV)
+    ops.residual_add(h, y.to(DEV))
+    assert torch.equal(h.cpu(), hidden + y.float())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 389, 96), (7, 64, 6), (130, 257, 97), (64, 192, 160), (33, 5, 4096)])
+def test_gemm_f32_is_true_fp32_and_row_independent(M, N, K):
+    torch.manual_seed(7)
+    a, w = torch.randn(M, K), torch.randn(N, K)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_f32(a.to(DEV), w.to(DEV), out)
+    expected = (a.double() @ w.double().t()).float()
+    assert torch.allclose(out.cpu(), expected, atol=1e-6 * K, rtol=1e-5)
+    # a TF32 product would be off by ~1e-3 relative; make sure we are far below that
+    assert float((out.cpu() - expected).abs().max()) < 2e-5 * math.sqrt(K)
+    # a row's result does not depend on the other rows of the batch
+    single = torch.empty(1, N, device=DEV)
+    ops.gemm_f32(a[M // 2:M // 2 + 1].to(DEV), w.to(DEV), single)
+    assert torch.equal(single[0], out[M // 2])
+    # residual, in place
+    res = torch.randn(M, N)
+    r = res.clone().to(DEV)
+    ops.gemm_f32(a.to(DEV), w.to(DEV), r, r)
+    assert torch.allclose(r.cpu(), res + out.cpu(), atol=1e-6, rtol=1e-6)
+
+
+def test_sample_greedy_ties_and_temperature_against_plain():
+    torch.manual_seed(8)
+    V = 1237
+    logits = torch.randn(6, V) * 2
+    logits[0, 100] = logits[0, 900] = 50.0          # tie: the lower index wins
+    logits[1, V - 1] = 60.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), out, 0.0)
+    assert out.tolist() == [int(torch.argmax(l)) for l in logits] and out[0] == 100 and out[1] == V - 1
+    streams = torch.arange(6, dtype=torch.int32, device=DEV)
+    for temperature in (0.8, 0.1, 2.5):
+        for step in range(20):
+            steps = torch.full((6,), step, dtype=torch.int32, device=DEV)
+            ops.sample(logits.to(DEV), out, temperature, 11, streams, steps)
+            for r in range(6):
+                u = plain.uniform_draw(11, r, step)
+                expected = plain.sample(logits[r], temperature, u)
+                if out[r].item() != expected:
+                    # only a draw within rounding of a CDF step may land on the neighbour
+                    p = torch.softmax(logits[r].double() / temperature, 0).cumsum(0)
+                    assert abs(out[r].item() - expected) == 1 and float((p - u).abs().min()) < 1e-5
+
+
+def test_kernels_refuse_what_they_cannot_take():
+    x = torch.zeros(2, 8, device=DEV)
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(x.cpu(), torch.ones(8), 1e-6, x.cpu())                       # no CPU path
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(x, torch.ones(9, device=DEV), 1e-6, torch.empty_like(x))     # sizes disagree
+    with pytest.raises(ops.KernelError):
+        ops.gemm_f32(x, torch.zeros(4, 7, device=DEV), torch.empty(2, 4, device=DEV))
+    with pytest.raises(ops.KernelError):
+        ops.attention_simt(x, x, x, x, None, None, None, None, n_seqs=1, max_q_len=1, nq=1, nkv=1, d=24,
+                           page_size=64, ring_pages=0, window=0, scale=1.0)       # head size not a multiple of 16
+    with pytest.raises(ops.KernelError):
+        ops.embed(x.half(), torch.zeros(2, dtype=torch.int32, device=DEV), torch.empty(2, 8, device=DEV))

@@ -1,0 +1,62 @@
+"""Host side of the step function: what is wanted, what is refused, the step's index tensors (no GPU)."""
+
+import pytest
+import torch
+
+from ondeviceinfer_b200.cache import PAGE_SIZE, KVNeed, SequenceCache
+from ondeviceinfer_b200.engine.step import StepContext, resolve_want, validate_step
+
+
+def make_cache(**kw):
+    return SequenceCache([(KVNeed(1, 16),), (KVNeed(1, 16, window=8),)], [None, None], dtype=torch.float32,
+                         device="cpu", max_tokens=16 * PAGE_SIZE, max_seqs=4, max_step_tokens=64, **kw)
+
+
+def test_resolve_want():
+    assert resolve_want("last", [3, 1]) == [[2], [0]]
+    assert resolve_want("all", [2, 1]) == [[0, 1], [0]]
+    assert resolve_want("none", [2, 1]) == [[], []]
+    assert resolve_want([[0, 2], []], [3, 1]) == [[0, 2], []]
+    with pytest.raises(ValueError):
+        resolve_want([[3]], [3])
+    with pytest.raises(ValueError):
+        resolve_want([[0]], [3, 1])
+    with pytest.raises(ValueError):
+        resolve_want("first", [1])
+
+
+def test_validate_step():
+    cache = make_cache()
+    a, b = cache.alloc(), cache.alloc()
+    validate_step(cache, [a, b], [[1, 2], [3]], 10)
+    for slots, tokens in (([a], [[1], [2]]), ([], []), ([a, a], [[1], [2]]), ([a], [[]]), ([3], [[1]]),
+                          ([a], [[10]]), ([a], [[-1]])):
+        with pytest.raises(ValueError):
+            validate_step(cache, slots, tokens, 10)
+
+
+def test_step_context_indexes_tokens_by_sequence_and_position():
+    cache = make_cache()
+    a, b, c = cache.alloc(), cache.alloc(), cache.alloc()
+    cache.reserve([b], [70])
+    cache.advance([b], [70])
+    tokens = [[5, 6, 7], [8], [9, 10]]
+    cache.reserve([a, b, c], [3, 1, 2])
+    ctx = StepContext(cache, [a, b, c], tokens, [2, 3, 5], "cpu")
+    assert (ctx.n_seqs, ctx.n_tokens, ctx.max_q_len, ctx.max_kv_len, ctx.n_want) == (3, 6, 3, 71, 3)
+    assert ctx.token_ids.tolist() == [5, 6, 7, 8, 9, 10]
+    assert ctx.tok_seq.tolist() == [0, 0, 0, 1, 2, 2]
+    assert ctx.tok_pos.tolist() == [0, 1, 2, 70, 0, 1]
+    assert ctx.cu_q.tolist() == [0, 3, 4, 6]
+    assert ctx.past.tolist() == [0, 70, 0]
+    assert ctx.slots.tolist() == [a, b, c]
+    assert ctx.want_rows.tolist() == [2, 3, 5]
+    for g, group in enumerate(cache.kv_groups):
+        start, ids = ctx.page_table(g)
+        assert start.tolist() == [0, len(group.slot_pages[a]), len(group.slot_pages[a]) + len(group.slot_pages[b]),
+                                  sum(len(group.slot_pages[s]) for s in (a, b, c))]
+        assert ids.tolist() == group.slot_pages[a] + group.slot_pages[b] + group.slot_pages[c]
+    assert all(t.dtype == torch.int32 for t in (ctx.token_ids, ctx.tok_pos, ctx.cu_q, ctx.want_rows))
+    calls = []
+    assert ctx.memo("k", lambda: calls.append(1) or 7) == 7 and ctx.memo("k", lambda: calls.append(1) or 8) == 7
+    assert len(calls) == 1
