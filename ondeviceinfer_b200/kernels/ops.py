@@ -37,9 +37,15 @@ def _cuda_error_text(code: int) -> str:
         return f"CUDA error {code}"
 
 
-def _check(code: int, what: str) -> None:
+# Kernels of this library launched so far in this process (library matrix products are
+# counted apart); the benchmark reads the difference over its timed region.
+LAUNCHES = {"own": 0, "library": 0}
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
     if code != 0:
         raise KernelError(f"{what}: {_cuda_error_text(code)} (code {code})")
+    LAUNCHES["own"] += kernels
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -243,7 +249,7 @@ def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, 
                      0, 0, scale)
     lib = load_library("attention_simt", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_simt(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(dtype_code(q.dtype)),
-                                  _stream()), "attention_simt")
+                                  _stream()), "attention_simt", 2 if splits > 1 else 1)
 
 
 # ------------------------------------------------------------------------------ sampling
