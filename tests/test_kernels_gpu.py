@@ -183,6 +183,28 @@ def test_attention_finds_one_far_key_among_hundreds(dtype):
 
 
 @pytest.mark.parametrize("dtype", DT)
+def test_attention_window_edge(dtype):
+    """The key just outside the window would dominate if it were seen; the key just inside
+    must be seen.  Window 50, query at position 199: keys 150..199 are visible."""
+    d, nq, nkv, window = 32, 2, 1, 50
+    for inside in (False, True):
+        setup = paged_setup([1], [199], nkv, d, dtype, seed=11)
+        k, v = setup["dense"][0]
+        key = 150 if inside else 149
+        q = torch.nn.functional.normalize(k[:, key], dim=-1).repeat_interleave(nq, 0)[None] * 60.0
+        out = torch.empty(1, nq * d, dtype=DT[dtype], device=DEV)
+        ops.attention_simt(q.to(DT[dtype]).to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"],
+                           setup["past"], setup["page_start"], setup["page_ids"], n_seqs=1, max_q_len=1, nq=nq,
+                           nkv=nkv, d=d, page_size=64, ring_pages=0, window=window, scale=1 / math.sqrt(d))
+        expected = plain_attention(q[0][None].reshape(1, nq, d), setup["dense"], [1], [199], nq, nkv, d, window,
+                                   1 / math.sqrt(d), dtype)
+        close(out, expected, dtype, scale=4.0)
+        value = v[:, key].to(DT[dtype]).float().repeat_interleave(nq, 0).reshape(-1)
+        gap = float((out[0].float().cpu() - value).abs().max())
+        assert (gap < 0.05) == inside, (inside, gap)
+
+
+@pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("d,rot,nq,nkv,norm,ring", [(16, 16, 4, 2, True, 0), (128, 128, 8, 2, True, 0),
                                                     (48, 32, 3, 1, False, 0), (256, 64, 2, 2, True, 0),
                                                     (32, 32, 2, 1, True, 3), (64, 0, 2, 2, True, 0)])
