@@ -1,0 +1,505 @@
+// bf16 matrix product on the 5th-generation tensor cores of sm_100a:
+//
+//     out[token, n] = sum_k X[token, k] * W[n, k]        (X and W row-major, K contiguous)
+//
+// with fp32 accumulation in tensor memory and one of four epilogues.  The weight matrix
+// Both operands are K-major, so either can be the 128-row operand of tcgen05.mma:
+//  * decode form: a tile of 128 output features on the lanes, BN = 16..256 tokens on the
+//    columns (few tokens: the step streams each weight once at HBM speed);
+//  * prefill form: a tile of 128 tokens on the lanes, BN = 64..256 features on the columns,
+//    so a thread of the epilogue owns 16 consecutive features of its token (16-byte stores).
+//
+// One CTA = one (feature tile, token tile, K split).  Six warps:
+//   warp 0   TMA producer: cp.async.bulk.tensor loads of W and X tiles (64 k per stage,
+//            128-byte swizzle) into a ring of shared-memory stages, completion on mbarriers;
+//   warp 1   allocates tensor memory; one thread issues tcgen05.mma (M=128, N=BN, K=16, four
+//            per stage) and tcgen05.commit, which releases stages and finally signals the epilogue;
+//   warps 2-5 epilogue: tcgen05.ld the accumulators (one feature row per thread, 16 tokens
+//            at a time) and write the result.
+// DUAL mode runs two weight tiles (rows n and n + dual_offset: gate and up) against the
+// same X tile into two accumulators and writes silu(gate) * up.
+//
+// K splits: when there are too few tiles to fill the GPU, grid.z CTAs share a tile.  Each
+// writes its fp32 partial to scratch; the CTA that arrives last (an atomic ticket, nobody
+// waits) adds the partials in split order and runs the epilogue, so the result does not
+// depend on timing.
+//
+// Every wait on an mbarrier is bounded: after about two seconds the kernel records an
+// error code in `status`, skips its work, still frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define EPI_STORE_BF16 0   // out_bf16[token, n] = acc
+#define EPI_STORE_F32 1    // out_f32[token, n] = acc
+#define EPI_RESIDUAL 2     // out_f32[token, n] += acc
+#define EPI_SWIGLU 3       // out_bf16[token, n] = silu(acc_gate) * acc_up   (DUAL)
+
+#define BM 128             // features per tile (UMMA M)
+#define BK 64              // k per stage: 64 bf16 = one 128-byte swizzle row
+#define GEMM_THREADS 192
+#define WAIT_CYCLES 4000000000ll   // about two seconds of SM clock
+
+#define GEMM_ERR_TIMEOUT_PRODUCER 1
+#define GEMM_ERR_TIMEOUT_MMA 2
+#define GEMM_ERR_TIMEOUT_EPILOGUE 3
+
+struct GemmArgs {
+  void* out;
+  float* scratch;          // split partials
+  int* tickets;            // one counter per tile, zero on entry, left zero
+  int* status;             // error word, 0 = fine
+  int tokens, N, K, ldo;
+  int dual_offset;         // DUAL: row distance between the two weight tiles
+  int splits;
+};
+
+// ------------------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or when another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const long long start = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 0x3ff) == 0x3ff) {
+      if (*abort_flag) return false;
+      if (clock64() - start > WAIT_CYCLES) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols));
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, written by TMA
+// with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the
+// leading byte offset is not used by swizzled K-major layouts, version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffff) >> 4);     // start address, bits [0, 14)
+  d |= (uint64_t)1 << 16;                      // leading byte offset (ignored), bits [16, 30)
+  d |= (uint64_t)(1024 >> 4) << 32;            // stride byte offset, bits [32, 46)
+  d |= (uint64_t)1 << 46;                      // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulator, bf16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
+
+// ------------------------------------------------------------------------------ the kernel
+
+// Features on the lanes (decode form): one value per call; the 32 lanes of a warp write 32
+// consecutive features of one token.
+template <int EPI>
+__device__ __forceinline__ void emit(const GemmArgs& a, int token, int n, float v, float v2) {
+  if (token >= a.tokens || n >= a.N) return;
+  const size_t at = (size_t)token * a.ldo + n;
+  if (EPI == EPI_STORE_BF16) ((bf16*)a.out)[at] = __float2bfloat16_rn(v);
+  else if (EPI == EPI_STORE_F32) ((float*)a.out)[at] = v;
+  else if (EPI == EPI_RESIDUAL) ((float*)a.out)[at] += v;
+  else ((bf16*)a.out)[at] = __float2bfloat16_rn(silu_f(v) * v2);
+}
+
+// Tokens on the lanes (prefill form): a thread holds 16 consecutive features of its token
+// and writes them with 16-byte stores when the row is aligned for that.
+template <int EPI>
+__device__ __forceinline__ void emit_row16(const GemmArgs& a, int token, int n, const float* v, const float* u,
+                                           bool vec_ok) {
+  if (token >= a.tokens || n >= a.N) return;
+  const size_t at = (size_t)token * a.ldo + n;
+  if (vec_ok && n + 16 <= a.N) {
+    if (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU) {
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float lo = EPI == EPI_SWIGLU ? silu_f(v[2 * i]) * u[2 * i] : v[2 * i];
+        const float hi = EPI == EPI_SWIGLU ? silu_f(v[2 * i + 1]) * u[2 * i + 1] : v[2 * i + 1];
+        __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+        packed[i] = *(uint32_t*)&pair;
+      }
+      uint4* dst = (uint4*)((bf16*)a.out + at);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+      float4* dst = (float4*)((float*)a.out + at);
+      float4 r[4];
+      if (EPI == EPI_RESIDUAL) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = dst[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        if (EPI == EPI_RESIDUAL) { o.x += r[i].x; o.y += r[i].y; o.z += r[i].z; o.w += r[i].w; }
+        dst[i] = o;
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) emit<EPI>(a, token, n + i, v[i], (EPI == EPI_SWIGLU) ? u[i] : 0.f);
+}
+
+// SWAP = false: the 128 lanes are features (weight rows), the BN columns are tokens.
+// SWAP = true : the 128 lanes are tokens, the BN columns are features.
+template <int BN, bool DUAL, int EPI, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GemmArgs a) {
+  constexpr int L_BYTES = BM * BK * 2;                    // lanes operand tile, 16 KB
+  constexpr int C_BYTES = BN * BK * 2;                    // columns operand tile
+  constexpr int L_TILES = (DUAL && !SWAP) ? 2 : 1;
+  constexpr int C_TILES = (DUAL && SWAP) ? 2 : 1;
+  constexpr int STAGE_BYTES = L_BYTES * L_TILES + C_BYTES * C_TILES;
+  constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
+  constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int ticket_slot;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok0 = blockIdx.x * (SWAP ? BM : BN), n0 = blockIdx.y * (SWAP ? BN : BM), split = blockIdx.z;
+  const int total_kb = (a.K + BK - 1) / BK;
+  const int kb_begin = (int)((long)total_kb * split / a.splits);
+  const int kb_count = (int)((long)total_kb * (split + 1) / a.splits) - kb_begin;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), acc_bar = smem_u32(&bars[2 * STAGES]);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(acc_bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const CUtensorMap* map_l = SWAP ? &map_x : &map_w;
+      const CUtensorMap* map_c = SWAP ? &map_w : &map_x;
+      const int l_row = SWAP ? tok0 : n0, c_row = SWAP ? n0 : tok0;
+      for (int i = 0; i < kb_count; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_ptr)) { atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_PRODUCER); break; }
+        const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const int k0 = (kb_begin + i) * BK;
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        tma_load_2d(dst, map_l, k0, l_row, full0 + 8 * s);
+        if (L_TILES == 2) tma_load_2d(dst + L_BYTES, map_l, k0, l_row + a.dual_offset, full0 + 8 * s);
+        tma_load_2d(dst + L_BYTES * L_TILES, map_c, k0, c_row, full0 + 8 * s);
+        if (C_TILES == 2) tma_load_2d(dst + L_BYTES * L_TILES + C_BYTES, map_c, k0, c_row + a.dual_offset, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < kb_count && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        if (!mbar_wait(full0 + 8 * s, phase, abort_ptr)) { atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_MMA); ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const uint64_t dl = smem_desc_k_sw128(sa);
+        const uint64_t dl2 = smem_desc_k_sw128(sa + L_BYTES);
+        const uint64_t dc = smem_desc_k_sw128(sa + L_BYTES * L_TILES);
+        const uint64_t dc2 = smem_desc_k_sw128(sa + L_BYTES * L_TILES + C_BYTES);
+#pragma unroll
+        for (int j = 0; j < BK / 16; ++j) {
+          const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
+          // 16 k = 32 bytes further inside the swizzle row: +2 in the (address >> 4) field
+          umma_bf16(tmem_base, dl + 2 * j, dc + 2 * j, idesc, acc);
+          if (DUAL) umma_bf16(tmem_base + BN, (SWAP ? dl : dl2) + 2 * j, (SWAP ? dc2 : dc) + 2 * j, idesc, acc);
+        }
+        umma_commit(empty0 + 8 * s);    // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(acc_bar);     // accumulators complete
+    }
+  } else {
+    // epilogue warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31
+    const int lane_group = warp & 3;
+    const int row = lane_group * 32 + lane;              // lane of the accumulator
+    const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    bool ok = mbar_wait(acc_bar, 0, abort_ptr);
+    if (!ok && lane == 0) atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_EPILOGUE);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    tc_fence_after();
+    if (ok && SWAP) {
+      const int token = tok0 + row;
+      const bool vec_ok = (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU)
+                              ? (a.ldo % 8 == 0 && ((uintptr_t)a.out & 15) == 0)
+                              : (a.ldo % 4 == 0 && ((uintptr_t)a.out & 15) == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (n0 + c >= a.N) break;
+        float v[16], u[16];
+        tmem_ld16(taddr + c, v);
+        if (DUAL) tmem_ld16(taddr + BN + c, u);
+        emit_row16<EPI>(a, token, n0 + c, v, u, vec_ok);
+      }
+    } else if (ok && a.splits == 1) {
+      const int n = n0 + row;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (tok0 + c >= a.tokens) break;
+        float v[16], u[16];
+        tmem_ld16(taddr + c, v);
+        if (DUAL) tmem_ld16(taddr + BN + c, u);
+        if (EPI == EPI_RESIDUAL) {
+          // read the 16 residual values first: the adds must not wait on one another
+          float r[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            r[i] = (tok0 + c + i < a.tokens && n < a.N) ? ((const float*)a.out)[(size_t)(tok0 + c + i) * a.ldo + n] : 0.f;
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (tok0 + c + i < a.tokens && n < a.N) ((float*)a.out)[(size_t)(tok0 + c + i) * a.ldo + n] = r[i] + v[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) emit<EPI>(a, tok0 + c + i, n, v[i], DUAL ? u[i] : 0.f);
+        }
+      }
+    } else if (ok) {
+      const int n = n0 + row;
+      constexpr int PER = (DUAL ? 2 : 1) * BN * BM;       // floats per partial
+      float* mine = a.scratch + ((size_t)tile_id * a.splits + split) * PER;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (tok0 + c >= a.tokens) break;
+        float v[16], u[16];
+        tmem_ld16(taddr + c, v);
+        if (DUAL) tmem_ld16(taddr + BN + c, u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          mine[(size_t)(c + i) * BM + row] = v[i];
+          if (DUAL) mine[(size_t)(BN + c + i) * BM + row] = u[i];
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+      if (threadIdx.x == 64) ticket_slot = atomicAdd(&a.tickets[tile_id], 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ticket_slot == a.splits - 1) {                   // every other split has published its partial
+        __threadfence();
+        const float* all = a.scratch + (size_t)tile_id * a.splits * PER;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 8) {
+          if (tok0 + c >= a.tokens) break;
+          float v[8], u[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { v[i] = 0.f; u[i] = 0.f; }
+          for (int s = 0; s < a.splits; ++s) {             // split order: the sum does not depend on timing
+            float pv[8], pu[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              pv[i] = __ldcg(all + (size_t)s * PER + (size_t)(c + i) * BM + row);
+              if (DUAL) pu[i] = __ldcg(all + (size_t)s * PER + (size_t)(BN + c + i) * BM + row);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { v[i] += pv[i]; if (DUAL) u[i] += pu[i]; }
+          }
+          if (EPI == EPI_RESIDUAL) {
+            float r[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              r[i] = (tok0 + c + i < a.tokens && n < a.N) ? ((const float*)a.out)[(size_t)(tok0 + c + i) * a.ldo + n] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (tok0 + c + i < a.tokens && n < a.N) ((float*)a.out)[(size_t)(tok0 + c + i) * a.ldo + n] = r[i] + v[i];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) emit<EPI>(a, tok0 + c + i, n, v[i], u[i]);
+          }
+        }
+        if (threadIdx.x == 64) a.tickets[tile_id] = 0;    // ready for the next launch
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, K] row-major bf16 matrix cut into boxes of box_rows x 64 with the 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return ODI_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
+}
+
+template <int BN, bool DUAL, int EPI, bool SWAP>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = BM * BK * 2 * ((DUAL && !SWAP) ? 2 : 1) + BN * BK * 2 * ((DUAL && SWAP) ? 2 : 1);
+  // The decode form keeps two CTAs per SM resident (about 100 KB each); the prefill form takes the SM alone.
+  constexpr int BUDGET = SWAP ? 200 * 1024 : 100 * 1024;
+  constexpr int STAGES = BUDGET / STAGE_BYTES < 2 ? 2 : (BUDGET / STAGE_BYTES > 12 ? 12 : BUDGET / STAGE_BYTES);
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, SWAP>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kernel<<<grid, GEMM_THREADS, SMEM, stream>>>(mw, mx, a);
+  return launch_status();
+}
+
+template <int BN, bool SWAP>
+static int dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid,
+                        cudaStream_t stream) {
+  switch (epi) {
+    case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, SWAP>(mw, mx, a, grid, stream);
+    case EPI_STORE_F32: return launch<BN, false, EPI_STORE_F32, SWAP>(mw, mx, a, grid, stream);
+    case EPI_RESIDUAL: return launch<BN, false, EPI_RESIDUAL, SWAP>(mw, mx, a, grid, stream);
+    case EPI_SWIGLU:
+      if constexpr (BN <= 128) return launch<BN, true, EPI_SWIGLU, SWAP>(mw, mx, a, grid, stream);
+      else return ODI_ERR_UNSUPPORTED;
+  }
+  return ODI_ERR_ARGUMENT;
+}
+
+// Scratch floats a launch with these sizes needs (0 when splits == 1).
+extern "C" long odi_gemm_bf16_scratch_floats(int tokens, int n_out, int bn, int splits, int dual) {
+  if (splits <= 1) return 0;
+  const long tiles = (long)((n_out + BM - 1) / BM) * ((tokens + bn - 1) / bn);
+  return tiles * splits * (dual ? 2 : 1) * bn * BM;
+}
+
+// x [tokens, K] bf16, w [w_rows, K] bf16 (for EPI_SWIGLU w holds the gate rows followed by
+// the up rows and n_out = w_rows / 2), out [tokens, ldo].
+// swap == 0 (decode form): tiles of 128 features x bn tokens, bn in {16, 32, 64, 128, 256}, K splits allowed.
+// swap == 1 (prefill form): tiles of 128 tokens x bn features, bn in {64, 128, 256}, no splits.
+extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
+                             int ldo, int epi, int bn, int splits, int swap, float* scratch, int* tickets,
+                             int* status, cudaStream_t stream) {
+  if (tokens <= 0 || n_out <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits < 1 || splits > total_kb || (swap && splits != 1)) return ODI_ERR_ARGUMENT;
+  if (splits > 1 && (scratch == nullptr || tickets == nullptr)) return ODI_ERR_ARGUMENT;
+  if (status == nullptr) return ODI_ERR_ARGUMENT;
+  const bool dual = epi == EPI_SWIGLU;
+  if (dual && w_rows != 2 * n_out) return ODI_ERR_ARGUMENT;
+  CUtensorMap mw, mx;
+  int rc = make_map(&mw, w, w_rows, K, swap ? bn : BM);
+  if (rc != 0) return rc;
+  rc = make_map(&mx, x, tokens, K, swap ? BM : bn);
+  if (rc != 0) return rc;
+  GemmArgs a;
+  a.out = out; a.scratch = scratch; a.tickets = tickets; a.status = status;
+  a.tokens = tokens; a.N = n_out; a.K = K; a.ldo = ldo; a.dual_offset = dual ? n_out : 0; a.splits = splits;
+  const int tok_tile = swap ? BM : bn, n_tile = swap ? bn : BM;
+  dim3 grid((tokens + tok_tile - 1) / tok_tile, (n_out + n_tile - 1) / n_tile, splits);
+  if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;
+  if (swap) {
+    switch (bn) {
+      case 64: return dispatch_epi<64, true>(epi, mw, mx, a, grid, stream);
+      case 128: return dispatch_epi<128, true>(epi, mw, mx, a, grid, stream);
+      case 256: return dispatch_epi<256, true>(epi, mw, mx, a, grid, stream);
+    }
+    return ODI_ERR_UNSUPPORTED;
+  }
+  switch (bn) {
+    case 16: return dispatch_epi<16, false>(epi, mw, mx, a, grid, stream);
+    case 32: return dispatch_epi<32, false>(epi, mw, mx, a, grid, stream);
+    case 64: return dispatch_epi<64, false>(epi, mw, mx, a, grid, stream);
+    case 128: return dispatch_epi<128, false>(epi, mw, mx, a, grid, stream);
+    case 256: return dispatch_epi<256, false>(epi, mw, mx, a, grid, stream);
+  }
+  return ODI_ERR_UNSUPPORTED;
+}

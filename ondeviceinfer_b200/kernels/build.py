@@ -147,6 +147,7 @@ ALL_SOURCES = {
     "elementwise": [{}],
     "gemm_f32": [{}],
     "sampling": [{}],
+    "gemm_tcgen05": [{}],
     "attention_simt": [{"ODI_HEAD_DIM": 128}],
 }
 

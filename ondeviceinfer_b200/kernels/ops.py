@@ -213,6 +213,99 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Opti
                             c_int(K), c_int(K), c_int(N), c_int(N), _stream()), "gemm_f32")
 
 
+EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+
+_gemm_state = {}
+
+
+def _gemm_buffers(device, scratch_floats: int):
+    """Scratch for split partials, tile tickets (kept zero between launches) and the error word."""
+    state = _gemm_state.setdefault(device, {})
+    if "tickets" not in state:
+        state["tickets"] = torch.zeros(16384, dtype=torch.int32, device=device)
+        state["status"] = torch.zeros(4, dtype=torch.int32, device=device)
+        state["scratch"] = torch.empty(1 << 22, dtype=torch.float32, device=device)
+    if state["scratch"].numel() < scratch_floats:
+        state["scratch"] = torch.empty(int(scratch_floats * 1.25), dtype=torch.float32, device=device)
+    return state["scratch"], state["tickets"], state["status"]
+
+
+def gemm_status(device=None) -> int:
+    """The error word of the tensor-core GEMM (0 = fine); reading it synchronises the device."""
+    codes = [int(s["status"][0].item()) for d, s in _gemm_state.items() if "status" in s and (device is None or d == device)]
+    return next((c for c in codes if c), 0)
+
+
+def raise_on_kernel_fault() -> None:
+    code = gemm_status()
+    if code:
+        names = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}
+        for state in _gemm_state.values():
+            state["status"].zero_()
+        raise KernelError(f"gemm_tcgen05 gave up waiting on a barrier in {names.get(code, code)}; its result is invalid")
+
+
+def gemm_bf16_plan(tokens: int, n_out: int, K: int, epi: int):
+    """(swap, tile, splits) for a shape.
+
+    Up to 64 tokens: decode form (128 features x `tile` tokens per CTA) with enough K
+    splits to fill 148 SMs twice over, each split at least four k-blocks of 64.
+    More tokens: prefill form (128 tokens x `tile` features per CTA), the largest tile
+    that still gives every SM a CTA.
+    """
+    total_kb = -(-K // 64)
+    if tokens <= 64:
+        bn = next(b for b in (16, 32, 64) if tokens <= b)
+        tiles = -(-n_out // 128)
+        splits = max(1, min(total_kb // 4, 296 // tiles)) if tiles < 296 else 1
+        return False, bn, splits
+    choices = (128, 64) if epi == EPI_SWIGLU else (256, 128, 64)
+    token_tiles = -(-tokens // 128)
+    for bn in choices:
+        if token_tiles * -(-n_out // bn) >= 120:
+            return True, bn, 1
+    return True, choices[-1], 1
+
+
+def gemm_bf16_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    K = x.shape[1]
+    return K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, swap: Optional[bool] = None,
+              bn: Optional[int] = None, splits: Optional[int] = None) -> None:
+    """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
+
+    ``EPI_STORE_BF16`` / ``EPI_STORE_F32``: out [tokens, rows]; ``EPI_RESIDUAL``: out (fp32) += product;
+    ``EPI_SWIGLU``: w holds the gate rows then the up rows, out [tokens, rows / 2] = silu(gate) * up.
+    """
+    _require(x, "x", torch.bfloat16, 2)
+    _require(w, "w", torch.bfloat16, 2)
+    _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
+    tokens, K = x.shape
+    rows = w.shape[0]
+    n_out = rows // 2 if epi == EPI_SWIGLU else rows
+    if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and rows % 2):
+        raise KernelError(f"gemm sizes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if not gemm_bf16_supported(x, w):
+        raise KernelError(f"gemm_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
+    plan_swap, plan_bn, plan_splits = gemm_bf16_plan(tokens, n_out, K, epi)
+    swap = plan_swap if swap is None else swap
+    bn = plan_bn if bn is None else bn
+    splits = plan_splits if splits is None else splits
+    lib = load_library("gemm_tcgen05")
+    lib.odi_gemm_bf16_scratch_floats.restype = c_long
+    need = lib.odi_gemm_bf16_scratch_floats(c_int(tokens), c_int(n_out), c_int(bn), c_int(splits),
+                                            c_int(1 if epi == EPI_SWIGLU else 0))
+    tiles = -(-n_out // 128) * -(-tokens // bn)
+    scratch, tickets, status = _gemm_buffers(x.device, need if not swap else 0)
+    if splits > 1 and tiles > tickets.numel():
+        raise KernelError("too many tiles for a split product")
+    _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(rows),
+                             c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if swap else 0),
+                             _ptr(scratch), _ptr(tickets), _ptr(status), _stream()), "gemm_tcgen05")
+
+
 # ------------------------------------------------------------------------------ attention
 
 

@@ -1,5 +1,5 @@
 from .base import Part, Runtime, build_part, register_part
-from .linear import linear
+from .linear import gated_linear, linear
 from . import norm, position, attention, mlp, block  # noqa: F401  (registers the built-in parts)
 from .attention import Attention
 from .block import PreNormBlock
@@ -7,5 +7,5 @@ from .mlp import GatedMLP
 from .norm import RMSNorm
 from .position import NoPosition, Rotary
 
-__all__ = ["Part", "Runtime", "build_part", "register_part", "linear", "Attention", "PreNormBlock",
+__all__ = ["Part", "Runtime", "build_part", "register_part", "linear", "gated_linear", "Attention", "PreNormBlock",
            "GatedMLP", "RMSNorm", "NoPosition", "Rotary"]

@@ -1,10 +1,16 @@
-"""y = x W^T for the two compute dtypes.
+"""y = x W^T for the two compute dtypes, with the epilogues the layers need.
 
 float32: this library's own FMA kernel (no tensor cores, no TF32), residual add fused.
-bfloat16: tensor-core matrix product with fp32 accumulation.  The reference leaves every
-projection to the vendor library through ``F.linear`` (ondeviceinfer/attention.py:149-157,
-ondeviceinfer/layers.py:109-113, ondeviceinfer/model.py:163); the same library call
-stands here for shapes the hand-written kernels do not take.
+
+bfloat16, up to 64 tokens (decode and short chunks): the hand-written tcgen05 kernel
+(``csrc/gemm_tcgen05.cu``): weights streamed by TMA, fp32 accumulators in tensor memory,
+the residual add, the fp32 store of logits and the SiLU-gate product fused into its epilogue.
+
+bfloat16, more tokens (prefill): the vendor library's matrix product with fp32
+accumulation, as the reference does for every projection through ``F.linear``
+(ondeviceinfer/attention.py:149-157, ondeviceinfer/layers.py:109-113,
+ondeviceinfer/model.py:163), followed by this library's elementwise kernels.  The same
+holds for shapes the tcgen05 kernel refuses (K not a multiple of 8).
 """
 
 from __future__ import annotations
@@ -14,6 +20,12 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+
+OWN_KERNEL_MAX_TOKENS = 64
+
+
+def _own(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return x.shape[0] <= OWN_KERNEL_MAX_TOKENS and ops.gemm_bf16_supported(x, weight)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
@@ -34,6 +46,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, residual: Optional[torch.Te
         return out
     if x.dtype != torch.bfloat16:
         raise ops.KernelError(f"linear takes float32 or bfloat16 activations, not {x.dtype}")
+    if _own(x, weight):
+        if residual is not None:
+            ops.gemm_bf16(x, weight, residual, ops.EPI_RESIDUAL)
+            return None
+        wide = out_dtype == torch.float32
+        out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
+        ops.gemm_bf16(x, weight, out, ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16)
+        return out
     y = torch.matmul(x, weight.t())
     ops.LAUNCHES["library"] += 1
     if residual is not None:
@@ -44,3 +64,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, residual: Optional[torch.Te
         ops.widen(y, out)
         return out
     return y
+
+
+def gated_linear(x: torch.Tensor, weight_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for ``weight_gate_up`` = gate rows followed by up rows."""
+    n, I = x.shape[0], weight_gate_up.shape[0] // 2
+    act = torch.empty((n, I), dtype=x.dtype, device=x.device)
+    if x.dtype == torch.bfloat16 and _own(x, weight_gate_up):
+        ops.gemm_bf16(x, weight_gate_up, act, ops.EPI_SWIGLU)
+        return act
+    ops.silu_mul(linear(x, weight_gate_up), act)
+    return act

@@ -5,10 +5,9 @@ from __future__ import annotations
 import torch
 
 from ..config.specs import GatedMLPSpec
-from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, register_part
-from .linear import linear
+from .linear import gated_linear, linear
 
 
 class GatedMLP(Part):
@@ -33,10 +32,7 @@ class GatedMLP(Part):
         self.w_down = fetch.matrix(s.name("down"))
 
     def forward(self, x, ctx, residual) -> None:
-        gate_up = linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gate_up, act)
-        linear(act, self.w_down, residual=residual)
+        linear(gated_linear(x, self.w_gate_up), self.w_down, residual=residual)
 
 
 register_part(GatedMLPSpec, GatedMLP)

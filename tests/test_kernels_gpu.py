@@ -340,3 +340,58 @@ def test_kernels_refuse_what_they_cannot_take():
                            page_size=64, ring_pages=0, window=0, scale=1.0)       # head size not a multiple of 16
     with pytest.raises(ops.KernelError):
         ops.embed(x.half(), torch.zeros(2, dtype=torch.int32, device=DEV), torch.empty(2, 8, device=DEV))
+
+
+GEMM_SHAPES = [
+    # tokens, features, K, swap, tile, splits (None: the plan's choice)
+    (1, 389, 96, None, None, None), (8, 4096, 4096, None, None, None), (16, 128, 64, False, 16, 1),
+    (33, 1000, 1000, None, None, None), (64, 1536, 2048, None, None, None), (40, 512, 4096, False, 64, 4),
+    (130, 4096, 1024, False, 128, 2), (100, 389, 96, True, 64, 1), (300, 520, 200, True, 128, 1),
+    (333, 208, 80, True, 64, 1), (1030, 1024, 512, None, None, None),
+]
+
+
+@pytest.mark.parametrize("epi", ["store_bf16", "store_f32", "residual", "swiglu"])
+@pytest.mark.parametrize("tokens,N,K,swap,tile,splits", GEMM_SHAPES)
+def test_gemm_tcgen05(tokens, N, K, swap, tile, splits, epi):
+    """The tensor-core product and its four epilogues against fp32 torch on the same bf16
+    inputs: both operand orders, every tile width, K splits, ragged edges in all three sizes."""
+    code = {"store_bf16": ops.EPI_STORE_BF16, "store_f32": ops.EPI_STORE_F32, "residual": ops.EPI_RESIDUAL,
+            "swiglu": ops.EPI_SWIGLU}[epi]
+    if epi == "swiglu" and tile == 256:
+        pytest.skip("the gated epilogue keeps two accumulators: tiles up to 128")
+    torch.manual_seed(9)
+    x = torch.randn(tokens, K).bfloat16().to(DEV)
+    rows = 2 * N if epi == "swiglu" else N
+    w = (torch.randn(rows, K) / math.sqrt(K)).bfloat16().to(DEV)
+    ref = (x.float() @ w.float().t()).cpu()
+    if epi == "store_bf16":
+        out, expected = torch.empty(tokens, N, dtype=torch.bfloat16, device=DEV), ref
+    elif epi == "store_f32":
+        out, expected = torch.empty(tokens, N, dtype=torch.float32, device=DEV), ref
+    elif epi == "residual":
+        res = torch.randn(tokens, N)
+        out, expected = res.clone().to(DEV), res + ref
+    else:
+        out = torch.empty(tokens, N, dtype=torch.bfloat16, device=DEV)
+        expected = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
+    ops.gemm_bf16(x, w, out, code, swap=swap, bn=tile, splits=splits)
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    if out.dtype == torch.bfloat16:
+        close(out, expected, "bfloat16")
+    else:
+        assert torch.allclose(out.cpu(), expected, atol=1e-4, rtol=1e-4), float((out.cpu() - expected).abs().max())
+    # launched again, the split tickets must have been left at zero
+    if epi == "store_f32":
+        again = torch.empty_like(out)
+        ops.gemm_bf16(x, w, again, code, swap=swap, bn=tile, splits=splits)
+        assert torch.equal(again, out)
+
+
+def test_gemm_tcgen05_refuses_unaligned_k():
+    x = torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)
+    assert not ops.gemm_bf16_supported(x, w)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_bf16(x, w, torch.empty(4, 8, dtype=torch.bfloat16, device=DEV), ops.EPI_STORE_BF16)
