@@ -175,24 +175,30 @@ def main() -> int:
         return torch.randint(0, cfg["vocab_size"], (batch, length), generator=gen).tolist()
 
     def decode_run(batch, steps, warmup, end_to_end):
-        """Prefill `batch` prompts of PROMPT tokens, then time `steps` decode steps."""
+        """Prefill `batch` prompts of PROMPT tokens, then time `steps` decode steps.
+
+        Device-timed: the steps replay back to back, sampled tokens stay on the device.
+        End to end: the public decode call per step, which copies the step's token ids from
+        pinned host memory to the device and reads the sampled tokens back to the host."""
         cache = model.make_cache(max_tokens=batch * CONTEXT, max_seqs=batch)
         slots = [cache.alloc() for _ in range(batch)]
         logits = model.step(cache, slots, prompts_for(batch, PROMPT), "last")
         tokens = sampler(logits, range(batch), [0] * batch)
-        pinned = torch.empty((batch,), dtype=torch.int32).pin_memory()
+        runner = odi.api.decode_runner(model, cache, temperature=0.0, seed=0)
+        runner.begin(slots, tokens, list(range(batch)), [1] * batch)
         for _ in range(warmup):
-            logits = model.step(cache, slots, [[t] for t in tokens], "last")
-            tokens = sampler(logits, range(batch), [0] * batch)
+            tokens = runner.step(tokens)
         torch.cuda.synchronize()
         before = dict(ops.LAUNCHES)
         start_len = cache.length(slots[0])
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wall = time.perf_counter()
         start.record()
-        for _ in range(steps):
-            logits = model.step(cache, slots, [[t] for t in tokens], "last")
-            tokens = sampler(logits, range(batch), [0] * batch)
+        if end_to_end:
+            for _ in range(steps):
+                tokens = runner.step(tokens)
+        else:
+            runner.step_device(steps)
         stop.record()
         torch.cuda.synchronize()
         wall = time.perf_counter() - wall
@@ -201,7 +207,8 @@ def main() -> int:
         mean_ctx = start_len + (steps - 1) / 2.0
         for slot in slots:
             cache.free(slot)
-        del cache
+        runner.close()
+        del cache, runner
         torch.cuda.empty_cache()
         seconds = wall if end_to_end else ms / 1000.0
         return {"tok_s": batch * steps / seconds, "ms_per_step": seconds * 1000.0 / steps, "launches": launches,

@@ -8,6 +8,7 @@ hand-written sm_100a CUDA kernels underneath (bfloat16 for serving, true float32
 reference path).  There is no CPU execution path.
 """
 
+from . import api
 from .api import (GenerationResult, ResidentModel, generate, greedy_generate, load_resident_model,
                   random_resident_model)
 from .cache import CacheCapacityError, KVNeed, SequenceCache, StateNeed

@@ -22,6 +22,7 @@ import torch
 
 from . import models  # noqa: F401  (registers the architectures)
 from .cache import PAGE_SIZE, SequenceCache, pages_for
+from .engine.decode import DecodeRunner
 from .engine.generate import GenerationResult, generate_requests, plan_batches
 from .engine.model import DecoderModel
 from .engine.step import run_step
@@ -112,10 +113,12 @@ def _as_prompts(prompts) -> List[List[int]]:
 
 def generate(model: ResidentModel, prompts, *, max_new_tokens: int, cache: Optional[SequenceCache] = None,
              temperature: float = 0.0, seed: int = 0,
-             eos_token_id: Union[int, Sequence[int], None] = None) -> GenerationResult:
+             eos_token_id: Union[int, Sequence[int], None] = None, use_graphs: bool = True) -> GenerationResult:
     """Generate for every prompt (lists of token ids of any lengths, or a ``[batch, T]``
     tensor).  ``eos_token_id`` None disables stopping, as in the reference; a stop token
-    is kept in the output.  Without ``cache`` one is made that fits all requests at once."""
+    is kept in the output.  Without ``cache`` one is made that fits all requests at once.
+    Decode steps replay CUDA graphs (``use_graphs``) when every part of the model allows it;
+    the kernels and the results are the same either way."""
     prompts = _as_prompts(prompts)
     if cache is None:
         need = sum(pages_for(len(p) + max_new_tokens) * PAGE_SIZE for p in prompts)
@@ -129,11 +132,23 @@ def generate(model: ResidentModel, prompts, *, max_new_tokens: int, cache: Optio
     batches = plan_batches([len(p) for p in prompts], max_new_tokens, max_seqs=cache.max_seqs,
                            max_tokens=cache.max_tokens, page_size=PAGE_SIZE)
     sampler = Sampler(temperature, seed)
+    decoder = None
+    if use_graphs and model.decoder.graph_safe:
+        decoder = decode_runner(model, cache, temperature=temperature, seed=seed)
     return generate_requests(
         prompts, max_new_tokens=max_new_tokens, alloc=cache.alloc, free=cache.free,
         step=lambda slots, runs: model.step(cache, slots, runs, "last"),
         sample=sampler, batches=batches, stop_token_ids=stop,
-        synchronize=lambda: torch.cuda.synchronize(model.device))
+        synchronize=lambda: torch.cuda.synchronize(model.device), decoder=decoder)
+
+
+def decode_runner(model: ResidentModel, cache: SequenceCache, *, temperature: float = 0.0, seed: int = 0) -> DecodeRunner:
+    """The graph-replaying decoder of ``cache`` for these sampling settings (made once, kept on the cache)."""
+    runners = cache.__dict__.setdefault("_decode_runners", {})
+    key = (id(model.decoder), float(temperature), int(seed))
+    if key not in runners:
+        runners[key] = DecodeRunner(model.decoder, cache, temperature=temperature, seed=seed)
+    return runners[key]
 
 
 def greedy_generate(model: ResidentModel, input_ids, *, max_new_tokens: int,

@@ -50,10 +50,12 @@ class KVGroup:
         else:
             # positions [p - window + 1, p + step - 1] must map to distinct rows of the ring
             self.ring_pages = pages_for(need.window + max_step_tokens - 1) + 1
-        self.pool = torch.zeros((len(owners), 2, n_pages, need.num_kv_heads, PAGE_SIZE, need.head_dim),
+        # one page and one slot beyond the capacity belong to padding rows of fixed-width steps
+        self.pool = torch.zeros((len(owners), 2, n_pages + 1, need.num_kv_heads, PAGE_SIZE, need.head_dim),
                                 dtype=dtype, device=device)
         self.pages = IndexAllocator(n_pages, "page")
-        self.slot_pages: List[List[int]] = [[] for _ in range(n_slots)]
+        self.pad_page = n_pages
+        self.slot_pages: List[List[int]] = [[] for _ in range(n_slots)] + [[self.pad_page]]
 
     def pages_needed(self, length: int) -> int:
         n = pages_for(length)
@@ -69,7 +71,7 @@ class KVGroup:
 class StateGroup:
     def __init__(self, index: int, need: StateNeed, owners: List[int], n_slots: int, device) -> None:
         self.index, self.need, self.owners = index, need, owners
-        self.data = torch.zeros((len(owners), n_slots) + tuple(need.shape), dtype=need.dtype, device=device)
+        self.data = torch.zeros((len(owners), n_slots + 1) + tuple(need.shape), dtype=need.dtype, device=device)
 
 
 @dataclass
@@ -98,7 +100,10 @@ class SequenceCache:
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.n_pages = pages_for(max_tokens)
         self.slots = IndexAllocator(max_seqs, "slot")
-        self.lengths = [0] * max_seqs
+        self.lengths = [0] * (max_seqs + 1)
+        # A slot outside the capacity, of constant length 0, with one page of its own in every
+        # group: rows that only pad a fixed-width batch run on it and their results are dropped.
+        self.pad_slot = max_seqs
         self.kv_groups: List[KVGroup] = []
         self.state_groups: List[StateGroup] = []
         self._views: List[CacheView] = []
@@ -220,7 +225,7 @@ class SequenceCache:
         for group in self.kv_groups:
             group.pages.check()
             seen = set()
-            for slot, pages in enumerate(group.slot_pages):
+            for slot, pages in enumerate(group.slot_pages[:self.max_seqs]):
                 if pages and not self.slots.is_held(slot):
                     raise AssertionError(f"free slot {slot} still holds pages")
                 for page in pages:

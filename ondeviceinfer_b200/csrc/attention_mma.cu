@@ -1,0 +1,456 @@
+// bf16 causal grouped-query attention over the paged cache on the tensor cores
+// (mma.sync m16n8k16, fp32 accumulation, fp32 running-maximum softmax), in two forms:
+//
+//  * attention_prefill: a block of 4 warps owns 64 consecutive query tokens of one query
+//    head of one sequence (16 rows per warp) and walks the sequence's key pages up to the
+//    diagonal; works for any q_len >= 1 on top of any cached length.
+//  * attention_decode: one query token per sequence.  A block owns one (sequence, kv head,
+//    key split); the rows of its MMA are the query heads that share the kv head (up to 16
+//    per block), its 4 warps take 16 keys each of every 64-key page and their partial
+//    results are merged in shared memory.  With splits > 1 the block writes an
+//    un-normalised partial (acc[d], max, sum) per (token, head, split) for the combine
+//    kernel of attention_simt.cu.
+//
+// Key/value pages (64 positions x head_dim, contiguous) are copied to shared memory with
+// cp.async, double or triple buffered; rows are padded by 16 bytes so that ldmatrix reads
+// are free of bank conflicts for every head size that is a multiple of 16.
+//
+// Compile with -DODI_HEAD_DIM=<d>, d a multiple of 16 up to 256.  No window, no ring:
+// layers that need those use attention_simt.cu.
+#include "common.cuh"
+
+#ifndef ODI_HEAD_DIM
+#error "compile with -DODI_HEAD_DIM=<head size>"
+#endif
+#define D ODI_HEAD_DIM
+#if (D % 16) != 0 || D > 256
+#error "head size must be a multiple of 16, at most 256"
+#endif
+
+#define KT 64                      // keys per tile = positions per page
+#define ROWB (2 * D + 16)          // bytes per shared-memory row
+#define TILE_BYTES (KT * ROWB)
+#define KSTEPS (D / 16)
+#define DTILES (D / 8)
+#define LOG2E 1.4426950408889634f
+
+struct MmaAttnArgs {
+  const bf16* q;          // [n_tokens, nq, D]
+  const bf16* k_pool;     // [pages, nkv, 64, D]
+  const bf16* v_pool;
+  bf16* out;              // [n_tokens, nq * D]
+  float* partial;         // [n_tokens, nq, splits, D + 2]
+  const int* cu_q;
+  const int* past;
+  const int* page_start;
+  const int* page_ids;
+  int n_seqs, nq, nkv, splits, head_chunks;
+  float scale;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(uint32_t*)&v;
+}
+
+// Copy one page tile (64 rows of D bf16, contiguous in global memory) into padded rows.
+__device__ __forceinline__ void load_tile(uint8_t* dst, const bf16* src, int tid, int nthreads) {
+  constexpr int CHUNKS = D / 8;    // 16-byte chunks per row
+  const uint32_t base = smem_addr(dst);
+  for (int i = tid; i < KT * CHUNKS; i += nthreads) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    cp_async16(base + r * ROWB + c * 16, src + (size_t)r * D + c * 8);
+  }
+}
+
+// Query rows as A fragments.  Row r of the 16-row MMA tile reads q_row(r) (null: a row of zeros).
+// a[ks][0]: row lane/4,     cols ks*16 + (lane%4)*2 + {0,1}     a[ks][1]: row lane/4 + 8, same cols
+// a[ks][2]: row lane/4,     cols + 8                             a[ks][3]: row lane/4 + 8, cols + 8
+__device__ __forceinline__ void load_q_frags(uint32_t (*a)[4], const bf16* row_lo, const bf16* row_hi, int lane) {
+  const int c = (lane & 3) * 2;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    a[ks][0] = row_lo ? *(const uint32_t*)(row_lo + ks * 16 + c) : 0u;
+    a[ks][1] = row_hi ? *(const uint32_t*)(row_hi + ks * 16 + c) : 0u;
+    a[ks][2] = row_lo ? *(const uint32_t*)(row_lo + ks * 16 + 8 + c) : 0u;
+    a[ks][3] = row_hi ? *(const uint32_t*)(row_hi + ks * 16 + 8 + c) : 0u;
+  }
+}
+
+// ------------------------------------------------------------------------------ prefill
+
+#define PF_WARPS 4
+#define PF_STAGES 2
+
+__global__ void __launch_bounds__(PF_WARPS * 32)
+attention_prefill_kernel(MmaAttnArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seq = blockIdx.z, head = blockIdx.y, hk = head / (a.nq / a.nkv);
+  const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
+  const int t0 = blockIdx.x * 64;
+  if (t0 >= q_len) return;
+  const int past = a.past[seq];
+  const int nt = min(64, q_len - t0);
+  const int n_tiles = (past + t0 + nt + KT - 1) / KT;       // keys 0 .. past + t0 + nt - 1
+  const int* pages = a.page_ids + a.page_start[seq];
+
+  // this warp's rows: tokens t0 + warp*16 + {lane/4, lane/4 + 8}
+  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const bf16* q_lo = r_lo < nt ? a.q + ((size_t)(q_begin + t0 + r_lo) * a.nq + head) * D : nullptr;
+  const bf16* q_hi = r_hi < nt ? a.q + ((size_t)(q_begin + t0 + r_hi) * a.nq + head) * D : nullptr;
+  uint32_t qf[KSTEPS][4];
+  load_q_frags(qf, q_lo, q_hi, lane);
+  const int pos_lo = past + t0 + r_lo, pos_hi = past + t0 + r_hi;
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  const float sl2 = a.scale * LOG2E;
+
+  auto issue = [&](int tile) {
+    uint8_t* st = smem + (size_t)(tile % PF_STAGES) * 2 * TILE_BYTES;
+    const size_t base = ((size_t)pages[tile] * a.nkv + hk) * KT * D;
+    load_tile(st, a.k_pool + base, tid, PF_WARPS * 32);
+    load_tile(st + TILE_BYTES, a.v_pool + base, tid, PF_WARPS * 32);
+    cp_async_commit();
+  };
+  issue(0);
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    if (tile + 1 < n_tiles) { issue(tile + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const uint8_t* ks_base = smem + (size_t)(tile % PF_STAGES) * 2 * TILE_BYTES;
+    const uint32_t k_smem = smem_addr(ks_base), v_smem = k_smem + TILE_BYTES;
+    const int kbase = tile * KT;
+    // a warp whose rows all lie before this tile has nothing to add (only on the diagonal tiles)
+    const bool active = kbase <= past + t0 + warp * 16 + 15;
+    if (active) {
+      float s[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {     // pairs of 8-key tiles
+          // matrices: (keys np*16 + 0..7, d ks*16 + 0..7), (same keys, d + 8), (keys + 8, d), (keys + 8, d + 8)
+          const int m = lane >> 3, r = lane & 7;
+          const int key = np * 16 + (m >> 1) * 8 + r, dd = ks * 16 + (m & 1) * 8;
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(k_smem + key * ROWB + dd * 2, b0, b1, b2, b3);
+          mma_bf16(s[np * 2], qf[ks], b0, b1);
+          mma_bf16(s[np * 2 + 1], qf[ks], b2, b3);
+        }
+      }
+      // mask, scale into the log2 domain, running maximum
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int kj = kbase + i * 8 + (lane & 3) * 2;
+        s[i][0] = (kj <= pos_lo) ? s[i][0] * sl2 : -INFINITY;
+        s[i][1] = (kj + 1 <= pos_lo) ? s[i][1] * sl2 : -INFINITY;
+        s[i][2] = (kj <= pos_hi) ? s[i][2] * sl2 : -INFINITY;
+        s[i][3] = (kj + 1 <= pos_hi) ? s[i][3] * sl2 : -INFINITY;
+        mx_lo = fmaxf(mx_lo, fmaxf(s[i][0], s[i][1]));
+        mx_hi = fmaxf(mx_hi, fmaxf(s[i][2], s[i][3]));
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      // rows with nothing visible yet keep a zero accumulator; avoid (-inf) - (-inf)
+      const float ref_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float al_lo = exp2f(m_lo - ref_lo), al_hi = exp2f(m_hi - ref_hi);
+      m_lo = mn_lo; m_hi = mn_hi;
+      float sum_lo = 0.f, sum_hi = 0.f;
+      uint32_t pf[4][4];                  // P as A fragments for the 4 key steps of 16
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p0 = exp2f(s[i][0] - ref_lo), p1 = exp2f(s[i][1] - ref_lo);
+        const float p2 = exp2f(s[i][2] - ref_hi), p3 = exp2f(s[i][3] - ref_hi);
+        sum_lo += p0 + p1; sum_hi += p2 + p3;
+        pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+      l_lo = l_lo * al_lo + sum_lo; l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {      // 16 keys per step
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+          // matrices: (keys kk*16 + 0..7, d dp*16 + 0..7), (keys + 8, same d), (keys, d + 8), (keys + 8, d + 8)
+          const int m = lane >> 3, r = lane & 7;
+          const int key = kk * 16 + (m & 1) * 8 + r, dd = dp * 16 + (m >> 1) * 8;
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(v_smem + key * ROWB + dd * 2, b0, b1, b2, b3);
+          mma_bf16(o[dp * 2], pf[kk], b0, b1);
+          mma_bf16(o[dp * 2 + 1], pf[kk], b2, b3);
+        }
+      }
+    }
+    __syncthreads();    // the stage may be overwritten by the load after next
+  }
+  // the row sums live spread over the 4 lanes of a quad
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+  const int c = (lane & 3) * 2;
+  if (r_lo < nt) {
+    bf16* dst = a.out + ((size_t)(q_begin + t0 + r_lo) * a.nq + head) * D;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) *(uint32_t*)(dst + i * 8 + c) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
+  }
+  if (r_hi < nt) {
+    bf16* dst = a.out + ((size_t)(q_begin + t0 + r_hi) * a.nq + head) * D;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) *(uint32_t*)(dst + i * 8 + c) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
+  }
+}
+
+// ------------------------------------------------------------------------------ decode
+
+#define DC_WARPS 4
+#define DC_STAGES (D <= 128 ? 3 : 2)
+
+__global__ void __launch_bounds__(DC_WARPS * 32)
+attention_decode_kernel(MmaAttnArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seq = blockIdx.z, split = blockIdx.x;
+  const int hk = blockIdx.y / a.head_chunks, chunk = blockIdx.y % a.head_chunks;
+  const int g = a.nq / a.nkv;
+  const int heads_here = min(16, g - chunk * 16);
+  const int head0 = hk * g + chunk * 16;
+  const int tok = a.cu_q[seq];
+  const int pos = a.past[seq];                     // the query's position; keys 0 .. pos are visible
+  const int n_tiles = pos / KT + 1;
+  const int per_split = (n_tiles + a.splits - 1) / a.splits;
+  const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
+  const int* pages = a.page_ids + a.page_start[seq];
+
+  // rows of the MMA tile are query heads
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;
+  const bf16* q_lo = r_lo < heads_here ? a.q + ((size_t)tok * a.nq + head0 + r_lo) * D : nullptr;
+  const bf16* q_hi = r_hi < heads_here ? a.q + ((size_t)tok * a.nq + head0 + r_hi) * D : nullptr;
+  uint32_t qf[KSTEPS][4];
+  load_q_frags(qf, q_lo, q_hi, lane);
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  const float sl2 = a.scale * LOG2E;
+
+  auto issue = [&](int tile) {
+    uint8_t* st = smem + (size_t)((tile - tile_begin) % DC_STAGES) * 2 * TILE_BYTES;
+    const size_t base = ((size_t)pages[tile] * a.nkv + hk) * KT * D;
+    load_tile(st, a.k_pool + base, tid, DC_WARPS * 32);
+    load_tile(st + TILE_BYTES, a.v_pool + base, tid, DC_WARPS * 32);
+  };
+  // prologue: DC_STAGES - 1 tiles in flight (empty groups keep the group count uniform)
+#pragma unroll
+  for (int i = 0; i < DC_STAGES - 1; ++i) {
+    if (tile_begin + i < tile_end) issue(tile_begin + i);
+    cp_async_commit();
+  }
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    if (tile + DC_STAGES - 1 < tile_end) issue(tile + DC_STAGES - 1);
+    cp_async_commit();
+    cp_async_wait<DC_STAGES - 1>();
+    __syncthreads();
+    const uint8_t* st = smem + (size_t)((tile - tile_begin) % DC_STAGES) * 2 * TILE_BYTES;
+    const uint32_t k_smem = smem_addr(st), v_smem = k_smem + TILE_BYTES;
+    const int kbase = tile * KT + warp * 16;        // this warp's 16 keys
+    if (kbase <= pos) {
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int m = lane >> 3, r = lane & 7;
+        const int key = warp * 16 + (m >> 1) * 8 + r, dd = ks * 16 + (m & 1) * 8;
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(k_smem + key * ROWB + dd * 2, b0, b1, b2, b3);
+        mma_bf16(s[0], qf[ks], b0, b1);
+        mma_bf16(s[1], qf[ks], b2, b3);
+      }
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int kj = kbase + i * 8 + (lane & 3) * 2;
+        s[i][0] = (kj <= pos) ? s[i][0] * sl2 : -INFINITY;
+        s[i][1] = (kj + 1 <= pos) ? s[i][1] * sl2 : -INFINITY;
+        s[i][2] = (kj <= pos) ? s[i][2] * sl2 : -INFINITY;
+        s[i][3] = (kj + 1 <= pos) ? s[i][3] * sl2 : -INFINITY;
+        mx_lo = fmaxf(mx_lo, fmaxf(s[i][0], s[i][1]));
+        mx_hi = fmaxf(mx_hi, fmaxf(s[i][2], s[i][3]));
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);   // finite: key kbase is visible
+      const float al_lo = exp2f(m_lo - mn_lo), al_hi = exp2f(m_hi - mn_hi);
+      m_lo = mn_lo; m_hi = mn_hi;
+      uint32_t pf[4];
+      float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float p0 = exp2f(s[i][0] - mn_lo), p1 = exp2f(s[i][1] - mn_lo);
+        const float p2 = exp2f(s[i][2] - mn_hi), p3 = exp2f(s[i][3] - mn_hi);
+        sum_lo += p0 + p1; sum_hi += p2 + p3;
+        pf[i * 2] = pack_bf16(p0, p1);
+        pf[i * 2 + 1] = pack_bf16(p2, p3);
+      }
+      l_lo = l_lo * al_lo + sum_lo; l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+#pragma unroll
+      for (int dp = 0; dp < DTILES / 2; ++dp) {
+        const int m = lane >> 3, r = lane & 7;
+        const int key = warp * 16 + (m & 1) * 8 + r, dd = dp * 16 + (m >> 1) * 8;
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(v_smem + key * ROWB + dd * 2, b0, b1, b2, b3);
+        mma_bf16(o[dp * 2], pf, b0, b1);
+        mma_bf16(o[dp * 2 + 1], pf, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+  // Merge the four warps (each saw a quarter of the keys): [warp][row][D + 2] floats in shared memory.
+  float* mg = (float*)smem;
+  constexpr int RS = D + 2;
+  __syncthreads();
+  {
+    const int c = (lane & 3) * 2;
+    float* lo = mg + ((size_t)warp * 16 + r_lo) * RS;
+    float* hi = mg + ((size_t)warp * 16 + r_hi) * RS;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+      lo[i * 8 + c] = o[i][0]; lo[i * 8 + c + 1] = o[i][1];
+      hi[i * 8 + c] = o[i][2]; hi[i * 8 + c + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) { lo[D] = m_lo; lo[D + 1] = l_lo; hi[D] = m_hi; hi[D + 1] = l_hi; }
+  }
+  __syncthreads();
+  for (int row = warp; row < heads_here; row += DC_WARPS) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) M = fmaxf(M, mg[((size_t)w * 16 + row) * RS + D]);
+    float wgt[DC_WARPS], L = 0.f;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) {
+      const float mw = mg[((size_t)w * 16 + row) * RS + D];
+      wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += wgt[w] * mg[((size_t)w * 16 + row) * RS + D + 1];
+    }
+    const int head = head0 + row;
+    if (a.splits == 1) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* dst = a.out + ((size_t)tok * a.nq + head) * D;
+      for (int dd = lane; dd < D; dd += 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
+        dst[dd] = __float2bfloat16_rn(v * inv);
+      }
+    } else {
+      // partial in the natural-log domain of the combine kernel: max * ln 2
+      float* dst = a.partial + (((size_t)tok * a.nq + head) * a.splits + split) * RS;
+      for (int dd = lane; dd < D; dd += 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
+        dst[dd] = v;
+      }
+      if (lane == 0) { dst[D] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f; dst[D + 1] = L; }
+    }
+  }
+}
+
+// Merge split partials: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
+__global__ void attention_mma_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits) {
+  const size_t row = blockIdx.x;
+  const float* p = partial + row * splits * (D + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * (D + 2) + D]);
+  float denom = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = p[s * (D + 2) + D];
+    if (ms != -INFINITY) denom += expf(ms - M) * p[s * (D + 2) + D + 1];
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = p[s * (D + 2) + D];
+      if (ms != -INFINITY) v += expf(ms - M) * p[s * (D + 2) + dd];
+    }
+    out[row * D + dd] = __float2bfloat16_rn(v * inv);
+  }
+}
+
+extern "C" int odi_attention_mma_head_dim() { return D; }
+
+// decode != 0 requires q_len == 1 for every sequence (max_q_len == 1).
+extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_tokens, int decode,
+                                 cudaStream_t stream) {
+  MmaAttnArgs a = *args;
+  if (a.n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.splits < 1) return ODI_ERR_UNSUPPORTED;
+  const int g = a.nq / a.nkv;
+  static bool configured = false;
+  const int pf_smem = PF_STAGES * 2 * TILE_BYTES;
+  const int dc_merge = DC_WARPS * 16 * (D + 2) * 4;
+  const int dc_smem = DC_STAGES * 2 * TILE_BYTES > dc_merge ? DC_STAGES * 2 * TILE_BYTES : dc_merge;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dc_smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  if (!decode) {
+    if (a.splits != 1 || a.nq > 65535) return ODI_ERR_UNSUPPORTED;
+    dim3 grid((max_q_len + 63) / 64, a.nq, a.n_seqs);
+    attention_prefill_kernel<<<grid, PF_WARPS * 32, pf_smem, stream>>>(a);
+    return launch_status();
+  }
+  if (max_q_len != 1) return ODI_ERR_ARGUMENT;
+  if (a.splits > 1 && a.partial == nullptr) return ODI_ERR_ARGUMENT;
+  a.head_chunks = (g + 15) / 16;
+  dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
+  if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+  attention_decode_kernel<<<grid, DC_WARPS * 32, dc_smem, stream>>>(a);
+  int rc = launch_status();
+  if (rc != 0 || a.splits == 1) return rc;
+  attention_mma_combine_kernel<<<n_tokens * a.nq, D >= 128 ? 128 : 64, 0, stream>>>(a.partial, a.out, a.splits);
+  return launch_status();
+}

@@ -9,6 +9,11 @@
 //   x ^= x >> 30; x *= 0xBF58476D1CE4E5B9; x ^= x >> 27; x *= 0x94D049BB133111EB; x ^= x >> 31
 //   u = (x >> 40) / 2^24
 // One block of 256 threads per row.  Ties of the maximum go to the lowest index.
+//
+// For a decode loop that stays on the device the kernel can also advance the step's
+// counters: with `advance` arrays given, row i adds active[i] (0 or 1) to its position,
+// cached length and step number after it has drawn its token, so the next step finds
+// its inputs in place.
 #include "common.cuh"
 
 #define SAMPLE_THREADS 256
@@ -26,7 +31,8 @@ __device__ __forceinline__ float uniform_draw(unsigned long long seed, unsigned 
 // streams / steps may be null when temperature == 0.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int ld, float temperature,
-              unsigned long long seed, const int* __restrict__ streams, const int* __restrict__ steps) {
+              unsigned long long seed, const int* __restrict__ streams, int* steps,
+              int* advance_pos, int* advance_past, const int* __restrict__ active) {
   __shared__ float s_val[SAMPLE_THREADS];
   __shared__ int s_idx[SAMPLE_THREADS];
   __shared__ float s_prefix[SAMPLE_THREADS + 1];
@@ -49,7 +55,17 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, in
   }
   const float mx = s_val[0];
   const int arg = s_idx[0];
-  if (temperature <= 0.f) { if (tid == 0) out[row] = arg < V ? arg : 0; return; }
+  if (temperature <= 0.f) {
+    if (tid == 0) {
+      out[row] = arg < V ? arg : 0;
+      if (active != nullptr) {
+        const int a = active[row];
+        advance_pos[row] += a; advance_past[row] += a;
+        if (steps != nullptr) steps[row] += a;
+      }
+    }
+    return;
+  }
   __syncthreads();
 
   const float inv_t = 1.f / temperature;
@@ -65,7 +81,9 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, in
   }
   __syncthreads();
   const float total = s_prefix[SAMPLE_THREADS];
-  const float target = uniform_draw(seed, (unsigned long long)streams[row], (unsigned long long)steps[row]) * total;
+  const int step_now = steps[row];   // read by every thread before thread 0 may advance it
+  __syncthreads();
+  const float target = uniform_draw(seed, (unsigned long long)streams[row], (unsigned long long)step_now) * total;
   // The first index whose cumulative weight exceeds the target lies in exactly one segment.
   const float before = s_prefix[tid], after = s_prefix[tid + 1];
   if (before <= target && target < after && lo < hi) {
@@ -77,14 +95,22 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, in
     s_idx[0] = pick;
   }
   __syncthreads();
-  if (tid == 0) out[row] = s_idx[0];
+  if (tid == 0) {
+    out[row] = s_idx[0];
+    if (active != nullptr) {
+      const int a = active[row];
+      advance_pos[row] += a; advance_past[row] += a; steps[row] += a;
+    }
+  }
 }
 
 extern "C" int odi_sample(const float* logits, int* out, int n, int V, int ld, float temperature,
-                          unsigned long long seed, const int* streams, const int* steps,
-                          cudaStream_t stream) {
+                          unsigned long long seed, const int* streams, int* steps, int* advance_pos,
+                          int* advance_past, const int* active, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (temperature > 0.f && (streams == nullptr || steps == nullptr)) return ODI_ERR_ARGUMENT;
-  sample_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, out, V, ld, temperature, seed, streams, steps);
+  if (active != nullptr && (advance_pos == nullptr || advance_past == nullptr)) return ODI_ERR_ARGUMENT;
+  sample_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, out, V, ld, temperature, seed, streams, steps,
+                                                  advance_pos, advance_past, active);
   return launch_status();
 }

@@ -1,0 +1,190 @@
+"""Decode steps as CUDA graphs: one token per live sequence per replay, nothing rebuilt on the host.
+
+The generic step function builds its index tensors on the host and launches some three
+hundred kernels from Python; for single-token steps that costs several times what the
+GPU needs.  A :class:`DecodeRunner` keeps the step's index tensors in fixed device
+buffers, captures embedding -> layers -> head -> sampling once per batch width as a CUDA
+graph, and replays it: the sampled token is written where the next step reads its
+input, and the sampling kernel advances positions, lengths and step numbers in place.
+Per step the host only makes sure every sequence has a page for its next position.
+
+Widths are powers of two; rows beyond the live sequences are padding: they run on a
+slot outside the cache's capacity with a constant length of zero and their results are dropped, so
+padding changes no result.  The same kernels run as in the generic step; only the way
+they are launched differs.  Models with parts that do host work per step (anything that
+is not marked ``graph_safe``) do not use this path.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+
+
+class _DecodeContext:
+    """The fixed-buffer counterpart of :class:`~ondeviceinfer_b200.engine.step.StepContext`
+    for ``width`` sequences that bring one token each."""
+
+    def __init__(self, cache, width: int, max_pages: int, device, kv_len_hint: int) -> None:
+        self.width = width
+        self.n_seqs = self.n_tokens = self.n_want = width
+        self.max_q_len = 1
+        self.q_lens = [1] * width
+        self.max_kv_len = kv_len_hint
+        self.max_pages = max_pages
+        arange = torch.arange(width + 1, dtype=torch.int32, device=device)
+        zeros = lambda n: torch.zeros(n, dtype=torch.int32, device=device)
+        self.token_ids, self.tok_pos, self.past, self.slots = zeros(width), zeros(width), zeros(width), zeros(width)
+        self.streams, self.steps, self.active = zeros(width), zeros(width), zeros(width)
+        self.tok_seq = arange[:width].clone()
+        self.want_rows = arange[:width].clone()
+        self.cu_q = arange.clone()
+        self._page_start = (arange * max_pages).contiguous()
+        self._page_ids = [zeros(width * max_pages) for _ in cache.kv_groups]
+        self._memo: Dict[object, object] = {}
+        self.slot_list: List[int] = []
+
+    def page_table(self, group_index: int):
+        return self._page_start, self._page_ids[group_index]
+
+    def memo(self, key, make):
+        if key not in self._memo:
+            self._memo[key] = make()
+        return self._memo[key]
+
+
+class DecodeRunner:
+    def __init__(self, model, cache, *, temperature: float = 0.0, seed: int = 0, kv_len_hint: int = 2048) -> None:
+        self.model, self.cache = model, cache
+        self.temperature, self.seed = float(temperature), int(seed)
+        self.kv_len_hint = kv_len_hint
+        self.max_pages = cache.n_pages
+        self._graphs: Dict[int, tuple] = {}
+        self.live_slots: List[int] = []
+        self.ctx: Optional[_DecodeContext] = None
+        self._host_pages: List[np.ndarray] = []
+        self._pinned_tokens: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ set-up
+
+    def close(self) -> None:
+        self._graphs.clear()
+
+    @staticmethod
+    def _width_for(n: int) -> int:
+        width = 1
+        while width < n:
+            width *= 2
+        return width
+
+    def begin(self, slots: Sequence[int], tokens: Sequence[int], streams: Sequence[int], steps: Sequence[int]) -> None:
+        """Make ``slots`` the live set: sequence i will be fed ``tokens[i]`` next; ``streams``
+        and ``steps`` are its request index and the number of tokens it has produced so far."""
+        n = len(slots)
+        if n == 0:
+            raise ValueError("a decode batch needs at least one sequence")
+        width = self._width_for(n)
+        if width not in self._graphs:
+            self._graphs[width] = self._capture(width)
+        ctx, _, _ = self._graphs[width]
+        self.ctx, self.live_slots = ctx, list(slots)
+        pad = self.cache.pad_slot
+        row_slots = list(slots) + [pad] * (width - n)
+        lengths = [self.cache.lengths[s] for s in slots] + [0] * (width - n)
+        fill = lambda values: torch.tensor(list(values) + [0] * (width - len(values)), dtype=torch.int32)
+        host = torch.stack([fill(tokens), torch.tensor(lengths, dtype=torch.int32), torch.tensor(row_slots, dtype=torch.int32),
+                            fill(streams), fill(steps), fill([1] * n)]).to(self.model.device)
+        ctx.token_ids.copy_(host[0]); ctx.tok_pos.copy_(host[1]); ctx.past.copy_(host[1]); ctx.slots.copy_(host[2])
+        ctx.streams.copy_(host[3]); ctx.steps.copy_(host[4]); ctx.active.copy_(host[5])
+        ctx.slot_list = row_slots
+        self._host_pages = []
+        for g, group in enumerate(self.cache.kv_groups):
+            table = np.zeros((width, self.max_pages), dtype=np.int32)
+            for i, slot in enumerate(row_slots):
+                pages = group.slot_pages[slot]
+                table[i, :len(pages)] = pages
+            self._host_pages.append(table)
+            ctx._page_ids[g].copy_(torch.from_numpy(table.reshape(-1)))
+
+    def _reserve_next(self, ahead: int = 1) -> None:
+        """Pages for the next ``ahead`` positions of every live sequence; upload what changed."""
+        n = len(self.live_slots)
+        before = [[len(g.slot_pages[s]) for s in self.live_slots] for g in self.cache.kv_groups]
+        self.cache.reserve(self.live_slots, [ahead] * n)
+        for g, group in enumerate(self.cache.kv_groups):
+            for i, slot in enumerate(self.live_slots):
+                pages = group.slot_pages[slot]
+                if len(pages) != before[g][i]:
+                    self._host_pages[g][i, :len(pages)] = pages
+                    lo = i * self.max_pages + before[g][i]
+                    self.ctx._page_ids[g][lo:lo + len(pages) - before[g][i]].copy_(
+                        torch.tensor(pages[before[g][i]:], dtype=torch.int32))
+
+    # ------------------------------------------------------------------ capture
+
+    def _run_once(self, ctx: _DecodeContext) -> None:
+        ctx._memo.clear()
+        logits = self.model.forward(ctx, self.cache)
+        ops.sample(logits, ctx.token_ids, self.temperature, self.seed, ctx.streams, ctx.steps,
+                   advance_pos=ctx.tok_pos, advance_past=ctx.past, active=ctx.active)
+
+    def _capture(self, width: int):
+        device = self.model.device
+        ctx = _DecodeContext(self.cache, width, self.max_pages, device, self.kv_len_hint)
+        pad = self.cache.pad_slot
+        ctx.slots.fill_(pad)
+        ctx.slot_list = [pad] * width
+        for g, group in enumerate(self.cache.kv_groups):
+            ctx._page_ids[g].fill_(group.slot_pages[pad][0])
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            self._run_once(ctx)           # warm-up: compiles, sizes scratch, sets function attributes
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
+        counted = dict(ops.LAUNCHES)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._run_once(ctx)
+        launches = {k: ops.LAUNCHES[k] - counted[k] for k in ("own", "library")}
+        ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
+        return ctx, graph, launches
+
+    # ------------------------------------------------------------------ steps
+
+    def step_device(self, n_steps: int = 1) -> None:
+        """Replay ``n_steps`` decode steps back to back; tokens stay on the device."""
+        self._reserve_next(n_steps)
+        _, graph, launches = self._graphs[self.ctx.width]
+        for _ in range(n_steps):
+            graph.replay()
+        ops.LAUNCHES["own"] += n_steps * launches["own"]
+        ops.LAUNCHES["library"] += n_steps * launches["library"]
+        self.cache.advance(self.live_slots, [n_steps] * len(self.live_slots))
+
+    def step(self, host_tokens: Optional[Sequence[int]] = None) -> List[int]:
+        """One decode step; returns the sampled tokens of the live sequences.  With
+        ``host_tokens`` the step's inputs are first copied from pinned host memory."""
+        n = len(self.live_slots)
+        if host_tokens is not None:
+            if self._pinned_tokens is None or self._pinned_tokens.numel() < n:
+                self._pinned_tokens = torch.empty(max(n, 64), dtype=torch.int32).pin_memory()
+            self._pinned_tokens[:n] = torch.as_tensor(host_tokens, dtype=torch.int32)
+            self.ctx.token_ids[:n].copy_(self._pinned_tokens[:n], non_blocking=True)
+        self.step_device(1)
+        return self.ctx.token_ids[:n].tolist()
+
+    def drop(self, finished_rows: Sequence[int], streams: Sequence[int], steps: Sequence[int]) -> None:
+        """Remove rows (indices into the live set) and continue with the others; ``streams``
+        and ``steps`` describe the sequences that stay, in order."""
+        keep = [i for i in range(len(self.live_slots)) if i not in set(finished_rows)]
+        if not keep:
+            self.live_slots = []
+            return
+        tokens = self.ctx.token_ids[:len(self.live_slots)].tolist()
+        self.begin([self.live_slots[i] for i in keep], [tokens[i] for i in keep], streams, steps)

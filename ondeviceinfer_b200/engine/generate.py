@@ -77,9 +77,13 @@ def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
                       step: Callable[[List[int], List[List[int]]], object],
                       sample: Callable[[object, List[int], List[int]], List[int]],
                       batches: Sequence[Sequence[int]], stop_token_ids: Sequence[int] = (),
-                      synchronize: Callable[[], None] = lambda: None) -> GenerationResult:
+                      synchronize: Callable[[], None] = lambda: None, decoder=None) -> GenerationResult:
     """``step(slots, token_runs)`` returns the logits at each run's last token;
-    ``sample(logits, request_indices, step_numbers)`` returns one token per row."""
+    ``sample(logits, request_indices, step_numbers)`` returns one token per row.
+
+    ``decoder`` (optional) fuses step and sampling for the one-token steps: an object with
+    ``begin(slots, last_tokens, request_indices, step_numbers)`` (called whenever the live
+    set changed) and ``step() -> tokens`` (one decode step of the live set, in order)."""
     if max_new_tokens <= 0:
         raise ValueError("max_new_tokens must be positive")
     stop = set(int(t) for t in stop_token_ids)
@@ -98,6 +102,7 @@ def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
             synchronize()
             prefill_seconds += time.perf_counter() - start
             start = time.perf_counter()
+            changed = True
             while True:
                 still = []
                 for r, tok in zip(live, tokens):
@@ -110,11 +115,19 @@ def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
                         still.append(r)
                         continue
                     free(slots.pop(r))
+                changed = changed or len(still) != len(live)
                 live = still
                 if not live:
                     break
-                logits = step([slots[r] for r in live], [[generated[r][-1]] for r in live])
-                tokens = sample(logits, live, [len(generated[r]) for r in live])
+                if decoder is None:
+                    logits = step([slots[r] for r in live], [[generated[r][-1]] for r in live])
+                    tokens = sample(logits, live, [len(generated[r]) for r in live])
+                else:
+                    if changed:
+                        decoder.begin([slots[r] for r in live], [generated[r][-1] for r in live], live,
+                                      [len(generated[r]) for r in live])
+                        changed = False
+                    tokens = decoder.step()
                 decode_steps += 1
             synchronize()
             decode_seconds += time.perf_counter() - start

@@ -82,6 +82,12 @@ class DecoderModel:
         if self.runtime is None:
             raise RuntimeError("the model has no weights yet: call load() first")
 
+    @property
+    def graph_safe(self) -> bool:
+        """True if every part may be captured in a CUDA graph (no host work per step)."""
+        return all(getattr(layer, "graph_safe", False) for layer in self.layers) and \
+            getattr(self.final_norm, "graph_safe", False)
+
     # ------------------------------------------------------------------ cache
 
     def make_cache(self, *, max_tokens: int, max_seqs: int, max_step_tokens: int = 256) -> SequenceCache:

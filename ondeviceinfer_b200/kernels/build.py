@@ -149,6 +149,7 @@ ALL_SOURCES = {
     "sampling": [{}],
     "gemm_tcgen05": [{}],
     "attention_simt": [{"ODI_HEAD_DIM": 128}],
+    "attention_mma": [{"ODI_HEAD_DIM": 128}],
 }
 
 

@@ -345,12 +345,57 @@ def attention_simt(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, 
                                   _stream()), "attention_simt", 2 if splits > 1 else 1)
 
 
+class _MmaAttnArgs(Structure):
+    _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p),
+                ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
+                ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("splits", c_int),
+                ("head_chunks", c_int), ("scale", c_float)]
+
+
+MMA_HEAD_DIMS = tuple(range(16, 257, 16))
+
+
+def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
+                  nq: int, nkv: int, d: int, page_size: int, scale: float, splits: int = 1,
+                  partial: Optional[torch.Tensor] = None) -> None:
+    """bf16 causal GQA on the tensor cores: the prefill kernel for any q_len, the split-key
+    decode kernel when every sequence brings exactly one token.  No window."""
+    if d not in MMA_HEAD_DIMS:
+        raise KernelError(f"the tensor-core attention takes head sizes in steps of 16 up to 256, not {d}")
+    if page_size != 64:
+        raise KernelError("the tensor-core attention works on pages of 64 positions")
+    _require(q, "q", torch.bfloat16)
+    _require(out, "out", torch.bfloat16)
+    _require(k_pool, "k_pool", torch.bfloat16)
+    _require(v_pool, "v_pool", torch.bfloat16)
+    n_tokens = q.numel() // (nq * d)
+    if out.numel() != q.numel():
+        raise KernelError("q and out disagree")
+    decode = max_q_len == 1
+    if not decode:
+        splits = 1
+    if splits > 1:
+        need = n_tokens * nq * splits * (d + 2)
+        if partial is None or partial.numel() < need or partial.dtype != torch.float32:
+            raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
+    args = _MmaAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
+                        _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale)
+    lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
+    _check(lib.odi_attention_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(1 if decode else 0),
+                                 _stream()), "attention_mma", 2 if splits > 1 else 1)
+
+
 # ------------------------------------------------------------------------------ sampling
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, seed: int = 0,
-           streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> None:
-    """out[i] = argmax(logits[i]) if temperature == 0 else a draw from softmax(logits[i] / temperature)."""
+           streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None, *,
+           advance_pos: Optional[torch.Tensor] = None, advance_past: Optional[torch.Tensor] = None,
+           active: Optional[torch.Tensor] = None) -> None:
+    """out[i] = argmax(logits[i]) if temperature == 0 else a draw from softmax(logits[i] / temperature).
+
+    With ``active`` (int32 0/1 per row) the kernel also adds ``active[i]`` to ``advance_pos[i]``,
+    ``advance_past[i]`` and ``steps[i]``: the bookkeeping of a decode loop that stays on the device."""
     _require(logits, "logits", torch.float32, 2)
     _require(out, "out", torch.int32, 1)
     n, V = logits.shape
@@ -359,6 +404,10 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, seed: in
     if temperature > 0:
         _require(streams, "streams", torch.int32, 1)
         _require(steps, "steps", torch.int32, 1)
+    if active is not None:
+        for name, t in (("active", active), ("advance_pos", advance_pos), ("advance_past", advance_past)):
+            _require(t, name, torch.int32, 1)
     lib = load_library("sampling")
     _check(lib.odi_sample(_ptr(logits), _ptr(out), c_int(n), c_int(V), c_int(V), c_float(temperature),
-                          c_ulonglong(seed & ((1 << 64) - 1)), _ptr(streams), _ptr(steps), _stream()), "sample")
+                          c_ulonglong(seed & ((1 << 64) - 1)), _ptr(streams), _ptr(steps), _ptr(advance_pos),
+                          _ptr(advance_past), _ptr(active), _stream()), "sample")

@@ -23,6 +23,8 @@ from .linear import linear
 
 
 class Attention(Part):
+    graph_safe = True   # no host work that depends on the step's values: may be captured in a CUDA graph
+
     def __init__(self, spec: AttentionSpec) -> None:
         super().__init__(spec)
         if spec.num_heads % spec.num_kv_heads != 0:
@@ -80,15 +82,25 @@ class Attention(Part):
         linear(o, self.w_o, residual=residual)
 
     def attend(self, q, o, ctx, view, page_start, page_ids) -> None:
+        """bf16 without a window: the tensor-core kernels (prefill form, or split-key decode form
+        when every sequence brings one token).  float32, windows, head sizes above 256: the
+        CUDA-core kernel."""
         s = self.spec
+        tensor_cores = q.dtype == torch.bfloat16 and s.window is None and s.head_dim <= 256
         splits, partial = 1, None
         if ctx.max_q_len == 1:
             # decode: cut long key ranges so that enough blocks run side by side
-            work = ctx.n_seqs * s.num_kv_heads
-            splits = max(1, min(16, 296 // max(work, 1), (ctx.max_kv_len + 255) // 256))
+            work = ctx.n_seqs * s.num_kv_heads * ((s.num_heads // s.num_kv_heads + 15) // 16)
+            tiles = (ctx.max_kv_len + PAGE_SIZE - 1) // PAGE_SIZE
+            splits = max(1, min(32, 592 // max(work, 1), tiles // 2 if tensor_cores else (ctx.max_kv_len + 255) // 256))
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.head_dim + 2),),
                                       dtype=torch.float32, device=q.device)
+        if tensor_cores:
+            ops.attention_mma(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
+                              n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
+                              d=s.head_dim, page_size=PAGE_SIZE, scale=self.scale, splits=splits, partial=partial)
+            return
         ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                            n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
                            d=s.head_dim, page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages,

@@ -30,6 +30,10 @@ class PreNormBlock(Part):
     def cache_needs(self):
         return tuple(self.mixer.cache_needs())
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(part, "graph_safe", False) for part in self._children())
+
     def forward(self, hidden, ctx, view) -> None:
         self.mixer.forward(self.mixer_norm(hidden), ctx, view, hidden)
         self.ffn.forward(self.ffn_norm(hidden), ctx, hidden)

@@ -11,6 +11,8 @@ from .linear import gated_linear, linear
 
 
 class GatedMLP(Part):
+    graph_safe = True   # no host work that depends on the step's values: may be captured in a CUDA graph
+
     """down(silu(gate(x)) * up(x)).  The gate and up matrices are concatenated at load so
     that one matrix product yields both; the activation is taken in fp32 and rounded once."""
 

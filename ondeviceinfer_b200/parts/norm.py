@@ -11,6 +11,8 @@ from .base import Part, register_part
 
 
 class RMSNorm(Part):
+    graph_safe = True   # no host work that depends on the step's values: may be captured in a CUDA graph
+
     """weight * cast(x * rsqrt(mean(x^2) + eps)): statistics in fp32, cast to the compute
     dtype before the multiplication by the weight."""
 

@@ -92,14 +92,14 @@ def test_groups_by_need_have_storage_of_their_own():
     g_full = next(g for g in cache.kv_groups if g.need.window is None)
     g_win = next(g for g in cache.kv_groups if g.need.window == 40)
     assert g_full.owners == [0, 2] and g_win.owners == [1, 3]
-    assert g_full.pool.shape == (2, 2, 16, 2, PAGE_SIZE, 16)
+    assert g_full.pool.shape == (2, 2, 16 + 1, 2, PAGE_SIZE, 16)   # one more page for padding rows
     assert g_full.pool.data_ptr() != g_win.pool.data_ptr()
     assert g_full.ring_pages == 0 and g_win.ring_pages == pages_for(40 + 32 - 1) + 1
     assert cache.max_step_tokens == 32
     # entry 5 reads entry 2's cache and writes nothing
     assert cache.view(5).keys.data_ptr() == cache.view(2).keys.data_ptr() and not cache.view(5).writes_kv
     assert cache.view(2).writes_kv and cache.view(0).keys.data_ptr() != cache.view(2).keys.data_ptr()
-    assert cache.view(4).state.shape == (4, 4, 8) and cache.view(4).keys is None
+    assert cache.view(4).state.shape == (4 + 1, 4, 8) and cache.view(4).keys is None
     s = cache.alloc()
     cache.reserve([s], [500])
     cache.advance([s], [500])
@@ -144,6 +144,18 @@ def test_random_traffic_never_loses_or_doubles_anything():
     cache.reset()
     cache.check()
     assert cache.kv_groups[0].pages.held_count == 0 and cache.slots.held_count == 0
+
+
+def test_padding_slot_lies_outside_the_capacity():
+    cache = make_cache(max_tokens=2 * PAGE_SIZE, max_seqs=2)
+    group = cache.kv_groups[0]
+    assert cache.pad_slot == 2 and group.slot_pages[cache.pad_slot] == [group.pad_page] and group.pad_page == 2
+    a, b = cache.alloc(), cache.alloc()
+    assert cache.pad_slot not in (a, b)
+    cache.reserve([a, b], [PAGE_SIZE, PAGE_SIZE])
+    assert group.pad_page not in group.slot_pages[a] + group.slot_pages[b]
+    assert cache.lengths[cache.pad_slot] == 0
+    cache.check()
 
 
 def test_bad_sizes():

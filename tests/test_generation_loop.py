@@ -122,3 +122,35 @@ def test_plan_batches_respects_slots_and_tokens():
     # prompt + max_new_tokens - 1 positions are cached: 64 + 1 - 1 fits one page, 64 + 2 - 1 does not
     assert plan_batches([64, 64], 1, max_seqs=8, max_tokens=128, page_size=64) == [[0, 1]]
     assert plan_batches([64, 64], 2, max_seqs=8, max_tokens=128, page_size=64) == [[0], [1]]
+
+
+def test_fused_decoder_is_told_when_the_live_set_changes():
+    """With a decoder, one-token steps go through begin/step instead of step/sample; begin is
+    called again only when a sequence has left the batch."""
+    scripts = {0: [10, 11, 12, 13], 1: [20, 99, 21, 22], 2: [30, 31, 32, 33]}
+    script = Script(scripts)
+
+    class Decoder:
+        begins, live, position = [], [], {}
+
+        def begin(self, slots, tokens, requests, steps):
+            self.begins.append((list(slots), list(tokens), list(requests), list(steps)))
+            self.live = list(requests)
+            self.position = dict(zip(requests, steps))
+
+        def step(self):
+            out = [scripts[r][self.position[r]] for r in self.live]
+            for r in self.live:
+                self.position[r] += 1
+            return out
+
+    decoder = Decoder()
+    result = generate_requests([[1, 2, 3], [4], [5, 6]], max_new_tokens=4, alloc=script.alloc, free=script.free,
+                               step=script.step, sample=script.sample, batches=[[0, 1, 2]], stop_token_ids=[99],
+                               decoder=decoder)
+    assert result.generated_ids == [[10, 11, 12, 13], [20, 99], [30, 31, 32, 33]]
+    assert len(script.steps) == 1                      # only the prompts went through step()
+    assert [b[2] for b in decoder.begins] == [[0, 1, 2], [0, 2]]
+    assert decoder.begins[0][1] == [10, 20, 30] and decoder.begins[0][3] == [1, 1, 1]
+    assert decoder.begins[1][1] == [11, 31] and decoder.begins[1][3] == [2, 2]
+    assert result.decode_steps == 3 and not script.held

@@ -395,3 +395,72 @@ def test_gemm_tcgen05_refuses_unaligned_k():
     assert not ops.gemm_bf16_supported(x, w)
     with pytest.raises(ops.KernelError):
         ops.gemm_bf16(x, w, torch.empty(4, 8, dtype=torch.bfloat16, device=DEV), ops.EPI_STORE_BF16)
+
+
+MMA_CASES = [
+    # d, nq, nkv, lengths, past, splits
+    (16, 4, 2, [5, 11, 17], [0, 0, 0], 1),
+    (48, 6, 2, [1, 70, 33], [0, 0, 0], 1),
+    (128, 32, 8, [200, 64, 65, 1], [0, 0, 0, 0], 1),           # whole prompts, page edges
+    (128, 4, 1, [40, 3, 130], [100, 200, 7], 1),                # chunks on a cache
+    (64, 8, 8, [1, 1, 1], [0, 63, 64], 1),                      # decode, the first positions and a page edge
+    (128, 32, 8, [1, 1, 1, 1], [300, 64, 63, 1000], 1),         # decode, ragged
+    (128, 32, 8, [1, 1, 1, 1], [300, 64, 63, 1000], 4),         # the same with split keys
+    (128, 40, 2, [1, 1], [500, 2], 3),                          # 20 query heads per kv head: two row chunks
+    (256, 2, 1, [20, 1], [0, 77], 1),
+    (80, 3, 1, [1], [129], 2),
+]
+
+
+@pytest.mark.parametrize("d,nq,nkv,lengths,past,splits", MMA_CASES)
+def test_attention_mma(d, nq, nkv, lengths, past, splits):
+    torch.manual_seed(12)
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=13)
+    n = sum(lengths)
+    q = torch.randn(n, nq, d)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.empty(n, nq * d, dtype=torch.bfloat16, device=DEV)
+    decode = max(lengths) == 1
+    splits = splits if decode else 1
+    partial = torch.empty(n * nq * splits * (d + 2), dtype=torch.float32, device=DEV) if splits > 1 else None
+    ops.attention_mma(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                      setup["page_start"], setup["page_ids"], n_seqs=len(lengths), max_q_len=max(lengths), nq=nq,
+                      nkv=nkv, d=d, page_size=64, scale=scale, splits=splits, partial=partial)
+    expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, 0, scale, "bfloat16")
+    close(out, expected, "bfloat16")
+
+
+def test_attention_mma_finds_one_far_key():
+    """One key among a thousand carries the answer (decode form with and without splits,
+    prefill form at the last row of a long prompt)."""
+    d, nq, nkv = 128, 8, 2
+    lengths, past = [1, 1], [1000, 190]
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=14)
+    q = torch.randn(2, nq, d) * 0.1
+    targets = {0: 3, 1: 127}
+    for tok, key in targets.items():
+        k = setup["dense"][tok][0]
+        q[tok] = torch.nn.functional.normalize(k[:, key], dim=-1).repeat_interleave(nq // nkv, 0) * 40.0
+    scale = 1.0 / math.sqrt(d)
+    for splits in (1, 6):
+        out = torch.empty(2, nq * d, dtype=torch.bfloat16, device=DEV)
+        partial = torch.empty(2 * nq * splits * (d + 2), dtype=torch.float32, device=DEV) if splits > 1 else None
+        ops.attention_mma(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                          setup["page_start"], setup["page_ids"], n_seqs=2, max_q_len=1, nq=nq, nkv=nkv, d=d,
+                          page_size=64, scale=scale, splits=splits, partial=partial)
+        for tok, key in targets.items():
+            value = setup["dense"][tok][1][:, key].bfloat16().float().repeat_interleave(nq // nkv, 0).reshape(-1)
+            assert float((out[tok].float().cpu() - value).abs().max()) < 0.05, (splits, tok)
+    # prefill form: 700 tokens, the last query must find key 5
+    setup = paged_setup([700], [0], nkv, d, "bfloat16", seed=15)
+    q = torch.randn(700, nq, d) * 0.1
+    k, v = setup["dense"][0]
+    q[699] = torch.nn.functional.normalize(k[:, 5], dim=-1).repeat_interleave(nq // nkv, 0) * 40.0
+    out = torch.empty(700, nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_mma(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                      setup["page_start"], setup["page_ids"], n_seqs=1, max_q_len=700, nq=nq, nkv=nkv, d=d,
+                      page_size=64, scale=scale)
+    value = v[:, 5].bfloat16().float().repeat_interleave(nq // nkv, 0).reshape(-1)
+    assert float((out[699].float().cpu() - value).abs().max()) < 0.05
+    expected = plain_attention(q, setup["dense"], [700], [0], nq, nkv, d, 0, scale, "bfloat16")
+    close(out, expected, "bfloat16")
