@@ -107,6 +107,8 @@ __device__ __forceinline__ void load_q_frags(uint32_t (*a)[4], const bf16* row_l
 
 __global__ void __launch_bounds__(PF_WARPS * 32)
 attention_prefill_kernel(MmaAttnArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seq = blockIdx.z, head = blockIdx.y, hk = head / (a.nq / a.nkv);
@@ -239,6 +241,8 @@ attention_prefill_kernel(MmaAttnArgs a) {
 
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_kernel(MmaAttnArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seq = blockIdx.z, split = blockIdx.x;
@@ -397,6 +401,8 @@ attention_decode_kernel(MmaAttnArgs a) {
 
 // Merge split partials: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
 __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const float* p = partial + row * splits * (D + 2);
   float M = -INFINITY;
@@ -440,7 +446,7 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   if (!decode) {
     if (a.splits != 1 || a.nq > 65535) return ODI_ERR_UNSUPPORTED;
     dim3 grid((max_q_len + 63) / 64, a.nq, a.n_seqs);
-    attention_prefill_kernel<<<grid, PF_WARPS * 32, pf_smem, stream>>>(a);
+    odi_rc = launch_pdl((attention_prefill_kernel), dim3(grid), dim3(PF_WARPS * 32), pf_smem, stream, a);
     return launch_status();
   }
   if (max_q_len != 1) return ODI_ERR_ARGUMENT;
@@ -448,9 +454,10 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   a.head_chunks = (g + 15) / 16;
   dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
-  attention_decode_kernel<<<grid, DC_WARPS * 32, dc_smem, stream>>>(a);
+  odi_rc = launch_pdl((attention_decode_kernel), dim3(grid), dim3(DC_WARPS * 32), dc_smem, stream, a);
   int rc = launch_status();
   if (rc != 0 || a.splits == 1) return rc;
-  attention_mma_combine_kernel<<<n_tokens * a.nq, D >= 128 ? 128 : 64, 0, stream>>>(a.partial, a.out, a.splits);
+  const int combine_threads = D >= 128 ? 128 : 64;
+  odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream, a.partial, a.out, a.splits);
   return launch_status();
 }

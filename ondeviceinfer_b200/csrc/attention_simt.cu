@@ -45,6 +45,8 @@ struct AttnArgs {
 template <typename T>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_simt_kernel(AttnArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) float smem[];
   float* Ks = smem;                    // [KT][KSTR]
   float* Vs = Ks + KT * KSTR;          // [KT][D]
@@ -198,6 +200,8 @@ attention_simt_kernel(AttnArgs a) {
 // Merge the partials of one (token, head): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;  // token * nq + head
   const float* p = partial + row * splits * (D + 2);
   float M = -INFINITY;
@@ -247,13 +251,13 @@ extern "C" int odi_attention_simt(const AttnArgs* args, int max_q_len, int n_tok
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  if (dtype == 0) attention_simt_kernel<float><<<grid, NWARPS * 32, smem, stream>>>(a);
-  else attention_simt_kernel<bf16><<<grid, NWARPS * 32, smem, stream>>>(a);
+  if (dtype == 0) odi_rc = launch_pdl((attention_simt_kernel<float>), dim3(grid), dim3(NWARPS * 32), smem, stream, a);
+  else odi_rc = launch_pdl((attention_simt_kernel<bf16>), dim3(grid), dim3(NWARPS * 32), smem, stream, a);
   int rc = launch_status();
   if (rc != 0 || a.splits == 1) return rc;
   const int rows = n_tokens * a.nq;
   const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
-  if (dtype == 0) attention_combine_kernel<float><<<rows, threads, 0, stream>>>(a.partial, (float*)a.out, a.splits);
-  else attention_combine_kernel<bf16><<<rows, threads, 0, stream>>>(a.partial, (bf16*)a.out, a.splits);
+  if (dtype == 0) odi_rc = launch_pdl((attention_combine_kernel<float>), dim3(rows), dim3(threads), 0, stream, a.partial, (float*)a.out, a.splits);
+  else odi_rc = launch_pdl((attention_combine_kernel<bf16>), dim3(rows), dim3(threads), 0, stream, a.partial, (bf16*)a.out, a.splits);
   return launch_status();
 }

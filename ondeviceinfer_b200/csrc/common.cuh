@@ -60,7 +60,48 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
-static inline int launch_status() { return (int)cudaGetLastError(); }
+// Result of the launches since the last call: the first launch error, else cudaGetLastError().
+static thread_local int odi_rc = 0;
+static inline int launch_status() {
+  const int rc = odi_rc != 0 ? odi_rc : (int)cudaGetLastError();
+  odi_rc = 0;
+  return rc;
+}
+
+// Programmatic dependent launch.  Every kernel of this library starts with pdl_wait() before it
+// touches memory that an earlier kernel of the stream may write or read, and tells the runtime
+// with pdl_launch_dependents() that the next kernel may be scheduled; launched through
+// launch_pdl() the next kernel's launch latency and set-up then overlap this kernel's run.
+// Both instructions do nothing in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline int pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("ODI_PDL");
+    enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args...);
+  return odi_rc != 0 ? odi_rc : (int)e;      // keep the first error of a launcher
+}
 
 // Position of key `pos` inside a sequence's page list.  A group that keeps every key
 // has ring_pages == 0; a windowed group keeps a ring of ring_pages pages per sequence.

@@ -18,6 +18,8 @@ template <bool VEC>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* C,
                 const float* R, int M, int N, int K, int lda, int ldw, int ldc, int ldr) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ __align__(16) float As[TK][TM + 4];
   __shared__ __align__(16) float Ws[TK][TN + 4];
   const int tid = threadIdx.x;
@@ -80,7 +82,7 @@ extern "C" int odi_gemm_f32(const float* A, const float* W, float* C, const floa
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
   const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) &&
                    ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
-  if (vec) gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr);
-  else gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(A, W, C, R, M, N, K, lda, ldw, ldc, ldr);
+  if (vec) odi_rc = launch_pdl((gemm_f32_kernel<true>), dim3(grid), dim3(256), 0, stream, A, W, C, R, M, N, K, lda, ldw, ldc, ldr);
+  else odi_rc = launch_pdl((gemm_f32_kernel<false>), dim3(grid), dim3(256), 0, stream, A, W, C, R, M, N, K, lda, ldw, ldc, ldr);
   return launch_status();
 }

@@ -239,13 +239,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
+  pdl_launch_dependents();      // the next kernel may be scheduled; it waits for this grid before it reads
 
   if (warp == 0) {
     if (lane == 0) {
       const CUtensorMap* map_l = SWAP ? &map_x : &map_w;
       const CUtensorMap* map_c = SWAP ? &map_w : &map_x;
       const int l_row = SWAP ? tok0 : n0, c_row = SWAP ? n0 : tok0;
-      for (int i = 0; i < kb_count; ++i) {
+      // Weights are never written by a kernel, so in the decode form their first tiles are
+      // requested before this grid waits for the kernels it depends on; only the activation
+      // tiles (and everything the epilogue touches, which runs after them) come after the wait.
+      const int pre = SWAP ? 0 : min(STAGES, kb_count);
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
+        const int k0 = (kb_begin + i) * BK;
+        mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+        tma_load_2d(dst, map_l, k0, l_row, full0 + 8 * i);
+        if (L_TILES == 2) tma_load_2d(dst + L_BYTES, map_l, k0, l_row + a.dual_offset, full0 + 8 * i);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+        const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
+        tma_load_2d(dst + L_BYTES * L_TILES, map_c, (kb_begin + i) * BK, c_row, full0 + 8 * i);
+      }
+      for (int i = pre; i < kb_count; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
         if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_ptr)) { atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_PRODUCER); break; }
@@ -435,7 +452,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kernel<<<grid, GEMM_THREADS, SMEM, stream>>>(mw, mx, a);
+  odi_rc = launch_pdl((kernel), dim3(grid), dim3(GEMM_THREADS), SMEM, stream, mw, mx, a);
   return launch_status();
 }
 

@@ -33,6 +33,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int ld, float temperature,
               unsigned long long seed, const int* __restrict__ streams, int* steps,
               int* advance_pos, int* advance_past, const int* __restrict__ active) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float s_val[SAMPLE_THREADS];
   __shared__ int s_idx[SAMPLE_THREADS];
   __shared__ float s_prefix[SAMPLE_THREADS + 1];
@@ -110,7 +112,7 @@ extern "C" int odi_sample(const float* logits, int* out, int n, int V, int ld, f
   if (n <= 0) return 0;
   if (temperature > 0.f && (streams == nullptr || steps == nullptr)) return ODI_ERR_ARGUMENT;
   if (active != nullptr && (advance_pos == nullptr || advance_past == nullptr)) return ODI_ERR_ARGUMENT;
-  sample_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, out, V, ld, temperature, seed, streams, steps,
-                                                  advance_pos, advance_past, active);
+  odi_rc = launch_pdl((sample_kernel), dim3(n), dim3(SAMPLE_THREADS), 0, stream, logits, out, V, ld, temperature, seed,
+                      streams, steps, advance_pos, advance_past, active);
   return launch_status();
 }
