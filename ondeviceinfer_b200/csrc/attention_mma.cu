@@ -461,3 +461,78 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream, a.partial, a.out, a.splits);
   return launch_status();
 }
+
+// ------------------------------------------------------------------------------ allocation-free entry point
+//
+// See attention_noalloc.h for who this is for and the rules of use.  The decode and combine
+// kernels above are used unchanged; only the scratch for the split partials differs: it is
+// the fixed array below instead of a caller-provided buffer.
+#include <stdio.h>
+
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float odi_noalloc_scratch[ODI_NOALLOC_SCRATCH_FLOATS];
+
+#define ODI_NOALLOC_MAX_DEVICES 64
+static float* noalloc_scratch_address[ODI_NOALLOC_MAX_DEVICES];   // device addresses, looked up once per device
+static bool noalloc_configured[ODI_NOALLOC_MAX_DEVICES];
+static thread_local char noalloc_error_text[256] = "";
+
+extern "C" long odi_attention_decode_noalloc_need(int n_tokens, int nq, int splits) {
+  return (long)n_tokens * nq * splits * (D + 2);
+}
+
+extern "C" long odi_attention_decode_noalloc_capacity() { return ODI_NOALLOC_SCRATCH_FLOATS; }
+
+extern "C" const char* odi_attention_decode_noalloc_error() { return noalloc_error_text; }
+
+extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_tokens, cudaStream_t stream) {
+  noalloc_error_text[0] = 0;
+  MmaAttnArgs a = *args;
+  if (a.n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.splits < 1 || n_tokens != a.n_seqs) {
+    snprintf(noalloc_error_text, sizeof(noalloc_error_text),
+             "decode attention needs one token per sequence (n_tokens=%d, n_seqs=%d), nq a multiple of nkv, splits >= 1",
+             n_tokens, a.n_seqs);
+    return ODI_ERR_ARGUMENT;
+  }
+  const long need = odi_attention_decode_noalloc_need(n_tokens, a.nq, a.splits);
+  if (need > ODI_NOALLOC_SCRATCH_FLOATS) {
+    snprintf(noalloc_error_text, sizeof(noalloc_error_text),
+             "the built-in scratch holds %d floats, this call needs %ld (n_tokens=%d * nq=%d * splits=%d * (head_dim=%d + 2)): "
+             "use fewer splits or the entry point that takes a buffer",
+             ODI_NOALLOC_SCRATCH_FLOATS, need, n_tokens, a.nq, a.splits, D);
+    return ODI_ERR_SCRATCH_LIMIT;
+  }
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= ODI_NOALLOC_MAX_DEVICES) return ODI_ERR_UNSUPPORTED;
+  const int dc_merge = DC_WARPS * 16 * (D + 2) * 4;
+  const int dc_smem = DC_STAGES * 2 * TILE_BYTES > dc_merge ? DC_STAGES * 2 * TILE_BYTES : dc_merge;
+  if (!noalloc_configured[device]) {
+    // Set-up, once per device with that device current: the array's name is a host-side
+    // handle; the address a kernel can use comes from cudaGetSymbolAddress.
+    float* address = nullptr;
+    e = cudaGetSymbolAddress((void**)&address, odi_noalloc_scratch);
+    if (e != cudaSuccess || address == nullptr) {
+      snprintf(noalloc_error_text, sizeof(noalloc_error_text), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : ODI_ERR_ARGUMENT;
+    }
+    e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dc_smem);
+    if (e != cudaSuccess) return (int)e;
+    noalloc_scratch_address[device] = address;
+    noalloc_configured[device] = true;
+  }
+  a.partial = noalloc_scratch_address[device];
+  a.head_chunks = (a.nq / a.nkv + 15) / 16;
+  dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
+  if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+  odi_rc = launch_pdl((attention_decode_kernel), dim3(grid), dim3(DC_WARPS * 32), dc_smem, stream, a);
+  int rc = launch_status();
+  if (rc != 0 || a.splits == 1) return rc;
+  const int combine_threads = D >= 128 ? 128 : 64;
+  odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream,
+                      (const float*)a.partial, a.out, a.splits);
+  return launch_status();
+}
