@@ -441,8 +441,13 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 template <int BN, bool DUAL, int EPI, bool SWAP>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   constexpr int STAGE_BYTES = BM * BK * 2 * ((DUAL && !SWAP) ? 2 : 1) + BN * BK * 2 * ((DUAL && SWAP) ? 2 : 1);
-  // The decode form keeps two CTAs per SM resident (about 100 KB each); the prefill form takes the SM alone.
-  constexpr int BUDGET = SWAP ? 200 * 1024 : 100 * 1024;
+  // The decode form takes about 72 KB, so that three CTAs fit on an SM: a launch fills two of the
+  // places and the CTAs of the next kernel of the stream move into the third while this one drains,
+  // where they already request their first weight tiles.  The prefill form takes the SM alone.
+#ifndef ODI_GEMM_DECODE_SMEM_KB
+#define ODI_GEMM_DECODE_SMEM_KB 72
+#endif
+  constexpr int BUDGET = SWAP ? 200 * 1024 : ODI_GEMM_DECODE_SMEM_KB * 1024;
   constexpr int STAGES = BUDGET / STAGE_BYTES < 2 ? 2 : (BUDGET / STAGE_BYTES > 12 ? 12 : BUDGET / STAGE_BYTES);
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
   auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, SWAP>;

@@ -1,0 +1,173 @@
+"""Timing single kernels at given sizes: ``python -m ondeviceinfer_b200.kernels.microbench <case> ...``
+
+Each case runs one kernel of the library on synthetic data with CUDA-event timing after
+warm-up.  Operands that a decode step reads once (weights, cached keys and values) are
+rotated over several copies larger than the 126 MB L2 together, so that the figures are
+HBM figures.  The same command line is what the ``ncu`` summaries under ``profiles/`` were
+captured with (on small cases).
+
+Cases: ``gemm`` (tcgen05 GEMM, or the library's with ``--library``), ``attention-decode``,
+``attention-prefill``, ``rmsnorm``, ``sample``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from . import ops
+
+L2_BYTES = 126e6
+
+
+def time_kernel(run, variants: int, reps: int, warmup: int = 3) -> float:
+    """Mean microseconds of ``run(i)`` cycling i over ``variants`` operand sets.
+
+    The launches are captured into one CUDA graph and the graph is replayed, so the figure
+    is device time per kernel as in a captured decode step (consecutive kernels overlap their
+    launch and set-up through programmatic dependent launch), not host launch throughput."""
+    for i in range(max(warmup, 1)):
+        run(i % variants)
+    torch.cuda.synchronize()
+    per_graph = max(variants, 8)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run(0)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(per_graph):
+            run(i % variants)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1000.0 / (reps * per_graph)
+
+
+def gemm_case(args) -> dict:
+    epi = {"store_bf16": ops.EPI_STORE_BF16, "store_f32": ops.EPI_STORE_F32, "residual": ops.EPI_RESIDUAL,
+           "swiglu": ops.EPI_SWIGLU}[args.epi]
+    rows = 2 * args.n if epi == ops.EPI_SWIGLU else args.n
+    copies = max(1, int(math.ceil(3 * L2_BYTES / (rows * args.k * 2)))) if args.rotate else 1
+    ws = [(torch.randn(rows, args.k, device="cuda") / math.sqrt(args.k)).bfloat16() for _ in range(copies)]
+    x = torch.randn(args.tokens, args.k, device="cuda").bfloat16()
+    wide = epi in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL)
+    out = torch.zeros(args.tokens, args.n, dtype=torch.float32 if wide else torch.bfloat16, device="cuda")
+    if args.library:
+        run = lambda i: torch.matmul(x, ws[i].t())
+    else:
+        run = lambda i: ops.gemm_bf16(x, ws[i], out, epi, swap=args.swap, bn=args.bn, splits=args.splits)
+    us = time_kernel(run, copies, args.reps)
+    ops.raise_on_kernel_fault()
+    weight_bytes, flops = rows * args.k * 2, 2.0 * args.tokens * rows * args.k
+    return {"case": "gemm", "tokens": args.tokens, "n": args.n, "k": args.k, "epi": args.epi,
+            "plan": None if args.library else list(ops.gemm_bf16_plan(args.tokens, args.n, args.k, epi)),
+            "us": us, "weight_GBps": weight_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
+
+
+def _cache_setup(batch: int, ctx: int, nkv: int, d: int, copies: int):
+    pages_per_seq = (ctx + 64) // 64 + 1
+    n_pages = batch * pages_per_seq
+    pools = [torch.randn(2, n_pages, nkv, 64, d, device="cuda").bfloat16() for _ in range(copies)]
+    order = torch.randperm(n_pages).to(torch.int32)
+    page_ids = order.cuda()
+    page_start = (torch.arange(batch + 1, dtype=torch.int32) * pages_per_seq).cuda()
+    return pools, page_start, page_ids
+
+
+def attention_decode_case(args) -> dict:
+    nq, nkv, d = args.heads, args.kv_heads, args.head_dim
+    kv_bytes = 2 * args.batch * args.ctx * nkv * d * 2
+    copies = max(1, int(math.ceil(3 * L2_BYTES / kv_bytes))) if args.rotate else 1
+    pools, page_start, page_ids = _cache_setup(args.batch, args.ctx, nkv, d, copies)
+    q = torch.randn(args.batch, nq, d, device="cuda").bfloat16()
+    out = torch.empty(args.batch, nq * d, dtype=torch.bfloat16, device="cuda")
+    cu_q = torch.arange(args.batch + 1, dtype=torch.int32, device="cuda")
+    past = torch.full((args.batch,), args.ctx - 1, dtype=torch.int32, device="cuda")
+    splits = args.splits
+    partial = torch.empty(args.batch * nq * splits * (d + 2), dtype=torch.float32, device="cuda") if splits > 1 else None
+    run = lambda i: ops.attention_mma(q, pools[i][0], pools[i][1], out, cu_q, past, page_start, page_ids,
+                                      n_seqs=args.batch, max_q_len=1, nq=nq, nkv=nkv, d=d, page_size=64,
+                                      scale=1 / math.sqrt(d), splits=splits, partial=partial)
+    us = time_kernel(run, copies, args.reps)
+    return {"case": "attention-decode", "batch": args.batch, "ctx": args.ctx, "splits": splits, "us": us,
+            "kv_GBps": kv_bytes / us / 1e3}
+
+
+def attention_prefill_case(args) -> dict:
+    nq, nkv, d, T = args.heads, args.kv_heads, args.head_dim, args.tokens
+    pools, page_start, page_ids = _cache_setup(args.batch, T, nkv, d, 1)
+    q = torch.randn(args.batch * T, nq, d, device="cuda").bfloat16()
+    out = torch.empty(args.batch * T, nq * d, dtype=torch.bfloat16, device="cuda")
+    cu_q = (torch.arange(args.batch + 1, dtype=torch.int32) * T).cuda()
+    past = torch.zeros(args.batch, dtype=torch.int32, device="cuda")
+    run = lambda i: ops.attention_mma(q, pools[0][0], pools[0][1], out, cu_q, past, page_start, page_ids,
+                                      n_seqs=args.batch, max_q_len=T, nq=nq, nkv=nkv, d=d, page_size=64,
+                                      scale=1 / math.sqrt(d))
+    us = time_kernel(run, 1, args.reps)
+    flops = 2.0 * args.batch * nq * d * T * T          # causal half of 4 * T^2 * d per head
+    return {"case": "attention-prefill", "batch": args.batch, "tokens": T, "us": us, "TFLOPs": flops / us / 1e6}
+
+
+def rmsnorm_case(args) -> dict:
+    x = torch.randn(args.tokens, args.n, device="cuda")
+    w = torch.ones(args.n, device="cuda")
+    out = torch.empty(args.tokens, args.n, dtype=torch.bfloat16, device="cuda")
+    us = time_kernel(lambda i: ops.rmsnorm(x, w, 1e-6, out), 1, args.reps)
+    return {"case": "rmsnorm", "tokens": args.tokens, "n": args.n, "us": us,
+            "GBps": args.tokens * args.n * 6 / us / 1e3}
+
+
+def sample_case(args) -> dict:
+    logits = torch.randn(args.tokens, args.n, device="cuda")
+    out = torch.empty(args.tokens, dtype=torch.int32, device="cuda")
+    streams = torch.arange(args.tokens, dtype=torch.int32, device="cuda")
+    steps = torch.zeros(args.tokens, dtype=torch.int32, device="cuda")
+    us = time_kernel(lambda i: ops.sample(logits, out, args.temperature, 1, streams, steps), 1, args.reps)
+    return {"case": "sample", "rows": args.tokens, "vocab": args.n, "temperature": args.temperature, "us": us}
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(prog="python -m ondeviceinfer_b200.kernels.microbench", description=__doc__,
+                                     formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("case", choices=("gemm", "attention-decode", "attention-prefill", "rmsnorm", "sample"))
+    parser.add_argument("--tokens", type=int, default=8)
+    parser.add_argument("--n", type=int, default=4096)
+    parser.add_argument("--k", type=int, default=4096)
+    parser.add_argument("--epi", default="store_bf16", choices=("store_bf16", "store_f32", "residual", "swiglu"))
+    parser.add_argument("--bn", type=int, default=None)
+    parser.add_argument("--splits", type=int, default=None)
+    parser.add_argument("--swap", type=int, default=None)
+    parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--ctx", type=int, default=2048)
+    parser.add_argument("--heads", type=int, default=32)
+    parser.add_argument("--kv-heads", type=int, default=8)
+    parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--temperature", type=float, default=0.0)
+    parser.add_argument("--reps", type=int, default=5)
+    parser.add_argument("--no-rotate", dest="rotate", action="store_false",
+                        help="one operand set only (small captures under a profiler)")
+    args = parser.parse_args(argv)
+    if args.swap is not None:
+        args.swap = bool(args.swap)
+    if args.case == "attention-decode" and args.splits is None:
+        args.splits = 1
+    torch.manual_seed(0)
+    result = {"gemm": gemm_case, "attention-decode": attention_decode_case,
+              "attention-prefill": attention_prefill_case, "rmsnorm": rmsnorm_case, "sample": sample_case}[args.case](args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

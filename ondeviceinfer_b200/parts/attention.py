@@ -92,7 +92,7 @@ class Attention(Part):
             # decode: cut long key ranges so that enough blocks run side by side
             work = ctx.n_seqs * s.num_kv_heads * ((s.num_heads // s.num_kv_heads + 15) // 16)
             tiles = (ctx.max_kv_len + PAGE_SIZE - 1) // PAGE_SIZE
-            splits = max(1, min(32, 592 // max(work, 1), tiles // 2 if tensor_cores else (ctx.max_kv_len + 255) // 256))
+            splits = max(1, min(32, 296 // max(work, 1), tiles // 2 if tensor_cores else (ctx.max_kv_len + 255) // 256))
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.head_dim + 2),),
                                       dtype=torch.float32, device=q.device)
