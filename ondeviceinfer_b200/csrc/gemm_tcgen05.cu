@@ -19,10 +19,13 @@
 // DUAL mode runs two weight tiles (rows n and n + dual_offset: gate and up) against the
 // same X tile into two accumulators and writes silu(gate) * up.
 //
-// K splits: when there are too few tiles to fill the GPU, grid.z CTAs share a tile.  Each
-// writes its fp32 partial to scratch; the CTA that arrives last (an atomic ticket, nobody
-// waits) adds the partials in split order and runs the epilogue, so the result does not
-// depend on timing.
+// K splits: when there are too few tiles to fill the GPU, grid.z CTAs share a tile.
+//  * Up to 8 splits form a thread-block cluster: every CTA leaves its fp32 partial in its own
+//    shared memory, the cluster synchronises, and CTA r adds, for the token columns it owns, the
+//    partials of all CTAs in rank order through distributed shared memory and runs the epilogue.
+//  * More splits: each CTA writes its partial to global scratch; the CTA that arrives last (an
+//    atomic ticket, nobody waits) adds the partials in split order and runs the epilogue.
+// Either way the sum is taken in a fixed order and does not depend on timing.
 //
 // Every wait on an mbarrier is bounded: after about two seconds the kernel records an
 // error code in `status`, skips its work, still frees its tensor memory and returns.
@@ -125,6 +128,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Read a float from the same shared-memory offset in the CTA of the given cluster rank.
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, written by TMA
 // with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the
 // leading byte offset is not used by swizzled K-major layouts, version 1, layout type 2.
@@ -201,7 +222,7 @@ __device__ __forceinline__ void emit_row16(const GemmArgs& a, int token, int n, 
 
 // SWAP = false: the 128 lanes are features (weight rows), the BN columns are tokens.
 // SWAP = true : the 128 lanes are tokens, the BN columns are features.
-template <int BN, bool DUAL, int EPI, int STAGES, bool SWAP>
+template <int BN, bool DUAL, int EPI, int STAGES, bool SWAP, bool CLUSTER>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs a) {
@@ -345,6 +366,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           for (int i = 0; i < 16; ++i) emit<EPI>(a, tok0 + c + i, n, v[i], DUAL ? u[i] : 0.f);
         }
       }
+    } else if (ok && CLUSTER) {
+      // leave the partial in this CTA's shared memory (the stages are free: every MMA has completed)
+      float* red = (float*)smem;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (tok0 + c >= a.tokens) break;
+        float v[16], u[16];
+        tmem_ld16(taddr + c, v);
+        if (DUAL) tmem_ld16(taddr + BN + c, u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          red[(c + i) * BM + row] = v[i];
+          if (DUAL) red[(BN + c + i) * BM + row] = u[i];
+        }
+      }
     } else if (ok) {
       const int n = n0 + row;
       constexpr int PER = (DUAL ? 2 : 1) * BN * BM;       // floats per partial
@@ -402,6 +438,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     tc_fence_before();
   }
+  if (CLUSTER && !SWAP && a.splits > 1) {
+    // Every thread of every CTA of the cluster takes part in both barriers, whatever happened before.
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2 && !abort_flag) {
+      const int row = (warp & 3) * 32 + lane, n = n0 + row;
+      const float* red = (const float*)smem;
+      const uint32_t rank = cluster_rank();
+      for (int c = (int)rank; c < BN && tok0 + c < a.tokens; c += a.splits) {   // the token columns this CTA owns
+        float v = 0.f, u = 0.f;
+        for (int p = 0; p < a.splits; ++p) {                                     // rank order: a fixed sum
+          v += ld_peer_f32(red + c * BM + row, (uint32_t)p);
+          if (DUAL) u += ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p);
+        }
+        emit<EPI>(a, tok0 + c, n, v, u);
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();     // nobody leaves while its shared memory may still be read
+  }
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
@@ -438,7 +494,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
 }
 
-template <int BN, bool DUAL, int EPI, bool SWAP>
+template <int BN, bool DUAL, int EPI, bool SWAP, bool CLUSTER>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   constexpr int STAGE_BYTES = BM * BK * 2 * ((DUAL && !SWAP) ? 2 : 1) + BN * BK * 2 * ((DUAL && SWAP) ? 2 : 1);
   // The decode form takes about 72 KB, so that three CTAs fit on an SM: a launch fills two of the
@@ -450,26 +506,45 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
   constexpr int BUDGET = SWAP ? 200 * 1024 : ODI_GEMM_DECODE_SMEM_KB * 1024;
   constexpr int STAGES = BUDGET / STAGE_BYTES < 2 ? 2 : (BUDGET / STAGE_BYTES > 12 ? 12 : BUDGET / STAGE_BYTES);
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
-  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, SWAP>;
+  static_assert(!CLUSTER || (DUAL ? 2 : 1) * BN * BM * 4 <= STAGES * STAGE_BYTES, "the split partial must fit the stage memory");
+  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, SWAP, CLUSTER>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  if (CLUSTER) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = grid.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    odi_rc = (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, a);
+    return launch_status();
+  }
   odi_rc = launch_pdl((kernel), dim3(grid), dim3(GEMM_THREADS), SMEM, stream, mw, mx, a);
   return launch_status();
 }
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, bool CLUSTER>
 static int dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid,
                         cudaStream_t stream) {
   switch (epi) {
-    case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, SWAP>(mw, mx, a, grid, stream);
-    case EPI_STORE_F32: return launch<BN, false, EPI_STORE_F32, SWAP>(mw, mx, a, grid, stream);
-    case EPI_RESIDUAL: return launch<BN, false, EPI_RESIDUAL, SWAP>(mw, mx, a, grid, stream);
+    case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, SWAP, CLUSTER>(mw, mx, a, grid, stream);
+    case EPI_STORE_F32: return launch<BN, false, EPI_STORE_F32, SWAP, CLUSTER>(mw, mx, a, grid, stream);
+    case EPI_RESIDUAL: return launch<BN, false, EPI_RESIDUAL, SWAP, CLUSTER>(mw, mx, a, grid, stream);
     case EPI_SWIGLU:
-      if constexpr (BN <= 128) return launch<BN, true, EPI_SWIGLU, SWAP>(mw, mx, a, grid, stream);
+      if constexpr (BN <= 128 && !(CLUSTER && BN > 64)) return launch<BN, true, EPI_SWIGLU, SWAP, CLUSTER>(mw, mx, a, grid, stream);
       else return ODI_ERR_UNSUPPORTED;
   }
   return ODI_ERR_ARGUMENT;
@@ -484,16 +559,18 @@ extern "C" long odi_gemm_bf16_scratch_floats(int tokens, int n_out, int bn, int 
 
 // x [tokens, K] bf16, w [w_rows, K] bf16 (for EPI_SWIGLU w holds the gate rows followed by
 // the up rows and n_out = w_rows / 2), out [tokens, ldo].
-// swap == 0 (decode form): tiles of 128 features x bn tokens, bn in {16, 32, 64, 128, 256}, K splits allowed.
+// swap == 0 (decode form): tiles of 128 features x bn tokens, bn in {16, 32, 64, 128, 256}, K splits allowed;
+//            cluster != 0 lets 2..8 splits (bn <= 64) exchange partials through distributed shared memory.
 // swap == 1 (prefill form): tiles of 128 tokens x bn features, bn in {64, 128, 256}, no splits.
 extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
-                             int ldo, int epi, int bn, int splits, int swap, float* scratch, int* tickets,
-                             int* status, cudaStream_t stream) {
+                             int ldo, int epi, int bn, int splits, int swap, int cluster, float* scratch,
+                             int* tickets, int* status, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
   const int total_kb = (K + BK - 1) / BK;
   if (splits < 1 || splits > total_kb || (swap && splits != 1)) return ODI_ERR_ARGUMENT;
-  if (splits > 1 && (scratch == nullptr || tickets == nullptr)) return ODI_ERR_ARGUMENT;
+  const bool clustered = cluster && splits > 1 && splits <= 8 && bn <= 64 && !swap;
+  if (splits > 1 && !clustered && (scratch == nullptr || tickets == nullptr)) return ODI_ERR_ARGUMENT;
   if (status == nullptr) return ODI_ERR_ARGUMENT;
   const bool dual = epi == EPI_SWIGLU;
   if (dual && w_rows != 2 * n_out) return ODI_ERR_ARGUMENT;
@@ -510,18 +587,26 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;
   if (swap) {
     switch (bn) {
-      case 64: return dispatch_epi<64, true>(epi, mw, mx, a, grid, stream);
-      case 128: return dispatch_epi<128, true>(epi, mw, mx, a, grid, stream);
-      case 256: return dispatch_epi<256, true>(epi, mw, mx, a, grid, stream);
+      case 64: return dispatch_epi<64, true, false>(epi, mw, mx, a, grid, stream);
+      case 128: return dispatch_epi<128, true, false>(epi, mw, mx, a, grid, stream);
+      case 256: return dispatch_epi<256, true, false>(epi, mw, mx, a, grid, stream);
     }
     return ODI_ERR_UNSUPPORTED;
   }
+  // 2..8 splits of a token tile of up to 64 exchange their partials inside a cluster
+  if (cluster && splits > 1 && splits <= 8 && bn <= 64) {
+    switch (bn) {
+      case 16: return dispatch_epi<16, false, true>(epi, mw, mx, a, grid, stream);
+      case 32: return dispatch_epi<32, false, true>(epi, mw, mx, a, grid, stream);
+      case 64: return dispatch_epi<64, false, true>(epi, mw, mx, a, grid, stream);
+    }
+  }
   switch (bn) {
-    case 16: return dispatch_epi<16, false>(epi, mw, mx, a, grid, stream);
-    case 32: return dispatch_epi<32, false>(epi, mw, mx, a, grid, stream);
-    case 64: return dispatch_epi<64, false>(epi, mw, mx, a, grid, stream);
-    case 128: return dispatch_epi<128, false>(epi, mw, mx, a, grid, stream);
-    case 256: return dispatch_epi<256, false>(epi, mw, mx, a, grid, stream);
+    case 16: return dispatch_epi<16, false, false>(epi, mw, mx, a, grid, stream);
+    case 32: return dispatch_epi<32, false, false>(epi, mw, mx, a, grid, stream);
+    case 64: return dispatch_epi<64, false, false>(epi, mw, mx, a, grid, stream);
+    case 128: return dispatch_epi<128, false, false>(epi, mw, mx, a, grid, stream);
+    case 256: return dispatch_epi<256, false, false>(epi, mw, mx, a, grid, stream);
   }
   return ODI_ERR_UNSUPPORTED;
 }

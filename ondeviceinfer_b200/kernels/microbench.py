@@ -65,7 +65,8 @@ def gemm_case(args) -> dict:
     if args.library:
         run = lambda i: torch.matmul(x, ws[i].t())
     else:
-        run = lambda i: ops.gemm_bf16(x, ws[i], out, epi, swap=args.swap, bn=args.bn, splits=args.splits)
+        run = lambda i: ops.gemm_bf16(x, ws[i], out, epi, swap=args.swap, bn=args.bn, splits=args.splits,
+                                      cluster=not args.no_cluster)
     us = time_kernel(run, copies, args.reps)
     ops.raise_on_kernel_fault()
     weight_bytes, flops = rows * args.k * 2, 2.0 * args.tokens * rows * args.k
@@ -148,6 +149,7 @@ def main(argv=None) -> int:
     parser.add_argument("--splits", type=int, default=None)
     parser.add_argument("--swap", type=int, default=None)
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
+    parser.add_argument("--no-cluster", action="store_true", help="K splits through global scratch, not a cluster")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--ctx", type=int, default=2048)
     parser.add_argument("--heads", type=int, default=32)

@@ -257,7 +257,9 @@ def gemm_bf16_plan(tokens: int, n_out: int, K: int, epi: int):
     if tokens <= 64:
         bn = next(b for b in (16, 32, 64) if tokens <= b)
         tiles = -(-n_out // 128)
-        splits = max(1, min(total_kb // 4, 296 // tiles)) if tiles < 296 else 1
+        # measured on B200: about 192 CTAs stream best (288 for the two-accumulator form with small token tiles)
+        target = 288 if (epi == EPI_SWIGLU and bn <= 32) else 192
+        splits = max(1, min(total_kb // 4, int(target / tiles + 0.5), 8)) if tiles < target else 1
         return False, bn, splits
     choices = (128, 64) if epi == EPI_SWIGLU else (256, 128, 64)
     token_tiles = -(-tokens // 128)
@@ -273,11 +275,13 @@ def gemm_bf16_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, swap: Optional[bool] = None,
-              bn: Optional[int] = None, splits: Optional[int] = None) -> None:
+              bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True) -> None:
     """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
 
     ``EPI_STORE_BF16`` / ``EPI_STORE_F32``: out [tokens, rows]; ``EPI_RESIDUAL``: out (fp32) += product;
     ``EPI_SWIGLU``: w holds the gate rows then the up rows, out [tokens, rows / 2] = silu(gate) * up.
+    ``cluster``: let 2..8 K splits exchange their partials inside a thread-block cluster (else, and for
+    more splits, through global scratch and a ticket).
     """
     _require(x, "x", torch.bfloat16, 2)
     _require(w, "w", torch.bfloat16, 2)
@@ -303,7 +307,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, 
         raise KernelError("too many tiles for a split product")
     _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(rows),
                              c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if swap else 0),
-                             _ptr(scratch), _ptr(tickets), _ptr(status), _stream()), "gemm_tcgen05")
+                             c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), _stream()),
+           "gemm_tcgen05")
 
 
 # ------------------------------------------------------------------------------ attention

@@ -15,15 +15,22 @@ import plain_qwen3 as plain
 # (observed ~5e-3 at |logit| ~ 1).
 F32_ATOL, F32_RTOL = 2e-5, 2e-5
 BF16_REL = 3e-2  # |d| <= BF16_REL * max(1, max |reference logit|)
+# The fp32 figure holds for sums of up to 256 terms (the tiny models).  The rounding error of an
+# fp32 sum taken in another order grows like the square root of its length, so a model whose
+# longest sum has K terms is compared with F32_ATOL * sqrt(K / 256): 1.4e-4 at the 12288-wide
+# feed-forward of Qwen3-8B (observed there: 3.2e-5).
+F32_SUM_LENGTH = 256
 
 
-def assert_logits_close(actual: torch.Tensor, expected: torch.Tensor, dtype: str, what: str = "") -> None:
+def assert_logits_close(actual: torch.Tensor, expected: torch.Tensor, dtype: str, what: str = "",
+                        longest_sum: int = F32_SUM_LENGTH) -> None:
     actual, expected = actual.float().cpu(), expected.float().cpu()
     assert actual.shape == expected.shape, (what, actual.shape, expected.shape)
     assert torch.isfinite(actual).all(), f"{what}: non-finite logits"
     gap = (actual - expected).abs()
     if dtype == "float32":
-        bad = gap > F32_ATOL + F32_RTOL * expected.abs()
+        atol = F32_ATOL * max(1.0, (longest_sum / F32_SUM_LENGTH) ** 0.5)
+        bad = gap > atol + F32_RTOL * expected.abs()
         assert not bad.any(), f"{what}: fp32 max |d| = {float(gap.max()):.3e} at {int(gap.argmax())}"
     else:
         limit = BF16_REL * max(1.0, float(expected.abs().max()))

@@ -194,3 +194,41 @@ def test_capacity_and_misuse_are_host_errors(tmp_root):
         model.step(cache, [slot], [[1]], "last")
     cache.free(slot)
     cache.check()
+
+
+LARGE = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 1, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+    "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 40960, "hidden_act": "silu",
+}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qwen3_8b_layer_sizes(dtype, tmp_path):
+    """One layer with the sizes of Qwen3-8B (width 4096, 32 query and 8 key/value heads of 128,
+    feed-forward 12288, vocabulary 151936): whole, the last tokens one by one, and an unequal batch,
+    against the plain implementation.  Logits of 4096-wide sums are compared at the wanted places."""
+    import ondeviceinfer_b200 as odi
+    from helpers import write_model_folder
+
+    weights = plain.random_weights(LARGE, 3)
+    model = odi.load_resident_model(write_model_folder(tmp_path / "large", LARGE, weights), dtype=dtype)
+    requests = plain.random_prompts(LARGE, [70, 9, 33], 3)
+    expected = [plain.forward_logits(weights, LARGE, r) for r in requests]
+    cache = model.make_cache(max_tokens=3 * 128, max_seqs=3)
+    # whole, alone
+    slot = cache.alloc()
+    assert_logits_close(model.step(cache, [slot], [requests[0]], "all"), expected[0], dtype, "8B sizes whole", longest_sum=12288)
+    cache.free(slot)
+    # unequal batch: prompts without their last 4 tokens, then one token each
+    slots = [cache.alloc() for _ in requests]
+    cut = [len(r) - 4 for r in requests]
+    logits = model.step(cache, slots, [r[:c] for r, c in zip(requests, cut)], "last")
+    assert_logits_close(logits, torch.stack([e[c - 1] for e, c in zip(expected, cut)]), dtype, "8B sizes batch prompt", longest_sum=12288)
+    for t in range(4):
+        logits = model.step(cache, slots, [[r[c + t]] for r, c in zip(requests, cut)], "last")
+        assert_logits_close(logits, torch.stack([e[c + t] for e, c in zip(expected, cut)]), dtype, f"8B sizes decode {t}", longest_sum=12288)
+    for slot in slots:
+        cache.free(slot)
+    cache.check()

@@ -347,6 +347,7 @@ GEMM_SHAPES = [
     (1, 389, 96, None, None, None), (8, 4096, 4096, None, None, None), (16, 128, 64, False, 16, 1),
     (33, 1000, 1000, None, None, None), (64, 1536, 2048, None, None, None), (40, 512, 4096, False, 64, 4),
     (130, 4096, 1024, False, 128, 2), (100, 389, 96, True, 64, 1), (300, 520, 200, True, 128, 1),
+    (8, 520, 2048, False, 16, 8), (50, 389, 1024, False, 64, 3), (20, 256, 4096, False, 32, 12),
     (333, 208, 80, True, 64, 1), (1030, 1024, 512, None, None, None),
 ]
 
@@ -378,6 +379,11 @@ def test_gemm_tcgen05(tokens, N, K, swap, tile, splits, epi):
     ops.gemm_bf16(x, w, out, code, swap=swap, bn=tile, splits=splits)
     torch.cuda.synchronize()
     ops.raise_on_kernel_fault()
+    if epi == "store_f32" and not swap:
+        # K splits through a cluster and through global scratch add in the same order: same bits
+        other = torch.empty_like(out)
+        ops.gemm_bf16(x, w, other, code, swap=swap, bn=tile, splits=splits, cluster=False)
+        assert torch.equal(other, out)
     if out.dtype == torch.bfloat16:
         close(out, expected, "bfloat16")
     else:
