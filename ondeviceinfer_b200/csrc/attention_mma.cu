@@ -7,9 +7,12 @@
 //  * attention_decode: one query token per sequence.  A block owns one (sequence, kv head,
 //    key split); the rows of its MMA are the query heads that share the kv head (up to 16
 //    per block), its 4 warps take 16 keys each of every 64-key page and their partial
-//    results are merged in shared memory.  With splits > 1 the block writes an
-//    un-normalised partial (acc[d], max, sum) per (token, head, split) for the combine
-//    kernel of attention_simt.cu.
+//    results are merged in shared memory.  With 2..8 splits the blocks of a (sequence, kv
+//    head) form a thread-block cluster: each leaves its merged (acc[d], max, sum) in its own
+//    shared memory and, after a cluster barrier, block r finishes the heads r, r + splits, ...
+//    by adding all blocks' partials in rank order through distributed shared memory.  With
+//    more splits (or when asked to) the block writes the partial to global memory for the
+//    combine kernel below.
 //
 // Key/value pages (64 positions x head_dim, contiguous) are copied to shared memory with
 // cp.async, double or triple buffered; rows are padded by 16 bytes so that ldmatrix reads
@@ -46,6 +49,7 @@ struct MmaAttnArgs {
   const int* page_ids;
   int n_seqs, nq, nkv, splits, head_chunks;
   float scale;
+  int clustered;          // decode: the splits of a (sequence, kv head) form a cluster and merge in shared memory
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -70,6 +74,22 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -376,7 +396,17 @@ attention_decode_kernel(MmaAttnArgs a) {
       L += wgt[w] * mg[((size_t)w * 16 + row) * RS + D + 1];
     }
     const int head = head0 + row;
-    if (a.splits == 1) {
+    if (a.clustered) {
+      // this split's merged partial stays in shared memory, behind the four warps' area
+      float* fin = mg + (size_t)DC_WARPS * 16 * RS + (size_t)row * RS;
+      for (int dd = lane; dd < D; dd += 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
+        fin[dd] = v;
+      }
+      if (lane == 0) { fin[D] = M; fin[D + 1] = L; }
+    } else if (a.splits == 1) {
       const float inv = L > 0.f ? 1.f / L : 0.f;
       bf16* dst = a.out + ((size_t)tok * a.nq + head) * D;
       for (int dd = lane; dd < D; dd += 32) {
@@ -396,6 +426,35 @@ attention_decode_kernel(MmaAttnArgs a) {
       }
       if (lane == 0) { dst[D] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f; dst[D + 1] = L; }
     }
+  }
+  if (a.clustered) {
+    // every thread of every block of the cluster takes part in both barriers
+    __syncwarp();
+    cluster_sync_all();
+    const float* fin = mg + (size_t)DC_WARPS * 16 * RS;
+    const uint32_t rank = cluster_rank();
+    for (int row = (int)rank + a.splits * warp; row < heads_here; row += a.splits * DC_WARPS) {
+      const float* mine = fin + (size_t)row * RS;
+      float M = -INFINITY;
+      for (int p = 0; p < a.splits; ++p) M = fmaxf(M, ld_peer_f32(mine + D, (uint32_t)p));
+      float L = 0.f;
+      for (int p = 0; p < a.splits; ++p) {            // rank order: a fixed sum
+        const float mp = ld_peer_f32(mine + D, (uint32_t)p);
+        if (mp != -INFINITY) L += exp2f(mp - M) * ld_peer_f32(mine + D + 1, (uint32_t)p);
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* dst = a.out + ((size_t)tok * a.nq + head0 + row) * D;
+      for (int dd = lane; dd < D; dd += 32) {
+        float v = 0.f;
+        for (int p = 0; p < a.splits; ++p) {
+          const float mp = ld_peer_f32(mine + D, (uint32_t)p);
+          if (mp != -INFINITY) v += exp2f(mp - M) * ld_peer_f32(mine + dd, (uint32_t)p);
+        }
+        dst[dd] = __float2bfloat16_rn(v * inv);
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();     // nobody leaves while its shared memory may still be read
   }
 }
 
@@ -434,7 +493,7 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   const int g = a.nq / a.nkv;
   static bool configured = false;
   const int pf_smem = PF_STAGES * 2 * TILE_BYTES;
-  const int dc_merge = DC_WARPS * 16 * (D + 2) * 4;
+  const int dc_merge = (DC_WARPS + 1) * 16 * (D + 2) * 4;    // the four warps' partials and the block's merged one
   const int dc_smem = DC_STAGES * 2 * TILE_BYTES > dc_merge ? DC_STAGES * 2 * TILE_BYTES : dc_merge;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem);
@@ -450,10 +509,29 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
     return launch_status();
   }
   if (max_q_len != 1) return ODI_ERR_ARGUMENT;
-  if (a.splits > 1 && a.partial == nullptr) return ODI_ERR_ARGUMENT;
+  a.clustered = (a.clustered && a.splits > 1 && a.splits <= 8) ? 1 : 0;
+  if (a.splits > 1 && !a.clustered && a.partial == nullptr) return ODI_ERR_ARGUMENT;
   a.head_chunks = (g + 15) / 16;
   dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+  if (a.clustered) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DC_WARPS * 32);
+    cfg.dynamicSmemBytes = dc_smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = a.splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    odi_rc = (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel, a);
+    return launch_status();
+  }
   odi_rc = launch_pdl((attention_decode_kernel), dim3(grid), dim3(DC_WARPS * 32), dc_smem, stream, a);
   int rc = launch_status();
   if (rc != 0 || a.splits == 1) return rc;
@@ -525,6 +603,7 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
     noalloc_configured[device] = true;
   }
   a.partial = noalloc_scratch_address[device];
+  a.clustered = 0;      // this entry point is the global-partial form
   a.head_chunks = (a.nq / a.nkv + 15) / 16;
   dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;

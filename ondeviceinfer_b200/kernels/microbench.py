@@ -98,7 +98,8 @@ def attention_decode_case(args) -> dict:
     partial = torch.empty(args.batch * nq * splits * (d + 2), dtype=torch.float32, device="cuda") if splits > 1 else None
     run = lambda i: ops.attention_mma(q, pools[i][0], pools[i][1], out, cu_q, past, page_start, page_ids,
                                       n_seqs=args.batch, max_q_len=1, nq=nq, nkv=nkv, d=d, page_size=64,
-                                      scale=1 / math.sqrt(d), splits=splits, partial=partial)
+                                      scale=1 / math.sqrt(d), splits=splits, partial=partial,
+                                      cluster=args.cluster_attention)
     us = time_kernel(run, copies, args.reps)
     return {"case": "attention-decode", "batch": args.batch, "ctx": args.ctx, "splits": splits, "us": us,
             "kv_GBps": kv_bytes / us / 1e3}
@@ -149,7 +150,8 @@ def main(argv=None) -> int:
     parser.add_argument("--splits", type=int, default=None)
     parser.add_argument("--swap", type=int, default=None)
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
-    parser.add_argument("--no-cluster", action="store_true", help="K splits through global scratch, not a cluster")
+    parser.add_argument("--no-cluster", action="store_true", help="GEMM K splits through global scratch, not a cluster")
+    parser.add_argument("--cluster-attention", action="store_true", help="merge decode-attention splits inside a cluster")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--ctx", type=int, default=2048)
     parser.add_argument("--heads", type=int, default=32)

@@ -354,7 +354,7 @@ class _MmaAttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p),
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("splits", c_int),
-                ("head_chunks", c_int), ("scale", c_float)]
+                ("head_chunks", c_int), ("scale", c_float), ("clustered", c_int)]
 
 
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -362,9 +362,14 @@ MMA_HEAD_DIMS = tuple(range(16, 257, 16))
 
 def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                   nq: int, nkv: int, d: int, page_size: int, scale: float, splits: int = 1,
-                  partial: Optional[torch.Tensor] = None) -> None:
+                  partial: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
     """bf16 causal GQA on the tensor cores: the prefill kernel for any q_len, the split-key
-    decode kernel when every sequence brings exactly one token.  No window."""
+    decode kernel when every sequence brings exactly one token.  No window.
+
+    Decode splits go through the fp32 ``partial`` buffer and a combine kernel.  ``cluster=True``
+    merges 2..8 splits inside a thread-block cluster instead (no scratch, no second kernel); on
+    B200 that measured no faster (19.4 against 19.3 us at 8 x 2048, slower at other split counts:
+    the co-scheduling of 104 KB blocks costs what the saved launch gains), so it is not the default."""
     if d not in MMA_HEAD_DIMS:
         raise KernelError(f"the tensor-core attention takes head sizes in steps of 16 up to 256, not {d}")
     if page_size != 64:
@@ -379,15 +384,16 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
     decode = max_q_len == 1
     if not decode:
         splits = 1
-    if splits > 1:
+    clustered = cluster and 1 < splits <= 8
+    if splits > 1 and not clustered:
         need = n_tokens * nq * splits * (d + 2)
         if partial is None or partial.numel() < need or partial.dtype != torch.float32:
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
     args = _MmaAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
-                        _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale)
+                        _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale, 1 if clustered else 0)
     lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(1 if decode else 0),
-                                 _stream()), "attention_mma", 2 if splits > 1 else 1)
+                                 _stream()), "attention_mma", 2 if (splits > 1 and not clustered) else 1)
 
 
 # ------------------------------------------------------------------------------ sampling

@@ -99,7 +99,8 @@ class Attention(Part):
         if tensor_cores:
             ops.attention_mma(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                               n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
-                              d=s.head_dim, page_size=PAGE_SIZE, scale=self.scale, splits=splits, partial=partial)
+                              d=s.head_dim, page_size=PAGE_SIZE, scale=self.scale, splits=splits, partial=partial,
+                              cluster=False)
             return
         ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                            n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,

@@ -415,6 +415,8 @@ MMA_CASES = [
     (128, 40, 2, [1, 1], [500, 2], 3),                          # 20 query heads per kv head: two row chunks
     (256, 2, 1, [20, 1], [0, 77], 1),
     (80, 3, 1, [1], [129], 2),
+    (128, 16, 2, [1, 1, 1], [900, 3, 450], 8),                  # eight splits, some of them empty for short sequences
+    (128, 32, 8, [1, 1], [1500, 64], 12),                       # more than a cluster holds: global partials
 ]
 
 
@@ -434,6 +436,14 @@ def test_attention_mma(d, nq, nkv, lengths, past, splits):
                       nkv=nkv, d=d, page_size=64, scale=scale, splits=splits, partial=partial)
     expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, 0, scale, "bfloat16")
     close(out, expected, "bfloat16")
+    if 1 < splits <= 8:
+        # the same splits merged inside a thread-block cluster instead of through global partials
+        other = torch.empty_like(out)
+        ops.attention_mma(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], other, setup["cu_q"], setup["past"],
+                          setup["page_start"], setup["page_ids"], n_seqs=len(lengths), max_q_len=1, nq=nq, nkv=nkv,
+                          d=d, page_size=64, scale=scale, splits=splits, cluster=True)
+        close(other, expected, "bfloat16")
+        assert float((other.float() - out.float()).abs().max()) <= 2e-2
 
 
 def test_attention_mma_finds_one_far_key():

@@ -68,7 +68,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         ops.attention_mma(q, setup["k_pool"], setup["v_pool"], theirs, setup["cu_q"], setup["past"],
                           setup["page_start"], setup["page_ids"], n_seqs=n, max_q_len=1, nq=call["nq"],
                           nkv=call["nkv"], d=D, page_size=64, scale=scale, splits=call["splits"],
-                          partial=partial if call["splits"] > 1 else None)
+                          partial=partial if call["splits"] > 1 else None, cluster=False)   # the caller-buffer form
         torch.cuda.synchronize()
         expected = plain_attention(q.float().cpu(), setup["dense"], [1] * n, call["past"], call["nq"], call["nkv"], D, 0,
                                    scale, "bfloat16")
