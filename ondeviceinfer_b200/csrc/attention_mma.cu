@@ -262,7 +262,9 @@ attention_prefill_kernel(MmaAttnArgs a) {
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_kernel(MmaAttnArgs a) {
   pdl_launch_dependents();
-  pdl_wait();
+  // What follows up to pdl_wait() reads only what no kernel of this step writes: the step's index
+  // arrays and the cache pages that earlier steps filled.  The page that holds the query's own
+  // position is written by the kernel before this one, so it is never requested ahead of the wait.
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seq = blockIdx.z, split = blockIdx.x;
@@ -277,6 +279,26 @@ attention_decode_kernel(MmaAttnArgs a) {
   const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
   const int* pages = a.page_ids + a.page_start[seq];
 
+  auto issue = [&](int tile) {
+    uint8_t* st = smem + (size_t)((tile - tile_begin) % DC_STAGES) * 2 * TILE_BYTES;
+    const size_t base = ((size_t)pages[tile] * a.nkv + hk) * KT * D;
+    load_tile(st, a.k_pool + base, tid, DC_WARPS * 32);
+    load_tile(st + TILE_BYTES, a.v_pool + base, tid, DC_WARPS * 32);
+  };
+  // prologue: DC_STAGES - 1 tiles in flight (empty groups keep the group count uniform)
+  bool early[DC_STAGES - 1];
+#pragma unroll
+  for (int i = 0; i < DC_STAGES - 1; ++i) {
+    early[i] = tile_begin + i < tile_end && tile_begin + i < n_tiles - 1;   // not the page of the query itself
+    if (early[i]) issue(tile_begin + i);
+  }
+  pdl_wait();
+#pragma unroll
+  for (int i = 0; i < DC_STAGES - 1; ++i) {
+    if (!early[i] && tile_begin + i < tile_end) issue(tile_begin + i);
+    cp_async_commit();
+  }
+
   // rows of the MMA tile are query heads
   const int r_lo = lane >> 2, r_hi = r_lo + 8;
   const bf16* q_lo = r_lo < heads_here ? a.q + ((size_t)tok * a.nq + head0 + r_lo) * D : nullptr;
@@ -290,18 +312,6 @@ attention_decode_kernel(MmaAttnArgs a) {
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   const float sl2 = a.scale * LOG2E;
 
-  auto issue = [&](int tile) {
-    uint8_t* st = smem + (size_t)((tile - tile_begin) % DC_STAGES) * 2 * TILE_BYTES;
-    const size_t base = ((size_t)pages[tile] * a.nkv + hk) * KT * D;
-    load_tile(st, a.k_pool + base, tid, DC_WARPS * 32);
-    load_tile(st + TILE_BYTES, a.v_pool + base, tid, DC_WARPS * 32);
-  };
-  // prologue: DC_STAGES - 1 tiles in flight (empty groups keep the group count uniform)
-#pragma unroll
-  for (int i = 0; i < DC_STAGES - 1; ++i) {
-    if (tile_begin + i < tile_end) issue(tile_begin + i);
-    cp_async_commit();
-  }
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     if (tile + DC_STAGES - 1 < tile_end) issue(tile + DC_STAGES - 1);
     cp_async_commit();
