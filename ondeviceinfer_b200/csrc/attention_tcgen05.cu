@@ -1,0 +1,434 @@
+// bf16 causal grouped-query attention for prefill on the 5th-generation tensor cores.
+//
+// One CTA owns 128 consecutive query tokens of one query head of one sequence and walks that
+// sequence's key/value pages (64 positions each) up to the diagonal:
+//
+//   S_j = Q K_j^T        tcgen05.mma, M = 128 query rows, N = 64 keys, K = head size; Q and K_j
+//                        in shared memory (TMA, 128-byte swizzle), S_j in tensor memory
+//   P_j = softmax part   by 8 warps: a query row is handled by two threads (32 keys each); fp32
+//                        running maximum and sum; P_j rounded to bf16 and written to shared
+//                        memory in the swizzled K-major layout the MMA reads
+//   O_j = P_j V_j        tcgen05.mma, M = 128, N = head size, K = 64 keys; V_j is read as it lies
+//                        in its page (MN-major operand); O_j in tensor memory
+//   O   = alpha_j O + O_j in registers (each thread keeps half a row of O in fp32)
+//
+// S and O are double buffered in tensor memory (2 x 64 + 2 x head-size columns), K/V pages in a
+// ring of shared-memory stages, so the MMAs of page j + 1 run while page j is in the softmax.
+// Warps: 0 = TMA producer, 1 = MMA issuer (one thread) and tensor-memory owner, 2..9 = softmax.
+//
+// Works for any q_len >= 1 on top of any cached length (query t of the step sits at position
+// past + t).  No window.  Compile with -DODI_HEAD_DIM=64 or 128.
+//
+// Every wait on an mbarrier is bounded (about two seconds of SM clock): a role that gives up
+// records a code in `status`, raises the CTA's abort flag, and all roles fall through to the
+// common exit, where tensor memory is freed.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef ODI_HEAD_DIM
+#error "compile with -DODI_HEAD_DIM=<head size>"
+#endif
+#define D ODI_HEAD_DIM
+#if D != 64 && D != 128
+#error "the tcgen05 attention takes head sizes 64 and 128"
+#endif
+
+#define BM 128                 // query rows per CTA
+#define BNK 64                 // keys per page / tile
+#define KB (D / 64)            // 64-wide blocks of the head size
+#define NST 3                  // key/value stages
+#define Q_BYTES (KB * BM * 128)
+#define KV_BYTES (KB * BNK * 128)     // one of K or V for a page
+#define P_BYTES (BM * 128)            // 128 rows x 64 keys bf16
+#define SMEM_BYTES (Q_BYTES + NST * 2 * KV_BYTES + 2 * P_BYTES)
+#define TMEM_COLS 512
+#define S_COL(b) ((b) * BNK)
+#define O_COL(b) (2 * BNK + (b) * D)
+#define ATT_THREADS 320
+#define WAIT_CYCLES 4000000000ll
+#define LOG2E 1.4426950408889634f
+
+#define ATT_ERR_PRODUCER 11
+#define ATT_ERR_MMA 12
+#define ATT_ERR_SOFTMAX 13
+
+struct TcAttnArgs {
+  bf16* out;              // [n_tokens, nq * D]
+  const int* cu_q;
+  const int* past;
+  const int* page_start;
+  const int* page_ids;
+  int* status;
+  int n_seqs, nq, nkv;
+  float scale;
+};
+
+// ------------------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const long long start = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 0x3ff) == 0x3ff) {
+      if (*abort_flag) return false;
+      if (clock64() - start > WAIT_CYCLES) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile written by TMA with the 128-byte swizzle (rows of 128 bytes, 8-row groups
+// 1024 bytes apart): Q, K and P.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffff) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// MN-major operand (V as the B operand of P V: rows are keys = the MMA's K, the 128-byte row holds
+// 64 consecutive head elements = the MMA's N): 8-key groups 1024 bytes apart (stride byte offset),
+// 64-element column blocks KV_BYTES / KB apart (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((BNK * 128) >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// kind::f16, fp32 accumulator, bf16 operands; b_mn selects an MN-major B operand.
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------ the kernel
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const TcAttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // barriers: q_full, kv_full[NST], kv_empty[NST], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2]
+  __shared__ __align__(8) uint64_t bars[1 + 2 * NST + 12];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ float row_max[2][BM];      // the two halves of a row exchange their maxima here
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.z, head = blockIdx.y, hk = head / (a.nq / a.nkv);
+  const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
+  const int t0 = blockIdx.x * BM;
+  if (t0 >= q_len) return;                       // whole CTA: nothing allocated yet
+  const int past = a.past[seq];
+  const int nt = min(BM, q_len - t0);
+  const int n_tiles = (past + t0 + nt + BNK - 1) / BNK;
+  const int* pages = a.page_ids + a.page_start[seq];
+
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * NST, s_full = kv_empty + 8 * NST,
+                 s_empty = s_full + 16, p_full = s_empty + 16, p_empty = p_full + 16, o_full = p_empty + 16,
+                 o_empty = o_full + 16;
+  uint8_t* q_smem = smem;
+  uint8_t* kv_smem = smem + Q_BYTES;             // stage s: K at s * 2 * KV_BYTES, V right after
+  uint8_t* p_smem = kv_smem + NST * 2 * KV_BYTES;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 1 + 2 * NST + 12; ++i) mbar_init(bar0 + 8 * i, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      pdl_wait();      // queries and this step's keys/values come from the kernel before
+      mbar_expect_tx(q_full, Q_BYTES);
+      for (int kb = 0; kb < KB; ++kb)
+        tma_load_2d(smem_u32(q_smem + kb * BM * 128), &map_q, head * D + kb * 64, q_begin + t0, q_full);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % NST;
+        if (!mbar_wait(kv_empty + 8 * s, ((uint32_t)(j / NST) & 1u) ^ 1u, abort_ptr)) { atomicCAS(a.status, 0, ATT_ERR_PRODUCER); break; }
+        const int row = (pages[j] * a.nkv + hk) * BNK;
+        uint8_t* st = kv_smem + (size_t)s * 2 * KV_BYTES;
+        mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_2d(smem_u32(st + kb * BNK * 128), &map_k, kb * 64, row, kv_full + 8 * s);
+          tma_load_2d(smem_u32(st + KV_BYTES + kb * BNK * 128), &map_v, kb * 64, row, kv_full + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(BM, BNK, false);
+      constexpr uint32_t idesc_o = idesc_bf16(BM, D, true);
+      bool ok = mbar_wait(q_full, 0, abort_ptr);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % NST, b = j & 1;
+        if (!mbar_wait(kv_full + 8 * s, (uint32_t)(j / NST) & 1u, abort_ptr)) return false;
+        if (!mbar_wait(s_empty + 8 * b, ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_ptr)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(kv_smem + (size_t)s * 2 * KV_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          const uint64_t dq = desc_k_major(smem_u32(q_smem + kb * BM * 128));
+          const uint64_t dk = desc_k_major(k_addr + kb * BNK * 128);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) umma(tmem_base + S_COL(b), dq + 2 * i, dk + 2 * i, idesc_s, (kb | i) ? 1u : 0u);
+        }
+        umma_commit(s_full + 8 * b);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);      // the next page's scores run under this page's softmax
+        if (!ok) break;
+        const int s = j % NST, b = j & 1;
+        if (!mbar_wait(p_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; break; }
+        if (!mbar_wait(o_empty + 8 * b, ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_ptr)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t dp = desc_k_major(smem_u32(p_smem + b * P_BYTES));
+        const uint64_t dv = desc_mn_major(smem_u32(kv_smem + (size_t)s * 2 * KV_BYTES + KV_BYTES));
+#pragma unroll
+        for (int i = 0; i < 4; ++i)      // 16 keys per MMA: 32 bytes along P's rows, 16 rows (2048 bytes) down V
+          umma(tmem_base + O_COL(b), dp + 2 * i, dv + (uint64_t)(i * 2048 >> 4), idesc_o, i ? 1u : 0u);
+        umma_commit(o_full + 8 * b);
+        umma_commit(kv_empty + 8 * s);
+        umma_commit(p_empty + 8 * b);
+      }
+      if (!ok) atomicCAS(a.status, 0, ATT_ERR_MMA);
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax and output (8 warps)
+    const int sw = warp - 2;                         // 0..7
+    const int lane_group = warp & 3;                 // the tensor-memory lanes this warp may read
+    const int half = sw >> 2;                        // warps 2..5 take keys 0..31 of a page, warps 6..9 keys 32..63
+    const int row = lane_group * 32 + lane;          // query row inside the tile
+    const int pos = past + t0 + row;
+    const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+    const float sl2 = a.scale * LOG2E;
+    float o[D / 2];
+#pragma unroll
+    for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
+    bool ok = true;
+
+    auto accumulate = [&](int j) {
+      // O = alpha * O + O_j for this thread's half of the head
+      const int b = j & 1;
+      if (!mbar_wait(o_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; return; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 2; c += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + lane_addr + O_COL(b) + half * (D / 2) + c, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[c + i] = o[c + i] * alpha_pending + v[i];
+      }
+      tc_fence_before();
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (threadIdx.x == 64) mbar_arrive(o_empty + 8 * b);
+    };
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(s_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; break; }
+      tc_fence_after();
+      float s[32];
+      tmem_ld16(tmem_base + lane_addr + S_COL(b) + half * 32, s);
+      tmem_ld16(tmem_base + lane_addr + S_COL(b) + half * 32 + 16, s + 16);
+      tc_fence_before();
+      const int kbase = j * BNK + half * 32;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        s[i] = (kbase + i <= pos) ? s[i] * sl2 : -INFINITY;
+        mx = fmaxf(mx, s[i]);
+      }
+      row_max[half][row] = mx;
+      asm volatile("bar.sync 2, 256;" ::: "memory");          // maxima exchanged; both halves have read S_j
+      if (threadIdx.x == 64) mbar_arrive(s_empty + 8 * b);
+      const float m_new = fmaxf(m, fmaxf(row_max[0][row], row_max[1][row]));
+      // key 0 is visible to every row, so m_new is finite from the first page on
+      const float alpha = exp2f(m - m_new);
+      m = m_new;
+      float sum = 0.f;
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = exp2f(s[2 * i] - m_new), p1 = exp2f(s[2 * i + 1] - m_new);
+        sum += p0 + p1;
+        __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+        packed[i] = *(uint32_t*)&pr;
+      }
+      l = l * alpha + sum;
+      // P_j: row `row`, keys half*32 .. +31 = 16-byte chunks half*4 .. +3 of the 128-byte row, swizzled
+      if (!mbar_wait(p_empty + 8 * b, ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_ptr)) { ok = false; break; }
+      uint8_t* prow = p_smem + b * P_BYTES + row * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int chunk = (half * 4 + c) ^ (row & 7);
+        *(uint4*)(prow + chunk * 16) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the tensor core's reads
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (threadIdx.x == 64) mbar_arrive(p_full + 8 * b);
+      // the previous page's product has had this page's softmax to finish
+      if (j > 0) accumulate(j - 1);
+      alpha_pending = alpha;
+    }
+    if (ok && n_tiles > 0) {
+      // alpha_pending belongs to the last page: O (relative to the maximum before it) is scaled by it
+      accumulate(n_tiles - 1);
+    }
+    if (!ok && lane == 0) atomicCAS(a.status, 0, ATT_ERR_SOFTMAX);
+    // total row sum = the two halves' sums (same maxima, same alphas)
+    row_max[half][row] = l;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    const float total = row_max[0][row] + row_max[1][row];
+    if (ok && row < nt) {
+      const float inv = total > 0.f ? 1.f / total : 0.f;
+      bf16* dst = a.out + ((size_t)(q_begin + t0 + row) * a.nq + head) * D + half * (D / 2);
+#pragma unroll
+      for (int c = 0; c < D / 2; c += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __nv_bfloat162 pr = __floats2bfloat162_rn(o[c + 2 * i] * inv, o[c + 2 * i + 1] * inv);
+          w[i] = *(uint32_t*)&pr;
+        }
+        *(uint4*)(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, cols] row-major bf16 matrix cut into boxes of box_rows x 64 with the 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long rows, long cols, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return ODI_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
+}
+
+extern "C" int odi_attention_tcgen05_head_dim() { return D; }
+
+// q [n_tokens, nq * D] bf16; k_pool, v_pool [pool_pages, nkv, 64, D] bf16; out [n_tokens, nq * D].
+extern "C" int odi_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const TcAttnArgs* args,
+                                     int n_tokens, int max_q_len, long pool_pages, cudaStream_t stream) {
+  TcAttnArgs a = *args;
+  if (a.n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.nq > 65535 || a.status == nullptr) return ODI_ERR_UNSUPPORTED;
+  if (((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)a.out & 15))
+    return ODI_ERR_UNSUPPORTED;
+  if (pool_pages * a.nkv * BNK > 0x7fffffffL) return ODI_ERR_UNSUPPORTED;    // row coordinates are 32-bit
+  CUtensorMap mq, mk, mv;
+  int rc = make_map(&mq, q, n_tokens, (long)a.nq * D, BM);
+  if (rc == 0) rc = make_map(&mk, k_pool, pool_pages * a.nkv * BNK, D, BNK);
+  if (rc == 0) rc = make_map(&mv, v_pool, pool_pages * a.nkv * BNK, D, BNK);
+  if (rc != 0) return rc;
+  static bool configured = false;
+  const int smem = SMEM_BYTES + 1024;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_q_len + BM - 1) / BM, a.nq, a.n_seqs);
+  odi_rc = launch_pdl((attention_tcgen05_kernel), dim3(grid), dim3(ATT_THREADS), smem, stream, mq, mk, mv, a);
+  return launch_status();
+}

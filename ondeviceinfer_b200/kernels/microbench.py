@@ -112,10 +112,11 @@ def attention_prefill_case(args) -> dict:
     out = torch.empty(args.batch * T, nq * d, dtype=torch.bfloat16, device="cuda")
     cu_q = (torch.arange(args.batch + 1, dtype=torch.int32) * T).cuda()
     past = torch.zeros(args.batch, dtype=torch.int32, device="cuda")
-    run = lambda i: ops.attention_mma(q, pools[0][0], pools[0][1], out, cu_q, past, page_start, page_ids,
-                                      n_seqs=args.batch, max_q_len=T, nq=nq, nkv=nkv, d=d, page_size=64,
-                                      scale=1 / math.sqrt(d))
+    kernel = ops.attention_mma if args.mma_sync else ops.attention_tcgen05
+    run = lambda i: kernel(q, pools[0][0], pools[0][1], out, cu_q, past, page_start, page_ids,
+                           n_seqs=args.batch, max_q_len=T, nq=nq, nkv=nkv, d=d, page_size=64, scale=1 / math.sqrt(d))
     us = time_kernel(run, 1, args.reps)
+    ops.raise_on_kernel_fault()
     flops = 2.0 * args.batch * nq * d * T * T          # causal half of 4 * T^2 * d per head
     return {"case": "attention-prefill", "batch": args.batch, "tokens": T, "us": us, "TFLOPs": flops / us / 1e6}
 
@@ -152,6 +153,7 @@ def main(argv=None) -> int:
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
     parser.add_argument("--no-cluster", action="store_true", help="GEMM K splits through global scratch, not a cluster")
     parser.add_argument("--cluster-attention", action="store_true", help="merge decode-attention splits inside a cluster")
+    parser.add_argument("--mma-sync", action="store_true", help="attention-prefill: the mma.sync kernel instead of tcgen05")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--ctx", type=int, default=2048)
     parser.add_argument("--heads", type=int, default=32)

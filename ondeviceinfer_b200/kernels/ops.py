@@ -239,10 +239,12 @@ def gemm_status(device=None) -> int:
 def raise_on_kernel_fault() -> None:
     code = gemm_status()
     if code:
-        names = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}
+        names = {1: "gemm_tcgen05: the TMA producer", 2: "gemm_tcgen05: the MMA issuer", 3: "gemm_tcgen05: the epilogue",
+                 11: "attention_tcgen05: the TMA producer", 12: "attention_tcgen05: the MMA issuer",
+                 13: "attention_tcgen05: the softmax warps"}
         for state in _gemm_state.values():
             state["status"].zero_()
-        raise KernelError(f"gemm_tcgen05 gave up waiting on a barrier in {names.get(code, code)}; its result is invalid")
+        raise KernelError(f"a kernel gave up waiting on a barrier ({names.get(code, code)}); its result is invalid")
 
 
 def gemm_bf16_plan(tokens: int, n_out: int, K: int, epi: int):
@@ -394,6 +396,35 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
     lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(1 if decode else 0),
                                  _stream()), "attention_mma", 2 if (splits > 1 and not clustered) else 1)
+
+
+class _TcAttnArgs(Structure):
+    _fields_ = [("out", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
+                ("page_ids", c_void_p), ("status", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int),
+                ("scale", c_float)]
+
+
+TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
+
+
+def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
+                      nq: int, nkv: int, d: int, page_size: int, scale: float) -> None:
+    """bf16 causal GQA for prefill on tcgen05: scores and outputs in tensor memory, TMA-fed pages."""
+    if d not in TCGEN05_ATTENTION_HEAD_DIMS:
+        raise KernelError(f"the tcgen05 attention takes head sizes {TCGEN05_ATTENTION_HEAD_DIMS}, not {d}")
+    if page_size != 64:
+        raise KernelError("the tcgen05 attention works on pages of 64 positions")
+    for name, t in (("q", q), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
+        _require(t, name, torch.bfloat16)
+    n_tokens = q.numel() // (nq * d)
+    if out.numel() != q.numel() or k_pool.shape != v_pool.shape or k_pool.dim() != 4:
+        raise KernelError("attention_tcgen05: q/out or the pools disagree")
+    _, _, status = _gemm_buffers(q.device, 0)
+    args = _TcAttnArgs(_ptr(out), _ptr(cu_q), _ptr(past), _ptr(page_start), _ptr(page_ids), _ptr(status),
+                       n_seqs, nq, nkv, scale)
+    lib = load_library("attention_tcgen05", {"ODI_HEAD_DIM": d})
+    _check(lib.odi_attention_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), byref(args), c_int(n_tokens),
+                                     c_int(max_q_len), c_long(k_pool.shape[0]), _stream()), "attention_tcgen05")
 
 
 # ------------------------------------------------------------------------------ sampling

@@ -22,6 +22,9 @@ from .base import Part, build_part, register_part
 from .linear import linear
 
 
+TCGEN05_MIN_Q_LEN = 16     # shorter chunks fill too little of a 128-row tile
+
+
 class Attention(Part):
     graph_safe = True   # no host work that depends on the step's values: may be captured in a CUDA graph
 
@@ -82,9 +85,10 @@ class Attention(Part):
         linear(o, self.w_o, residual=residual)
 
     def attend(self, q, o, ctx, view, page_start, page_ids) -> None:
-        """bf16 without a window: the tensor-core kernels (prefill form, or split-key decode form
-        when every sequence brings one token).  float32, windows, head sizes above 256: the
-        CUDA-core kernel."""
+        """bf16 without a window: the tensor-core kernels -- tcgen05 flash attention for steps that
+        bring more than 16 tokens per sequence (head sizes 64 and 128), the mma.sync prefill form for
+        short chunks and other head sizes, the split-key decode form when every sequence brings one
+        token.  float32, windows, head sizes above 256: the CUDA-core kernel."""
         s = self.spec
         tensor_cores = q.dtype == torch.bfloat16 and s.window is None and s.head_dim <= 256
         splits, partial = 1, None
@@ -96,6 +100,11 @@ class Attention(Part):
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.head_dim + 2),),
                                       dtype=torch.float32, device=q.device)
+        if tensor_cores and ctx.max_q_len > TCGEN05_MIN_Q_LEN and s.head_dim in ops.TCGEN05_ATTENTION_HEAD_DIMS:
+            ops.attention_tcgen05(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
+                                  n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
+                                  d=s.head_dim, page_size=PAGE_SIZE, scale=self.scale)
+            return
         if tensor_cores:
             ops.attention_mma(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                               n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,

@@ -480,3 +480,51 @@ def test_attention_mma_finds_one_far_key():
     assert float((out[699].float().cpu() - value).abs().max()) < 0.05
     expected = plain_attention(q, setup["dense"], [700], [0], nq, nkv, d, 0, scale, "bfloat16")
     close(out, expected, "bfloat16")
+
+
+TC_ATTN_CASES = [
+    # d, nq, nkv, lengths, past
+    (128, 4, 2, [128], [0]),                      # exactly one tile of queries, two pages of keys
+    (128, 8, 2, [200, 64, 65, 1], [0, 0, 0, 0]),  # whole prompts, page and tile edges
+    (128, 4, 1, [40, 3, 130], [100, 200, 7]),     # chunks on a cache
+    (64, 6, 3, [300, 17], [0, 50]),
+    (128, 32, 8, [700], [0]),                     # many pages: every buffer and stage wraps several times
+]
+
+
+@pytest.mark.parametrize("d,nq,nkv,lengths,past", TC_ATTN_CASES)
+def test_attention_tcgen05(d, nq, nkv, lengths, past):
+    torch.manual_seed(16)
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=17)
+    n = sum(lengths)
+    q = torch.randn(n, nq, d)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(n, nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_tcgen05(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                          setup["page_start"], setup["page_ids"], n_seqs=len(lengths), max_q_len=max(lengths), nq=nq,
+                          nkv=nkv, d=d, page_size=64, scale=scale)
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, 0, scale, "bfloat16")
+    close(out, expected, "bfloat16")
+
+
+def test_attention_tcgen05_finds_one_far_key():
+    d, nq, nkv = 128, 8, 2
+    setup = paged_setup([700], [0], nkv, d, "bfloat16", seed=18)
+    q = torch.randn(700, nq, d) * 0.1
+    k, v = setup["dense"][0]
+    q[699] = torch.nn.functional.normalize(k[:, 5], dim=-1).repeat_interleave(nq // nkv, 0) * 40.0
+    q[130] = torch.nn.functional.normalize(k[:, 129], dim=-1).repeat_interleave(nq // nkv, 0) * 40.0
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(700, nq * d, dtype=torch.bfloat16, device=DEV)
+    ops.attention_tcgen05(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                          setup["page_start"], setup["page_ids"], n_seqs=1, max_q_len=700, nq=nq, nkv=nkv, d=d,
+                          page_size=64, scale=scale)
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    for tok, key in ((699, 5), (130, 129)):
+        value = v[:, key].bfloat16().float().repeat_interleave(nq // nkv, 0).reshape(-1)
+        assert float((out[tok].float().cpu() - value).abs().max()) < 0.05, (tok, key)
+    expected = plain_attention(q, setup["dense"], [700], [0], nq, nkv, d, 0, scale, "bfloat16")
+    close(out, expected, "bfloat16")
