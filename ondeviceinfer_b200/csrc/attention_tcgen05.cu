@@ -6,15 +6,22 @@
 //   S_j = Q K_j^T        tcgen05.mma, M = 128 query rows, N = 64 keys, K = head size; Q and K_j
 //                        in shared memory (TMA, 128-byte swizzle), S_j in tensor memory
 //   P_j = softmax part   by 8 warps: a query row is handled by two threads (32 keys each); fp32
-//                        running maximum and sum; P_j rounded to bf16 and written to shared
-//                        memory in the swizzled K-major layout the MMA reads
-//   O_j = P_j V_j        tcgen05.mma, M = 128, N = head size, K = 64 keys; V_j is read as it lies
-//                        in its page (MN-major operand); O_j in tensor memory
-//   O   = alpha_j O + O_j in registers (each thread keeps half a row of O in fp32)
+//                        running maximum and sum; P_j rounded to bf16 and written, in the swizzled
+//                        K-major layout the MMA reads, over the shared memory of K_j (which S_j
+//                        has consumed by then)
+//   O  += P_j V_j        tcgen05.mma, M = 128, N = head size, K = 64 keys; V_j is read as it lies
+//                        in its page (MN-major operand); O accumulates in tensor memory
 //
-// S and O are double buffered in tensor memory (2 x 64 + 2 x head-size columns), K/V pages in a
-// ring of shared-memory stages, so the MMAs of page j + 1 run while page j is in the softmax.
-// Warps: 0 = TMA producer, 1 = MMA issuer (one thread) and tensor-memory owner, 2..9 = softmax.
+// The accumulator in tensor memory cannot be scaled by the MMA, so the running maximum that P is
+// taken against is only raised when a row's new maximum exceeds it by more than 2^8: then that
+// row of O is read, scaled and written back (tcgen05.ld / st) before the row's next product is
+// issued.  P stays below 2^8, which bf16 and the fp32 accumulator hold without loss, and the
+// result is the same as with a maximum that is raised every time.
+//
+// S is double buffered in tensor memory (2 x 64 columns, O takes head-size columns: 256 in all),
+// K/V pages sit in three shared-memory stages, so the scores of page j + 1 are computed and page
+// j + 2 is loaded while page j is in the softmax.  Warps: 0 = TMA producer, 1 = MMA issuer (one thread)
+// and tensor-memory owner, 2..9 = softmax.
 //
 // Works for any q_len >= 1 on top of any cached length (query t of the step sits at position
 // past + t).  No window.  Compile with -DODI_HEAD_DIM=64 or 128.
@@ -37,14 +44,19 @@
 #define BM 128                 // query rows per CTA
 #define BNK 64                 // keys per page / tile
 #define KB (D / 64)            // 64-wide blocks of the head size
+#ifndef NST
 #define NST 3                  // key/value stages
+#endif
 #define Q_BYTES (KB * BM * 128)
 #define KV_BYTES (KB * BNK * 128)     // one of K or V for a page
 #define P_BYTES (BM * 128)            // 128 rows x 64 keys bf16
-#define SMEM_BYTES (Q_BYTES + NST * 2 * KV_BYTES + 2 * P_BYTES)
-#define TMEM_COLS 512
+#define KP_BYTES (KV_BYTES > P_BYTES ? KV_BYTES : P_BYTES)   // K_j, later overwritten by P_j
+#define STAGE_BYTES (KP_BYTES + KV_BYTES)
+#define SMEM_BYTES (Q_BYTES + NST * STAGE_BYTES)
+#define TMEM_COLS 256
 #define S_COL(b) ((b) * BNK)
-#define O_COL(b) (2 * BNK + (b) * D)
+#define O_COL (2 * BNK)
+#define RESCALE_THRESHOLD 8.0f        // log2 units
 #define ATT_THREADS 320
 #define WAIT_CYCLES 4000000000ll
 #define LOG2E 1.4426950408889634f
@@ -126,6 +138,38 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive columns of this thread's lane: two loads in flight, one wait.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // K-major operand tile written by TMA with the 128-byte swizzle (rows of 128 bytes, 8-row groups
 // 1024 bytes apart): Q, K and P.
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
@@ -157,16 +201,19 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_mn) {
 
 // ------------------------------------------------------------------------------ the kernel
 
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+#ifndef ATT_MIN_BLOCKS
+#define ATT_MIN_BLOCKS 1
+#endif
+__global__ void __launch_bounds__(ATT_THREADS, ATT_MIN_BLOCKS)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const TcAttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  // barriers: q_full, kv_full[NST], kv_empty[NST], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2]
-  __shared__ __align__(8) uint64_t bars[1 + 2 * NST + 12];
+  // barriers: q_full, kv_full[NST], kv_empty[NST], s_full[2], s_empty[2], p_full[2], pv_done
+  __shared__ __align__(8) uint64_t bars[1 + 2 * NST + 7];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float row_max[2][BM];      // the two halves of a row exchange their maxima here
+  __shared__ float row_max[2][BM];      // the two halves of a row exchange their maxima (and sums) here
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -181,14 +228,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   const uint32_t bar0 = smem_u32(&bars[0]);
   const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * NST, s_full = kv_empty + 8 * NST,
-                 s_empty = s_full + 16, p_full = s_empty + 16, p_empty = p_full + 16, o_full = p_empty + 16,
-                 o_empty = o_full + 16;
+                 s_empty = s_full + 16, p_full = s_empty + 16, pv_done = p_full + 16;
   uint8_t* q_smem = smem;
-  uint8_t* kv_smem = smem + Q_BYTES;             // stage s: K at s * 2 * KV_BYTES, V right after
-  uint8_t* p_smem = kv_smem + NST * 2 * KV_BYTES;
+  uint8_t* kv_smem = smem + Q_BYTES;             // stage s: K (later P) at s * 2 * KV_BYTES, V right after
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 1 + 2 * NST + 12; ++i) mbar_init(bar0 + 8 * i, 1);
+    for (int i = 0; i < 1 + 2 * NST + 7; ++i) mbar_init(bar0 + 8 * i, 1);
+    for (int b = 0; b < 2; ++b) {      // signalled by the four pairs of softmax warps
+      mbar_init(s_empty + 8 * b, 4);
+      mbar_init(p_full + 8 * b, 4);
+    }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -213,11 +262,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int s = j % NST;
         if (!mbar_wait(kv_empty + 8 * s, ((uint32_t)(j / NST) & 1u) ^ 1u, abort_ptr)) { atomicCAS(a.status, 0, ATT_ERR_PRODUCER); break; }
         const int row = (pages[j] * a.nkv + hk) * BNK;
-        uint8_t* st = kv_smem + (size_t)s * 2 * KV_BYTES;
+        uint8_t* st = kv_smem + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
         for (int kb = 0; kb < KB; ++kb) {
           tma_load_2d(smem_u32(st + kb * BNK * 128), &map_k, kb * 64, row, kv_full + 8 * s);
-          tma_load_2d(smem_u32(st + KV_BYTES + kb * BNK * 128), &map_v, kb * 64, row, kv_full + 8 * s);
+          tma_load_2d(smem_u32(st + KP_BYTES + kb * BNK * 128), &map_v, kb * 64, row, kv_full + 8 * s);
         }
       }
     }
@@ -232,7 +281,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (!mbar_wait(kv_full + 8 * s, (uint32_t)(j / NST) & 1u, abort_ptr)) return false;
         if (!mbar_wait(s_empty + 8 * b, ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_ptr)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(kv_smem + (size_t)s * 2 * KV_BYTES);
+        const uint32_t k_addr = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) {
           const uint64_t dq = desc_k_major(smem_u32(q_smem + kb * BM * 128));
@@ -245,123 +294,129 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) ok = issue_s(j + 1);      // the next page's scores run under this page's softmax
+        // The next page's scores run under this page's softmax.  With two stages the next page's
+        // stage is the one page j - 1 used: its product has been issued, the producer refills it.
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);
         if (!ok) break;
         const int s = j % NST, b = j & 1;
         if (!mbar_wait(p_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; break; }
-        if (!mbar_wait(o_empty + 8 * b, ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_ptr)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t dp = desc_k_major(smem_u32(p_smem + b * P_BYTES));
-        const uint64_t dv = desc_mn_major(smem_u32(kv_smem + (size_t)s * 2 * KV_BYTES + KV_BYTES));
+        const uint32_t stage = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
+        const uint64_t dp = desc_k_major(stage);                 // P_j lies where K_j was
+        const uint64_t dv = desc_mn_major(stage + KP_BYTES);
 #pragma unroll
         for (int i = 0; i < 4; ++i)      // 16 keys per MMA: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-          umma(tmem_base + O_COL(b), dp + 2 * i, dv + (uint64_t)(i * 2048 >> 4), idesc_o, i ? 1u : 0u);
-        umma_commit(o_full + 8 * b);
+          umma(tmem_base + O_COL, dp + 2 * i, dv + (uint64_t)(i * 2048 >> 4), idesc_o, (j | i) ? 1u : 0u);
+        umma_commit(pv_done);
         umma_commit(kv_empty + 8 * s);
-        umma_commit(p_empty + 8 * b);
       }
       if (!ok) atomicCAS(a.status, 0, ATT_ERR_MMA);
     }
   } else {
     // ---------------------------------------------------------------- softmax and output (8 warps)
-    const int sw = warp - 2;                         // 0..7
     const int lane_group = warp & 3;                 // the tensor-memory lanes this warp may read
-    const int half = sw >> 2;                        // warps 2..5 take keys 0..31 of a page, warps 6..9 keys 32..63
+    const int half = (warp - 2) >> 2;                // warps 2..5 take keys 0..31 of a page, warps 6..9 keys 32..63
     const int row = lane_group * 32 + lane;          // query row inside the tile
     const int pos = past + t0 + row;
     const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
     const float sl2 = a.scale * LOG2E;
-    float o[D / 2];
-#pragma unroll
-    for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
+    float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-
-    auto accumulate = [&](int j) {
-      // O = alpha * O + O_j for this thread's half of the head
-      const int b = j & 1;
-      if (!mbar_wait(o_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; return; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 2; c += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + lane_addr + O_COL(b) + half * (D / 2) + c, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) o[c + i] = o[c + i] * alpha_pending + v[i];
-      }
-      tc_fence_before();
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      if (threadIdx.x == 64) mbar_arrive(o_empty + 8 * b);
-    };
+    // The two warps that share a lane group (the two halves of 32 rows) synchronise among themselves
+    // on a named barrier of their own; the mbarriers they signal expect one arrival per pair.
+    const bool pair_leader = half == 0 && lane == 0;
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(2 + lane_group) : "memory"); };
 
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1;
+      const int b = j & 1, st = j % NST;
       if (!mbar_wait(s_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; break; }
       tc_fence_after();
       float s[32];
-      tmem_ld16(tmem_base + lane_addr + S_COL(b) + half * 32, s);
-      tmem_ld16(tmem_base + lane_addr + S_COL(b) + half * 32 + 16, s + 16);
+      tmem_ld32(tmem_base + lane_addr + S_COL(b) + half * 32, s);
       tc_fence_before();
       const int kbase = j * BNK + half * 32;
       float mx = -INFINITY;
+      if (kbase + 31 <= pos) {             // every key of this half is visible: no mask
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        s[i] = (kbase + i <= pos) ? s[i] * sl2 : -INFINITY;
-        mx = fmaxf(mx, s[i]);
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (kbase + i > pos) s[i] = -INFINITY;
+          mx = fmaxf(mx, s[i]);
+        }
       }
-      row_max[half][row] = mx;
-      asm volatile("bar.sync 2, 256;" ::: "memory");          // maxima exchanged; both halves have read S_j
-      if (threadIdx.x == 64) mbar_arrive(s_empty + 8 * b);
-      const float m_new = fmaxf(m, fmaxf(row_max[0][row], row_max[1][row]));
-      // key 0 is visible to every row, so m_new is finite from the first page on
-      const float alpha = exp2f(m - m_new);
-      m = m_new;
+      row_max[half][row] = mx * sl2;       // sl2 > 0: the maximum of the scaled scores
+      pair_sync();                          // maxima exchanged; both halves have read S_j
+      if (pair_leader) mbar_arrive(s_empty + 8 * b);
+      const float m_tile = fmaxf(row_max[0][row], row_max[1][row]);    // finite: key 0 is visible to every row
+      // Raise the maximum this row's P is taken against only when it is exceeded by a wide margin;
+      // what O holds for the row was taken against the old one and is scaled down first.  The
+      // tensor-memory accesses are warp-wide, so the warp goes through them together whenever
+      // one of its rows needs it (the others scale by 1); the partner warp sees the same rows.
+      const bool need = m_tile > m_used + RESCALE_THRESHOLD;
+      const float alpha = need ? exp2f(m_used - m_tile) : 1.f;
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        if (!mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_ptr)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 2; c += 32) {
+          float v[32];
+          tmem_ld32(tmem_base + lane_addr + O_COL + half * (D / 2) + c, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= alpha;
+          tmem_st32(tmem_base + lane_addr + O_COL + half * (D / 2) + c, v);
+        }
+      }
+      if (need) { l *= alpha; m_used = m_tile; }
       float sum = 0.f;
       uint32_t packed[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = exp2f(s[2 * i] - m_new), p1 = exp2f(s[2 * i + 1] - m_new);
+        const float p0 = exp2f(fmaf(s[2 * i], sl2, -m_used)), p1 = exp2f(fmaf(s[2 * i + 1], sl2, -m_used));
         sum += p0 + p1;
         __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
         packed[i] = *(uint32_t*)&pr;
       }
-      l = l * alpha + sum;
-      // P_j: row `row`, keys half*32 .. +31 = 16-byte chunks half*4 .. +3 of the 128-byte row, swizzled
-      if (!mbar_wait(p_empty + 8 * b, ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_ptr)) { ok = false; break; }
-      uint8_t* prow = p_smem + b * P_BYTES + row * 128;
+      l += sum;
+      // P_j over K_j (consumed by S_j): row `row`, keys half*32 .. +31 = 16-byte chunks half*4 .. +3, swizzled
+      uint8_t* prow = kv_smem + (size_t)st * STAGE_BYTES + row * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int chunk = (half * 4 + c) ^ (row & 7);
         *(uint4*)(prow + chunk * 16) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the tensor core's reads
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      if (threadIdx.x == 64) mbar_arrive(p_full + 8 * b);
-      // the previous page's product has had this page's softmax to finish
-      if (j > 0) accumulate(j - 1);
-      alpha_pending = alpha;
+      tc_fence_before();
+      pair_sync();
+      if (pair_leader) mbar_arrive(p_full + 8 * b);
     }
-    if (ok && n_tiles > 0) {
-      // alpha_pending belongs to the last page: O (relative to the maximum before it) is scaled by it
-      accumulate(n_tiles - 1);
-    }
+    if (ok && !mbar_wait(pv_done, (uint32_t)(n_tiles - 1) & 1u, abort_ptr)) ok = false;
+    tc_fence_after();
     if (!ok && lane == 0) atomicCAS(a.status, 0, ATT_ERR_SOFTMAX);
-    // total row sum = the two halves' sums (same maxima, same alphas)
+    // total row sum = the two halves' sums (both taken against the same maxima)
     row_max[half][row] = l;
-    asm volatile("bar.sync 2, 256;" ::: "memory");
+    pair_sync();
     const float total = row_max[0][row] + row_max[1][row];
-    if (ok && row < nt) {
+    if (ok) {
       const float inv = total > 0.f ? 1.f / total : 0.f;
       bf16* dst = a.out + ((size_t)(q_begin + t0 + row) * a.nq + head) * D + half * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 2; c += 8) {
-        uint32_t w[4];
+      for (int c = 0; c < D / 2; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_base + lane_addr + O_COL + half * (D / 2) + c, v);     // every thread of the warp loads
+        if (row < nt) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 pr = __floats2bfloat162_rn(o[c + 2 * i] * inv, o[c + 2 * i + 1] * inv);
-          w[i] = *(uint32_t*)&pr;
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 pr = __floats2bfloat162_rn(v[i + 2 * k] * inv, v[i + 2 * k + 1] * inv);
+              w[k] = *(uint32_t*)&pr;
+            }
+            *(uint4*)(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
-        *(uint4*)(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
     tc_fence_before();
