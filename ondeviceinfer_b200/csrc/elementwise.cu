@@ -223,63 +223,76 @@ __global__ void head_prep_kernel(HeadPrepArgs a) {
 // as one vector; the rotation partner of an element (d / 2 further) sits in lane i + 16 at the
 // same register, reached by a shuffle.  Same arithmetic as head_prep_kernel.
 template <int VEC>
-__global__ void head_prep_vec_kernel(HeadPrepArgs a) {
+__global__ void head_prep_vec_kernel(HeadPrepArgs a, int heads_per_warp) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int heads = a.nq + (a.write_kv ? 2 * a.nkv : 0);
+  const int groups = (heads + heads_per_warp - 1) / heads_per_warp;      // warps per token
   const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= (long)a.n_tokens * heads) return;
-  const int t = (int)(item / heads), h = (int)(item % heads);
-  const int d = a.d;
-  const bf16* src = (const bf16*)a.qkv + (size_t)t * (a.nq + 2 * a.nkv) * d + (size_t)h * d + VEC * lane;
-  const int kind = h < a.nq ? 0 : (h < a.nq + a.nkv ? 1 : 2);
+  if (item >= (long)a.n_tokens * groups) return;
+  const int t = (int)(item / groups), h_begin = (int)(item % groups) * heads_per_warp;
+  const int h_end = min(heads, h_begin + heads_per_warp);
+  const int d = a.d, half = d >> 1;
   const int pos = a.tok_pos[t];
-  bf16* dst;
-  if (kind == 0) {
-    dst = (bf16*)a.q_out + ((size_t)t * a.nq + h) * d;
-  } else {
-    const int hk = kind == 1 ? h - a.nq : h - a.nq - a.nkv;
-    const int page = a.page_ids[a.page_start[a.tok_seq[t]] + page_slot_of(pos, a.page_size, a.ring_pages)];
-    bf16* pool = (bf16*)(kind == 1 ? a.k_pool : a.v_pool);
-    dst = pool + (((size_t)page * a.nkv + hk) * a.page_size + (pos % a.page_size)) * d;
+  // what does not depend on the head is read once per token: the rotation table entries of this
+  // lane's elements, the norm weights, the token's cache page
+  float cs[VEC], sn[VEC], wq[VEC], wk[VEC];
+#pragma unroll
+  for (int r = 0; r < VEC; ++r) {
+    const int i = VEC * lane + r, f = i < half ? i : i - half;
+    cs[r] = a.cos_t ? a.cos_t[(size_t)t * half + f] : 1.f;
+    sn[r] = a.cos_t ? a.sin_t[(size_t)t * half + f] : 0.f;
+    wq[r] = a.q_norm_w ? a.q_norm_w[i] : 1.f;
+    wk[r] = a.k_norm_w ? a.k_norm_w[i] : 1.f;
   }
-  dst += VEC * lane;
-  bf16 raw[VEC];
-  if (VEC == 1) raw[0] = src[0];
-  else if (VEC == 2) *(uint32_t*)raw = *(const uint32_t*)src;
-  else if (VEC == 4) *(uint2*)raw = *(const uint2*)src;
-  else *(uint4*)raw = *(const uint4*)src;
-  if (kind != 2) {
-    float x[VEC];
-    float ss = 0.f;
-#pragma unroll
-    for (int r = 0; r < VEC; ++r) { x[r] = __bfloat162float(raw[r]); ss += x[r] * x[r]; }
-    const float* w = kind == 0 ? a.q_norm_w : a.k_norm_w;
-    if (w != nullptr) {
-      ss = warp_sum(ss);
-      const float inv = rsqrtf(ss / (float)d + a.eps);
-#pragma unroll
-      for (int r = 0; r < VEC; ++r) x[r] = round_to<bf16>(w[VEC * lane + r] * round_to<bf16>(x[r] * inv));
+  int page = 0;
+  if (a.write_kv && h_end > a.nq)
+    page = a.page_ids[a.page_start[a.tok_seq[t]] + page_slot_of(pos, a.page_size, a.ring_pages)];
+  const bf16* token_src = (const bf16*)a.qkv + (size_t)t * (a.nq + 2 * a.nkv) * d + VEC * lane;
+  for (int h = h_begin; h < h_end; ++h) {
+    const bf16* src = token_src + (size_t)h * d;
+    const int kind = h < a.nq ? 0 : (h < a.nq + a.nkv ? 1 : 2);
+    bf16* dst;
+    if (kind == 0) {
+      dst = (bf16*)a.q_out + ((size_t)t * a.nq + h) * d;
+    } else {
+      const int hk = kind == 1 ? h - a.nq : h - a.nq - a.nkv;
+      bf16* pool = (bf16*)(kind == 1 ? a.k_pool : a.v_pool);
+      dst = pool + (((size_t)page * a.nkv + hk) * a.page_size + (pos % a.page_size)) * d;
     }
-    if (a.cos_t != nullptr) {
-      const int half = d >> 1;
+    dst += VEC * lane;
+    bf16 raw[VEC];
+    if (VEC == 1) raw[0] = src[0];
+    else if (VEC == 2) *(uint32_t*)raw = *(const uint32_t*)src;
+    else if (VEC == 4) *(uint2*)raw = *(const uint2*)src;
+    else *(uint4*)raw = *(const uint4*)src;
+    if (kind != 2) {
+      float x[VEC];
+      float ss = 0.f;
 #pragma unroll
-      for (int r = 0; r < VEC; ++r) {
-        const float partner = __shfl_xor_sync(0xffffffffu, x[r], 16);
-        const int i = VEC * lane + r;
-        const int f = i < half ? i : i - half;
-        const float cs = a.cos_t[(size_t)t * half + f], sn = a.sin_t[(size_t)t * half + f];
-        x[r] = x[r] * cs + (i < half ? -partner : partner) * sn;
+      for (int r = 0; r < VEC; ++r) { x[r] = __bfloat162float(raw[r]); ss += x[r] * x[r]; }
+      if ((kind == 0 ? a.q_norm_w : a.k_norm_w) != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)d + a.eps);
+#pragma unroll
+        for (int r = 0; r < VEC; ++r) x[r] = round_to<bf16>((kind == 0 ? wq[r] : wk[r]) * round_to<bf16>(x[r] * inv));
       }
-    }
+      if (a.cos_t != nullptr) {
 #pragma unroll
-    for (int r = 0; r < VEC; ++r) raw[r] = __float2bfloat16_rn(x[r]);
+        for (int r = 0; r < VEC; ++r) {
+          const float partner = __shfl_xor_sync(0xffffffffu, x[r], 16);
+          x[r] = x[r] * cs[r] + ((VEC * lane + r) < half ? -partner : partner) * sn[r];
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < VEC; ++r) raw[r] = __float2bfloat16_rn(x[r]);
+    }
+    if (VEC == 1) dst[0] = raw[0];
+    else if (VEC == 2) *(uint32_t*)dst = *(uint32_t*)raw;
+    else if (VEC == 4) *(uint2*)dst = *(uint2*)raw;
+    else *(uint4*)dst = *(uint4*)raw;
   }
-  if (VEC == 1) dst[0] = raw[0];
-  else if (VEC == 2) *(uint32_t*)dst = *(uint32_t*)raw;
-  else if (VEC == 4) *(uint2*)dst = *(uint2*)raw;
-  else *(uint4*)dst = *(uint4*)raw;
 }
 
 extern "C" int odi_head_prep(const HeadPrepArgs* args, int dtype, cudaStream_t stream) {
@@ -291,11 +304,16 @@ extern "C" int odi_head_prep(const HeadPrepArgs* args, int dtype, cudaStream_t s
   const int blocks = (int)((items + 3) / 4);
   if (dtype == 1 && a.d % 32 == 0 && a.d <= 256 && (a.cos_t == nullptr || a.rot_dim == a.d) &&
       ((uintptr_t)a.qkv % 16 == 0) && ((uintptr_t)a.q_out % 16 == 0)) {
+    // few tokens (decode): a warp per (token, head) for parallelism; many tokens (prefill): a warp
+    // takes a quarter of a token's heads, so the per-token table entries are read once for all of them
+    const int hpw = a.n_tokens >= 256 ? (heads + 3) / 4 : 1;
+    const long warps = (long)a.n_tokens * ((heads + hpw - 1) / hpw);
+    const int vblocks = (int)((warps + 3) / 4);
     switch (a.d / 32) {
-      case 1: odi_rc = launch_pdl((head_prep_vec_kernel<1>), dim3(blocks), dim3(128), 0, stream, a); return launch_status();
-      case 2: odi_rc = launch_pdl((head_prep_vec_kernel<2>), dim3(blocks), dim3(128), 0, stream, a); return launch_status();
-      case 4: odi_rc = launch_pdl((head_prep_vec_kernel<4>), dim3(blocks), dim3(128), 0, stream, a); return launch_status();
-      case 8: odi_rc = launch_pdl((head_prep_vec_kernel<8>), dim3(blocks), dim3(128), 0, stream, a); return launch_status();
+      case 1: odi_rc = launch_pdl((head_prep_vec_kernel<1>), dim3(vblocks), dim3(128), 0, stream, a, hpw); return launch_status();
+      case 2: odi_rc = launch_pdl((head_prep_vec_kernel<2>), dim3(vblocks), dim3(128), 0, stream, a, hpw); return launch_status();
+      case 4: odi_rc = launch_pdl((head_prep_vec_kernel<4>), dim3(vblocks), dim3(128), 0, stream, a, hpw); return launch_status();
+      case 8: odi_rc = launch_pdl((head_prep_vec_kernel<8>), dim3(vblocks), dim3(128), 0, stream, a, hpw); return launch_status();
       default: break;
     }
   }

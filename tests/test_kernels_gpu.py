@@ -207,13 +207,16 @@ def test_attention_window_edge(dtype):
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("d,rot,nq,nkv,norm,ring", [(16, 16, 4, 2, True, 0), (128, 128, 8, 2, True, 0),
                                                     (48, 32, 3, 1, False, 0), (256, 64, 2, 2, True, 0),
-                                                    (32, 32, 2, 1, True, 3), (64, 0, 2, 2, True, 0)])
+                                                    (32, 32, 2, 1, True, 3), (64, 0, 2, 2, True, 0),
+                                                    (128, 128, 6, 2, True, -1)])
 def test_head_prep(dtype, d, rot, nq, nkv, norm, ring):
     """Per-head norm (or none), rotation of the first `rot` lanes (or none), cache write
     into shuffled pages (or a ring of pages), against plain torch."""
     torch.manual_seed(4)
     lengths, past = [3, 1, 70], [0, 200, 10]
-    if ring:
+    if ring == -1:          # many tokens: the form in which a warp takes several heads of a token
+        lengths, past, ring = [200, 90], [0, 30], 0
+    elif ring:
         lengths, past = [3, 1, 20], [0, 200, 100]
     setup = paged_setup(lengths, past, nkv, d, dtype, ring_pages=ring, seed=5)
     n = sum(lengths)
