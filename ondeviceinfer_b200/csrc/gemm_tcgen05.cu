@@ -497,9 +497,12 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 template <int BN, bool DUAL, int EPI, bool SWAP, bool CLUSTER>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   constexpr int STAGE_BYTES = BM * BK * 2 * ((DUAL && !SWAP) ? 2 : 1) + BN * BK * 2 * ((DUAL && SWAP) ? 2 : 1);
-  // The decode form takes about 72 KB, so that three CTAs fit on an SM: a launch fills two of the
-  // places and the CTAs of the next kernel of the stream move into the third while this one drains,
-  // where they already request their first weight tiles.  The prefill form takes the SM alone.
+  // The decode form takes about 72 KB (four stages of a 128 x 16 tile), so that three CTAs fit on an
+  // SM: several short pipelines per SM hide each other's set-up, drain and split exchange, and the
+  // CTAs of the next kernel of the stream find room to move in and request their first weight tiles
+  // while this one drains.  Measured on whole captured decode steps (Qwen3-8B sizes, batch 1 / 8):
+  // 72-84 KB 3.39 / 3.86 ms, 56-64 KB 3.46 / 4.13 ms, 100 KB 3.50 / 4.13 ms; one CTA of 144-200 KB
+  // per SM is 1.5x slower per kernel.  The prefill form takes the SM alone.
 #ifndef ODI_GEMM_DECODE_SMEM_KB
 #define ODI_GEMM_DECODE_SMEM_KB 72
 #endif

@@ -251,7 +251,7 @@ def gemm_bf16_plan(tokens: int, n_out: int, K: int, epi: int):
     """(swap, tile, splits) for a shape.
 
     Up to 64 tokens: decode form (128 features x `tile` tokens per CTA) with enough K
-    splits to fill 148 SMs twice over, each split at least four k-blocks of 64.
+    splits for about 384 CTAs (at most 8, a cluster), each split at least four k-blocks of 64.
     More tokens: prefill form (128 tokens x `tile` features per CTA), the largest tile
     that still gives every SM a CTA.
     """
@@ -259,8 +259,9 @@ def gemm_bf16_plan(tokens: int, n_out: int, K: int, epi: int):
     if tokens <= 64:
         bn = next(b for b in (16, 32, 64) if tokens <= b)
         tiles = -(-n_out // 128)
-        # measured on B200: about 192 CTAs stream best (288 for the two-accumulator form with small token tiles)
-        target = 288 if (epi == EPI_SWIGLU and bn <= 32) else 192
+        # measured on whole decode steps on B200: about 384 CTAs (three of 72 KB per SM) stream best,
+        # in clusters of up to 8 splits (192: +7 %, 288: +2 %, 512: +7 % step time)
+        target = 384
         splits = max(1, min(total_kb // 4, int(target / tiles + 0.5), 8)) if tiles < target else 1
         return False, bn, splits
     choices = (128, 64) if epi == EPI_SWIGLU else (256, 128, 64)
