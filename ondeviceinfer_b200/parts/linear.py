@@ -2,7 +2,7 @@
 
 float32: this library's own FMA kernel (no tensor cores, no TF32), residual add fused.
 
-bfloat16, up to 16 tokens (decode and short chunks; ``ODI_OWN_GEMM_MAX_TOKENS`` moves the limit,
+bfloat16, up to 32 tokens (decode and short chunks; ``ODI_OWN_GEMM_MAX_TOKENS`` moves the limit,
 the kernel itself takes any number): the hand-written tcgen05 kernel
 (``csrc/gemm_tcgen05.cu``): weights streamed by TMA, fp32 accumulators in tensor memory,
 the residual add, the fp32 store of logits and the SiLU-gate product fused into its epilogue.
@@ -24,10 +24,10 @@ from ..kernels import ops
 
 import os
 
-# Measured on B200 inside captured decode steps at Qwen3-8B sizes: the own kernel wins up to 8 tokens
-# (1950 against 1710 tokens/s at batch 8), ties at 16, and loses to the library product at 64
-# (7420 against 8540 tokens/s), so it serves up to 16 tokens by default.
-OWN_KERNEL_MAX_TOKENS = int(os.environ.get("ODI_OWN_GEMM_MAX_TOKENS", "16"))
+# Measured on B200 on whole captured decode steps at Qwen3-8B sizes (own kernel / library product):
+# batch 8: 3.79 / 4.68 ms, batch 16: 4.45 / 4.65 ms, batch 32: 5.39 / 5.42 ms, batch 64: 8.2 / 7.5 ms,
+# so the own kernel serves up to 32 tokens by default.
+OWN_KERNEL_MAX_TOKENS = int(os.environ.get("ODI_OWN_GEMM_MAX_TOKENS", "32"))
 
 
 def _own(x: torch.Tensor, weight: torch.Tensor) -> bool:
