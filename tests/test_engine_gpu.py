@@ -232,3 +232,26 @@ def test_qwen3_8b_layer_sizes(dtype, tmp_path):
     for slot in slots:
         cache.free(slot)
     cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_context(dtype, tmp_root):
+    """1,100 tokens (18 pages): whole in one step, then in two chunks with 40 single tokens at the
+    end; prefill tiles, page rings and decode splits all wrap several times."""
+    model, _, cfg = engine_model("C", dtype, tmp_root)
+    tokens = plain.random_prompts(cfg, [1100], 91)[0]
+    expected = plain_logits("C", tokens)
+    cache = model.make_cache(max_tokens=1152, max_seqs=1)
+    slot = cache.alloc()
+    whole = model.step(cache, [slot], [tokens], "all")
+    assert_logits_close(whole, expected, dtype, "long context whole")
+    cache.free(slot)
+    slot = cache.alloc()
+    rows = [model.step(cache, [slot], [tokens[:700]], [[0, 350, 699]]),
+            model.step(cache, [slot], [tokens[700:1060]], [[0, 359]])]
+    picks = [0, 350, 699, 700, 1059]
+    for t in range(1060, 1100):
+        rows.append(model.step(cache, [slot], [[tokens[t]]], "last"))
+        picks.append(t)
+    assert_logits_close(torch.cat(rows), expected[picks], dtype, "long context in chunks")
+    cache.free(slot)

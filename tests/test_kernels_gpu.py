@@ -420,6 +420,7 @@ MMA_CASES = [
     (80, 3, 1, [1], [129], 2),
     (128, 16, 2, [1, 1, 1], [900, 3, 450], 8),                  # eight splits, some of them empty for short sequences
     (128, 32, 8, [1, 1], [1500, 64], 12),                       # more than a cluster holds: global partials
+    (128, 8, 2, [1, 1], [5000, 4095], 32),                      # long contexts, the most splits the engine uses
 ]
 
 
@@ -492,6 +493,7 @@ TC_ATTN_CASES = [
     (128, 4, 1, [40, 3, 130], [100, 200, 7]),     # chunks on a cache
     (64, 6, 3, [300, 17], [0, 50]),
     (128, 32, 8, [700], [0]),                     # many pages: every buffer and stage wraps several times
+    (128, 4, 1, [900, 1], [2100, 3000]),          # a long chunk and a single token on long caches
 ]
 
 
