@@ -71,7 +71,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
@@ -81,7 +81,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const long long start = clock64();
   for (uint32_t i = 0;; ++i) {
     if (mbar_test(bar, parity)) return true;
-    if ((i & 0x3ff) == 0x3ff) {
+    // try_wait suspends the thread for a bounded, implementation-defined time instead of spinning
+    if ((i & 0xf) == 0xf) {
       if (*abort_flag) return false;
       if (clock64() - start > WAIT_CYCLES) break;
     }

@@ -112,9 +112,10 @@ def attention_prefill_case(args) -> dict:
     out = torch.empty(args.batch * T, nq * d, dtype=torch.bfloat16, device="cuda")
     cu_q = (torch.arange(args.batch + 1, dtype=torch.int32) * T).cuda()
     past = torch.zeros(args.batch, dtype=torch.int32, device="cuda")
+    extra = {} if args.mma_sync else {"heads_per_cta": args.heads_per_cta}
     kernel = ops.attention_mma if args.mma_sync else ops.attention_tcgen05
-    run = lambda i: kernel(q, pools[0][0], pools[0][1], out, cu_q, past, page_start, page_ids,
-                           n_seqs=args.batch, max_q_len=T, nq=nq, nkv=nkv, d=d, page_size=64, scale=1 / math.sqrt(d))
+    run = lambda i: kernel(q, pools[0][0], pools[0][1], out, cu_q, past, page_start, page_ids, n_seqs=args.batch,
+                           max_q_len=T, nq=nq, nkv=nkv, d=d, page_size=64, scale=1 / math.sqrt(d), **extra)
     us = time_kernel(run, 1, args.reps)
     ops.raise_on_kernel_fault()
     flops = 2.0 * args.batch * nq * d * T * T          # causal half of 4 * T^2 * d per head
@@ -154,6 +155,7 @@ def main(argv=None) -> int:
     parser.add_argument("--no-cluster", action="store_true", help="GEMM K splits through global scratch, not a cluster")
     parser.add_argument("--cluster-attention", action="store_true", help="merge decode-attention splits inside a cluster")
     parser.add_argument("--mma-sync", action="store_true", help="attention-prefill: the mma.sync kernel instead of tcgen05")
+    parser.add_argument("--heads-per-cta", type=int, default=0, help="attention-prefill on tcgen05: 1, 2 or 0 (default choice)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--ctx", type=int, default=2048)
     parser.add_argument("--heads", type=int, default=32)

@@ -409,8 +409,10 @@ TCGEN05_ATTENTION_HEAD_DIMS = (64, 128)
 
 
 def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
-                      nq: int, nkv: int, d: int, page_size: int, scale: float) -> None:
-    """bf16 causal GQA for prefill on tcgen05: scores and outputs in tensor memory, TMA-fed pages."""
+                      nq: int, nkv: int, d: int, page_size: int, scale: float, heads_per_cta: int = 0) -> None:
+    """bf16 causal GQA for prefill on tcgen05: scores and outputs in tensor memory, TMA-fed pages.
+    ``heads_per_cta``: 1, or 2 (two heads of a key/value group share a CTA and its K/V pages; needs an
+    even group size), or 0 for the library's choice."""
     if d not in TCGEN05_ATTENTION_HEAD_DIMS:
         raise KernelError(f"the tcgen05 attention takes head sizes {TCGEN05_ATTENTION_HEAD_DIMS}, not {d}")
     if page_size != 64:
@@ -425,7 +427,8 @@ def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, 
                        n_seqs, nq, nkv, scale)
     lib = load_library("attention_tcgen05", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_tcgen05(_ptr(q), _ptr(k_pool), _ptr(v_pool), byref(args), c_int(n_tokens),
-                                     c_int(max_q_len), c_long(k_pool.shape[0]), _stream()), "attention_tcgen05")
+                                     c_int(max_q_len), c_long(k_pool.shape[0]), c_int(heads_per_cta), _stream()),
+           "attention_tcgen05")
 
 
 # ------------------------------------------------------------------------------ sampling

@@ -494,6 +494,8 @@ TC_ATTN_CASES = [
     (64, 6, 3, [300, 17], [0, 50]),
     (128, 32, 8, [700], [0]),                     # many pages: every buffer and stage wraps several times
     (128, 4, 1, [900, 1], [2100, 3000]),          # a long chunk and a single token on long caches
+    (128, 3, 1, [150, 70], [0, 10]),              # an odd group size: one head per CTA
+    (64, 2, 2, [130], [5]),                       # no grouping
 ]
 
 
@@ -505,13 +507,39 @@ def test_attention_tcgen05(d, nq, nkv, lengths, past):
     q = torch.randn(n, nq, d)
     scale = 1.0 / math.sqrt(d)
     out = torch.zeros(n, nq * d, dtype=torch.bfloat16, device=DEV)
-    ops.attention_tcgen05(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
-                          setup["page_start"], setup["page_ids"], n_seqs=len(lengths), max_q_len=max(lengths), nq=nq,
-                          nkv=nkv, d=d, page_size=64, scale=scale)
-    torch.cuda.synchronize()
-    ops.raise_on_kernel_fault()
     expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, 0, scale, "bfloat16")
-    close(out, expected, "bfloat16")
+    for heads_per_cta in (1, 2) if (nq // nkv) % 2 == 0 else (1,):
+        out.zero_()
+        ops.attention_tcgen05(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"],
+                              setup["past"], setup["page_start"], setup["page_ids"], n_seqs=len(lengths),
+                              max_q_len=max(lengths), nq=nq, nkv=nkv, d=d, page_size=64, scale=scale,
+                              heads_per_cta=heads_per_cta)
+        torch.cuda.synchronize()
+        ops.raise_on_kernel_fault()
+        close(out, expected, "bfloat16")
+
+
+@pytest.mark.parametrize("heads_per_cta", (1, 2))
+def test_attention_tcgen05_repeats_bit_for_bit(heads_per_cta):
+    """More CTAs than SMs, so that CTAs share an SM and their warps drift apart: a wait that took
+    one phase of a barrier for another showed as a few rows that changed from run to run."""
+    d, nq, nkv, lengths, past = 128, 32, 8, [700], [0]
+    torch.manual_seed(19)
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=20)
+    q = torch.randn(700, nq, d).bfloat16().to(DEV)
+    first = None
+    for _ in range(60):
+        out = torch.zeros(700, nq * d, dtype=torch.bfloat16, device=DEV)
+        ops.attention_tcgen05(q, setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                              setup["page_start"], setup["page_ids"], n_seqs=1, max_q_len=700, nq=nq, nkv=nkv, d=d,
+                              page_size=64, scale=1.0 / math.sqrt(d), heads_per_cta=heads_per_cta)
+        torch.cuda.synchronize()
+        if first is None:
+            first = out
+        assert torch.equal(out, first)
+    ops.raise_on_kernel_fault()
+    expected = plain_attention(q.float().cpu(), setup["dense"], lengths, past, nq, nkv, d, 0, 1.0 / math.sqrt(d), "bfloat16")
+    close(first, expected, "bfloat16")
 
 
 def test_attention_tcgen05_finds_one_far_key():
