@@ -434,6 +434,21 @@ def attention_tcgen05(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, 
 # ------------------------------------------------------------------------------ sampling
 
 
+_sample_state = {}
+
+
+def _sample_buffers(device, rows: int, chunks: int):
+    """Per-chunk partial results (16 bytes each) and one ticket per row (kept zero between launches)."""
+    state = _sample_state.setdefault(device, {})
+    if state.get("rows", 0) < rows:
+        state["tickets"] = torch.zeros(max(rows, 256), dtype=torch.int32, device=device)
+        state["rows"] = state["tickets"].numel()
+    if state.get("entries", 0) < rows * chunks:
+        state["partials"] = torch.empty(max(rows * chunks, 4096) * 4, dtype=torch.float32, device=device)
+        state["entries"] = state["partials"].numel() // 4
+    return state["partials"], state["tickets"]
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, seed: int = 0,
            streams: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None, *,
            advance_pos: Optional[torch.Tensor] = None, advance_past: Optional[torch.Tensor] = None,
@@ -454,6 +469,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: float, seed: in
         for name, t in (("active", active), ("advance_pos", advance_pos), ("advance_past", advance_past)):
             _require(t, name, torch.int32, 1)
     lib = load_library("sampling")
+    partials, tickets = _sample_buffers(logits.device, n, int(lib.odi_sample_chunks(c_int(V))))
     _check(lib.odi_sample(_ptr(logits), _ptr(out), c_int(n), c_int(V), c_int(V), c_float(temperature),
                           c_ulonglong(seed & ((1 << 64) - 1)), _ptr(streams), _ptr(steps), _ptr(advance_pos),
-                          _ptr(advance_past), _ptr(active), _stream()), "sample")
+                          _ptr(advance_past), _ptr(active), _ptr(partials), _ptr(tickets), _stream()), "sample")

@@ -330,6 +330,39 @@ def test_sample_greedy_ties_and_temperature_against_plain():
                     assert abs(out[r].item() - expected) == 1 and float((p - u).abs().min()) < 1e-5
 
 
+def test_sample_wide_vocabulary_over_many_chunks():
+    """A row cut into many chunks: ties across chunks, the maximum in the last (partial) chunk, and
+    draws that land in early, middle and late chunks; twice, so that the tickets are seen to return to zero."""
+    torch.manual_seed(9)
+    V = 150001                                       # odd: rows start at unaligned addresses
+    logits = torch.randn(5, V) * 3
+    logits[0, 4097] = logits[0, 140000] = 40.0       # tie across chunks: the lower index wins
+    logits[1, V - 1] = 45.0
+    logits[2, 2048] = 45.0                           # first element of the second chunk
+    logits[3] = -2.0                                 # flat but for a few heavy tokens spread over the row
+    for i, idx in enumerate((5, 70000, 149990)):
+        logits[3, idx] = 9.0 + i
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    dev = logits.to(DEV)
+    streams = torch.arange(5, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        ops.sample(dev, out, 0.0)
+        assert out.tolist() == [int(torch.argmax(l)) for l in logits] and out[0] == 4097
+        seen = set()
+        for temperature in (1.0, 0.3):
+            cdfs = [torch.softmax(l.double() / temperature, 0).cumsum(0) for l in logits]
+            for step in range(12):
+                steps = torch.full((5,), step, dtype=torch.int32, device=DEV)
+                ops.sample(dev, out, temperature, 5, streams, steps)
+                for r in range(5):
+                    u = plain.uniform_draw(5, r, step)
+                    expected = plain.sample(logits[r], temperature, u)
+                    seen.add((r, expected * 3 // V))
+                    if out[r].item() != expected:
+                        assert abs(out[r].item() - expected) == 1 and float((cdfs[r] - u).abs().min()) < 1e-5
+        assert {(4, 0), (4, 1), (4, 2)} <= seen      # early, middle and late chunks were all drawn from
+
+
 def test_kernels_refuse_what_they_cannot_take():
     x = torch.zeros(2, 8, device=DEV)
     with pytest.raises(ops.KernelError):
