@@ -55,6 +55,17 @@ struct GemmArgs {
   int tokens, N, K, ldo;
   int dual_offset;         // DUAL: row distance between the two weight tiles
   int splits;
+  // NORM (decode form): the activation operand is rmsnorm(norm_x) * norm_w, made on the fly from the
+  // fp32 rows norm_x [tokens, K]; a row's sum of squares is the sum of its norm_n_parts pieces in
+  // norm_parts [norm_n_parts, tokens].
+  const float* norm_x;
+  const float* norm_w;
+  const float* norm_parts;
+  int norm_n_parts;
+  float norm_eps;
+  // EPI_RESIDUAL (decode form): when not null, the sums of squares of the rows it leaves, one piece
+  // per tile of 128 features: sumsq_out [ceil(N / 128), tokens].
+  float* sumsq_out;
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -66,6 +77,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -171,15 +185,18 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 
 // Features on the lanes (decode form): one value per call; the 32 lanes of a warp write 32
 // consecutive features of one token.
+// Returns what it left in `out` for EPI_RESIDUAL (0 outside the matrix), else 0.
 template <int EPI>
-__device__ __forceinline__ void emit(const GemmArgs& a, int token, int n, float v, float v2) {
-  if (token >= a.tokens || n >= a.N) return;
+__device__ __forceinline__ float emit(const GemmArgs& a, int token, int n, float v, float v2) {
+  if (token >= a.tokens || n >= a.N) return 0.f;
   const size_t at = (size_t)token * a.ldo + n;
   if (EPI == EPI_STORE_BF16) ((bf16*)a.out)[at] = __float2bfloat16_rn(v);
   else if (EPI == EPI_STORE_F32) ((float*)a.out)[at] = v;
-  else if (EPI == EPI_RESIDUAL) ((float*)a.out)[at] += v;
+  else if (EPI == EPI_RESIDUAL) { const float r = ((float*)a.out)[at] + v; ((float*)a.out)[at] = r; return r; }
   else ((bf16*)a.out)[at] = __float2bfloat16_rn(silu_f(v) * v2);
+  return 0.f;
 }
+
 
 // Tokens on the lanes (prefill form): a thread holds 16 consecutive features of its token
 // and writes them with 16-byte stores when the row is aligned for that.
@@ -223,7 +240,11 @@ __device__ __forceinline__ void emit_row16(const GemmArgs& a, int token, int n, 
 
 // SWAP = false: the 128 lanes are features (weight rows), the BN columns are tokens.
 // SWAP = true : the 128 lanes are tokens, the BN columns are features.
-template <int BN, bool DUAL, int EPI, int STAGES, bool SWAP, bool CLUSTER>
+// NORM (decode form only): the four epilogue warps first serve as converters: for every k-block they
+// read the fp32 rows, scale them by the row's 1/rms and the norm weight with the roundings of the
+// stand-alone RMSNorm kernel, and write the bf16 operand tile in the swizzled layout that TMA would
+// have produced; the MMA thread waits for them (`ready`) as well as for the weight tile (`full`).
+template <int BN, bool DUAL, int EPI, int STAGES, bool SWAP, bool CLUSTER, bool NORM>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs a) {
@@ -237,10 +258,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+  static_assert(!NORM || (!SWAP && BN % 16 == 0 && BN <= 64), "the norm prologue belongs to the decode form");
+  __shared__ __align__(8) uint64_t bars[3 * STAGES + 1];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int ticket_slot;
+  __shared__ float sumsq_part[4][SWAP ? 1 : (BN <= 64 ? BN : 1)];    // per epilogue warp and token column
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok0 = blockIdx.x * (SWAP ? BM : BN), n0 = blockIdx.y * (SWAP ? BN : BM), split = blockIdx.z;
@@ -248,9 +271,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const int kb_begin = (int)((long)total_kb * split / a.splits);
   const int kb_count = (int)((long)total_kb * (split + 1) / a.splits) - kb_begin;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), acc_bar = smem_u32(&bars[2 * STAGES]);
+  const uint32_t ready0 = smem_u32(&bars[2 * STAGES + 1]);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); mbar_init(ready0 + 8 * s, 4); }
     mbar_init(acc_bar, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -271,18 +295,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // Weights are never written by a kernel, so in the decode form their first tiles are
       // requested before this grid waits for the kernels it depends on; only the activation
       // tiles (and everything the epilogue touches, which runs after them) come after the wait.
+      constexpr uint32_t TX_BYTES = NORM ? L_BYTES * L_TILES : STAGE_BYTES;   // NORM: the converters fill the rest
       const int pre = SWAP ? 0 : min(STAGES, kb_count);
       for (int i = 0; i < pre; ++i) {
         const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
         const int k0 = (kb_begin + i) * BK;
-        mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+        mbar_expect_tx(full0 + 8 * i, TX_BYTES);
         tma_load_2d(dst, map_l, k0, l_row, full0 + 8 * i);
         if (L_TILES == 2) tma_load_2d(dst + L_BYTES, map_l, k0, l_row + a.dual_offset, full0 + 8 * i);
       }
-      pdl_wait();
-      for (int i = 0; i < pre; ++i) {
-        const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
-        tma_load_2d(dst + L_BYTES * L_TILES, map_c, (kb_begin + i) * BK, c_row, full0 + 8 * i);
+      if (!NORM) {
+        pdl_wait();
+        for (int i = 0; i < pre; ++i) {
+          const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
+          tma_load_2d(dst + L_BYTES * L_TILES, map_c, (kb_begin + i) * BK, c_row, full0 + 8 * i);
+        }
       }
       for (int i = pre; i < kb_count; ++i) {
         const int s = i % STAGES;
@@ -290,10 +317,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_ptr)) { atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_PRODUCER); break; }
         const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
         const int k0 = (kb_begin + i) * BK;
-        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        mbar_expect_tx(full0 + 8 * s, TX_BYTES);
         tma_load_2d(dst, map_l, k0, l_row, full0 + 8 * s);
         if (L_TILES == 2) tma_load_2d(dst + L_BYTES, map_l, k0, l_row + a.dual_offset, full0 + 8 * s);
-        tma_load_2d(dst + L_BYTES * L_TILES, map_c, k0, c_row, full0 + 8 * s);
+        if (!NORM) tma_load_2d(dst + L_BYTES * L_TILES, map_c, k0, c_row, full0 + 8 * s);
         if (C_TILES == 2) tma_load_2d(dst + L_BYTES * L_TILES + C_BYTES, map_c, k0, c_row + a.dual_offset, full0 + 8 * s);
       }
     }
@@ -304,7 +331,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int i = 0; i < kb_count && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
-        if (!mbar_wait(full0 + 8 * s, phase, abort_ptr)) { atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_MMA); ok = false; break; }
+        if (!mbar_wait(full0 + 8 * s, phase, abort_ptr) || (NORM && !mbar_wait(ready0 + 8 * s, phase, abort_ptr))) {
+          atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_MMA); ok = false; break;
+        }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
         const uint64_t dl = smem_desc_k_sw128(sa);
@@ -328,6 +357,80 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int row = lane_group * 32 + lane;              // lane of the accumulator
     const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
     const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    if (NORM) {
+      constexpr int ITEMS = BN / 16;                  // token rows per thread: trow, trow + 16, ...
+      constexpr int WANT = ITEMS == 1 ? 4 : 2;        // k-blocks in flight per thread, as registers allow (three CTAs per SM)
+      constexpr int DEPTH = STAGES < WANT ? STAGES : WANT;
+      const int tid_c = threadIdx.x - 64, chunk = tid_c & 7, trow = tid_c >> 3;   // a 16-byte chunk of a 128-byte row
+      struct Piece { float4 g[2]; float4 x[ITEMS][2]; };
+      auto fetch_g = [&](Piece& pc, int i) {          // the norm weight: no kernel writes it
+        const int k = (kb_begin + i) * BK + chunk * 8;
+        const bool in = i < kb_count && k < a.K;      // K is a multiple of 8: a chunk is inside or outside
+        pc.g[0] = in ? *(const float4*)(a.norm_w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        pc.g[1] = in ? *(const float4*)(a.norm_w + k + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      };
+      Piece ring[DEPTH];
+#pragma unroll
+      for (int j = 0; j < DEPTH; ++j) fetch_g(ring[j], j);
+      pdl_wait();                                     // the rows and their sums of squares come from the kernel before
+      auto fetch_x = [&](Piece& pc, int i) {
+        const int k = (kb_begin + i) * BK + chunk * 8;
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+          const int token = tok0 + trow + 16 * it;
+          const bool in = i < kb_count && k < a.K && token < a.tokens;
+          const float* src = a.norm_x + (size_t)token * a.K + k;
+          pc.x[it][0] = in ? *(const float4*)src : make_float4(0.f, 0.f, 0.f, 0.f);
+          pc.x[it][1] = in ? *(const float4*)(src + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      };
+#pragma unroll
+      for (int j = 0; j < DEPTH; ++j) fetch_x(ring[j], j);     // in flight together with the sums below
+      float rstd[ITEMS];
+#pragma unroll
+      for (int it = 0; it < ITEMS; ++it) {
+        const int token = tok0 + trow + 16 * it;
+        float ss = 0.f;
+        if (token < a.tokens)
+          for (int p = chunk; p < a.norm_n_parts; p += 8) ss += a.norm_parts[(size_t)p * a.tokens + token];
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);    // the eight threads of a row are neighbours in a warp
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        rstd[it] = rsqrtf(ss / (float)a.K + a.norm_eps);
+      }
+      auto norm2 = [](float x0, float x1, float g0, float g1, float r) -> uint32_t {
+        // the stand-alone kernel's roundings: bf16(x / rms), then bf16(weight * that)
+        const float y0 = __bfloat162float(__float2bfloat16_rn(x0 * r)), y1 = __bfloat162float(__float2bfloat16_rn(x1 * r));
+        __nv_bfloat162 pr = __floats2bfloat162_rn(g0 * y0, g1 * y1);
+        return *(uint32_t*)&pr;
+      };
+      bool conv_ok = true;
+      for (int base = 0; base < kb_count && conv_ok; base += DEPTH) {
+#pragma unroll
+        for (int j = 0; j < DEPTH; ++j) {
+          const int i = base + j;
+          if (i >= kb_count) break;
+          const int s = i % STAGES;
+          if (i >= STAGES && !mbar_wait(empty0 + 8 * s, (((uint32_t)(i / STAGES) & 1u) ^ 1u), abort_ptr)) { conv_ok = false; break; }
+          const float4 g0 = ring[j].g[0], g1 = ring[j].g[1];
+          uint8_t* tile = smem + (size_t)s * STAGE_BYTES + L_BYTES * L_TILES;
+#pragma unroll
+          for (int it = 0; it < ITEMS; ++it) {
+            const int r = trow + 16 * it;
+            const float4 x0 = ring[j].x[it][0], x1 = ring[j].x[it][1];
+            const uint4 packed = make_uint4(norm2(x0.x, x0.y, g0.x, g0.y, rstd[it]), norm2(x0.z, x0.w, g0.z, g0.w, rstd[it]),
+                                            norm2(x1.x, x1.y, g1.x, g1.y, rstd[it]), norm2(x1.z, x1.w, g1.z, g1.w, rstd[it]));
+            *(uint4*)(tile + r * 128 + ((chunk ^ (r & 7)) << 4)) = packed;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the tensor core's reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(ready0 + 8 * s);
+          fetch_g(ring[j], i + DEPTH);                 // zeros past the end
+          fetch_x(ring[j], i + DEPTH);
+        }
+      }
+      if (!conv_ok && lane == 0) atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_EPILOGUE);
+    }
     bool ok = mbar_wait(acc_bar, 0, abort_ptr);
     if (!ok && lane == 0) atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_EPILOGUE);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -360,8 +463,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           for (int i = 0; i < 16; ++i)
             r[i] = (tok0 + c + i < a.tokens && n < a.N) ? ((const float*)a.out)[(size_t)(tok0 + c + i) * a.ldo + n] : 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (tok0 + c + i < a.tokens && n < a.N) ((float*)a.out)[(size_t)(tok0 + c + i) * a.ldo + n] = r[i] + v[i];
+          for (int i = 0; i < 16; ++i) {
+            const bool in = tok0 + c + i < a.tokens && n < a.N;
+            const float left = in ? r[i] + v[i] : 0.f;
+            if (in) ((float*)a.out)[(size_t)(tok0 + c + i) * a.ldo + n] = left;
+            if (a.sumsq_out != nullptr && BN <= 64) {
+              const float sq = warp_sum(left * left);
+              if (lane == 0) sumsq_part[lane_group][BN <= 64 ? c + i : 0] = sq;
+            }
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) emit<EPI>(a, tok0 + c + i, n, v[i], DUAL ? u[i] : 0.f);
@@ -437,23 +547,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (threadIdx.x == 64) a.tickets[tile_id] = 0;    // ready for the next launch
       }
     }
+    if (!SWAP && EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr && a.splits == 1) {
+      // every epilogue warp comes here, whatever happened above: the four warps' sums, in warp order
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int c = threadIdx.x - 64;
+      if (ok && c < BN && tok0 + c < a.tokens)
+        a.sumsq_out[(size_t)blockIdx.y * a.tokens + tok0 + c] =
+            sumsq_part[0][c] + sumsq_part[1][c] + sumsq_part[2][c] + sumsq_part[3][c];
+    }
     tc_fence_before();
   }
   if (CLUSTER && !SWAP && a.splits > 1) {
     // Every thread of every CTA of the cluster takes part in both barriers, whatever happened before.
     __syncwarp();
     cluster_sync_all();
-    if (warp >= 2 && !abort_flag) {
+    if (warp >= 2) {
+      const bool live = !abort_flag;            // nobody writes the flag any more: the same for all four warps
       const int row = (warp & 3) * 32 + lane, n = n0 + row;
       const float* red = (const float*)smem;
       const uint32_t rank = cluster_rank();
-      for (int c = (int)rank; c < BN && tok0 + c < a.tokens; c += a.splits) {   // the token columns this CTA owns
-        float v = 0.f, u = 0.f;
-        for (int p = 0; p < a.splits; ++p) {                                     // rank order: a fixed sum
-          v += ld_peer_f32(red + c * BM + row, (uint32_t)p);
-          if (DUAL) u += ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p);
+      const bool sums = EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr;
+      int slot = 0;
+      if (live)
+        for (int c = (int)rank; c < BN && tok0 + c < a.tokens; c += a.splits, ++slot) {   // the token columns this CTA owns
+          float v = 0.f, u = 0.f;
+          for (int p = 0; p < a.splits; ++p) {                                     // rank order: a fixed sum
+            v += ld_peer_f32(red + c * BM + row, (uint32_t)p);
+            if (DUAL) u += ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p);
+          }
+          const float left = emit<EPI>(a, tok0 + c, n, v, u);
+          if (sums) {
+            const float sq = warp_sum(left * left);
+            if (lane == 0) sumsq_part[warp & 3][BN <= 64 ? slot : 0] = sq;
+          }
         }
-        emit<EPI>(a, tok0 + c, n, v, u);
+      if (sums) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+        const int mine = threadIdx.x - 64, c = (int)rank + mine * a.splits;
+        if (live && mine < slot && c < BN && tok0 + c < a.tokens)
+          a.sumsq_out[(size_t)blockIdx.y * a.tokens + tok0 + c] =
+              sumsq_part[0][mine] + sumsq_part[1][mine] + sumsq_part[2][mine] + sumsq_part[3][mine];
       }
     }
     __syncwarp();
@@ -495,7 +628,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
 }
 
-template <int BN, bool DUAL, int EPI, bool SWAP, bool CLUSTER>
+template <int BN, bool DUAL, int EPI, bool SWAP, bool CLUSTER, bool NORM = false>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
   constexpr int STAGE_BYTES = BM * BK * 2 * ((DUAL && !SWAP) ? 2 : 1) + BN * BK * 2 * ((DUAL && SWAP) ? 2 : 1);
   // The decode form takes about 72 KB (four stages of a 128 x 16 tile), so that three CTAs fit on an
@@ -511,7 +644,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
   constexpr int STAGES = BUDGET / STAGE_BYTES < 2 ? 2 : (BUDGET / STAGE_BYTES > 12 ? 12 : BUDGET / STAGE_BYTES);
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
   static_assert(!CLUSTER || (DUAL ? 2 : 1) * BN * BM * 4 <= STAGES * STAGE_BYTES, "the split partial must fit the stage memory");
-  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, SWAP, CLUSTER>;
+  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, SWAP, CLUSTER, NORM>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -543,6 +676,14 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
 template <int BN, bool SWAP, bool CLUSTER>
 static int dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid,
                         cudaStream_t stream) {
+  if (a.norm_x != nullptr) {
+    // the norm prologue exists for the two products that follow a norm in a decoder layer, at decode widths
+    if constexpr (!SWAP && BN <= 32) {
+      if (epi == EPI_STORE_BF16) return launch<BN, false, EPI_STORE_BF16, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
+      if (epi == EPI_SWIGLU) return launch<BN, true, EPI_SWIGLU, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
+    }
+    return ODI_ERR_UNSUPPORTED;
+  }
   switch (epi) {
     case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, SWAP, CLUSTER>(mw, mx, a, grid, stream);
     case EPI_STORE_F32: return launch<BN, false, EPI_STORE_F32, SWAP, CLUSTER>(mw, mx, a, grid, stream);
@@ -568,9 +709,12 @@ extern "C" long odi_gemm_bf16_scratch_floats(int tokens, int n_out, int bn, int 
 // swap == 1 (prefill form): tiles of 128 tokens x bn features, bn in {64, 128, 256}, no splits.
 extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
                              int ldo, int epi, int bn, int splits, int swap, int cluster, float* scratch,
-                             int* tickets, int* status, cudaStream_t stream) {
+                             int* tickets, int* status, const float* norm_x, const float* norm_w,
+                             const float* norm_parts, int norm_n_parts, float norm_eps, float* sumsq_out,
+                             cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
+  if (x == nullptr && norm_x == nullptr) return ODI_ERR_ARGUMENT;
   const int total_kb = (K + BK - 1) / BK;
   if (splits < 1 || splits > total_kb || (swap && splits != 1)) return ODI_ERR_ARGUMENT;
   const bool clustered = cluster && splits > 1 && splits <= 8 && bn <= 64 && !swap;
@@ -581,11 +725,19 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   CUtensorMap mw, mx;
   int rc = make_map(&mw, w, w_rows, K, swap ? bn : BM);
   if (rc != 0) return rc;
-  rc = make_map(&mx, x, tokens, K, swap ? BM : bn);
+  rc = make_map(&mx, norm_x != nullptr ? w : x, tokens, K, swap ? BM : bn);    // with the norm prologue the map is not used
   if (rc != 0) return rc;
   GemmArgs a;
   a.out = out; a.scratch = scratch; a.tickets = tickets; a.status = status;
   a.tokens = tokens; a.N = n_out; a.K = K; a.ldo = ldo; a.dual_offset = dual ? n_out : 0; a.splits = splits;
+  if (norm_x != nullptr) {
+    if (swap || bn > 32 || (epi != EPI_STORE_BF16 && epi != EPI_SWIGLU)) return ODI_ERR_UNSUPPORTED;
+    if (norm_w == nullptr || norm_parts == nullptr || norm_n_parts < 1) return ODI_ERR_ARGUMENT;
+    if (((uintptr_t)norm_x & 15) || ((uintptr_t)norm_w & 15)) return ODI_ERR_UNSUPPORTED;
+  }
+  if (sumsq_out != nullptr && (epi != EPI_RESIDUAL || swap || bn > 64 || !(clustered || splits == 1))) return ODI_ERR_UNSUPPORTED;
+  a.norm_x = norm_x; a.norm_w = norm_w; a.norm_parts = norm_parts; a.norm_n_parts = norm_n_parts; a.norm_eps = norm_eps;
+  a.sumsq_out = sumsq_out;
   const int tok_tile = swap ? BM : bn, n_tile = swap ? bn : BM;
   dim3 grid((tokens + tok_tile - 1) / tok_tile, (n_out + n_tile - 1) / n_tile, splits);
   if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;

@@ -103,6 +103,7 @@ class DecoderModel:
         """Run the step described by ``ctx``; return fp32 logits at ``ctx.want_rows``."""
         hidden = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.runtime.device)
         ops.embed(self.embedding, ctx.token_ids, hidden)
+        ctx.residual_sumsq = None          # nothing is known about the rows of `hidden` yet
         for index, entry in enumerate(self.plan.order):
             self.layers[entry.layer].forward(hidden, ctx, cache.view(index))
         if ctx.n_want == 0:

@@ -277,24 +277,65 @@ def gemm_bf16_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     return K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, swap: Optional[bool] = None,
-              bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True) -> None:
+def gemm_bf16_sumsq_parts(n_out: int) -> int:
+    """Rows of the ``sumsq_out`` a residual product over ``n_out`` features fills: one per tile of 128."""
+    return -(-n_out // 128)
+
+
+def gemm_bf16_fuses_norm(tokens: int, n_out: int, K: int, epi: int) -> bool:
+    """Whether the planned form of this product can take its operand through the norm prologue."""
+    swap, bn, _ = gemm_bf16_plan(tokens, n_out, K, epi)
+    return not swap and bn <= 32 and epi in (EPI_STORE_BF16, EPI_SWIGLU)
+
+
+def gemm_bf16_gives_sumsq(tokens: int, n_out: int, K: int) -> bool:
+    """Whether the planned form of this residual product can leave the rows' sums of squares."""
+    swap, bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_RESIDUAL)
+    return not swap and bn <= 64 and splits <= 8
+
+
+def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, epi: int, *, swap: Optional[bool] = None,
+              bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True,
+              norm: Optional[tuple] = None, sumsq_out: Optional[torch.Tensor] = None) -> None:
     """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
 
     ``EPI_STORE_BF16`` / ``EPI_STORE_F32``: out [tokens, rows]; ``EPI_RESIDUAL``: out (fp32) += product;
     ``EPI_SWIGLU``: w holds the gate rows then the up rows, out [tokens, rows / 2] = silu(gate) * up.
     ``cluster``: let 2..8 K splits exchange their partials inside a thread-block cluster (else, and for
     more splits, through global scratch and a ticket).
+    ``norm = (rows, weight, parts, eps)`` instead of ``x``: the operand is RMSNorm(rows) * weight with the
+    roundings of :func:`rmsnorm`, made inside the kernel from the fp32 ``rows`` [tokens, K]; ``parts``
+    [pieces, tokens] holds sums of squares of pieces of each row (what ``sumsq_out`` of the product that
+    wrote the rows received).  Decode form only (``gemm_bf16_fuses_norm``).
+    ``sumsq_out`` (fp32 [gemm_bf16_sumsq_parts(features), tokens]) with ``EPI_RESIDUAL``: receives, per tile
+    of 128 features, the sums of squares of the rows the product leaves in ``out``.
     """
-    _require(x, "x", torch.bfloat16, 2)
+    if norm is not None:
+        if x is not None:
+            raise KernelError("gemm_bf16 takes either x or norm")
+        rows, norm_w, parts, eps = norm
+        _require(rows, "norm rows", torch.float32, 2)
+        _require(norm_w, "norm weight", torch.float32, 1)
+        _require(parts, "norm parts", torch.float32, 2)
+        if norm_w.numel() != rows.shape[1] or parts.shape[1] != rows.shape[0]:
+            raise KernelError(f"norm operands disagree: rows {tuple(rows.shape)}, weight {tuple(norm_w.shape)}, "
+                              f"parts {tuple(parts.shape)}")
+        x_like = rows
+    else:
+        _require(x, "x", torch.bfloat16, 2)
+        x_like = x
     _require(w, "w", torch.bfloat16, 2)
     _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
-    tokens, K = x.shape
-    rows = w.shape[0]
-    n_out = rows // 2 if epi == EPI_SWIGLU else rows
-    if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and rows % 2):
-        raise KernelError(f"gemm sizes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    if not gemm_bf16_supported(x, w):
+    tokens, K = x_like.shape
+    w_rows = w.shape[0]
+    n_out = w_rows // 2 if epi == EPI_SWIGLU else w_rows
+    if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
+        raise KernelError(f"gemm sizes disagree: x {tuple(x_like.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if sumsq_out is not None:
+        _require(sumsq_out, "sumsq_out", torch.float32, 2)
+        if epi != EPI_RESIDUAL or sumsq_out.shape != (gemm_bf16_sumsq_parts(n_out), tokens):
+            raise KernelError("sumsq_out goes with EPI_RESIDUAL and has one row per tile of 128 features")
+    if not gemm_bf16_supported(x_like, w):
         raise KernelError(f"gemm_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
     plan_swap, plan_bn, plan_splits = gemm_bf16_plan(tokens, n_out, K, epi)
     swap = plan_swap if swap is None else swap
@@ -305,12 +346,17 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, *, 
     need = lib.odi_gemm_bf16_scratch_floats(c_int(tokens), c_int(n_out), c_int(bn), c_int(splits),
                                             c_int(1 if epi == EPI_SWIGLU else 0))
     tiles = -(-n_out // 128) * -(-tokens // bn)
-    scratch, tickets, status = _gemm_buffers(x.device, need if not swap else 0)
+    scratch, tickets, status = _gemm_buffers(w.device, need if not swap else 0)
     if splits > 1 and tiles > tickets.numel():
         raise KernelError("too many tiles for a split product")
-    _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(rows),
+    if norm is not None:
+        norm_args = (_ptr(norm[0]), _ptr(norm[1]), _ptr(norm[2]), c_int(norm[2].shape[0]), c_float(norm[3]))
+    else:
+        norm_args = (_ptr(None), _ptr(None), _ptr(None), c_int(0), c_float(0.0))
+    _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
                              c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if swap else 0),
-                             c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), _stream()),
+                             c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
+                             _ptr(sumsq_out), _stream()),
            "gemm_tcgen05")
 
 

@@ -27,6 +27,7 @@ TCGEN05_MIN_Q_LEN = 16     # shorter chunks fill too little of a 128-row tile
 
 class Attention(Part):
     graph_safe = True   # no host work that depends on the step's values: may be captured in a CUDA graph
+    takes_lazy_norm = True   # x may be a NormedRows: its first product makes the normed operand itself
 
     def __init__(self, spec: AttentionSpec) -> None:
         super().__init__(spec)
@@ -82,7 +83,7 @@ class Attention(Part):
                       eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0)
         o = torch.empty_like(q)
         self.attend(q, o, ctx, view, page_start, page_ids)
-        linear(o, self.w_o, residual=residual)
+        linear(o, self.w_o, residual=residual, track=ctx)
 
     def attend(self, q, o, ctx, view, page_start, page_ids) -> None:
         """bf16 without a window: the tensor-core kernels -- tcgen05 flash attention for steps that

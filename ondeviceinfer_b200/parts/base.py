@@ -32,6 +32,14 @@ On top of that each kind of part has one call:
                residual stream in place; owns the arrangement of norms, mixer and
                feed-forward.
 
+Optional, for speed only (a part that knows nothing of it loses nothing but a fusion): a mixer or
+feed-forward that ends with ``linear(..., residual=residual, track=ctx)`` lets that product leave the
+sums of squares of the rows it wrote (``ctx.residual_sumsq``); the block then gives the next part, if
+it says ``takes_lazy_norm = True`` and the norm has ``lazy(x, parts)``, a
+:class:`~ondeviceinfer_b200.parts.linear.NormedRows` instead of a tensor, which ``linear`` and
+``gated_linear`` turn into the normed operand inside the tensor-core kernel (``.materialize()`` gives
+the tensor).  A part that passes ``track`` must not touch ``residual`` after that product.
+
 Parts are chosen by the *type* of their spec.  ``register_part(SpecType, PartClass)``
 adds a kind; nothing else in the library has to change for it.
 """

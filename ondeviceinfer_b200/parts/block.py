@@ -34,9 +34,19 @@ class PreNormBlock(Part):
     def graph_safe(self) -> bool:
         return all(getattr(part, "graph_safe", False) for part in self._children())
 
+    @staticmethod
+    def _normed(norm, consumer, hidden, ctx):
+        """norm(hidden); left to the consumer's first product when the product that wrote ``hidden``
+        has left the rows' sums of squares in ``ctx.residual_sumsq`` and both sides know how."""
+        known = getattr(ctx, "residual_sumsq", None)
+        ctx.residual_sumsq = None
+        if known is not None and known[0] is hidden and hasattr(norm, "lazy") and getattr(consumer, "takes_lazy_norm", False):
+            return norm.lazy(hidden, known[1])
+        return norm(hidden)
+
     def forward(self, hidden, ctx, view) -> None:
-        self.mixer.forward(self.mixer_norm(hidden), ctx, view, hidden)
-        self.ffn.forward(self.ffn_norm(hidden), ctx, hidden)
+        self.mixer.forward(self._normed(self.mixer_norm, self.mixer, hidden, ctx), ctx, view, hidden)
+        self.ffn.forward(self._normed(self.ffn_norm, self.ffn, hidden, ctx), ctx, hidden)
 
 
 register_part(PreNormBlockSpec, PreNormBlock)

@@ -30,19 +30,68 @@ import os
 OWN_KERNEL_MAX_TOKENS = int(os.environ.get("ODI_OWN_GEMM_MAX_TOKENS", "32"))
 
 
-def _own(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    return x.shape[0] <= OWN_KERNEL_MAX_TOKENS and ops.gemm_bf16_supported(x, weight)
+class NormedRows:
+    """``RMSNorm(rows) * weight`` that has not been computed yet.
+
+    A norm part may hand this to the part after it instead of a tensor when the sums of squares of
+    the rows are already known (``parts`` [pieces, tokens]: the product that wrote the rows left
+    them).  :func:`linear` and :func:`gated_linear` then make the normed operand inside the
+    tensor-core kernel, which saves a kernel and a round trip of the activations; ``materialize()``
+    gives the ordinary tensor (the stand-alone norm kernel) to anybody else.
+    """
+
+    def __init__(self, rows: torch.Tensor, weight: torch.Tensor, eps: float, parts: torch.Tensor,
+                 dtype: torch.dtype) -> None:
+        self.rows, self.weight, self.eps, self.parts, self.dtype = rows, weight, eps, parts, dtype
+        self._tensor: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def device(self):
+        return self.rows.device
+
+    def materialize(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = torch.empty(self.rows.shape, dtype=self.dtype, device=self.rows.device)
+            ops.rmsnorm(self.rows, self.weight, self.eps, self._tensor)
+        return self._tensor
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
-    """``x`` [tokens, in], ``weight`` [out, in].
+def _own(x, weight: torch.Tensor) -> bool:
+    like = x.rows if isinstance(x, NormedRows) else x
+    return x.shape[0] <= OWN_KERNEL_MAX_TOKENS and ops.gemm_bf16_supported(like, weight)
+
+
+def _operand(x, weight: torch.Tensor, n_out: int, epi: int):
+    """(x, norm) for ops.gemm_bf16: a lazy norm goes into the kernel if its planned form can take it."""
+    if not isinstance(x, NormedRows):
+        return x, None
+    if ops.gemm_bf16_fuses_norm(x.shape[0], n_out, weight.shape[1], epi):
+        return None, (x.rows, x.weight, x.parts, x.eps)
+    return x.materialize(), None
+
+
+def linear(x, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, track=None) -> Optional[torch.Tensor]:
+    """``x`` [tokens, in] (a tensor or :class:`NormedRows`), ``weight`` [out, in].
 
     With ``residual`` (fp32 [tokens, out]) the product is added to it in place and
     nothing is returned; otherwise a new [tokens, out] tensor in ``out_dtype`` (default:
     the dtype of ``x``) is returned.
+
+    ``track`` (the step context) with ``residual``: if the kernel can, it also leaves the sums of
+    squares of the rows it wrote, and ``track.residual_sumsq = (residual, parts)`` says so to the
+    next norm; otherwise ``track.residual_sumsq`` is set to None.  Whoever passes ``track`` promises
+    not to change ``residual`` afterwards.
     """
     n, N = x.shape[0], weight.shape[0]
+    if track is not None:
+        track.residual_sumsq = None
+    if isinstance(x, NormedRows) and not (x.dtype == torch.bfloat16 and _own(x, weight)):
+        x = x.materialize()
     if x.dtype == torch.float32:
         if residual is not None:
             ops.gemm_f32(x, weight, residual, residual)
@@ -54,11 +103,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, residual: Optional[torch.Te
         raise ops.KernelError(f"linear takes float32 or bfloat16 activations, not {x.dtype}")
     if _own(x, weight):
         if residual is not None:
-            ops.gemm_bf16(x, weight, residual, ops.EPI_RESIDUAL)
+            x, norm = _operand(x, weight, N, ops.EPI_RESIDUAL)
+            parts = None
+            if track is not None and ops.gemm_bf16_gives_sumsq(n, N, weight.shape[1]):
+                parts = torch.empty((ops.gemm_bf16_sumsq_parts(N), n), dtype=torch.float32, device=residual.device)
+            ops.gemm_bf16(x, weight, residual, ops.EPI_RESIDUAL, norm=norm, sumsq_out=parts)
+            if parts is not None:
+                track.residual_sumsq = (residual, parts)
             return None
         wide = out_dtype == torch.float32
-        out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
-        ops.gemm_bf16(x, weight, out, ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16)
+        epi = ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16
+        x, norm = _operand(x, weight, N, epi)
+        out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=weight.device)
+        ops.gemm_bf16(x, weight, out, epi, norm=norm)
         return out
     y = torch.matmul(x, weight.t())
     ops.LAUNCHES["library"] += 1
@@ -72,12 +129,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, residual: Optional[torch.Te
     return y
 
 
-def gated_linear(x: torch.Tensor, weight_gate_up: torch.Tensor) -> torch.Tensor:
+def gated_linear(x, weight_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for ``weight_gate_up`` = gate rows followed by up rows."""
     n, I = x.shape[0], weight_gate_up.shape[0] // 2
     act = torch.empty((n, I), dtype=x.dtype, device=x.device)
     if x.dtype == torch.bfloat16 and _own(x, weight_gate_up):
-        ops.gemm_bf16(x, weight_gate_up, act, ops.EPI_SWIGLU)
+        x, norm = _operand(x, weight_gate_up, I, ops.EPI_SWIGLU)
+        ops.gemm_bf16(x, weight_gate_up, act, ops.EPI_SWIGLU, norm=norm)
         return act
+    if isinstance(x, NormedRows):
+        x = x.materialize()
     ops.silu_mul(linear(x, weight_gate_up), act)
     return act

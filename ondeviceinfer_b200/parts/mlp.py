@@ -12,6 +12,7 @@ from .linear import gated_linear, linear
 
 class GatedMLP(Part):
     graph_safe = True   # no host work that depends on the step's values: may be captured in a CUDA graph
+    takes_lazy_norm = True   # x may be a NormedRows: its first product makes the normed operand itself
 
     """down(silu(gate(x)) * up(x)).  The gate and up matrices are concatenated at load so
     that one matrix product yields both; the activation is taken in fp32 and rounded once."""
@@ -34,7 +35,7 @@ class GatedMLP(Part):
         self.w_down = fetch.matrix(s.name("down"))
 
     def forward(self, x, ctx, residual) -> None:
-        linear(gated_linear(x, self.w_gate_up), self.w_down, residual=residual)
+        linear(gated_linear(x, self.w_gate_up), self.w_down, residual=residual, track=ctx)
 
 
 register_part(GatedMLPSpec, GatedMLP)

@@ -8,6 +8,7 @@ from ..config.specs import RMSNormSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, register_part
+from .linear import NormedRows
 
 
 class RMSNorm(Part):
@@ -22,6 +23,12 @@ class RMSNorm(Part):
     def load(self, fetch, runtime) -> None:
         self.runtime = runtime
         self.weight = fetch.vector(self.spec.weight_name)
+
+    def lazy(self, x: torch.Tensor, parts: torch.Tensor):
+        """The norm of the whole of ``x`` as a :class:`~ondeviceinfer_b200.parts.linear.NormedRows`:
+        ``parts`` [pieces, tokens] are sums of squares of pieces of each row, left by the product that
+        wrote ``x``.  For a consumer that says ``takes_lazy_norm``."""
+        return NormedRows(x, self.weight, self.spec.eps, parts, self.runtime.dtype)
 
     def __call__(self, x: torch.Tensor, rows=None) -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.numel()

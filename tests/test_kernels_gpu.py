@@ -431,6 +431,60 @@ def test_gemm_tcgen05(tokens, N, K, swap, tile, splits, epi):
         assert torch.equal(again, out)
 
 
+NORM_GEMM_SHAPES = [
+    # tokens, hidden (the normed rows' width), features of the product that consumes them, tile, splits
+    (8, 4096, 6144, None, None), (1, 200, 389, None, None), (16, 1000, 520, 16, 1), (5, 136, 256, 16, 2),
+    (32, 4096, 1024, None, None), (20, 520, 640, 32, 3), (3, 64, 128, 16, 1),
+]
+
+
+@pytest.mark.parametrize("gated", [False, True])
+@pytest.mark.parametrize("tokens,H,N,tile,splits", NORM_GEMM_SHAPES)
+def test_gemm_tcgen05_norm_prologue_and_sums_of_squares(tokens, H, N, tile, splits, gated):
+    """A residual product that leaves the sums of squares of its rows, then a product that takes those
+    rows through the fused RMSNorm: against the stand-alone norm kernel followed by the plain product
+    (same roundings, so nearly the same bits) and against fp32 torch."""
+    torch.manual_seed(21)
+    K0 = 192
+    a = torch.randn(tokens, K0).bfloat16().to(DEV)
+    w0 = (torch.randn(H, K0) / math.sqrt(K0)).bfloat16().to(DEV)
+    rows = (torch.randn(tokens, H) * 3).to(DEV)
+    start = rows.clone()
+    parts = torch.full((ops.gemm_bf16_sumsq_parts(H), tokens), float("nan"), device=DEV)
+    assert ops.gemm_bf16_gives_sumsq(tokens, H, K0)
+    ops.gemm_bf16(a, w0, rows, ops.EPI_RESIDUAL, sumsq_out=parts)
+    torch.cuda.synchronize()
+    expected_rows = start.cpu() + a.float().cpu() @ w0.float().cpu().t()
+    assert torch.allclose(rows.cpu(), expected_rows, atol=1e-4, rtol=1e-4)
+    padded = torch.zeros(tokens, parts.shape[0] * 128)
+    padded[:, :H] = rows.cpu()
+    expected_parts = (padded.view(tokens, -1, 128) ** 2).sum(-1).t()
+    assert torch.allclose(parts.cpu(), expected_parts, rtol=1e-5, atol=1e-6), float((parts.cpu() - expected_parts).abs().max())
+
+    g = (1.0 + 0.2 * torch.randn(H)).to(DEV)
+    eps = 1e-5
+    w_rows = 2 * N if gated else N
+    w = (torch.randn(w_rows, H) / math.sqrt(H)).bfloat16().to(DEV)
+    epi = ops.EPI_SWIGLU if gated else ops.EPI_STORE_BF16
+    fused = torch.empty(tokens, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16(None, w, fused, epi, bn=tile, splits=splits, norm=(rows, g, parts, eps))
+    normed = torch.empty(tokens, H, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(rows, g, eps, normed)
+    plain_way = torch.empty_like(fused)
+    ops.gemm_bf16(normed, w, plain_way, epi, bn=tile, splits=splits)
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    # the two ways differ only where 1/rms, summed in another order, moves a value across a rounding step
+    differ = (fused.float() - plain_way.float()).abs()
+    scale = plain_way.float().abs().max().item()
+    assert float(differ.max()) <= 0.02 * scale and float((differ > 0).float().mean()) < 0.05, (float(differ.max()), scale)
+    r = rows.cpu()
+    y = (r * torch.rsqrt((r * r).mean(-1, keepdim=True) + eps)).bfloat16().float() * g.cpu()
+    ref = y.bfloat16().float() @ w.float().cpu().t()
+    expected = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:] if gated else ref
+    close(fused, expected, "bfloat16")
+
+
 def test_gemm_tcgen05_refuses_unaligned_k():
     x = torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)
