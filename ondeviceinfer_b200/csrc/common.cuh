@@ -103,6 +103,25 @@ static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return odi_rc != 0 ? odi_rc : (int)e;      // keep the first error of a launcher
 }
 
+// Arguments of the fused head preparation (elementwise.cu; also the epilogue of the tensor-core
+// product that makes the projections).
+struct HeadPrepArgs {
+  const void* qkv;
+  void* q_out;
+  void* k_pool;
+  void* v_pool;
+  const float* q_norm_w;  // null: no norm
+  const float* k_norm_w;
+  const float* cos_t;     // null: no rotation; [n_tokens, rot_dim / 2]
+  const float* sin_t;
+  const int* tok_seq;
+  const int* tok_pos;
+  const int* page_start;
+  const int* page_ids;
+  int n_tokens, nq, nkv, d, rot_dim, page_size, ring_pages, write_kv;
+  float eps;
+};
+
 // Position of key `pos` inside a sequence's page list.  A group that keeps every key
 // has ring_pages == 0; a windowed group keeps a ring of ring_pages pages per sequence.
 __device__ __forceinline__ int page_slot_of(int pos, int page_size, int ring_pages) {

@@ -128,23 +128,6 @@ extern "C" int odi_rmsnorm(const float* x, const float* w, void* out, const int*
 // Cache layout: pool[page][kv_head][row][d], row = position % page_size.
 // write_kv == 0 skips the key/value heads (a layer that reads another layer's cache).
 // ---------------------------------------------------------------------------------
-struct HeadPrepArgs {
-  const void* qkv;
-  void* q_out;
-  void* k_pool;
-  void* v_pool;
-  const float* q_norm_w;  // null: no norm
-  const float* k_norm_w;
-  const float* cos_t;     // null: no rotation; [n_tokens, rot_dim / 2]
-  const float* sin_t;
-  const int* tok_seq;
-  const int* tok_pos;
-  const int* page_start;
-  const int* page_ids;
-  int n_tokens, nq, nkv, d, rot_dim, page_size, ring_pages, write_kv;
-  float eps;
-};
-
 template <typename T, int MAXP>
 __global__ void head_prep_kernel(HeadPrepArgs a) {
   pdl_launch_dependents();

@@ -37,6 +37,7 @@
 #define EPI_STORE_F32 1    // out_f32[token, n] = acc
 #define EPI_RESIDUAL 2     // out_f32[token, n] += acc
 #define EPI_SWIGLU 3       // out_bf16[token, n] = silu(acc_gate) * acc_up   (DUAL)
+#define EPI_HEAD_PREP 4    // the rows are q, k and v heads of 128: per-head norm, rotation, cache write (decode form)
 
 #define BM 128             // features per tile (UMMA M)
 #define BK 64              // k per stage: 64 bf16 = one 128-byte swizzle row
@@ -66,6 +67,9 @@ struct GemmArgs {
   // EPI_RESIDUAL (decode form): when not null, the sums of squares of the rows it leaves, one piece
   // per tile of 128 features: sumsq_out [ceil(N / 128), tokens].
   float* sumsq_out;
+  // EPI_HEAD_PREP: a tile of 128 features is one head (query heads, then key heads, then value heads);
+  // what the stand-alone head preparation would do with the bf16 projections happens in the epilogue.
+  HeadPrepArgs hp;
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -181,6 +185,49 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
+// One warp finishes one head of one token: `vals` holds the head's 128 projections (already rounded
+// to bf16), lane i takes elements 4i .. 4i+3, whose rotation partners sit in lane i ^ 16.  The
+// arithmetic, its order and its roundings are those of head_prep_vec_kernel<4> (elementwise.cu).
+__device__ __forceinline__ void head_prep_finish(const HeadPrepArgs& hp, int t, int h, const float* vals, int lane) {
+  constexpr int d = 128, half = 64;
+  const int kind = h < hp.nq ? 0 : (h < hp.nq + hp.nkv ? 1 : 2);     // 0 q, 1 k, 2 v
+  const int pos = hp.tok_pos[t];
+  bf16* dst;
+  if (kind == 0) {
+    dst = (bf16*)hp.q_out + ((size_t)t * hp.nq + h) * d;
+  } else {
+    const int hk = kind == 1 ? h - hp.nq : h - hp.nq - hp.nkv;
+    const int page = hp.page_ids[hp.page_start[hp.tok_seq[t]] + page_slot_of(pos, hp.page_size, hp.ring_pages)];
+    bf16* pool = (bf16*)(kind == 1 ? hp.k_pool : hp.v_pool);
+    dst = pool + (((size_t)page * hp.nkv + hk) * hp.page_size + (pos % hp.page_size)) * d;
+  }
+  const float4 in = *(const float4*)(vals + 4 * lane);
+  float x[4] = {in.x, in.y, in.z, in.w};
+  if (kind != 2) {
+    const float* w = kind == 0 ? hp.q_norm_w : hp.k_norm_w;
+    if (w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) ss += x[r] * x[r];
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)d + hp.eps);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) x[r] = round_to<bf16>(w[4 * lane + r] * round_to<bf16>(x[r] * inv));
+    }
+    if (hp.cos_t != nullptr) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i = 4 * lane + r, f = i < half ? i : i - half;
+        const float cs = hp.cos_t[(size_t)t * half + f], sn = hp.sin_t[(size_t)t * half + f];
+        const float partner = __shfl_xor_sync(0xffffffffu, x[r], 16);
+        x[r] = x[r] * cs + (i < half ? -partner : partner) * sn;
+      }
+    }
+  }
+  __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+  *(uint2*)(dst + 4 * lane) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+}
+
 // ------------------------------------------------------------------------------ the kernel
 
 // Features on the lanes (decode form): one value per call; the 32 lanes of a warp write 32
@@ -193,7 +240,7 @@ __device__ __forceinline__ float emit(const GemmArgs& a, int token, int n, float
   if (EPI == EPI_STORE_BF16) ((bf16*)a.out)[at] = __float2bfloat16_rn(v);
   else if (EPI == EPI_STORE_F32) ((float*)a.out)[at] = v;
   else if (EPI == EPI_RESIDUAL) { const float r = ((float*)a.out)[at] + v; ((float*)a.out)[at] = r; return r; }
-  else ((bf16*)a.out)[at] = __float2bfloat16_rn(silu_f(v) * v2);
+  else if (EPI == EPI_SWIGLU) ((bf16*)a.out)[at] = __float2bfloat16_rn(silu_f(v) * v2);
   return 0.f;
 }
 
@@ -259,6 +306,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   static_assert(!NORM || (!SWAP && BN % 16 == 0 && BN <= 64), "the norm prologue belongs to the decode form");
+  // EPI_HEAD_PREP stages the finished rows behind the split partials (which peers may still be reading)
+  constexpr int HP_STAGE_OFFSET = BN * BM * 4;
+  static_assert(EPI != EPI_HEAD_PREP || (!SWAP && !DUAL && BN <= 64 && 2 * BN * BM * 4 <= STAGES * STAGE_BYTES),
+                "the head-preparation epilogue belongs to the decode form");
   __shared__ __align__(8) uint64_t bars[3 * STAGES + 1];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -472,6 +523,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               if (lane == 0) sumsq_part[lane_group][BN <= 64 ? c + i : 0] = sq;
             }
           }
+        } else if (EPI == EPI_HEAD_PREP) {
+          float* stage = (float*)(smem + HP_STAGE_OFFSET);       // [token column][128]; every MMA has completed
+#pragma unroll
+          for (int i = 0; i < 16; ++i) stage[(c + i) * BM + row] = round_to<bf16>(v[i]);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) emit<EPI>(a, tok0 + c + i, n, v[i], DUAL ? u[i] : 0.f);
@@ -547,6 +602,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (threadIdx.x == 64) a.tickets[tile_id] = 0;    // ready for the next launch
       }
     }
+    if (!SWAP && EPI == EPI_HEAD_PREP && a.splits == 1) {
+      // every epilogue warp comes here, whatever happened above; then a warp per token column
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const float* stage = (const float*)(smem + HP_STAGE_OFFSET);
+      if (ok)
+        for (int c = lane_group; c < BN && tok0 + c < a.tokens; c += 4)
+          head_prep_finish(a.hp, tok0 + c, blockIdx.y, stage + c * BM, lane);
+    }
     if (!SWAP && EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr && a.splits == 1) {
       // every epilogue warp comes here, whatever happened above: the four warps' sums, in warp order
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -575,12 +638,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             v += ld_peer_f32(red + c * BM + row, (uint32_t)p);
             if (DUAL) u += ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p);
           }
+          if (EPI == EPI_HEAD_PREP) ((float*)(smem + HP_STAGE_OFFSET))[slot * BM + row] = round_to<bf16>(v);
           const float left = emit<EPI>(a, tok0 + c, n, v, u);
           if (sums) {
             const float sq = warp_sum(left * left);
             if (lane == 0) sumsq_part[warp & 3][BN <= 64 ? slot : 0] = sq;
           }
         }
+      if (EPI == EPI_HEAD_PREP) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps: the owned columns are staged
+        if (live)
+          for (int sl = warp & 3; sl < slot; sl += 4)       // a warp per owned token column
+            head_prep_finish(a.hp, tok0 + (int)rank + sl * a.splits, blockIdx.y, (const float*)(smem + HP_STAGE_OFFSET) + sl * BM, lane);
+      }
       if (sums) {
         asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
         const int mine = threadIdx.x - 64, c = (int)rank + mine * a.splits;
@@ -681,8 +751,13 @@ static int dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx, c
     if constexpr (!SWAP && BN <= 32) {
       if (epi == EPI_STORE_BF16) return launch<BN, false, EPI_STORE_BF16, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
       if (epi == EPI_SWIGLU) return launch<BN, true, EPI_SWIGLU, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
+      if (epi == EPI_HEAD_PREP) return launch<BN, false, EPI_HEAD_PREP, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
     }
     return ODI_ERR_UNSUPPORTED;
+  }
+  if (epi == EPI_HEAD_PREP) {
+    if constexpr (!SWAP && BN <= 32) return launch<BN, false, EPI_HEAD_PREP, SWAP, CLUSTER>(mw, mx, a, grid, stream);
+    else return ODI_ERR_UNSUPPORTED;
   }
   switch (epi) {
     case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, SWAP, CLUSTER>(mw, mx, a, grid, stream);
@@ -711,7 +786,7 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
                              int ldo, int epi, int bn, int splits, int swap, int cluster, float* scratch,
                              int* tickets, int* status, const float* norm_x, const float* norm_w,
                              const float* norm_parts, int norm_n_parts, float norm_eps, float* sumsq_out,
-                             cudaStream_t stream) {
+                             const HeadPrepArgs* head_prep, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
   if (x == nullptr && norm_x == nullptr) return ODI_ERR_ARGUMENT;
@@ -731,13 +806,24 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   a.out = out; a.scratch = scratch; a.tickets = tickets; a.status = status;
   a.tokens = tokens; a.N = n_out; a.K = K; a.ldo = ldo; a.dual_offset = dual ? n_out : 0; a.splits = splits;
   if (norm_x != nullptr) {
-    if (swap || bn > 32 || (epi != EPI_STORE_BF16 && epi != EPI_SWIGLU)) return ODI_ERR_UNSUPPORTED;
+    if (swap || bn > 32 || (epi != EPI_STORE_BF16 && epi != EPI_SWIGLU && epi != EPI_HEAD_PREP)) return ODI_ERR_UNSUPPORTED;
     if (norm_w == nullptr || norm_parts == nullptr || norm_n_parts < 1) return ODI_ERR_ARGUMENT;
     if (((uintptr_t)norm_x & 15) || ((uintptr_t)norm_w & 15)) return ODI_ERR_UNSUPPORTED;
   }
   if (sumsq_out != nullptr && (epi != EPI_RESIDUAL || swap || bn > 64 || !(clustered || splits == 1))) return ODI_ERR_UNSUPPORTED;
   a.norm_x = norm_x; a.norm_w = norm_w; a.norm_parts = norm_parts; a.norm_n_parts = norm_n_parts; a.norm_eps = norm_eps;
   a.sumsq_out = sumsq_out;
+  if (epi == EPI_HEAD_PREP) {
+    // heads of 128 (a tile is a head), whole-head rotation or none, keys and values written, tokens in columns
+    if (head_prep == nullptr) return ODI_ERR_ARGUMENT;
+    a.hp = *head_prep;
+    const HeadPrepArgs& hp = a.hp;
+    if (swap || bn > 32 || !(clustered || splits == 1) || hp.d != BM || n_out != (hp.nq + 2 * hp.nkv) * BM ||
+        !hp.write_kv || (hp.cos_t != nullptr && hp.rot_dim != hp.d) || hp.n_tokens != tokens)
+      return ODI_ERR_UNSUPPORTED;
+  } else {
+    a.hp = HeadPrepArgs{};
+  }
   const int tok_tile = swap ? BM : bn, n_tile = swap ? bn : BM;
   dim3 grid((tokens + tok_tile - 1) / tok_tile, (n_out + n_tile - 1) / n_tile, splits);
   if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;

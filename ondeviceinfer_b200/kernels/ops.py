@@ -136,15 +136,21 @@ def rope_table(inv_freq: torch.Tensor, tok_pos: torch.Tensor, cos_t: torch.Tenso
 def head_prep(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, cos_t, sin_t, tok_seq, tok_pos, page_start,
               page_ids, *, nq: int, nkv: int, d: int, rot_dim: int, page_size: int, ring_pages: int,
               write_kv: bool, eps: float) -> None:
-    """Per-head Q/K RMSNorm (optional), rotary embedding (optional) and cache write, fused."""
-    n = qkv.shape[0]
-    _require(qkv, "qkv", ndim=2)
-    _require(q_out, "q_out", qkv.dtype)
-    if qkv.shape[1] != (nq + 2 * nkv) * d or q_out.numel() != n * nq * d:
-        raise KernelError(f"head_prep sizes disagree: qkv {tuple(qkv.shape)}, nq={nq}, nkv={nkv}, d={d}")
+    """Per-head Q/K RMSNorm (optional), rotary embedding (optional) and cache write, fused.
+
+    With ``qkv=None`` nothing runs: the checked argument block is returned, for the tensor-core product
+    that does the same in its epilogue (``gemm_bf16(..., EPI_HEAD_PREP, head_prep=...)``; bf16 only)."""
+    _require(q_out, "q_out", torch.bfloat16 if qkv is None else qkv.dtype, 2)
+    n = q_out.shape[0]
+    if qkv is not None:
+        _require(qkv, "qkv", ndim=2)
+        if qkv.shape[0] != n or qkv.shape[1] != (nq + 2 * nkv) * d:
+            raise KernelError(f"head_prep sizes disagree: qkv {tuple(qkv.shape)}, nq={nq}, nkv={nkv}, d={d}")
+    if q_out.numel() != n * nq * d:
+        raise KernelError(f"head_prep sizes disagree: q_out {tuple(q_out.shape)}, nq={nq}, d={d}")
     if write_kv:
-        _require(k_pool, "k_pool", qkv.dtype)
-        _require(v_pool, "v_pool", qkv.dtype)
+        _require(k_pool, "k_pool", q_out.dtype)
+        _require(v_pool, "v_pool", q_out.dtype)
     for name, w in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w)):
         if w is not None:
             _require(w, name, torch.float32, 1)
@@ -158,6 +164,8 @@ def head_prep(qkv, q_out, k_pool, v_pool, q_norm_w, k_norm_w, cos_t, sin_t, tok_
     args = _HeadPrepArgs(_ptr(qkv), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w), _ptr(k_norm_w),
                          _ptr(cos_t), _ptr(sin_t), _ptr(tok_seq), _ptr(tok_pos), _ptr(page_start), _ptr(page_ids),
                          n, nq, nkv, d, rot_dim, page_size, ring_pages, 1 if write_kv else 0, eps)
+    if qkv is None:
+        return args
     lib = load_library("elementwise")
     _check(lib.odi_head_prep(byref(args), c_int(dtype_code(qkv.dtype)), _stream()), "head_prep")
 
@@ -213,7 +221,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Opti
                             c_int(K), c_int(K), c_int(N), c_int(N), _stream()), "gemm_f32")
 
 
-EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU, EPI_HEAD_PREP = 0, 1, 2, 3, 4
 
 _gemm_state = {}
 
@@ -285,7 +293,16 @@ def gemm_bf16_sumsq_parts(n_out: int) -> int:
 def gemm_bf16_fuses_norm(tokens: int, n_out: int, K: int, epi: int) -> bool:
     """Whether the planned form of this product can take its operand through the norm prologue."""
     swap, bn, _ = gemm_bf16_plan(tokens, n_out, K, epi)
-    return not swap and bn <= 32 and epi in (EPI_STORE_BF16, EPI_SWIGLU)
+    return not swap and bn <= 32 and epi in (EPI_STORE_BF16, EPI_SWIGLU, EPI_HEAD_PREP)
+
+
+def gemm_bf16_fuses_head_prep(tokens: int, n_out: int, K: int, *, d: int, rot_dim: int, rotated: bool,
+                              write_kv: bool) -> bool:
+    """Whether the planned form of the q/k/v product can prepare the heads in its epilogue: heads of 128
+    (a tile of the product is a head), whole-head rotation or none, keys and values written, decode widths."""
+    swap, bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_STORE_BF16)
+    return (not swap and bn <= 32 and splits <= 8 and d == 128 and n_out % 128 == 0 and write_kv
+            and (not rotated or rot_dim == d))
 
 
 def gemm_bf16_gives_sumsq(tokens: int, n_out: int, K: int) -> bool:
@@ -294,9 +311,9 @@ def gemm_bf16_gives_sumsq(tokens: int, n_out: int, K: int) -> bool:
     return not swap and bn <= 64 and splits <= 8
 
 
-def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, epi: int, *, swap: Optional[bool] = None,
-              bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True,
-              norm: Optional[tuple] = None, sumsq_out: Optional[torch.Tensor] = None) -> None:
+def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *,
+              swap: Optional[bool] = None, bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True,
+              norm: Optional[tuple] = None, sumsq_out: Optional[torch.Tensor] = None, head_prep=None) -> None:
     """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
 
     ``EPI_STORE_BF16`` / ``EPI_STORE_F32``: out [tokens, rows]; ``EPI_RESIDUAL``: out (fp32) += product;
@@ -309,6 +326,9 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, epi
     wrote the rows received).  Decode form only (``gemm_bf16_fuses_norm``).
     ``sumsq_out`` (fp32 [gemm_bf16_sumsq_parts(features), tokens]) with ``EPI_RESIDUAL``: receives, per tile
     of 128 features, the sums of squares of the rows the product leaves in ``out``.
+    ``EPI_HEAD_PREP`` with ``head_prep`` (the block that ``head_prep(None, ...)`` returns) and ``out=None``:
+    w holds query, key and value heads of 128 rows each; the epilogue rounds the projections to bf16 and
+    does what :func:`head_prep` does with them (``gemm_bf16_fuses_head_prep`` says when).
     """
     if norm is not None:
         if x is not None:
@@ -325,12 +345,18 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, epi
         _require(x, "x", torch.bfloat16, 2)
         x_like = x
     _require(w, "w", torch.bfloat16, 2)
-    _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
     tokens, K = x_like.shape
     w_rows = w.shape[0]
     n_out = w_rows // 2 if epi == EPI_SWIGLU else w_rows
-    if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
-        raise KernelError(f"gemm sizes disagree: x {tuple(x_like.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if epi == EPI_HEAD_PREP:
+        if out is not None or head_prep is None:
+            raise KernelError("EPI_HEAD_PREP takes head_prep and no out")
+        if w.shape[1] != K:
+            raise KernelError(f"gemm sizes disagree: x {tuple(x_like.shape)}, w {tuple(w.shape)}")
+    else:
+        _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
+        if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
+            raise KernelError(f"gemm sizes disagree: x {tuple(x_like.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     if sumsq_out is not None:
         _require(sumsq_out, "sumsq_out", torch.float32, 2)
         if epi != EPI_RESIDUAL or sumsq_out.shape != (gemm_bf16_sumsq_parts(n_out), tokens):
@@ -356,7 +382,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, epi
     _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
                              c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if swap else 0),
                              c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
-                             _ptr(sumsq_out), _stream()),
+                             _ptr(sumsq_out), byref(head_prep) if head_prep is not None else _ptr(None), _stream()),
            "gemm_tcgen05")
 
 

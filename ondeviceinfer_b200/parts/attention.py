@@ -19,7 +19,7 @@ from ..config.specs import AttentionSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
-from .linear import linear
+from .linear import heads_in_epilogue, linear, project_heads
 
 
 TCGEN05_MIN_Q_LEN = 16     # shorter chunks fill too little of a 128-row tile
@@ -72,15 +72,19 @@ class Attention(Part):
         n = x.shape[0]
         group = view.kv_group
         page_start, page_ids = ctx.page_table(group.index)
-        qkv = linear(x, self.w_qkv)
         q = torch.empty((n, s.num_heads * s.head_dim), dtype=x.dtype, device=x.device)
         tables = self.position.rotary_tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
-        ops.head_prep(qkv, q, view.keys, view.values, self.q_norm, self.k_norm, cos, sin,
-                      ctx.tok_seq, ctx.tok_pos, page_start, page_ids,
-                      nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, rot_dim=self.position.rot_dim,
-                      page_size=PAGE_SIZE, ring_pages=group.ring_pages, write_kv=view.writes_kv,
-                      eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0)
+        # with heads of 128 at decode widths the product's epilogue prepares the heads itself
+        fused = heads_in_epilogue(x, self.w_qkv, head_dim=s.head_dim, rot_dim=self.position.rot_dim,
+                                  rotated=cos is not None, write_kv=view.writes_kv)
+        prepared = ops.head_prep(None if fused else linear(x, self.w_qkv), q, view.keys, view.values,
+                                 self.q_norm, self.k_norm, cos, sin, ctx.tok_seq, ctx.tok_pos, page_start, page_ids,
+                                 nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, rot_dim=self.position.rot_dim,
+                                 page_size=PAGE_SIZE, ring_pages=group.ring_pages, write_kv=view.writes_kv,
+                                 eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0)
+        if fused:
+            project_heads(x, self.w_qkv, prepared)
         o = torch.empty_like(q)
         self.attend(q, o, ctx, view, page_start, page_ids)
         linear(o, self.w_o, residual=residual, track=ctx)

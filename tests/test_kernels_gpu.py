@@ -485,6 +485,62 @@ def test_gemm_tcgen05_norm_prologue_and_sums_of_squares(tokens, H, N, tile, spli
     close(fused, expected, "bfloat16")
 
 
+@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,lazy", [
+    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, True),     # a decode step, a cluster per head
+    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, False),
+    ([3, 1, 16], [0, 200, 10], 256, 4, 2, True, True, False),                          # a short K: one split, 32 columns
+    ([3, 1, 16], [0, 200, 10], 256, 4, 2, False, False, True),                         # neither norm nor rotation
+    ([1, 1, 1], [70, 2, 900], 1024, 6, 3, True, False, True),
+    ([5, 6], [0, 64], 2048, 2, 1, False, True, False),
+])
+def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, lazy):
+    """The q/k/v product with the head preparation in its epilogue against the product followed by the
+    head-preparation kernel: the same bits in the queries and in the cache, nothing written elsewhere."""
+    torch.manual_seed(23)
+    d = 128
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=24)
+    n = sum(lengths)
+    w = (torch.randn((nq + 2 * nkv) * d, K) / math.sqrt(K)).bfloat16().to(DEV)
+    qw = (1 + 0.1 * torch.randn(d)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(d)).to(DEV) if norm else None
+    cos = sin = None
+    if rot:
+        inv_freq = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+        cos = torch.empty(n, d // 2, dtype=torch.float32, device=DEV)
+        sin = torch.empty_like(cos)
+        ops.rope_table(inv_freq.to(DEV), setup["tok_pos"], cos, sin)
+    rows = (torch.randn(n, K) * 2).to(DEV)
+    g = (1 + 0.1 * torch.randn(K)).to(DEV)
+    x = torch.empty(n, K, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(rows, g, 1e-6, x)
+    parts = torch.zeros(ops.gemm_bf16_sumsq_parts(K), n, device=DEV)
+    padded = torch.zeros(n, parts.shape[0] * 128, device=DEV)
+    padded[:, :K] = rows
+    parts.copy_((padded.view(n, -1, 128) ** 2).sum(-1).t())
+    common = dict(nq=nq, nkv=nkv, d=d, rot_dim=d if rot else 0, page_size=64, ring_pages=0, write_kv=True, eps=1e-5)
+    tail = (qw, kw, cos, sin, setup["tok_seq"], setup["tok_pos"], setup["page_start"], setup["page_ids"])
+
+    qkv = torch.empty(n, w.shape[0], dtype=torch.bfloat16, device=DEV)
+    if lazy:
+        ops.gemm_bf16(None, w, qkv, ops.EPI_STORE_BF16, norm=(rows, g, parts, 1e-6))
+    else:
+        ops.gemm_bf16(x, w, qkv, ops.EPI_STORE_BF16)
+    q_two = torch.zeros(n, nq * d, dtype=torch.bfloat16, device=DEV)
+    k_two, v_two = torch.zeros_like(setup["k_pool"]), torch.zeros_like(setup["v_pool"])
+    ops.head_prep(qkv, q_two, k_two, v_two, *tail, **common)
+
+    assert ops.gemm_bf16_fuses_head_prep(n, w.shape[0], K, d=d, rot_dim=d if rot else 0, rotated=rot, write_kv=True)
+    q_one = torch.zeros_like(q_two)
+    k_one, v_one = torch.zeros_like(k_two), torch.zeros_like(v_two)
+    block = ops.head_prep(None, q_one, k_one, v_one, *tail, **common)
+    ops.gemm_bf16(None if lazy else x, w, None, ops.EPI_HEAD_PREP, head_prep=block,
+                  norm=(rows, g, parts, 1e-6) if lazy else None)
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    assert float(q_two.float().abs().sum()) > 0 and float(k_two.float().abs().sum()) > 0
+    assert torch.equal(q_one, q_two) and torch.equal(k_one, k_two) and torch.equal(v_one, v_two)
+
+
 def test_gemm_tcgen05_refuses_unaligned_k():
     x = torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)
