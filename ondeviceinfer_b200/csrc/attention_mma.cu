@@ -50,6 +50,8 @@ struct MmaAttnArgs {
   int n_seqs, nq, nkv, splits, head_chunks;
   float scale;
   int clustered;          // decode: the splits of a (sequence, kv head) form a cluster and merge in shared memory
+  int* tickets;           // decode with global partials: one counter per (sequence, block row), zero before and
+                          // after; the block that finishes a row of splits last merges them (null: a combine kernel does)
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -256,6 +258,28 @@ attention_prefill_kernel(MmaAttnArgs a) {
 
 // ------------------------------------------------------------------------------ decode
 
+// Merge the split partials of one (token, head) row: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s,
+// the splits in order.  `first`, `step`: which elements of the row this thread writes.
+__device__ __forceinline__ void combine_row(const float* p, bf16* out_row, int splits, int first, int step) {
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(p + s * (D + 2) + D));
+  float denom = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = __ldcg(p + s * (D + 2) + D);
+    if (ms != -INFINITY) denom += expf(ms - M) * __ldcg(p + s * (D + 2) + D + 1);
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  for (int dd = first; dd < D; dd += step) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = __ldcg(p + s * (D + 2) + D);
+      if (ms != -INFINITY) v += expf(ms - M) * __ldcg(p + s * (D + 2) + dd);
+    }
+    out_row[dd] = __float2bfloat16_rn(v * inv);
+  }
+}
+
+
 #define DC_WARPS 4
 #define DC_STAGES (D <= 128 ? 3 : 2)
 
@@ -437,6 +461,26 @@ attention_decode_kernel(MmaAttnArgs a) {
       if (lane == 0) { dst[D] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f; dst[D + 1] = L; }
     }
   }
+  if (a.splits > 1 && !a.clustered && a.tickets != nullptr) {
+    // Whoever publishes the last partial of this (sequence, block row) merges them: nobody waits, and the
+    // merge reads the splits in order, so the result does not depend on who came last.
+    __shared__ int last_block;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* ticket = a.tickets + (size_t)seq * gridDim.y + blockIdx.y;
+      last_block = atomicAdd(ticket, 1) == a.splits - 1;
+      if (last_block) *ticket = 0;                 // ready for the next launch
+    }
+    __syncthreads();
+    if (last_block) {
+      __threadfence();
+      for (int row = warp; row < heads_here; row += DC_WARPS) {
+        const size_t r = (size_t)tok * a.nq + head0 + row;
+        combine_row(a.partial + r * a.splits * RS, a.out + r * D, a.splits, lane, 32);
+      }
+    }
+  }
   if (a.clustered) {
     // every thread of every block of the cluster takes part in both barriers
     __syncwarp();
@@ -468,28 +512,11 @@ attention_decode_kernel(MmaAttnArgs a) {
   }
 }
 
-// Merge split partials: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s.
 __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;
-  const float* p = partial + row * splits * (D + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, p[s * (D + 2) + D]);
-  float denom = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = p[s * (D + 2) + D];
-    if (ms != -INFINITY) denom += expf(ms - M) * p[s * (D + 2) + D + 1];
-  }
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
-    float v = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = p[s * (D + 2) + D];
-      if (ms != -INFINITY) v += expf(ms - M) * p[s * (D + 2) + dd];
-    }
-    out[row * D + dd] = __float2bfloat16_rn(v * inv);
-  }
+  combine_row(partial + row * splits * (D + 2), out + row * D, splits, threadIdx.x, blockDim.x);
 }
 
 extern "C" int odi_attention_mma_head_dim() { return D; }
@@ -544,7 +571,7 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   }
   odi_rc = launch_pdl((attention_decode_kernel), dim3(grid), dim3(DC_WARPS * 32), dc_smem, stream, a);
   int rc = launch_status();
-  if (rc != 0 || a.splits == 1) return rc;
+  if (rc != 0 || a.splits == 1 || a.tickets != nullptr) return rc;
   const int combine_threads = D >= 128 ? 128 : 64;
   odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream, a.partial, a.out, a.splits);
   return launch_status();
@@ -614,6 +641,7 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
   }
   a.partial = noalloc_scratch_address[device];
   a.clustered = 0;      // this entry point is the global-partial form
+  a.tickets = nullptr;  // ... with the combine kernel
   a.head_chunks = (a.nq / a.nkv + 15) / 16;
   dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;

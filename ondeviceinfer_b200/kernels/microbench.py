@@ -99,7 +99,7 @@ def attention_decode_case(args) -> dict:
     run = lambda i: ops.attention_mma(q, pools[i][0], pools[i][1], out, cu_q, past, page_start, page_ids,
                                       n_seqs=args.batch, max_q_len=1, nq=nq, nkv=nkv, d=d, page_size=64,
                                       scale=1 / math.sqrt(d), splits=splits, partial=partial,
-                                      cluster=args.cluster_attention)
+                                      cluster=args.cluster_attention, merge_in_kernel=args.merge_in_kernel)
     us = time_kernel(run, copies, args.reps)
     return {"case": "attention-decode", "batch": args.batch, "ctx": args.ctx, "splits": splits, "us": us,
             "kv_GBps": kv_bytes / us / 1e3}
@@ -154,6 +154,8 @@ def main(argv=None) -> int:
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
     parser.add_argument("--no-cluster", action="store_true", help="GEMM K splits through global scratch, not a cluster")
     parser.add_argument("--cluster-attention", action="store_true", help="merge decode-attention splits inside a cluster")
+    parser.add_argument("--merge-in-kernel", action="store_true",
+                        help="decode-attention splits merged by the block that comes last, not by a second kernel")
     parser.add_argument("--mma-sync", action="store_true", help="attention-prefill: the mma.sync kernel instead of tcgen05")
     parser.add_argument("--heads-per-cta", type=int, default=0, help="attention-prefill on tcgen05: 1, 2 or 0 (default choice)")
     parser.add_argument("--batch", type=int, default=8)

@@ -429,19 +429,33 @@ class _MmaAttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p),
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("splits", c_int),
-                ("head_chunks", c_int), ("scale", c_float), ("clustered", c_int)]
+                ("head_chunks", c_int), ("scale", c_float), ("clustered", c_int), ("tickets", c_void_p)]
 
 
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))
 
+_attention_state = {}
+
+
+def _attention_tickets(device, count: int) -> torch.Tensor:
+    """Counters of the split-key decode attention, one per (sequence, block row); kept zero between launches."""
+    have = _attention_state.get(device)
+    if have is None or have.numel() < count:
+        have = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+        _attention_state[device] = have
+    return have
+
 
 def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                   nq: int, nkv: int, d: int, page_size: int, scale: float, splits: int = 1,
-                  partial: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
+                  partial: Optional[torch.Tensor] = None, cluster: bool = False, merge_in_kernel: bool = False) -> None:
     """bf16 causal GQA on the tensor cores: the prefill kernel for any q_len, the split-key
     decode kernel when every sequence brings exactly one token.  No window.
 
-    Decode splits go through the fp32 ``partial`` buffer and a combine kernel.  ``cluster=True``
+    Decode splits go through the fp32 ``partial`` buffer and a combine kernel.  ``merge_in_kernel=True``
+    lets the block that finishes a (sequence, kv head) last merge them instead (an atomic ticket; the same
+    bits); on B200 that measured slower (20.1 against 17.5 us at 8 x 2048 with 4 splits, 17.1 against 10.8 us
+    at 1 x 2048 with 16: the fence, the ticket and the merge lengthen the slowest block).  ``cluster=True``
     merges 2..8 splits inside a thread-block cluster instead (no scratch, no second kernel); on
     B200 that measured no faster (19.4 against 19.3 us at 8 x 2048, slower at other split counts:
     the co-scheduling of 104 KB blocks costs what the saved launch gains), so it is not the default."""
@@ -464,11 +478,16 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
         need = n_tokens * nq * splits * (d + 2)
         if partial is None or partial.numel() < need or partial.dtype != torch.float32:
             raise KernelError(f"splits={splits} needs an fp32 partial buffer of {need} elements")
+    tickets = None
+    if decode and splits > 1 and not clustered and merge_in_kernel:
+        tickets = _attention_tickets(q.device, n_seqs * nkv * (-(-(nq // nkv) // 16)))
     args = _MmaAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
-                        _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale, 1 if clustered else 0)
+                        _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale, 1 if clustered else 0,
+                        _ptr(tickets))
     lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(1 if decode else 0),
-                                 _stream()), "attention_mma", 2 if (splits > 1 and not clustered) else 1)
+                                 _stream()), "attention_mma",
+           2 if (splits > 1 and not clustered and tickets is None) else 1)
 
 
 class _TcAttnArgs(Structure):

@@ -583,6 +583,16 @@ def test_attention_mma(d, nq, nkv, lengths, past, splits):
                       nkv=nkv, d=d, page_size=64, scale=scale, splits=splits, partial=partial)
     expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, 0, scale, "bfloat16")
     close(out, expected, "bfloat16")
+    if splits > 1:
+        # merged by a second kernel instead of by the block that comes last: the same bits, and launched
+        # again the tickets must have been left at zero
+        for merge_in_kernel in (False, True):
+            other = torch.zeros_like(out)
+            ops.attention_mma(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], other, setup["cu_q"], setup["past"],
+                              setup["page_start"], setup["page_ids"], n_seqs=len(lengths), max_q_len=1, nq=nq, nkv=nkv,
+                              d=d, page_size=64, scale=scale, splits=splits, partial=partial,
+                              merge_in_kernel=merge_in_kernel)
+            assert torch.equal(other, out)
     if 1 < splits <= 8:
         # the same splits merged inside a thread-block cluster instead of through global partials
         other = torch.empty_like(out)
