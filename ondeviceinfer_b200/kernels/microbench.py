@@ -55,22 +55,48 @@ def time_kernel(run, variants: int, reps: int, warmup: int = 3) -> float:
 
 def gemm_case(args) -> dict:
     epi = {"store_bf16": ops.EPI_STORE_BF16, "store_f32": ops.EPI_STORE_F32, "residual": ops.EPI_RESIDUAL,
-           "swiglu": ops.EPI_SWIGLU}[args.epi]
+           "swiglu": ops.EPI_SWIGLU, "head_prep": ops.EPI_HEAD_PREP}[args.epi]
     rows = 2 * args.n if epi == ops.EPI_SWIGLU else args.n
     copies = max(1, int(math.ceil(3 * L2_BYTES / (rows * args.k * 2)))) if args.rotate else 1
     ws = [(torch.randn(rows, args.k, device="cuda") / math.sqrt(args.k)).bfloat16() for _ in range(copies)]
     x = torch.randn(args.tokens, args.k, device="cuda").bfloat16()
     wide = epi in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL)
     out = torch.zeros(args.tokens, args.n, dtype=torch.float32 if wide else torch.bfloat16, device="cuda")
+    extra = {}
+    if args.norm:      # the operand comes through the fused RMSNorm: fp32 rows and their sums of squares
+        hidden = torch.randn(args.tokens, args.k, device="cuda")
+        parts = torch.zeros(ops.gemm_bf16_sumsq_parts(args.k), args.tokens, device="cuda")
+        padded = torch.zeros(args.tokens, parts.shape[0] * 128, device="cuda")
+        padded[:, :args.k] = hidden
+        parts.copy_((padded.view(args.tokens, -1, 128) ** 2).sum(-1).t())
+        extra["norm"] = (hidden, torch.ones(args.k, device="cuda"), parts, 1e-6)
+        x = None
+    if epi == ops.EPI_RESIDUAL and args.sumsq:
+        extra["sumsq_out"] = torch.empty(ops.gemm_bf16_sumsq_parts(args.n), args.tokens, device="cuda")
+    if epi == ops.EPI_HEAD_PREP:   # rows of w are query, key and value heads of 128 (4 query heads per kv head)
+        d, heads = 128, args.n // 128
+        nkv = heads // 6
+        nq = heads - 2 * nkv
+        pools, page_start, page_ids = _cache_setup(args.tokens, args.ctx, nkv, d, 1)
+        tok = torch.arange(args.tokens, dtype=torch.int32, device="cuda")
+        pos = torch.full((args.tokens,), args.ctx - 1, dtype=torch.int32, device="cuda")
+        cos = torch.ones(args.tokens, d // 2, device="cuda")
+        sin = torch.zeros(args.tokens, d // 2, device="cuda")
+        ones = torch.ones(d, device="cuda")
+        q_out = torch.empty(args.tokens, nq * d, dtype=torch.bfloat16, device="cuda")
+        extra["head_prep"] = ops.head_prep(None, q_out, pools[0][0], pools[0][1], ones, ones, cos, sin, tok, pos,
+                                           page_start, page_ids, nq=nq, nkv=nkv, d=d, rot_dim=d, page_size=64,
+                                           ring_pages=0, write_kv=True, eps=1e-6)
+        out = None
     if args.library:
         run = lambda i: torch.matmul(x, ws[i].t())
     else:
         run = lambda i: ops.gemm_bf16(x, ws[i], out, epi, swap=args.swap, bn=args.bn, splits=args.splits,
-                                      cluster=not args.no_cluster)
+                                      cluster=not args.no_cluster, **extra)
     us = time_kernel(run, copies, args.reps)
     ops.raise_on_kernel_fault()
     weight_bytes, flops = rows * args.k * 2, 2.0 * args.tokens * rows * args.k
-    return {"case": "gemm", "tokens": args.tokens, "n": args.n, "k": args.k, "epi": args.epi,
+    return {"case": "gemm", "tokens": args.tokens, "n": args.n, "k": args.k, "epi": args.epi, "norm": bool(args.norm),
             "plan": None if args.library else list(ops.gemm_bf16_plan(args.tokens, args.n, args.k, epi)),
             "us": us, "weight_GBps": weight_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
 
@@ -147,7 +173,9 @@ def main(argv=None) -> int:
     parser.add_argument("--tokens", type=int, default=8)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--k", type=int, default=4096)
-    parser.add_argument("--epi", default="store_bf16", choices=("store_bf16", "store_f32", "residual", "swiglu"))
+    parser.add_argument("--epi", default="store_bf16", choices=("store_bf16", "store_f32", "residual", "swiglu", "head_prep"))
+    parser.add_argument("--norm", action="store_true", help="gemm: the operand through the fused RMSNorm prologue")
+    parser.add_argument("--sumsq", action="store_true", help="gemm --epi residual: also leave the rows' sums of squares")
     parser.add_argument("--bn", type=int, default=None)
     parser.add_argument("--splits", type=int, default=None)
     parser.add_argument("--swap", type=int, default=None)
