@@ -197,6 +197,76 @@ def test_prenorm_block_alone(dtype):
     assert_logits_close(h, expected.float(), dtype)
 
 
+def test_two_blocks_decode_through_the_fused_products(monkeypatch):
+    """Two blocks with heads of 128 at decode width: the second norm of a block and the first of the next
+    are left to the following product (`NormedRows`), the heads are prepared in the q/k/v product's epilogue.
+    Against the plain layers over the whole sequence, and against the same blocks with the fusions refused."""
+    from ondeviceinfer_b200.parts import Attention, GatedMLP
+    import importlib
+    linear_module = importlib.import_module("ondeviceinfer_b200.parts.linear")
+    cfg = {"num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 128, "hidden_size": 192,
+           "rms_norm_eps": 1e-5, "intermediate_size": 320}
+    blocks, tensors = [], {}
+    for i in range(2):
+        p = f"model.layers.{i}."
+        spec = PreNormBlockSpec(
+            mixer_norm=RMSNormSpec(192, 1e-5, p + "input_layernorm.weight"),
+            mixer=AttentionSpec(192, 2, 1, 128, RotarySpec(128, 5000.0), p + "self_attn.",
+                                names(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight",
+                                      q_norm="q_norm.weight", k_norm="k_norm.weight"), qk_norm_eps=1e-5),
+            ffn_norm=RMSNormSpec(192, 1e-5, p + "post_attention_layernorm.weight"),
+            ffn=GatedMLPSpec(192, 320, "silu", p + "mlp.", names(gate="gate_proj.weight", up="up_proj.weight",
+                                                                down="down_proj.weight")))
+        block = build_part(spec)
+        mine = random_tensors(block, 40 + i)
+        load(block, mine, "bfloat16")
+        blocks.append(block)
+        tensors.update(mine)
+    n, tail = 75, 5
+    hidden = torch.randn(n, 192)
+    cos, sin = plain.rope_tables(torch.arange(n), 128, 5000.0, torch.bfloat16)
+    w = {k: v.to(torch.bfloat16) for k, v in tensors.items()}
+    expected = plain.decoder_layer(plain.decoder_layer(hidden.bfloat16(), w, 0, cfg, cos, sin), w, 1, cfg, cos, sin).float()
+
+    def run(count_fused):
+        cache = SequenceCache([b.cache_needs() for b in blocks], [None, None], dtype=torch.bfloat16, device=DEV,
+                              max_tokens=128, max_seqs=1)
+        slot = cache.alloc()
+        rows, seen = [], {"lazy": 0, "heads": 0}
+        real_operand, real_heads = linear_module._operand, linear_module.project_heads
+
+        def counting_operand(x, *args):
+            seen["lazy"] += isinstance(x, linear_module.NormedRows)
+            return real_operand(x, *args)
+
+        def counting_heads(*args):
+            seen["heads"] += 1
+            return real_heads(*args)
+
+        monkeypatch.setattr(linear_module, "_operand", counting_operand)
+        monkeypatch.setattr("ondeviceinfer_b200.parts.attention.project_heads", counting_heads)
+        for start, stop in [(0, n - tail)] + [(t, t + 1) for t in range(n - tail, n)]:
+            cache.reserve([slot], [stop - start])
+            ctx = StepContext(cache, [slot], [[0] * (stop - start)], [], DEV)
+            ctx.residual_sumsq = None
+            h = hidden[start:stop].clone().to(DEV)
+            for i, block in enumerate(blocks):
+                block.forward(h, ctx, cache.view(i))
+            cache.advance([slot], [stop - start])
+            rows.append(h.cpu())
+        assert (seen["lazy"] > 0) == count_fused and (seen["heads"] > 0) == count_fused, seen
+        return torch.cat(rows)
+
+    fused = run(True)
+    assert_logits_close(fused, expected, "bfloat16")
+    monkeypatch.setattr(Attention, "takes_lazy_norm", False)
+    monkeypatch.setattr(GatedMLP, "takes_lazy_norm", False)
+    monkeypatch.setattr("ondeviceinfer_b200.parts.attention.heads_in_epilogue", lambda *a, **k: False)
+    plain_way = run(False)
+    assert_logits_close(plain_way, expected, "bfloat16")
+    assert float((fused - plain_way).abs().max()) <= 0.02 * float(expected.abs().max())
+
+
 def test_unknown_spec_and_bad_sizes_are_refused():
     class Unknown:
         pass
