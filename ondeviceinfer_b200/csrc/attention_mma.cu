@@ -133,9 +133,11 @@ attention_prefill_kernel(MmaAttnArgs a) {
   pdl_wait();
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int seq = blockIdx.z, head = blockIdx.y, hk = head / (a.nq / a.nkv);
+  // heads along x, sequences along y, query tiles along z from the last (the most keys) to the first:
+  // blocks are handed out x-fastest, so the long tiles start first and the short ones fill the tail
+  const int seq = blockIdx.y, head = blockIdx.x, hk = head / (a.nq / a.nkv);
   const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
-  const int t0 = blockIdx.x * 64;
+  const int t0 = (gridDim.z - 1 - blockIdx.z) * 64;
   if (t0 >= q_len) return;
   const int past = a.past[seq];
   const int nt = min(64, q_len - t0);
@@ -281,7 +283,9 @@ __device__ __forceinline__ void combine_row(const float* p, bf16* out_row, int s
 
 
 #define DC_WARPS 4
+#ifndef DC_STAGES
 #define DC_STAGES (D <= 128 ? 3 : 2)
+#endif
 
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_kernel(MmaAttnArgs a) {
@@ -541,7 +545,8 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   }
   if (!decode) {
     if (a.splits != 1 || a.nq > 65535) return ODI_ERR_UNSUPPORTED;
-    dim3 grid((max_q_len + 63) / 64, a.nq, a.n_seqs);
+    if ((max_q_len + 63) / 64 > 65535) return ODI_ERR_UNSUPPORTED;
+    dim3 grid(a.nq, a.n_seqs, (max_q_len + 63) / 64);
     odi_rc = launch_pdl((attention_prefill_kernel), dim3(grid), dim3(PF_WARPS * 32), pf_smem, stream, a);
     return launch_status();
   }

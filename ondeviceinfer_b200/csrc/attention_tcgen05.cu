@@ -242,9 +242,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.z, head0 = blockIdx.y * TILES, hk = head0 / (a.nq / a.nkv);
+  // Heads along x, sequences along y, query tiles along z from the last (which sees the most keys) to the
+  // first: blocks are handed out x-fastest, so the long tiles of all heads and sequences start first and
+  // the short ones fill the tail.
+  const int seq = blockIdx.y, head0 = blockIdx.x * TILES, hk = head0 / (a.nq / a.nkv);
   const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
-  const int t0 = blockIdx.x * BM;
+  const int t0 = (gridDim.z - 1 - blockIdx.z) * BM;
   if (t0 >= q_len) return;                       // whole CTA: nothing allocated yet
   const int past = a.past[seq];
   const int nt = min(BM, q_len - t0);
@@ -531,12 +534,13 @@ extern "C" int odi_attention_tcgen05(const void* q, const void* k_pool, const vo
     configured = true;
   }
   if (heads_per_cta == 2 && (a.nq / a.nkv) % 2 != 0) return ODI_ERR_ARGUMENT;
+  if ((max_q_len + BM - 1) / BM > 65535) return ODI_ERR_UNSUPPORTED;
   if (heads_per_cta == 0) heads_per_cta = ODI_ATT_DEFAULT_HEADS_PER_CTA;
   if (heads_per_cta == 2 && (a.nq / a.nkv) % 2 == 0) {
-    dim3 grid((max_q_len + BM - 1) / BM, a.nq / 2, a.n_seqs);
+    dim3 grid(a.nq / 2, a.n_seqs, (max_q_len + BM - 1) / BM);
     odi_rc = launch_pdl((attention_tcgen05_kernel<2>), dim3(grid), dim3(64 + 512), smem2, stream, mq, mk, mv, a);
   } else {
-    dim3 grid((max_q_len + BM - 1) / BM, a.nq, a.n_seqs);
+    dim3 grid(a.nq, a.n_seqs, (max_q_len + BM - 1) / BM);
     odi_rc = launch_pdl((attention_tcgen05_kernel<1>), dim3(grid), dim3(64 + 256), smem1, stream, mq, mk, mv, a);
   }
   return launch_status();
