@@ -633,13 +633,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       int slot = 0;
       if (live)
         for (int c = (int)rank; c < BN && tok0 + c < a.tokens; c += a.splits, ++slot) {   // the token columns this CTA owns
+          // all peers' values are requested before the first is used (the loads do not wait on one
+          // another), then added in rank order: a fixed sum
+          float pv[8], pu[8];
+          const bool inside = tok0 + c < a.tokens && n < a.N;
+          float* res_at = (float*)a.out + (size_t)(tok0 + c) * a.ldo + n;
+          const float res = (EPI == EPI_RESIDUAL && inside) ? *res_at : 0.f;     // in flight with the peers' values
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            pv[p] = p < a.splits ? ld_peer_f32(red + c * BM + row, (uint32_t)p) : 0.f;
+            if (DUAL) pu[p] = p < a.splits ? ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p) : 0.f;
+          }
           float v = 0.f, u = 0.f;
-          for (int p = 0; p < a.splits; ++p) {                                     // rank order: a fixed sum
-            v += ld_peer_f32(red + c * BM + row, (uint32_t)p);
-            if (DUAL) u += ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p);
+#pragma unroll
+          for (int p = 0; p < 8; ++p) {
+            if (p < a.splits) { v += pv[p]; if (DUAL) u += pu[p]; }
           }
           if (EPI == EPI_HEAD_PREP) ((float*)(smem + HP_STAGE_OFFSET))[slot * BM + row] = round_to<bf16>(v);
-          const float left = emit<EPI>(a, tok0 + c, n, v, u);
+          float left = 0.f;
+          if (EPI == EPI_RESIDUAL) { left = inside ? res + v : 0.f; if (inside) *res_at = left; }
+          else emit<EPI>(a, tok0 + c, n, v, u);
           if (sums) {
             const float sq = warp_sum(left * left);
             if (lane == 0) sumsq_part[warp & 3][BN <= 64 ? slot : 0] = sq;
