@@ -204,14 +204,23 @@ LARGE = {
 }
 
 
+# two layers with the sizes of Qwen3-14B (width 5120, 40 query heads): seven K splits, a fused norm at the
+# start of a layer as well as in its middle, a tied head over a small vocabulary
+LARGE_TWO = dict(LARGE, num_hidden_layers=2, hidden_size=5120, num_attention_heads=40, intermediate_size=17408,
+                 vocab_size=30000, tie_word_embeddings=True)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_qwen3_8b_layer_sizes(dtype, tmp_path):
+@pytest.mark.parametrize("sizes", ["8B", "14B"])
+def test_qwen3_8b_layer_sizes(sizes, dtype, tmp_path):
     """One layer with the sizes of Qwen3-8B (width 4096, 32 query and 8 key/value heads of 128,
-    feed-forward 12288, vocabulary 151936): whole, the last tokens one by one, and an unequal batch,
-    against the plain implementation.  Logits of 4096-wide sums are compared at the wanted places."""
+    feed-forward 12288, vocabulary 151936), and two with those of Qwen3-14B: whole, the last tokens one
+    by one, and an unequal batch, against the plain implementation.  Logits of wide sums are compared
+    at the wanted places."""
     import ondeviceinfer_b200 as odi
     from helpers import write_model_folder
 
+    LARGE = {"8B": globals()["LARGE"], "14B": LARGE_TWO}[sizes]
     weights = plain.random_weights(LARGE, 3)
     model = odi.load_resident_model(write_model_folder(tmp_path / "large", LARGE, weights), dtype=dtype)
     requests = plain.random_prompts(LARGE, [70, 9, 33], 3)
@@ -219,16 +228,16 @@ def test_qwen3_8b_layer_sizes(dtype, tmp_path):
     cache = model.make_cache(max_tokens=3 * 128, max_seqs=3)
     # whole, alone
     slot = cache.alloc()
-    assert_logits_close(model.step(cache, [slot], [requests[0]], "all"), expected[0], dtype, "8B sizes whole", longest_sum=12288)
+    assert_logits_close(model.step(cache, [slot], [requests[0]], "all"), expected[0], dtype, "8B sizes whole", longest_sum=LARGE["intermediate_size"])
     cache.free(slot)
     # unequal batch: prompts without their last 4 tokens, then one token each
     slots = [cache.alloc() for _ in requests]
     cut = [len(r) - 4 for r in requests]
     logits = model.step(cache, slots, [r[:c] for r, c in zip(requests, cut)], "last")
-    assert_logits_close(logits, torch.stack([e[c - 1] for e, c in zip(expected, cut)]), dtype, "8B sizes batch prompt", longest_sum=12288)
+    assert_logits_close(logits, torch.stack([e[c - 1] for e, c in zip(expected, cut)]), dtype, "8B sizes batch prompt", longest_sum=LARGE["intermediate_size"])
     for t in range(4):
         logits = model.step(cache, slots, [[r[c + t]] for r, c in zip(requests, cut)], "last")
-        assert_logits_close(logits, torch.stack([e[c + t] for e, c in zip(expected, cut)]), dtype, f"8B sizes decode {t}", longest_sum=12288)
+        assert_logits_close(logits, torch.stack([e[c + t] for e, c in zip(expected, cut)]), dtype, f"8B sizes decode {t}", longest_sum=LARGE["intermediate_size"])
     for slot in slots:
         cache.free(slot)
     cache.check()
