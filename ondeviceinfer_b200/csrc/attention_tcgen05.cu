@@ -6,12 +6,11 @@
 //
 //   S_j = Q K_j^T        tcgen05.mma, M = 128 query rows, N = 64 keys, K = head size; Q and K_j
 //                        in shared memory (TMA, 128-byte swizzle), S_j in tensor memory
-//   P_j = softmax part   by 8 warps: a query row is handled by two threads (32 keys each); fp32
-//                        running maximum and sum; P_j rounded to bf16 and written, in the swizzled
-//                        K-major layout the MMA reads, over the shared memory of K_j (which S_j
-//                        has consumed by then)
-//   O  += P_j V_j        tcgen05.mma, M = 128, N = head size, K = 64 keys; V_j is read as it lies
-//                        in its page (MN-major operand); O accumulates in tensor memory
+//   P_j = softmax part   by 4 warps, a thread per query row: it reads its row's 64 scores into
+//                        registers, keeps an fp32 running maximum and sum, and writes P_j (pairs of
+//                        bf16, 32 columns) over the first half of those scores' columns
+//   O  += P_j V_j        tcgen05.mma with the A operand (P_j) read from tensor memory; V_j is read as
+//                        it lies in its page (MN-major operand); O accumulates in tensor memory
 //
 // The accumulator in tensor memory cannot be scaled by the MMA, so the running maximum that P is
 // taken against is only raised when a row's new maximum exceeds it by more than 2^8: then that
@@ -20,14 +19,20 @@
 // result is the same as with a maximum that is raised every time.
 //
 // Per head S is double buffered in tensor memory (2 x 64 columns) and O takes head-size columns:
-// 256 columns a head.  K/V pages sit in two shared-memory stages, so the scores of page j + 1 are
-// computed while page j is in the softmax.  With one head per CTA (the default) a CTA takes 97 KB
-// of shared memory, 256 columns and 80 registers a thread, so two CTAs share an SM and one's MMAs
-// run under the other's softmax: measured 381 / 562 / 620 TFLOP/s at 1 x 2048, 8 x 2048 and
-// 1 x 8192 tokens.  Two heads of a key/value group per CTA (K/V pages loaded once for both, the
-// second head's P in buffers of its own) measured no faster (284-462 TFLOP/s with two stages,
-// 323-551 with three) and stays an option.  Warps: 0 = TMA producer, 1 = MMA issuer (one thread)
-// and tensor-memory owner, 2..9 = softmax of the first head, 10..17 = of the second.
+// 256 columns a head.  Shared memory holds Q and two rings of two K and two V pages with lives of
+// their own: a K slot is free once its scores are computed, so the keys of page j + 2 are on their
+// way while page j is still in the softmax; a V slot once its product has run.  The tensor pipe
+// executes one thread's MMAs in order, so the scores of page j + 2, issued after the product of
+// page j, cannot overwrite P_j before it has been read.  With one head per CTA (the default) a CTA
+// takes 97 KB of shared memory, 256 columns and 127 registers a thread, so two CTAs share an SM and
+// one's MMAs run under the other's softmax.  Query tiles are handed out longest first.  Measured
+// on B200: 882 TFLOP/s at 8 sequences of 2,048 tokens, 1,128 at one of 8,192, 1,047 at one of 32,768
+// (32 query / 8 key-value heads of 128).  The form this replaced kept P in shared memory (written
+// swizzled over the consumed K tile, two threads per row): 578 / 719 TFLOP/s; its K slot stayed
+// busy until the product, and the MMA thread spent 40 % of a page's time waiting for the next keys.
+// Two heads of a key/value group per CTA (K/V pages loaded once for both) measured slower
+// (676 / 823) and stays an option.  Warps: 0 = TMA producer, 1 = MMA issuer (one thread) and
+// tensor-memory owner, 2..5 = softmax and output of the first head, 6..9 = of the second.
 //
 // Works for any q_len >= 1 on top of any cached length (query t of the step sits at position
 // past + t).  No window.  Compile with -DODI_HEAD_DIM=64 or 128.
@@ -50,14 +55,9 @@
 #define BM 128                 // query rows per CTA
 #define BNK 64                 // keys per page / tile
 #define KB (D / 64)            // 64-wide blocks of the head size
-#ifndef NST
-#define NST 2                  // key/value stages
-#endif
+#define RING 2                 // K pages, and V pages, in flight
 #define Q_BYTES (KB * BM * 128)
 #define KV_BYTES (KB * BNK * 128)     // one of K or V for a page
-#define P_BYTES (BM * 128)            // 128 rows x 64 keys bf16
-#define KP_BYTES (KV_BYTES > P_BYTES ? KV_BYTES : P_BYTES)   // K_j, later overwritten by P_j
-#define STAGE_BYTES (KP_BYTES + KV_BYTES)
 #define HEAD_COLS 256                  // tensor-memory columns per head: S0, S1, O
 #define S_COL(t, b) ((t) * HEAD_COLS + (b) * BNK)
 #define O_COL(t) ((t) * HEAD_COLS + 2 * BNK)
@@ -134,18 +134,6 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // 32 consecutive columns of this thread's lane: two loads in flight, one wait.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   uint32_t r[32];
@@ -162,6 +150,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 64 consecutive columns of this thread's lane (a whole row of scores): two loads in flight, one wait.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* v) {
+  uint32_t r[64];
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[32 * h + 0]), "=r"(r[32 * h + 1]), "=r"(r[32 * h + 2]), "=r"(r[32 * h + 3]), "=r"(r[32 * h + 4]),
+          "=r"(r[32 * h + 5]), "=r"(r[32 * h + 6]), "=r"(r[32 * h + 7]), "=r"(r[32 * h + 8]), "=r"(r[32 * h + 9]),
+          "=r"(r[32 * h + 10]), "=r"(r[32 * h + 11]), "=r"(r[32 * h + 12]), "=r"(r[32 * h + 13]), "=r"(r[32 * h + 14]),
+          "=r"(r[32 * h + 15]), "=r"(r[32 * h + 16]), "=r"(r[32 * h + 17]), "=r"(r[32 * h + 18]), "=r"(r[32 * h + 19]),
+          "=r"(r[32 * h + 20]), "=r"(r[32 * h + 21]), "=r"(r[32 * h + 22]), "=r"(r[32 * h + 23]), "=r"(r[32 * h + 24]),
+          "=r"(r[32 * h + 25]), "=r"(r[32 * h + 26]), "=r"(r[32 * h + 27]), "=r"(r[32 * h + 28]), "=r"(r[32 * h + 29]),
+          "=r"(r[32 * h + 30]), "=r"(r[32 * h + 31])
+        : "r"(taddr + 32 * h));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -174,17 +183,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
         "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
         "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
         "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -227,24 +225,43 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_mn) {
 
 // ------------------------------------------------------------------------------ the kernel
 
+
+// 32 columns of packed values (two bf16 each) into this thread's lane.
+__device__ __forceinline__ void tmem_st32_packed(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// D += A B with A (M x 16, K-major, two bf16 per 32-bit column) read from tensor memory.
+__device__ __forceinline__ void umma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 template <int TILES>
-__global__ void __launch_bounds__(64 + 256 * TILES, TILES == 1 ? 2 : 1)
+__global__ void __launch_bounds__(64 + 128 * TILES, TILES == 1 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const TcAttnArgs a) {
   constexpr int TMEM_COLS = TILES * HEAD_COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  // barriers: q_full, kv_full[NST], kv_empty[NST], s_full[2], s_empty[2], p_full[TILES][2], pv_done[TILES]
-  __shared__ __align__(8) uint64_t bars[1 + 2 * NST + 4 + 3 * TILES];
+  // barriers: q_full, k_full[R], k_empty[R], v_full[R], v_empty[R], s_full[2], p_full[TILES][2], pv_done[TILES]
+  __shared__ __align__(8) uint64_t bars[1 + 4 * RING + 2 + 3 * TILES];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float row_max[TILES][2][BM];   // the two halves of a row exchange their maxima (and sums) here
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Heads along x, sequences along y, query tiles along z from the last (which sees the most keys) to the
-  // first: blocks are handed out x-fastest, so the long tiles of all heads and sequences start first and
-  // the short ones fill the tail.
+  // heads along x, sequences along y, query tiles along z from the last (the most keys) to the first
   const int seq = blockIdx.y, head0 = blockIdx.x * TILES, hk = head0 / (a.nq / a.nkv);
   const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
   const int t0 = (gridDim.z - 1 - blockIdx.z) * BM;
@@ -255,18 +272,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int* pages = a.page_ids + a.page_start[seq];
 
   const uint32_t bar0 = smem_u32(&bars[0]);
-  const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * NST, s_full = kv_empty + 8 * NST,
-                 s_empty = s_full + 16, p_full = s_empty + 16, pv_done = p_full + 16 * TILES;
+  const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = k_full + 8 * RING, v_full = k_empty + 8 * RING,
+                 v_empty = v_full + 8 * RING, s_full = v_empty + 8 * RING, p_full = s_full + 16,
+                 pv_done = p_full + 16 * TILES;
   uint8_t* q_smem = smem;                                    // head t at t * Q_BYTES
-  uint8_t* kv_smem = smem + TILES * Q_BYTES;                 // stage s: K (later the first head's P), then V
-  uint8_t* p1_smem = kv_smem + NST * STAGE_BYTES;            // the second head's P, two buffers
+  uint8_t* k_smem = smem + TILES * Q_BYTES;                  // ring of K pages
+  uint8_t* v_smem = k_smem + RING * KV_BYTES;             // ring of V pages
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 1 + 2 * NST + 4 + 3 * TILES; ++i) mbar_init(bar0 + 8 * i, 1);
-    for (int b = 0; b < 2; ++b) {      // signalled by the pairs of softmax warps: four pairs a head
-      mbar_init(s_empty + 8 * b, 4 * TILES);
-      for (int t = 0; t < TILES; ++t) mbar_init(p_full + 16 * t + 8 * b, 4);
-    }
+    for (int i = 0; i < 1 + 4 * RING + 2 + 3 * TILES; ++i) mbar_init(bar0 + 8 * i, 1);
+    for (int b = 0; b < 2; ++b)
+      for (int t = 0; t < TILES; ++t) mbar_init(p_full + 16 * t + 8 * b, 4);     // one arrival per softmax warp
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -281,24 +297,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   volatile int* abort_ptr = &abort_flag;
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
+    // ---------------------------------------------------------------- TMA producer: K_0, K_1, V_0, then K_j, V_{j-1}
     if (lane == 0) {
       pdl_wait();      // queries and this step's keys/values come from the kernel before
       mbar_expect_tx(q_full, TILES * Q_BYTES);
       for (int t = 0; t < TILES; ++t)
         for (int kb = 0; kb < KB; ++kb)
           tma_load_2d(smem_u32(q_smem + t * Q_BYTES + kb * BM * 128), &map_q, (head0 + t) * D + kb * 64, q_begin + t0, q_full);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % NST;
-        if (!mbar_wait(kv_empty + 8 * s, ((uint32_t)(j / NST) & 1u) ^ 1u, abort_ptr)) { atomicCAS(a.status, 0, ATT_ERR_PRODUCER); break; }
+      bool ok = true;
+      auto load_page = [&](int j, const CUtensorMap* map, uint8_t* ring, uint32_t full, uint32_t empty) {
+        const int s = j % RING;
+        if (!mbar_wait(empty + 8 * s, ((uint32_t)(j / RING) & 1u) ^ 1u, abort_ptr)) { ok = false; return; }
         const int row = (pages[j] * a.nkv + hk) * BNK;
-        uint8_t* st = kv_smem + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(kv_full + 8 * s, 2 * KV_BYTES);
-        for (int kb = 0; kb < KB; ++kb) {
-          tma_load_2d(smem_u32(st + kb * BNK * 128), &map_k, kb * 64, row, kv_full + 8 * s);
-          tma_load_2d(smem_u32(st + KP_BYTES + kb * BNK * 128), &map_v, kb * 64, row, kv_full + 8 * s);
-        }
+        mbar_expect_tx(full + 8 * s, KV_BYTES);
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(smem_u32(ring + (size_t)s * KV_BYTES + kb * BNK * 128), map, kb * 64, row, full + 8 * s);
+      };
+      // keys run one page ahead of values: a K slot is free as soon as its scores are computed
+      load_page(0, &map_k, k_smem, k_full, k_empty);
+      for (int j = 1; j <= n_tiles && ok; ++j) {
+        if (j < n_tiles) load_page(j, &map_k, k_smem, k_full, k_empty);
+        if (ok) load_page(j - 1, &map_v, v_smem, v_full, v_empty);
       }
+      if (!ok) atomicCAS(a.status, 0, ATT_ERR_PRODUCER);
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
@@ -307,11 +328,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       constexpr uint32_t idesc_o = idesc_bf16(BM, D, true);
       bool ok = mbar_wait(q_full, 0, abort_ptr);
       auto issue_s = [&](int j) -> bool {
-        const int s = j % NST, b = j & 1;
-        if (!mbar_wait(kv_full + 8 * s, (uint32_t)(j / NST) & 1u, abort_ptr)) return false;
-        if (!mbar_wait(s_empty + 8 * b, ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_ptr)) return false;
+        const int s = j % RING, b = j & 1;
+        if (!mbar_wait(k_full + 8 * s, (uint32_t)(j / RING) & 1u, abort_ptr)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
+        const uint32_t k_addr = smem_u32(k_smem + (size_t)s * KV_BYTES);
 #pragma unroll
         for (int t = 0; t < TILES; ++t) {
 #pragma unroll
@@ -322,137 +342,118 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int i = 0; i < 4; ++i) umma(tmem_base + S_COL(t, b), dq + 2 * i, dk + 2 * i, idesc_s, (kb | i) ? 1u : 0u);
           }
         }
-        umma_commit(s_full + 8 * b);       // both heads' scores done: K_j is free for the first head's P
+        umma_commit(s_full + 8 * b);       // the scores are done ...
+        umma_commit(k_empty + 8 * s);      // ... and the K slot is free
         return true;
       };
+      // S_{j+1} overwrites the buffer whose first columns held P_{j-1}: it is issued after the product of
+      // page j - 1, and the softmax threads read S_{j-1} before they signalled P_{j-1}.
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) ok = issue_s(j + 1);      // the next page's scores run under this page's softmax
         if (!ok) break;
-        const int s = j % NST, b = j & 1;
-        const uint32_t stage = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
-        const uint64_t dv = desc_mn_major(stage + KP_BYTES);
+        const int s = j % RING, b = j & 1;
+        if (!mbar_wait(v_full + 8 * s, (uint32_t)(j / RING) & 1u, abort_ptr)) { ok = false; break; }
+        const uint64_t dv = desc_mn_major(smem_u32(v_smem + (size_t)s * KV_BYTES));
 #pragma unroll
         for (int t = 0; t < TILES; ++t) {
           if (!mbar_wait(p_full + 16 * t + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t dp = desc_k_major(t == 0 ? stage : smem_u32(p1_smem + b * P_BYTES));
 #pragma unroll
-          for (int i = 0; i < 4; ++i)      // 16 keys per MMA: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-            umma(tmem_base + O_COL(t), dp + 2 * i, dv + (uint64_t)(i * 2048 >> 4), idesc_o, (j | i) ? 1u : 0u);
+          for (int i = 0; i < 4; ++i)      // 16 keys per MMA: 8 columns of packed P, 16 rows (2048 bytes) down V
+            umma_a_tmem(tmem_base + O_COL(t), tmem_base + S_COL(t, b) + 8 * i, dv + (uint64_t)(i * 2048 >> 4), idesc_o,
+                        (j | i) ? 1u : 0u);
           umma_commit(pv_done + 8 * t);
         }
-        umma_commit(kv_empty + 8 * s);
+        umma_commit(v_empty + 8 * s);
       }
       if (!ok) atomicCAS(a.status, 0, ATT_ERR_MMA);
     }
   } else {
-    // ---------------------------------------------------------------- softmax and output (8 warps a head)
-    const int tile = (warp - 2) >> 3;                // which of the CTA's heads
+    // ---------------------------------------------------------------- softmax and output (4 warps a head, a thread a row)
+    const int tile = (warp - 2) >> 2;                // which of the CTA's heads
     const int head = head0 + tile;
     const int lane_group = warp & 3;                 // the tensor-memory lanes this warp may read
-    const int half = ((warp - 2) >> 2) & 1;          // keys 0..31 or 32..63 of a page
     const int row = lane_group * 32 + lane;          // query row inside the tile
     const int pos = past + t0 + row;
     const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
     const float sl2 = a.scale * LOG2E;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    // The two warps that share a lane group (the two halves of 32 rows of a head) synchronise among
-    // themselves on a named barrier of their own; the mbarriers they signal expect one arrival per pair.
-    const bool pair_leader = half == 0 && lane == 0;
-    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(2 + tile * 4 + lane_group) : "memory"); };
     const uint32_t my_p_full = p_full + 16 * tile, my_pv_done = pv_done + 8 * tile;
+    const uint32_t o_addr = tmem_base + lane_addr + O_COL(tile);
 
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1, st = j % NST;
+      const int b = j & 1;
       if (!mbar_wait(s_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; break; }
       tc_fence_after();
-      // Two passes over this thread's 32 scores, 16 at a time, to keep few registers live: the
-      // maximum first, then (after the exchange with the other half of the row) the exponentials.
-      const uint32_t s_addr = tmem_base + lane_addr + S_COL(tile, b) + half * 32;
-      const int kbase = j * BNK + half * 32;
-      const bool all_visible = kbase + 31 <= pos;
+      const uint32_t s_addr = tmem_base + lane_addr + S_COL(tile, b);
+      float s[BNK];
+      tmem_ld64(s_addr, s);
+      const int kbase = j * BNK;
       float mx = -INFINITY;
+      if (kbase + BNK - 1 <= pos) {
 #pragma unroll
-      for (int c = 0; c < 32; c += 16) {
-        float s[16];
-        tmem_ld16(s_addr + c, s);
+        for (int i = 0; i < BNK; ++i) mx = fmaxf(mx, s[i]);
+      } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) mx = fmaxf(mx, (all_visible || kbase + c + i <= pos) ? s[i] : -INFINITY);
+        for (int i = 0; i < BNK; ++i) { if (kbase + i > pos) s[i] = -INFINITY; mx = fmaxf(mx, s[i]); }
       }
-      row_max[tile][half][row] = mx * sl2;   // sl2 > 0: the maximum of the scaled scores
-      pair_sync();                            // maxima exchanged
-      const float m_tile = fmaxf(row_max[tile][0][row], row_max[tile][1][row]);    // finite: key 0 is visible to every row
       // Raise the maximum this row's P is taken against only when it is exceeded by a wide margin;
       // what O holds for the row was taken against the old one and is scaled down first.  The
       // tensor-memory accesses are warp-wide, so the warp goes through them together whenever
-      // one of its rows needs it (the others scale by 1); the partner warp sees the same rows.
+      // one of its rows needs it (the others scale by 1).  A row that sees no key of this page
+      // (mx = -inf) needs nothing and gets P = 0.
+      const float m_tile = mx * sl2;                 // sl2 > 0
       const bool need = m_tile > m_used + RESCALE_THRESHOLD;
       const float alpha = need ? exp2f(m_used - m_tile) : 1.f;
       if (j > 0 && __any_sync(0xffffffffu, need)) {
         if (!mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_ptr)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < D / 2; c += 16) {
-          float v[16];
-          tmem_ld16(tmem_base + lane_addr + O_COL(tile) + half * (D / 2) + c, v);
+        for (int c = 0; c < D; c += 32) {
+          float v[32];
+          tmem_ld32(o_addr + c, v);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] *= alpha;
-          tmem_st16(tmem_base + lane_addr + O_COL(tile) + half * (D / 2) + c, v);
+          for (int i = 0; i < 32; ++i) v[i] *= alpha;
+          tmem_st32(o_addr + c, v);
         }
       }
       if (need) { l *= alpha; m_used = m_tile; }
-      // P_j: row `row`, keys half*32 .. +31 = 16-byte chunks half*4 .. +3 of the 128-byte row, swizzled.
-      // The first head writes over K_j (both heads' S_j have consumed it), the second into its own buffer.
-      uint8_t* prow = (tile == 0 ? kv_smem + (size_t)st * STAGE_BYTES : p1_smem + b * P_BYTES) + row * 128;
+      // P_j: pairs of bf16 over the first 32 columns of this row's scores (masked scores are -inf: 0)
+      uint32_t packed[BNK / 2];
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 32; c += 16) {
-        float s[16];
-        tmem_ld16(s_addr + c, s);
-        uint32_t packed[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const bool v0 = all_visible || kbase + c + 2 * i <= pos, v1 = all_visible || kbase + c + 2 * i + 1 <= pos;
-          const float p0 = v0 ? fast_exp2(fmaf(s[2 * i], sl2, -m_used)) : 0.f;
-          const float p1 = v1 ? fast_exp2(fmaf(s[2 * i + 1], sl2, -m_used)) : 0.f;
-          sum += p0 + p1;
-          __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-          packed[i] = *(uint32_t*)&pr;
-        }
-        const int chunk0 = (half * 4 + c / 8) ^ (row & 7), chunk1 = (half * 4 + c / 8 + 1) ^ (row & 7);
-        *(uint4*)(prow + chunk0 * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        *(uint4*)(prow + chunk1 * 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      for (int i = 0; i < BNK / 2; ++i) {
+        const float p0 = fast_exp2(fmaf(s[2 * i], sl2, -m_used));
+        const float p1 = fast_exp2(fmaf(s[2 * i + 1], sl2, -m_used));
+        sum += p0 + p1;
+        __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+        packed[i] = *(uint32_t*)&pr;
       }
       l += sum;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P visible to the tensor core's reads
+      tmem_st32_packed(s_addr, packed);
       // A parity wait tells two phases apart, no more.  Page j-1's product cannot have been followed by
-      // page j's yet (that one needs this pair's P_j), so here its phase is the current or the last
-      // one; seen complete here, it keeps every later wait on this barrier (the next page's rescale,
-      // the output's) within one phase of the barrier's state, however far the pairs drift apart.
+      // page j's yet (that one needs this warp's P_j), so here its phase is the current or the last one;
+      // seen complete here, it keeps every later wait on this barrier within one phase of its state.
       if (j > 0 && !mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_ptr)) { ok = false; break; }
       tc_fence_before();
-      pair_sync();                            // both halves have read S_j for the last time and written P_j
-      if (pair_leader) { mbar_arrive(s_empty + 8 * b); mbar_arrive(my_p_full + 8 * b); }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_p_full + 8 * b);
     }
     if (ok && !mbar_wait(my_pv_done, (uint32_t)(n_tiles - 1) & 1u, abort_ptr)) ok = false;
     tc_fence_after();
     if (!ok && lane == 0) atomicCAS(a.status, 0, ATT_ERR_SOFTMAX);
-    // total row sum = the two halves' sums (both taken against the same maxima)
-    row_max[tile][half][row] = l;
-    pair_sync();
-    const float total = row_max[tile][0][row] + row_max[tile][1][row];
     if (ok) {
-      const float inv = total > 0.f ? 1.f / total : 0.f;
-      bf16* dst = a.out + ((size_t)(q_begin + t0 + row) * a.nq + head) * D + half * (D / 2);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = a.out + ((size_t)(q_begin + t0 + row) * a.nq + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 2; c += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + lane_addr + O_COL(tile) + half * (D / 2) + c, v);     // every thread of the warp loads
+      for (int c = 0; c < D; c += 32) {
+        float v[32];
+        tmem_ld32(o_addr + c, v);                    // every thread of the warp loads
         if (row < nt) {
 #pragma unroll
-          for (int i = 0; i < 16; i += 8) {
+          for (int i = 0; i < 32; i += 8) {
             uint32_t w[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -509,6 +510,22 @@ extern "C" int odi_attention_tcgen05_head_dim() { return D; }
 
 // q [n_tokens, nq * D] bf16; k_pool, v_pool [pool_pages, nkv, 64, D] bf16; out [n_tokens, nq * D].
 // heads_per_cta: 2 = two heads of a key/value group per CTA (needs an even group size), 1 = one, 0 = choose.
+template <int TILES>
+static int launch_attention(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnArgs& a,
+                            int max_q_len, cudaStream_t stream) {
+  const int smem = TILES * Q_BYTES + 2 * RING * KV_BYTES + 1024;
+  auto kernel = attention_tcgen05_kernel<TILES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(a.nq / TILES, a.n_seqs, (max_q_len + BM - 1) / BM);
+  odi_rc = launch_pdl((kernel), dim3(grid), dim3(64 + 128 * TILES), smem, stream, mq, mk, mv, a);
+  return launch_status();
+}
+
 extern "C" int odi_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const TcAttnArgs* args,
                                      int n_tokens, int max_q_len, long pool_pages, int heads_per_cta,
                                      cudaStream_t stream) {
@@ -518,30 +535,15 @@ extern "C" int odi_attention_tcgen05(const void* q, const void* k_pool, const vo
   if (((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) || ((uintptr_t)a.out & 15))
     return ODI_ERR_UNSUPPORTED;
   if (pool_pages * a.nkv * BNK > 0x7fffffffL) return ODI_ERR_UNSUPPORTED;    // row coordinates are 32-bit
+  if ((max_q_len + BM - 1) / BM > 65535) return ODI_ERR_UNSUPPORTED;
+  if (heads_per_cta < 0 || heads_per_cta > 2) return ODI_ERR_ARGUMENT;
+  if (heads_per_cta == 2 && (a.nq / a.nkv) % 2 != 0) return ODI_ERR_ARGUMENT;
   CUtensorMap mq, mk, mv;
   int rc = make_map(&mq, q, n_tokens, (long)a.nq * D, BM);
   if (rc == 0) rc = make_map(&mk, k_pool, pool_pages * a.nkv * BNK, D, BNK);
   if (rc == 0) rc = make_map(&mv, v_pool, pool_pages * a.nkv * BNK, D, BNK);
   if (rc != 0) return rc;
-  static bool configured = false;
-  const int smem1 = Q_BYTES + NST * STAGE_BYTES + 1024;
-  const int smem2 = 2 * Q_BYTES + NST * STAGE_BYTES + 2 * P_BYTES + 1024;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  if (heads_per_cta == 2 && (a.nq / a.nkv) % 2 != 0) return ODI_ERR_ARGUMENT;
-  if ((max_q_len + BM - 1) / BM > 65535) return ODI_ERR_UNSUPPORTED;
   if (heads_per_cta == 0) heads_per_cta = ODI_ATT_DEFAULT_HEADS_PER_CTA;
-  if (heads_per_cta == 2 && (a.nq / a.nkv) % 2 == 0) {
-    dim3 grid(a.nq / 2, a.n_seqs, (max_q_len + BM - 1) / BM);
-    odi_rc = launch_pdl((attention_tcgen05_kernel<2>), dim3(grid), dim3(64 + 512), smem2, stream, mq, mk, mv, a);
-  } else {
-    dim3 grid(a.nq, a.n_seqs, (max_q_len + BM - 1) / BM);
-    odi_rc = launch_pdl((attention_tcgen05_kernel<1>), dim3(grid), dim3(64 + 256), smem1, stream, mq, mk, mv, a);
-  }
-  return launch_status();
+  return heads_per_cta == 2 ? launch_attention<2>(mq, mk, mv, a, max_q_len, stream)
+                            : launch_attention<1>(mq, mk, mv, a, max_q_len, stream);
 }
