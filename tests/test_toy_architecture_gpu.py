@@ -1,9 +1,10 @@
-"""The framework is open: a mixer with state of its own and a whole architecture are
-defined HERE, registered, built, loaded from a random model folder and stepped without
-touching the library's files.  The architecture mixes what the Qwen3 plan never does: a
-stateful mixer, a windowed attention layer beside full ones (two cache groups plus a
-state group), a layer that runs twice, and a layer execution that reads the cache of an
-earlier one.  It is a toy for this test only."""
+"""The framework is open: a mixer with state of its own, a feed-forward with routing, a position
+encoding and a whole architecture are defined HERE, registered, built, loaded from a random model
+folder and stepped without touching the library's files.  The architecture mixes what the Qwen3
+plan never does: a stateful mixer, a windowed attention layer beside full ones (two cache groups
+plus a state group), a layer that runs twice, a layer execution that reads the cache of an earlier
+one, and a layer whose attention rotates by half positions and whose feed-forward sends each token
+to one of three experts.  It is a toy for this test only."""
 
 import json
 import math
@@ -65,6 +66,79 @@ class DecayMixer:
             offset += n
 
 
+# ----------------------------------------------------------------------------- a toy position encoding
+
+
+@dataclass(frozen=True)
+class HalfStepRotarySpec:
+    rot_dim: int
+    theta: float
+
+
+class HalfStepRotary:
+    """Rotary embedding whose angle advances by half a step per position (position interpolation)."""
+
+    def __init__(self, spec):
+        self.spec = spec
+        self.rot_dim = spec.rot_dim
+
+    def tensor_decls(self):
+        return []
+
+    def load(self, fetch, runtime):
+        d = self.spec.rot_dim
+        self.inv_freq = (1.0 / (self.spec.theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(runtime.device)
+
+    def rotary_tables(self, ctx):
+        def make():
+            angles = (ctx.tok_pos.float() * 0.5)[:, None] * self.inv_freq[None, :]
+            return torch.cos(angles).contiguous(), torch.sin(angles).contiguous()
+        return ctx.memo(("half-step rotary", self.spec), make)
+
+
+# ----------------------------------------------------------------------------- a toy feed-forward with routing
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    intermediate_size: int
+    experts: int
+    prefix: str
+
+
+class RoutedFeedForward:
+    """Each token goes to the expert with the largest router logit (fp32), whose gated MLP output is
+    scaled by that expert's softmax probability and added to the residual."""
+
+    def __init__(self, spec):
+        self.spec = spec
+
+    def tensor_decls(self):
+        s = self.spec
+        decls = [TensorDecl(s.prefix + "router", (s.experts, s.hidden_size))]
+        for e in range(s.experts):
+            decls += [TensorDecl(f"{s.prefix}{e}.g", (s.intermediate_size, s.hidden_size)),
+                      TensorDecl(f"{s.prefix}{e}.u", (s.intermediate_size, s.hidden_size)),
+                      TensorDecl(f"{s.prefix}{e}.d", (s.hidden_size, s.intermediate_size))]
+        return decls
+
+    def load(self, fetch, runtime):
+        s = self.spec
+        self.router = fetch.matrix(s.prefix + "router").float()
+        self.experts = [tuple(fetch.matrix(f"{s.prefix}{e}.{n}").float() for n in "gud") for e in range(s.experts)]
+
+    def forward(self, x, ctx, residual):
+        x = x.float()
+        prob = torch.softmax(x @ self.router.t(), -1)
+        weight, choice = prob.max(-1)
+        for e, (g, u, d) in enumerate(self.experts):
+            rows = torch.nonzero(choice == e).flatten()
+            if rows.numel():
+                y = (torch.nn.functional.silu(x[rows] @ g.t()) * (x[rows] @ u.t())) @ d.t()
+                residual[rows] += weight[rows, None] * y
+
+
 # ----------------------------------------------------------------------------- a toy architecture
 
 
@@ -94,9 +168,14 @@ class ToyConfig:
             return PreNormBlockSpec(RMSNormSpec(H, self.eps, f"l{i}.n1"), mixer, RMSNormSpec(H, self.eps, f"l{i}.n2"),
                                     GatedMLPSpec(H, 2 * H, "silu", f"l{i}.ff.", names(gate="g", up="u", down="d")))
 
+        routed = PreNormBlockSpec(
+            RMSNormSpec(H, self.eps, "l3.n1"),
+            AttentionSpec(H, 3, 3, 16, HalfStepRotarySpec(16, 500.0), "l3.attn.",
+                          names(q="q", k="k", v="v", o="o", q_norm="qn", k_norm="kn"), qk_norm_eps=self.eps),
+            RMSNormSpec(H, self.eps, "l3.n2"), RoutedSpec(H, 40, 3, "l3.moe."))
         layers = (block(0, attention(0, None, 4, 2, 16)), block(1, DecaySpec(H, 0.9, "l1.mix")),
-                  block(2, attention(2, WINDOW, 2, 1, 32)))
-        order = (OrderEntry(0), OrderEntry(1), OrderEntry(2), OrderEntry(0), OrderEntry(2, cache_from=2))
+                  block(2, attention(2, WINDOW, 2, 1, 32)), routed)
+        order = (OrderEntry(0), OrderEntry(1), OrderEntry(2), OrderEntry(0), OrderEntry(2, cache_from=2), OrderEntry(3))
         return ModelPlan(EmbeddingSpec(self.vocab_size, H, "emb"), layers, order, RMSNormSpec(H, self.eps, "nf"),
                          HeadSpec(self.vocab_size, H, None))
 
@@ -111,12 +190,12 @@ def toy_plain_logits(w, ids):
     h = w["emb"][torch.tensor(ids)]
     pos = torch.arange(T)
 
-    def qkv(i, x, nq, nkv, d):
+    def qkv(i, x, nq, nkv, d, theta=3000.0, step=1.0):
         p = f"l{i}.attn."
         q = plain.rms_norm(plain.linear(x, w[p + "q"]).view(T, nq, d), w[p + "qn"], eps).transpose(0, 1)
         k = plain.rms_norm(plain.linear(x, w[p + "k"]).view(T, nkv, d), w[p + "kn"], eps).transpose(0, 1)
         v = plain.linear(x, w[p + "v"]).view(T, nkv, d).transpose(0, 1)
-        cos, sin = plain.rope_tables(pos, d, 3000.0, torch.float32)
+        cos, sin = plain.rope_tables(pos.float() * step, d, theta, torch.float32)
         return plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v
 
     def attend(i, q, k, v, window):
@@ -152,12 +231,27 @@ def toy_plain_logits(w, ids):
     h, kv2 = attention_layer(2, h, 2, 1, 32, WINDOW)
     h, _ = attention_layer(0, h, 4, 2, 16, None)               # the same layer again, on its own cache
     h, _ = attention_layer(2, h, 2, 1, 32, WINDOW, shared=kv2)  # reads the third execution's keys and values
+    # half-step rotation, then a routed feed-forward
+    q, k, v = qkv(3, plain.rms_norm(h, w["l3.n1"], eps), 3, 3, 16, theta=500.0, step=0.5)
+    h = h + attend(3, q, k, v, None)
+    m = plain.rms_norm(h, w["l3.n2"], eps)
+    prob = torch.softmax(m @ w["l3.moe.router"].t(), -1)
+    weight, choice = prob.max(-1)
+    routed = torch.zeros_like(h)
+    for t in range(T):
+        e = int(choice[t])
+        y = plain.linear(torch.nn.functional.silu(plain.linear(m[t:t + 1], w[f"l3.moe.{e}.g"])) *
+                         plain.linear(m[t:t + 1], w[f"l3.moe.{e}.u"]), w[f"l3.moe.{e}.d"])
+        routed[t] = weight[t] * y[0]
+    h = h + routed
     return plain.linear(plain.rms_norm(h, w["nf"], eps), w["emb"])
 
 
 @pytest.fixture(scope="module")
 def toy(tmp_path_factory):
     register_part(DecaySpec, DecayMixer)
+    register_part(HalfStepRotarySpec, HalfStepRotary)
+    register_part(RoutedSpec, RoutedFeedForward)
     register_architecture("ToyForCausalLM", ToyConfig)
     folder = write_random_model(tmp_path_factory.mktemp("toy"), TOY, seed=5)
     source = SafetensorsSource(folder)
@@ -165,16 +259,17 @@ def toy(tmp_path_factory):
     return folder, weights
 
 
-def test_registered_toy_is_built_with_three_cache_groups(toy):
+def test_registered_toy_is_built_with_its_cache_groups(toy):
     folder, weights = toy
     assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
-    assert "l1.mix" in weights and "l2.attn.kn" in weights
+    assert "l1.mix" in weights and "l2.attn.kn" in weights and "l3.moe.router" in weights and "l3.moe.2.d" in weights
     model = load_resident_model(folder, dtype="float32")
     cache = model.make_cache(max_tokens=1024, max_seqs=2)
-    assert len(cache.kv_groups) == 2 and len(cache.state_groups) == 1
+    assert len(cache.kv_groups) == 3 and len(cache.state_groups) == 1
     windowed = next(g for g in cache.kv_groups if g.need.window == WINDOW)
-    full = next(g for g in cache.kv_groups if g.need.window is None)
-    assert full.owners == [0, 3] and windowed.owners == [2] and cache.state_groups[0].owners == [1]
+    full = next(g for g in cache.kv_groups if g.need.window is None and g.need.num_kv_heads == 2)
+    routed = next(g for g in cache.kv_groups if g.need.num_kv_heads == 3)
+    assert full.owners == [0, 3] and windowed.owners == [2] and routed.owners == [5] and cache.state_groups[0].owners == [1]
     assert cache.max_step_tokens == 256 and windowed.ring_pages > 0
 
 
