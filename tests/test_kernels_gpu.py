@@ -485,20 +485,21 @@ def test_gemm_tcgen05_norm_prologue_and_sums_of_squares(tokens, H, N, tile, spli
     close(fused, expected, "bfloat16")
 
 
-@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,lazy", [
-    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, True),     # a decode step, a cluster per head
-    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, False),
-    ([3, 1, 16], [0, 200, 10], 256, 4, 2, True, True, False),                          # a short K: one split, 32 columns
-    ([3, 1, 16], [0, 200, 10], 256, 4, 2, False, False, True),                         # neither norm nor rotation
-    ([1, 1, 1], [70, 2, 900], 1024, 6, 3, True, False, True),
-    ([5, 6], [0, 64], 2048, 2, 1, False, True, False),
+@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,lazy,ring", [
+    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, True, 0),     # a decode step, a cluster per head
+    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, False, 0),
+    ([3, 1, 16], [0, 200, 10], 256, 4, 2, True, True, False, 0),                          # a short K: one split, 32 columns
+    ([3, 1, 16], [0, 200, 10], 256, 4, 2, False, False, True, 0),                         # neither norm nor rotation
+    ([1, 1, 1], [70, 2, 900], 1024, 6, 3, True, False, True, 0),
+    ([5, 6], [0, 64], 2048, 2, 1, False, True, False, 0),
+    ([1, 1, 2], [500, 130, 62], 512, 4, 2, True, True, True, 2),                          # a ring of two pages per sequence
 ])
-def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, lazy):
+def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, lazy, ring):
     """The q/k/v product with the head preparation in its epilogue against the product followed by the
     head-preparation kernel: the same bits in the queries and in the cache, nothing written elsewhere."""
     torch.manual_seed(23)
     d = 128
-    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=24)
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", ring_pages=ring, seed=24)
     n = sum(lengths)
     w = (torch.randn((nq + 2 * nkv) * d, K) / math.sqrt(K)).bfloat16().to(DEV)
     qw = (1 + 0.1 * torch.randn(d)).to(DEV) if norm else None
@@ -517,7 +518,7 @@ def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, 
     padded = torch.zeros(n, parts.shape[0] * 128, device=DEV)
     padded[:, :K] = rows
     parts.copy_((padded.view(n, -1, 128) ** 2).sum(-1).t())
-    common = dict(nq=nq, nkv=nkv, d=d, rot_dim=d if rot else 0, page_size=64, ring_pages=0, write_kv=True, eps=1e-5)
+    common = dict(nq=nq, nkv=nkv, d=d, rot_dim=d if rot else 0, page_size=64, ring_pages=ring, write_kv=True, eps=1e-5)
     tail = (qw, kw, cos, sin, setup["tok_seq"], setup["tok_pos"], setup["page_start"], setup["page_ids"])
 
     qkv = torch.empty(n, w.shape[0], dtype=torch.bfloat16, device=DEV)
