@@ -31,7 +31,10 @@
 // swizzled over the consumed K tile, two threads per row): 578 / 719 TFLOP/s; its K slot stayed
 // busy until the product, and the MMA thread spent 40 % of a page's time waiting for the next keys.
 // Two heads of a key/value group per CTA (K/V pages loaded once for both) measured slower
-// (676 / 823) and stays an option.  Warps: 0 = TMA producer, 1 = MMA issuer (one thread) and
+// (676 / 823) and stays an option; so did a form with two heads per CTA and keys in blocks of two
+// pages (scores as N = 128 products into a single buffer per head: 700 / 856): with a thread per
+// row the exponentials take about as long as the MMAs (512 cycles per page and head each), and one
+// CTA per SM overlaps the two less well than two CTAs do.  Warps: 0 = TMA producer, 1 = MMA issuer (one thread) and
 // tensor-memory owner, 2..5 = softmax and output of the first head, 6..9 = of the second.
 //
 // Works for any q_len >= 1 on top of any cached length (query t of the step sits at position
@@ -247,6 +250,85 @@ __device__ __forceinline__ void umma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, ui
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// One query row, 64 keys: the row's scores at s_addr (tensor memory, this thread's lane) become P (bf16
+// pairs, 32 columns at p_addr) against the row's running maximum; n counts this head's PV products
+// (the one that will read this P is product n), kbase is the first key's position.  Returns false if a
+// wait gave up.  The caller signals P afterwards.
+struct RowState { float m_used, l; };
+__device__ __forceinline__ bool softmax_keys64(uint32_t s_addr, uint32_t p_addr, uint32_t o_addr, int kbase, int pos, float sl2,
+                                               int n, uint32_t pv_done, RowState& st, volatile int* abort_ptr) {
+  float s[BNK];
+  tmem_ld64(s_addr, s);
+  float mx = -INFINITY;
+  if (kbase + BNK - 1 <= pos) {
+#pragma unroll
+    for (int i = 0; i < BNK; ++i) mx = fmaxf(mx, s[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < BNK; ++i) { if (kbase + i > pos) s[i] = -INFINITY; mx = fmaxf(mx, s[i]); }
+  }
+  // Raise the maximum this row's P is taken against only when it is exceeded by a wide margin;
+  // what O holds for the row was taken against the old one and is scaled down first.  The
+  // tensor-memory accesses are warp-wide, so the warp goes through them together whenever
+  // one of its rows needs it (the others scale by 1).  A row that sees none of these keys
+  // (mx = -inf) needs nothing and gets P = 0.
+  const float m_tile = mx * sl2;                 // sl2 > 0
+  const bool need = m_tile > st.m_used + RESCALE_THRESHOLD;
+  const float alpha = need ? exp2f(st.m_used - m_tile) : 1.f;
+  if (n > 0 && __any_sync(0xffffffffu, need)) {
+    if (!mbar_wait(pv_done, (uint32_t)(n - 1) & 1u, abort_ptr)) return false;
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < D; c += 32) {
+      float v[32];
+      tmem_ld32(o_addr + c, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= alpha;
+      tmem_st32(o_addr + c, v);
+    }
+  }
+  if (need) { st.l *= alpha; st.m_used = m_tile; }
+  uint32_t packed[BNK / 2];                      // masked scores are -inf: exp2 gives 0
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < BNK / 2; ++i) {
+    const float p0 = fast_exp2(fmaf(s[2 * i], sl2, -st.m_used));
+    const float p1 = fast_exp2(fmaf(s[2 * i + 1], sl2, -st.m_used));
+    sum += p0 + p1;
+    __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+    packed[i] = *(uint32_t*)&pr;
+  }
+  st.l += sum;
+  tmem_st32_packed(p_addr, packed);
+  // A parity wait tells two phases apart, no more.  Product n-1 cannot have been followed by product n
+  // yet (that one needs this warp's P), so here its phase is the current or the last one; seen complete
+  // here, it keeps every later wait on this barrier within one phase of its state.
+  if (n > 0 && !mbar_wait(pv_done, (uint32_t)(n - 1) & 1u, abort_ptr)) return false;
+  return true;
+}
+
+// The finished row of O, divided by the row's sum, as bf16 to dst (D elements).
+__device__ __forceinline__ void write_row(uint32_t o_addr, bf16* dst, float l, bool valid) {
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll 1
+  for (int c = 0; c < D; c += 32) {
+    float v[32];
+    tmem_ld32(o_addr + c, v);                    // every thread of the warp loads
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          __nv_bfloat162 pr = __floats2bfloat162_rn(v[i + 2 * k] * inv, v[i + 2 * k + 1] * inv);
+          w[k] = *(uint32_t*)&pr;
+        }
+        *(uint4*)(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+}
+
 template <int TILES>
 __global__ void __launch_bounds__(64 + 128 * TILES, TILES == 1 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -378,7 +460,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int pos = past + t0 + row;
     const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
     const float sl2 = a.scale * LOG2E;
-    float m_used = -INFINITY, l = 0.f;
+    RowState st = {-INFINITY, 0.f};
     bool ok = true;
     const uint32_t my_p_full = p_full + 16 * tile, my_pv_done = pv_done + 8 * tile;
     const uint32_t o_addr = tmem_base + lane_addr + O_COL(tile);
@@ -388,55 +470,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!mbar_wait(s_full + 8 * b, (uint32_t)(j >> 1) & 1u, abort_ptr)) { ok = false; break; }
       tc_fence_after();
       const uint32_t s_addr = tmem_base + lane_addr + S_COL(tile, b);
-      float s[BNK];
-      tmem_ld64(s_addr, s);
-      const int kbase = j * BNK;
-      float mx = -INFINITY;
-      if (kbase + BNK - 1 <= pos) {
-#pragma unroll
-        for (int i = 0; i < BNK; ++i) mx = fmaxf(mx, s[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < BNK; ++i) { if (kbase + i > pos) s[i] = -INFINITY; mx = fmaxf(mx, s[i]); }
-      }
-      // Raise the maximum this row's P is taken against only when it is exceeded by a wide margin;
-      // what O holds for the row was taken against the old one and is scaled down first.  The
-      // tensor-memory accesses are warp-wide, so the warp goes through them together whenever
-      // one of its rows needs it (the others scale by 1).  A row that sees no key of this page
-      // (mx = -inf) needs nothing and gets P = 0.
-      const float m_tile = mx * sl2;                 // sl2 > 0
-      const bool need = m_tile > m_used + RESCALE_THRESHOLD;
-      const float alpha = need ? exp2f(m_used - m_tile) : 1.f;
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
-        if (!mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_ptr)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
-          float v[32];
-          tmem_ld32(o_addr + c, v);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= alpha;
-          tmem_st32(o_addr + c, v);
-        }
-      }
-      if (need) { l *= alpha; m_used = m_tile; }
-      // P_j: pairs of bf16 over the first 32 columns of this row's scores (masked scores are -inf: 0)
-      uint32_t packed[BNK / 2];
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < BNK / 2; ++i) {
-        const float p0 = fast_exp2(fmaf(s[2 * i], sl2, -m_used));
-        const float p1 = fast_exp2(fmaf(s[2 * i + 1], sl2, -m_used));
-        sum += p0 + p1;
-        __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-        packed[i] = *(uint32_t*)&pr;
-      }
-      l += sum;
-      tmem_st32_packed(s_addr, packed);
-      // A parity wait tells two phases apart, no more.  Page j-1's product cannot have been followed by
-      // page j's yet (that one needs this warp's P_j), so here its phase is the current or the last one;
-      // seen complete here, it keeps every later wait on this barrier within one phase of its state.
-      if (j > 0 && !mbar_wait(my_pv_done, (uint32_t)(j - 1) & 1u, abort_ptr)) { ok = false; break; }
+      // P_j goes over the first 32 columns of this row's scores
+      if (!softmax_keys64(s_addr, s_addr, o_addr, j * BNK, pos, sl2, j, my_pv_done, st, abort_ptr)) { ok = false; break; }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(my_p_full + 8 * b);
@@ -444,27 +479,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (ok && !mbar_wait(my_pv_done, (uint32_t)(n_tiles - 1) & 1u, abort_ptr)) ok = false;
     tc_fence_after();
     if (!ok && lane == 0) atomicCAS(a.status, 0, ATT_ERR_SOFTMAX);
-    if (ok) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = a.out + ((size_t)(q_begin + t0 + row) * a.nq + head) * D;
-#pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        float v[32];
-        tmem_ld32(o_addr + c, v);                    // every thread of the warp loads
-        if (row < nt) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              __nv_bfloat162 pr = __floats2bfloat162_rn(v[i + 2 * k] * inv, v[i + 2 * k + 1] * inv);
-              w[k] = *(uint32_t*)&pr;
-            }
-            *(uint4*)(dst + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-      }
-    }
+    if (ok) write_row(o_addr, a.out + ((size_t)(q_begin + t0 + row) * a.nq + head) * D, st.l, row < nt);
     tc_fence_before();
   }
   __syncthreads();
