@@ -68,6 +68,7 @@ class DecodeRunner:
         self.ctx: Optional[_DecodeContext] = None
         self._host_pages: List[np.ndarray] = []
         self._pinned_tokens: Optional[torch.Tensor] = None
+        self._pinned_out: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ set-up
 
@@ -177,7 +178,12 @@ class DecodeRunner:
             self._pinned_tokens[:n] = torch.as_tensor(host_tokens, dtype=torch.int32)
             self.ctx.token_ids[:n].copy_(self._pinned_tokens[:n], non_blocking=True)
         self.step_device(1)
-        return self.ctx.token_ids[:n].tolist()
+        # the sampled tokens back through pinned memory: one asynchronous copy, one wait on the stream
+        if self._pinned_out is None or self._pinned_out.numel() < n:
+            self._pinned_out = torch.empty(max(n, 64), dtype=torch.int32).pin_memory()
+        self._pinned_out[:n].copy_(self.ctx.token_ids[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._pinned_out[:n].tolist()
 
     def drop(self, finished_rows: Sequence[int], streams: Sequence[int], steps: Sequence[int]) -> None:
         """Remove rows (indices into the live set) and continue with the others; ``streams``
