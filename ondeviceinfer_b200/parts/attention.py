@@ -1,11 +1,11 @@
 """Grouped-query causal attention over the paged cache
 (ondeviceinfer/attention.py:88-177 of UESlubei/ondeviceinfer).
 
-Steps of ``forward``: one matrix product for the concatenated q, k, v projections; one
-fused kernel for the per-head Q/K RMSNorm, the rotary embedding and the cache write;
-attention over the cache pages of each sequence; the output projection with the
-residual add.  Head counts, head size, eps, window, scale and the position encoding are
-all fields of the spec.
+Steps of ``forward``: one matrix product for the concatenated q, k, v projections; the
+per-head Q/K RMSNorm, the rotary embedding and the cache write (a fused kernel of their own,
+or, at decode widths with heads of 128, the epilogue of that product); attention over the
+cache pages of each sequence; the output projection with the residual add.  Head counts,
+head size, eps, window, scale and the position encoding are all fields of the spec.
 """
 
 from __future__ import annotations
