@@ -8,7 +8,7 @@ graph, and replays it: the sampled token is written where the next step reads it
 input, and the sampling kernel advances positions, lengths and step numbers in place.
 Per step the host only makes sure every sequence has a page for its next position.
 
-Widths are powers of two; rows beyond the live sequences are padding: they run on a
+Widths are powers of two up to 32, then multiples of 16; rows beyond the live sequences are padding: they run on a
 slot outside the cache's capacity with a constant length of zero and their results are dropped, so
 padding changes no result.  The same kernels run as in the generic step; only the way
 they are launched differs.  Models with parts that do host work per step (anything that
@@ -77,6 +77,10 @@ class DecodeRunner:
 
     @staticmethod
     def _width_for(n: int) -> int:
+        """Captured widths: powers of two up to 32, then multiples of 16 (the padding rows cost a full
+        row of every kernel, so a batch of 33 should not run as 64)."""
+        if n > 32:
+            return -(-n // 16) * 16
         width = 1
         while width < n:
             width *= 2
