@@ -344,8 +344,9 @@ __global__ void silu_mul_vec_kernel(const bf16* __restrict__ gu, bf16* __restric
   __nv_bfloat162* o2 = (__nv_bfloat162*)&ov;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
+    // fast exponential and division: their error (a few ulp of fp32) is far below the bf16 rounding of the result
     const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-    o2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
   }
   *(uint4*)(out + t * I + i) = ov;
 }
