@@ -154,3 +154,10 @@ def test_fused_decoder_is_told_when_the_live_set_changes():
     assert decoder.begins[0][1] == [10, 20, 30] and decoder.begins[0][3] == [1, 1, 1]
     assert decoder.begins[1][1] == [11, 31] and decoder.begins[1][3] == [2, 2]
     assert result.decode_steps == 3 and not script.held
+
+
+def test_decode_widths_pad_little_above_32():
+    """Captured decode widths: powers of two up to 32, multiples of 16 beyond (33 must not run as 64)."""
+    from ondeviceinfer_b200.engine.decode import DecodeRunner
+    widths = {n: DecodeRunner._width_for(n) for n in (1, 2, 3, 8, 9, 17, 32, 33, 48, 49, 64, 65, 100)}
+    assert widths == {1: 1, 2: 2, 3: 4, 8: 8, 9: 16, 17: 32, 32: 32, 33: 48, 48: 48, 49: 64, 64: 64, 65: 80, 100: 112}
