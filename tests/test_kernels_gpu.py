@@ -435,6 +435,7 @@ NORM_GEMM_SHAPES = [
     # tokens, hidden (the normed rows' width), features of the product that consumes them, tile, splits
     (8, 4096, 6144, None, None), (1, 200, 389, None, None), (16, 1000, 520, 16, 1), (5, 136, 256, 16, 2),
     (32, 4096, 1024, None, None), (20, 520, 640, 32, 3), (3, 64, 128, 16, 1),
+    (1, 8, 8, None, None), (32, 72, 136, None, None), (17, 4104, 200, None, None),      # one k-block; widths off every tile edge
 ]
 
 
