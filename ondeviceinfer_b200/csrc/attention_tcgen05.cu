@@ -32,9 +32,10 @@
 // busy until the product, and the MMA thread spent 40 % of a page's time waiting for the next keys.
 // Two heads of a key/value group per CTA (K/V pages loaded once for both) measured slower
 // (676 / 823) and stays an option; so did a form with two heads per CTA and keys in blocks of two
-// pages (scores as N = 128 products into a single buffer per head: 700 / 856): with a thread per
-// row the exponentials take about as long as the MMAs (512 cycles per page and head each), and one
-// CTA per SM overlaps the two less well than two CTAs do.  Warps: 0 = TMA producer, 1 = MMA issuer (one thread) and
+// pages (scores as N = 128 products into a single buffer per head: 700 / 856 issued in a fixed
+// order, 628 / 746 with the MMA thread issuing whichever head was ready): a trace showed its MMA
+// thread blocked on issue for more than half of a block's time, the N = 128 products taking about
+// 125 cycles each and the P V products about 190, twice what they take when two CTAs share the SM.  Warps: 0 = TMA producer, 1 = MMA issuer (one thread) and
 // tensor-memory owner, 2..5 = softmax and output of the first head, 6..9 = of the second.
 //
 // Works for any q_len >= 1 on top of any cached length (query t of the step sits at position
