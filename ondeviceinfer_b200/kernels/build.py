@@ -148,6 +148,7 @@ ALL_SOURCES = {
     "gemm_f32": [{}],
     "sampling": [{}],
     "gemm_tcgen05": [{}],
+    "gemm_prefill_tcgen05": [{}],
     "attention_simt": [{"ODI_HEAD_DIM": 128}],
     "attention_mma": [{"ODI_HEAD_DIM": 128}],
     "attention_tcgen05": [{"ODI_HEAD_DIM": 128}],

@@ -90,6 +90,8 @@ def gemm_case(args) -> dict:
         out = None
     if args.library:
         run = lambda i: torch.matmul(x, ws[i].t())
+    elif args.persistent:
+        run = lambda i: ops.gemm_prefill_bf16(x, ws[i], out, epi)
     else:
         run = lambda i: ops.gemm_bf16(x, ws[i], out, epi, swap=args.swap, bn=args.bn, splits=args.splits,
                                       cluster=not args.no_cluster, **extra)
@@ -180,6 +182,7 @@ def main(argv=None) -> int:
     parser.add_argument("--splits", type=int, default=None)
     parser.add_argument("--swap", type=int, default=None)
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
+    parser.add_argument("--persistent", action="store_true", help="gemm: the persistent kernel for many tokens")
     parser.add_argument("--no-cluster", action="store_true", help="GEMM K splits through global scratch, not a cluster")
     parser.add_argument("--cluster-attention", action="store_true", help="merge decode-attention splits inside a cluster")
     parser.add_argument("--merge-in-kernel", action="store_true",

@@ -248,6 +248,8 @@ def raise_on_kernel_fault() -> None:
     code = gemm_status()
     if code:
         names = {1: "gemm_tcgen05: the TMA producer", 2: "gemm_tcgen05: the MMA issuer", 3: "gemm_tcgen05: the epilogue",
+                 21: "gemm_prefill_tcgen05: the TMA producer", 22: "gemm_prefill_tcgen05: the MMA issuer",
+                 23: "gemm_prefill_tcgen05: the epilogue",
                  11: "attention_tcgen05: the TMA producer", 12: "attention_tcgen05: the MMA issuer",
                  13: "attention_tcgen05: the softmax warps"}
         for state in _gemm_state.values():
@@ -384,6 +386,28 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
                              c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
                              _ptr(sumsq_out), byref(head_prep) if head_prep is not None else _ptr(None), _stream()),
            "gemm_tcgen05")
+
+
+def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> None:
+    """The persistent tensor-core product for many tokens (``csrc/gemm_prefill_tcgen05.cu``): tiles of 128
+    tokens x 256 features, two accumulators in tensor memory so that a tile's epilogue runs under the next
+    tile's MMAs.  Same operands and epilogues as :func:`gemm_bf16` (without ``EPI_HEAD_PREP``)."""
+    _require(x, "x", torch.bfloat16, 2)
+    _require(w, "w", torch.bfloat16, 2)
+    _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
+    tokens, K = x.shape
+    w_rows = w.shape[0]
+    n_out = w_rows // 2 if epi == EPI_SWIGLU else w_rows
+    if epi not in (EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU):
+        raise KernelError(f"gemm_prefill_bf16 has no epilogue {epi}")
+    if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
+        raise KernelError(f"gemm sizes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if not gemm_bf16_supported(x, w):
+        raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
+    _, _, status = _gemm_buffers(w.device, 0)
+    lib = load_library("gemm_prefill_tcgen05")
+    _check(lib.odi_gemm_prefill_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
+                                     c_int(n_out), c_int(epi), _ptr(status), _stream()), "gemm_prefill_tcgen05")
 
 
 # ------------------------------------------------------------------------------ attention

@@ -30,6 +30,26 @@ import os
 OWN_KERNEL_MAX_TOKENS = int(os.environ.get("ODI_OWN_GEMM_MAX_TOKENS", "32"))
 
 
+# The projections of many tokens.  "auto": the library's product, except where the persistent tcgen05
+# kernel with a fused epilogue measured faster than the library's product plus the elementwise kernel it
+# saves (B200, Qwen3-8B sizes, 2,048 tokens: gate/up with the SiLU gate 287 against 274 + 24 us, the
+# output projection with the residual add 53 against 46 + 11 us; not the down projection, 159 against
+# 133 + 11 us, nor anything at 8,192 tokens, where the library reaches 1.5-1.6 PFLOP/s against 1.3-1.4).
+# "own" / "library" force one of them.
+PREFILL_GEMM = os.environ.get("ODI_PREFILL_GEMM", "auto")
+PERSISTENT_MIN_TOKENS, PERSISTENT_MAX_TOKENS = 256, 4096
+
+
+def _persistent(tokens: int, weight: torch.Tensor, x: torch.Tensor, epi: int) -> bool:
+    if PREFILL_GEMM == "library" or not ops.gemm_bf16_supported(x, weight):
+        return False
+    if PREFILL_GEMM == "own":
+        return True
+    if not PERSISTENT_MIN_TOKENS <= tokens <= PERSISTENT_MAX_TOKENS:
+        return False
+    return epi == ops.EPI_SWIGLU or (epi == ops.EPI_RESIDUAL and weight.shape[1] <= weight.shape[0])
+
+
 class NormedRows:
     """``RMSNorm(rows) * weight`` that has not been computed yet.
 
@@ -117,6 +137,14 @@ def linear(x, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
         out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=weight.device)
         ops.gemm_bf16(x, weight, out, epi, norm=norm)
         return out
+    if residual is not None and _persistent(n, weight, x, ops.EPI_RESIDUAL):
+        ops.gemm_prefill_bf16(x, weight, residual, ops.EPI_RESIDUAL)
+        return None
+    if residual is None and PREFILL_GEMM == "own" and _persistent(n, weight, x, ops.EPI_STORE_BF16):
+        wide = out_dtype == torch.float32
+        out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
+        ops.gemm_prefill_bf16(x, weight, out, ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16)
+        return out
     y = torch.matmul(x, weight.t())
     ops.LAUNCHES["library"] += 1
     if residual is not None:
@@ -154,5 +182,8 @@ def gated_linear(x, weight_gate_up: torch.Tensor) -> torch.Tensor:
         return act
     if isinstance(x, NormedRows):
         x = x.materialize()
+    if x.dtype == torch.bfloat16 and _persistent(n, weight_gate_up, x, ops.EPI_SWIGLU):
+        ops.gemm_prefill_bf16(x, weight_gate_up, act, ops.EPI_SWIGLU)
+        return act
     ops.silu_mul(linear(x, weight_gate_up), act)
     return act

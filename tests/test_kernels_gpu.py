@@ -716,3 +716,42 @@ def test_attention_tcgen05_finds_one_far_key():
         assert float((out[tok].float().cpu() - value).abs().max()) < 0.05, (tok, key)
     expected = plain_attention(q, setup["dense"], [700], [0], nq, nkv, d, 0, scale, "bfloat16")
     close(out, expected, "bfloat16")
+
+
+PREFILL_GEMM_SHAPES = [
+    # tokens, features, K: whole tiles, ragged edges in all three sizes, fewer tiles than SMs, many tiles per CTA
+    (128, 256, 64), (2048, 4096, 4096), (300, 520, 200), (33, 1000, 1000), (1030, 1024, 512), (130, 6144, 72),
+    (5000, 389, 96),
+]
+
+
+@pytest.mark.parametrize("epi", ["store_bf16", "store_f32", "residual", "swiglu"])
+@pytest.mark.parametrize("tokens,N,K", PREFILL_GEMM_SHAPES)
+def test_gemm_prefill_tcgen05(tokens, N, K, epi):
+    """The persistent product for many tokens and its four epilogues against fp32 torch on the same
+    bf16 inputs; twice, so that a second launch finds the same result."""
+    code = {"store_bf16": ops.EPI_STORE_BF16, "store_f32": ops.EPI_STORE_F32, "residual": ops.EPI_RESIDUAL,
+            "swiglu": ops.EPI_SWIGLU}[epi]
+    torch.manual_seed(31)
+    x = torch.randn(tokens, K).bfloat16().to(DEV)
+    rows = 2 * N if epi == "swiglu" else N
+    w = (torch.randn(rows, K) / math.sqrt(K)).bfloat16().to(DEV)
+    ref = (x.float() @ w.float().t()).cpu()
+    res = torch.randn(tokens, N)
+    for _ in range(2):
+        if epi == "store_bf16":
+            out, expected = torch.zeros(tokens, N, dtype=torch.bfloat16, device=DEV), ref
+        elif epi == "store_f32":
+            out, expected = torch.zeros(tokens, N, dtype=torch.float32, device=DEV), ref
+        elif epi == "residual":
+            out, expected = res.clone().to(DEV), res + ref
+        else:
+            out = torch.zeros(tokens, N, dtype=torch.bfloat16, device=DEV)
+            expected = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
+        ops.gemm_prefill_bf16(x, w, out, code)
+        torch.cuda.synchronize()
+        ops.raise_on_kernel_fault()
+        if out.dtype == torch.bfloat16:
+            close(out, expected, "bfloat16")
+        else:
+            assert torch.allclose(out.cpu(), expected, atol=1e-4, rtol=1e-4), float((out.cpu() - expected).abs().max())
