@@ -7,11 +7,13 @@ the kernel itself takes any number): the hand-written tcgen05 kernel
 (``csrc/gemm_tcgen05.cu``): weights streamed by TMA, fp32 accumulators in tensor memory,
 the residual add, the fp32 store of logits and the SiLU-gate product fused into its epilogue.
 
-bfloat16, more tokens (prefill): the vendor library's matrix product with fp32
-accumulation, as the reference does for every projection through ``F.linear``
-(ondeviceinfer/attention.py:149-157, ondeviceinfer/layers.py:109-113,
-ondeviceinfer/model.py:163), followed by this library's elementwise kernels.  The same
-holds for shapes the tcgen05 kernel refuses (K not a multiple of 8).
+bfloat16, more tokens (prefill): the persistent tcgen05 kernel (``csrc/gemm_prefill_tcgen05.cu``)
+where its fused epilogue beats the library's product plus the elementwise kernel it saves (gate/up
+with the SiLU gate, the output projection with the residual add; see ``PREFILL_GEMM`` below), else
+the vendor library's matrix product with fp32 accumulation, as the reference does for every
+projection through ``F.linear`` (ondeviceinfer/attention.py:149-157, ondeviceinfer/layers.py:109-113,
+ondeviceinfer/model.py:163), followed by this library's elementwise kernels.  The library also
+takes shapes the tcgen05 kernels refuse (K not a multiple of 8).
 """
 
 from __future__ import annotations
