@@ -1,26 +1,43 @@
 // bf16 matrix product for many tokens (prefill) on the 5th-generation tensor cores:
 //   out[token, n] = epilogue( sum_k x[token, k] * w[n, k] ),  fp32 accumulation.
 //
-// A persistent kernel, one CTA per SM.  Every CTA walks tiles of 128 tokens x 256 features (its
-// own, then every gridDim.x-th; token tiles vary fastest, so the CTAs that run side by side share
-// weight tiles in L2 and the weights come from HBM about once).  Per tile the K dimension streams
-// through a ring of shared-memory stages (64 k each: 16 KB of activations, 32 KB of weights, TMA
-// with the 128-byte swizzle) into tcgen05.mma instructions of M = 128, N = 256, K = 16, which run
-// at the full rate of the tensor pipe (128 cycles each, measured).  The accumulator lives in tensor
-// memory, which holds two of them (2 x 256 columns): while the four epilogue warps read one tile's
-// result, convert it and write it out, the MMA thread is already filling the other.  Nothing but
-// the ring's fill at the start and the last tile's epilogue is left uncovered.
+// A persistent kernel of clusters of two CTAs (two SMs), the two-CTA form of the MMA.  A cluster owns
+// tiles of 256 tokens x 256 features and walks them (its own, then every n-th; token tiles vary fastest
+// inside groups of 16, so that the clusters that run side by side share weight tiles and a bounded set of
+// activation rows in L2).  CTA r of the pair holds token rows r * 128 .. + 127 of the activations and
+// feature rows r * 128 .. + 127 of the weights: per k-block of 64 that is 16 KB + 16 KB by TMA (128-byte
+// swizzle) into a ring of six stages.  One thread of the leader CTA issues tcgen05.mma.cta_group::2
+// (M = 256, N = 256, K = 16), which reads both CTAs' shared memory and fills 128 lanes x 256 columns of
+// tensor memory in each CTA.  A single CTA with a 128 x 256 tile moves 48 KB into shared memory and reads
+// 48 KB back per 512 cycles of math, more than the 128 bytes per cycle shared memory delivers (measured:
+// 1.3-1.4 PFLOP/s); the pair moves and reads 32 KB per CTA for the same math.
 //
-//   warp 0   TMA producer (one thread)
-//   warp 1   allocates tensor memory; one thread issues the MMAs and commits
-//   warps 2-5 epilogue: a thread per token row of the tile, 32 columns at a time
+// Tensor memory holds two accumulators (2 x 256 columns): while the four epilogue warps of each CTA read
+// one tile's result, convert it, stage it swizzled in shared memory (two buffers of 128 rows x 128 bytes)
+// and hand it to a TMA store -- for the residual a TMA fp32 reduce-add, which never reads the residual --
+// the MMA thread is already filling the other accumulator.
 //
-// Epilogues: store bf16, store fp32, add into an fp32 residual, SiLU gate.  For the gate the weight
-// rows are the gate rows followed by the up rows; a tile's 256 columns are 128 gate features and
-// the same 128 up features, and silu(gate) * up gives 128 outputs.
+//   warp 0   TMA producer (one thread per CTA)
+//   warp 1   allocates tensor memory; in the leader one thread issues the MMAs and commits
+//   warps 2-5 epilogue: a thread per token row of the CTA's half tile
 //
-// Every wait on an mbarrier is bounded: after about two seconds of SM clock the role records an
-// error code in `status`, all roles leave their loops, tensor memory is freed and the kernel returns.
+//   full[s]      (leader's) both producers announce their bytes and their TMA loads complete on it
+//   empty[s]     (each CTA's) the leader's commit reaches both: the stage may be refilled
+//   acc_full[b]  (each CTA's) the leader's commit reaches both: the tile's accumulator is complete
+//   acc_empty[b] (leader's) the epilogue warps of both CTAs arrive: the accumulator may be overwritten
+//
+// Epilogues: store bf16, store fp32, add into an fp32 residual, SiLU gate.  For the gate the weight rows
+// are the gate rows followed by the up rows; the leader holds 128 gate rows and the peer the same 128 up
+// rows, a tile's 256 columns are gate | up, and silu(gate) * up gives 128 outputs.
+//
+// Measured on B200 against the library's product plus the elementwise kernel a fused epilogue saves
+// (Qwen3-8B sizes, us): 2,048 tokens q/k/v 70 / 69, output projection + residual 49 / 46 + 11, gate/up +
+// SiLU gate 273 / 274 + 24, down + residual 145 / 133 + 11; 8,192 tokens 267 / 270, 191 / 180 + 44,
+// 1,040 / 1,031 + 96, 558 / 529 + 44.  Below about a thousand tokens there are too few tiles for 74 clusters.
+//
+// The output rows must start on 16-byte boundaries (the TMA store's rule); K a multiple of 8.
+// Every wait on an mbarrier is bounded: after about two seconds of SM clock the role records an error code
+// in `status`, all roles leave their loops, tensor memory is freed and the kernel returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -30,13 +47,10 @@
 #define EPI_RESIDUAL 2
 #define EPI_SWIGLU 3
 
-#define BM 128             // tokens per tile (UMMA M, the lanes of tensor memory)
+#define BM 128             // token rows per CTA (the lanes of its tensor memory); a tile has 2 * BM
 #define BN 256             // accumulator columns per tile
 #define BK 64              // k per stage: 64 bf16 = one 128-byte swizzle row
-#define STAGES 4
-#define A_BYTES (BM * BK * 2)
-#define B_BYTES (BN * BK * 2)
-#define STAGE_BYTES (A_BYTES + B_BYTES)
+#define A_BYTES (BM * BK * 2)     // 128 rows of 64 k: a CTA's activation rows, and as much for its weight rows
 #define THREADS 192
 #define WAIT_CYCLES 4000000000ll
 
@@ -45,22 +59,16 @@
 #define ERR_EPILOGUE 23
 
 struct PrefillGemmArgs {
-  void* out;
+  void* out;               // only its alignment matters here: the output goes through a tensor map
   int* status;
   int tokens, N, K, ldo;   // N: output features (for the gate: half of the weight rows)
   int up_offset;           // EPI_SWIGLU: row distance from a gate row to its up row
-  int m_tiles, n_tiles;
+  int m_tiles, n_tiles;    // tiles of 256 tokens, tiles of 256 columns
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -84,11 +92,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   return false;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
 // A staged tile (128 rows of 128 bytes, 128-byte swizzle) to global memory: plain store, or fp32 add.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -105,16 +108,6 @@ __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   uint32_t r[32];
   asm volatile(
@@ -146,89 +139,99 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
 }
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
-// 32 consecutive accumulator columns of one token row, written to the features n .. n + 31
-// (for the gate: v holds the gate columns, u the up columns).
-template <int EPI>
-__device__ __forceinline__ void emit32(const PrefillGemmArgs& a, int token, int n, const float* v, const float* u, bool vec_ok) {
-  if (token >= a.tokens || n >= a.N) return;
-  const size_t at = (size_t)token * a.ldo + n;
-  if (vec_ok && n + 32 <= a.N) {
-    if (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU) {
-      uint4* dst = (uint4*)((bf16*)a.out + at);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = 8 * q + 2 * i;
-          const float lo = EPI == EPI_SWIGLU ? silu_f(v[c]) * u[c] : v[c];
-          const float hi = EPI == EPI_SWIGLU ? silu_f(v[c + 1]) * u[c + 1] : v[c + 1];
-          __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
-          w[i] = *(uint32_t*)&pair;
-        }
-        dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    } else {
-      float4* dst = (float4*)((float*)a.out + at);
-      float4 r[8];
-      if (EPI == EPI_RESIDUAL) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) r[i] = dst[i];
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        if (EPI == EPI_RESIDUAL) { o.x += r[i].x; o.y += r[i].y; o.z += r[i].z; o.w += r[i].w; }
-        dst[i] = o;
-      }
-    }
-    return;
-  }
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    if (n + i >= a.N) continue;
-    if (EPI == EPI_STORE_BF16) ((bf16*)a.out)[at + i] = __float2bfloat16_rn(v[i]);
-    else if (EPI == EPI_STORE_F32) ((float*)a.out)[at + i] = v[i];
-    else if (EPI == EPI_RESIDUAL) ((float*)a.out)[at + i] += v[i];
-    else ((bf16*)a.out)[at + i] = __float2bfloat16_rn(silu_f(v[i]) * u[i]);
-  }
+// ------------------------------------------------------------------------------ the kernel
+
+#define STAGES 6
+#define STAGE_BYTES (2 * A_BYTES)
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address, in the cluster's shared window, of the same variable in the CTA of the given rank.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// A TMA load into this CTA's shared memory whose bytes are counted on a barrier of the pair's leader.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void umma_pair_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives, once the MMAs issued so far have completed, on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both) : "memory");
 }
 
-// TMA_OUT: the epilogue stages 128 rows x 128 bytes of output in shared memory (swizzled, two buffers) and a
-// TMA store, or for the residual a TMA fp32 add, carries them out: whole lines, no read of the residual.
-// Without it (rows of the output not 16-byte aligned) the threads write their rows themselves.
-template <int EPI, bool TMA_OUT>
-__global__ void __launch_bounds__(THREADS, 1)
+// Tile t of the walk: token tiles vary fastest inside groups of TILE_GROUP token tiles, so that the CTAs that run
+// side by side share a few weight tiles and a bounded set of activation rows (both stay in L2 however many tokens
+// there are).
+#define TILE_GROUP 16
+__device__ __forceinline__ void tile_of(int t, int m_tiles, int n_tiles, int& m, int& n) {
+  const int per_group = TILE_GROUP * n_tiles;
+  const int g = t / per_group, r = t - g * per_group;
+  const int rows = min(TILE_GROUP, m_tiles - g * TILE_GROUP);
+  m = g * TILE_GROUP + r % rows;
+  n = r / rows;
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_out, const PrefillGemmArgs a) {
+                         const __grid_constant__ CUtensorMap map_out, const PrefillGemmArgs a) {
   constexpr bool GATE = EPI == EPI_SWIGLU;
   constexpr int OUT_PER_TILE = GATE ? BN / 2 : BN;      // output features a tile covers
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int epilogue_ok;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = a.m_tiles * a.n_tiles;
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int total_tiles = a.m_tiles * a.n_tiles;        // m_tiles here: tiles of 256 tokens
   const int total_kb = (a.K + BK - 1) / BK;
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = full0 + 8 * STAGES, acc_full0 = empty0 + 8 * STAGES,
                  acc_empty0 = acc_full0 + 16;
+  const uint32_t leader_full0 = map_to_rank(full0, 0), leader_acc_empty0 = map_to_rank(acc_empty0, 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 4); }   // four epilogue warps
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 2); mbar_init(empty0 + 8 * s, 1); }   // two producers
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 8); }     // 4 + 4 epilogue warps
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(2 * BN));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(2 * BN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();               // both CTAs' barriers exist before anybody signals across
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
@@ -237,34 +240,32 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       pdl_wait();                     // the activations come from the kernel before
-      int it = 0;                     // stage uses so far
+      int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int tok0 = (tile % a.m_tiles) * BM, n0 = (tile / a.m_tiles) * OUT_PER_TILE;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        int tm, tn;
+        tile_of(tile, a.m_tiles, a.n_tiles, tm, tn);
+        const int tok0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * OUT_PER_TILE;
+        // this CTA's weight rows: its half of the 256 columns (for the gate: gate rows in the leader, up rows in the peer)
+        const int w_row = GATE ? n0 + (int)rank * a.up_offset : n0 + (int)rank * (BN / 2);
         for (int kb = 0; kb < total_kb; ++kb, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty0 + 8 * s, (((uint32_t)(it / STAGES) & 1u) ^ 1u), abort_ptr)) { ok = false; break; }
           const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
-          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-          tma_load_2d(dst, &map_x, kb * BK, tok0, full0 + 8 * s);
-          if (GATE) {     // 128 gate rows, then the same 128 up rows
-            tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
-            tma_load_2d(dst + A_BYTES + B_BYTES / 2, &map_w, kb * BK, n0 + a.up_offset, full0 + 8 * s);
-          } else {
-            tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
-          }
+          mbar_expect_tx_cluster(leader_full0 + 8 * s, STAGE_BYTES);
+          tma_load_2d_pair(dst, &map_x, kb * BK, tok0, leader_full0 + 8 * s);
+          tma_load_2d_pair(dst + A_BYTES, &map_w, kb * BK, w_row, leader_full0 + 8 * s);
         }
       }
       if (!ok) atomicCAS(a.status, 0, ERR_PRODUCER);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
-      int it = 0, local = 0;          // stage uses, tiles of this CTA so far
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = instr_desc_bf16(2 * BM, BN);
+      int it = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
         const int buf = local & 1;
-        // the epilogue must have drained this accumulator (two tiles ago)
         if (local >= 2 && !mbar_wait(acc_empty0 + 8 * buf, (((uint32_t)(local >> 1) & 1u) ^ 1u), abort_ptr)) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < total_kb; ++kb, ++it) {
@@ -274,100 +275,90 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
           const uint64_t da = smem_desc_k_sw128(sa), db = smem_desc_k_sw128(sa + A_BYTES);
 #pragma unroll
-          for (int j = 0; j < BK / 16; ++j)      // 16 k = 32 bytes further inside the swizzle row: +2 in the address field
-            umma_bf16(tmem_base + buf * BN, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          umma_commit(empty0 + 8 * s);          // the stage is free once these MMAs have read it
+          for (int j = 0; j < BK / 16; ++j)
+            umma_pair_bf16(tmem_base + buf * BN, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          umma_commit_pair(empty0 + 8 * s);         // both CTAs may refill the stage
         }
-        if (ok) umma_commit(acc_full0 + 8 * buf);
+        if (ok) umma_commit_pair(acc_full0 + 8 * buf);
       }
       if (!ok) atomicCAS(a.status, 0, ERR_MMA);
     }
   } else {
-    // epilogue warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31: a thread is a token row of the tile
+    // epilogue warps 2..5 of each CTA: its 128 token rows of the tile
     const int lane_group = warp & 3, row = lane_group * 32 + lane;
     constexpr bool OUT32 = EPI == EPI_STORE_F32 || EPI == EPI_RESIDUAL;
-    constexpr int COLS_PER_OP = OUT32 ? 32 : 64;        // output features per staged tile: 128 bytes a row
-    uint8_t* stage_out = smem + STAGES * STAGE_BYTES;   // two staged tiles of 16 KB
+    constexpr int COLS_PER_OP = OUT32 ? 32 : 64;
+    uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
     int local = 0, op = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
       const int buf = local & 1;
-      const int tok0 = (tile % a.m_tiles) * BM, n0 = (tile / a.m_tiles) * OUT_PER_TILE;
-      // one warp waits for the accumulator, all four learn the outcome together: the barriers below
-      // need every epilogue thread or none
+      int tm, tn;
+      tile_of(tile, a.m_tiles, a.n_tiles, tm, tn);
+      const int tok0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * OUT_PER_TILE;
       if (warp == 2) {
         const bool got = mbar_wait(acc_full0 + 8 * buf, (uint32_t)(local >> 1) & 1u, abort_ptr);
         if (lane == 0) epilogue_ok = got ? 1 : 0;
       }
       epilogue_sync();
       ok = epilogue_ok != 0;
-      epilogue_sync();                            // all have read the outcome before it is written again
+      epilogue_sync();
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * BN;
-      if (TMA_OUT) {
 #pragma unroll 1
-        for (int c = 0; c < OUT_PER_TILE; c += COLS_PER_OP, ++op) {
-          if (n0 + c >= a.N) break;               // uniform for the CTA
-          uint8_t* tile_out = stage_out + (op & 1) * 16384;
-          uint8_t* mine = tile_out + row * 128;
-          epilogue_sync();                        // the staged tile of two operations ago has been read
+      for (int c = 0; c < OUT_PER_TILE; c += COLS_PER_OP, ++op) {
+        if (n0 + c >= a.N) break;
+        uint8_t* tile_out = stage_out + (op & 1) * 16384;
+        uint8_t* mine = tile_out + row * 128;
+        epilogue_sync();
 #pragma unroll
-          for (int part = 0; part < COLS_PER_OP / 32; ++part) {
-            float v[32], u[32];
-            tmem_ld32(taddr + c + 32 * part, v);
-            if (GATE) tmem_ld32(taddr + BN / 2 + c + 32 * part, u);
-            if (OUT32) {
+        for (int part = 0; part < COLS_PER_OP / 32; ++part) {
+          float v[32], u[32];
+          tmem_ld32(taddr + c + 32 * part, v);
+          if (GATE) tmem_ld32(taddr + BN / 2 + c + 32 * part, u);
+          if (OUT32) {
 #pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *(float4*)(mine + ((q ^ (row & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
+            for (int q = 0; q < 8; ++q)
+              *(float4*)(mine + ((q ^ (row & 7)) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          } else {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint32_t w[4];
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int e = 8 * q + 2 * i;
-                  const float lo = GATE ? silu_f(v[e]) * u[e] : v[e];
-                  const float hi = GATE ? silu_f(v[e + 1]) * u[e + 1] : v[e + 1];
-                  __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
-                  w[i] = *(uint32_t*)&pair;
-                }
-                *(uint4*)(mine + (((4 * part + q) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+              for (int i = 0; i < 4; ++i) {
+                const int e = 8 * q + 2 * i;
+                const float lo = GATE ? silu_f(v[e]) * u[e] : v[e];
+                const float hi = GATE ? silu_f(v[e + 1]) * u[e + 1] : v[e + 1];
+                __nv_bfloat162 pr = __floats2bfloat162_rn(lo, hi);
+                w[i] = *(uint32_t*)&pr;
               }
+              *(uint4*)(mine + (((4 * part + q) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the staged tile is visible to the TMA
-          epilogue_sync();
-          if (threadIdx.x == 64) {
-            if (EPI == EPI_RESIDUAL) tma_reduce_add_2d(&map_out, smem_u32(tile_out), n0 + c, tok0);
-            else tma_store_2d(&map_out, smem_u32(tile_out), n0 + c, tok0);
-            bulk_commit();
-            bulk_wait_read<1>();                  // the operation before this one has read its staged tile
-          }
         }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < OUT_PER_TILE; c += 32) {
-          if (n0 + c >= a.N) break;               // uniform for the warp
-          float v[32], u[32];
-          tmem_ld32(taddr + c, v);
-          if (GATE) tmem_ld32(taddr + BN / 2 + c, u);
-          emit32<EPI>(a, tok0 + row, n0 + c, v, u, false);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        epilogue_sync();
+        if (threadIdx.x == 64) {
+          if (EPI == EPI_RESIDUAL) tma_reduce_add_2d(&map_out, smem_u32(tile_out), n0 + c, tok0);
+          else tma_store_2d(&map_out, smem_u32(tile_out), n0 + c, tok0);
+          bulk_commit();
+          bulk_wait_read<1>();
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8 * buf);
     }
-    if (TMA_OUT && threadIdx.x == 64) bulk_wait_all();     // every output tile has left shared memory and landed
+    if (threadIdx.x == 64) bulk_wait_all();
     if (!ok && lane == 0) atomicCAS(a.status, 0, ERR_EPILOGUE);
     tc_fence_before();
   }
   __syncthreads();
+  cluster_sync_all();               // nobody leaves while its barriers or tensor memory may still be used by the peer
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN));
   }
 }
 
@@ -418,11 +409,11 @@ static int make_out_map(CUtensorMap* map, void* base, int tokens, int N, int ldo
   return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
 }
 
-template <int EPI, bool TMA_OUT>
+template <int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PrefillGemmArgs& a, int sms,
-                  cudaStream_t stream) {
-  constexpr int SMEM = STAGES * STAGE_BYTES + (TMA_OUT ? 2 * 16384 : 0) + 1024;
-  auto kernel = gemm_prefill_kernel<EPI, TMA_OUT>;
+                       cudaStream_t stream) {
+  constexpr int SMEM = STAGES * STAGE_BYTES + 2 * 16384 + 1024;
+  auto kernel = gemm_prefill_kernel<EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -430,24 +421,22 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMa
     configured = true;
   }
   const int tiles = a.m_tiles * a.n_tiles;
-  odi_rc = launch_pdl((kernel), dim3(tiles < sms ? tiles : sms), dim3(THREADS), SMEM, stream, mx, mw, mo, a);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  odi_rc = launch_pdl((kernel), dim3(2 * pairs), dim3(THREADS), SMEM, stream, mx, mw, mo, a);
   return launch_status();
 }
 
-template <int EPI>
-static int launch_either(bool tma_out, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo,
-                         const PrefillGemmArgs& a, int sms, cudaStream_t stream) {
-  return tma_out ? launch<EPI, true>(mx, mw, mo, a, sms, stream) : launch<EPI, false>(mx, mw, mo, a, sms, stream);
-}
-
 // x [tokens, K] bf16, w [w_rows, K] bf16 (for EPI_SWIGLU the gate rows followed by the up rows,
-// n_out = w_rows / 2), out [tokens, ldo]; status: an int that receives an error code if a wait gives up.
+// n_out = w_rows / 2), out [tokens, ldo] with rows that start on 16-byte boundaries; status: an int that
+// receives an error code if a wait gives up.
 extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
                                      int ldo, int epi, int* status, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || status == nullptr) return ODI_ERR_UNSUPPORTED;
   const bool gate = epi == EPI_SWIGLU;
   if (gate ? w_rows != 2 * n_out : w_rows != n_out) return ODI_ERR_ARGUMENT;
+  const bool f32 = epi == EPI_STORE_F32 || epi == EPI_RESIDUAL;
+  if (((uintptr_t)out & 15) || ((long)ldo * (f32 ? 4 : 2)) % 16 != 0) return ODI_ERR_UNSUPPORTED;
   static int sms = 0;
   if (sms == 0) {
     int device = 0;
@@ -455,30 +444,23 @@ extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, in
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (e != cudaSuccess) return (int)e;
   }
-  CUtensorMap mx, mw;
+  CUtensorMap mx, mw, mo;
   int rc = make_map(&mx, x, tokens, K, BM);
-  if (rc == 0) rc = make_map(&mw, w, w_rows, K, gate ? BN / 2 : BN);
+  if (rc == 0) rc = make_map(&mw, w, w_rows, K, BN / 2);
+  if (rc == 0) rc = make_out_map(&mo, out, tokens, n_out, ldo, f32);
   if (rc != 0) return rc;
   PrefillGemmArgs a;
   a.out = out; a.status = status; a.tokens = tokens; a.N = n_out; a.K = K; a.ldo = ldo;
   a.up_offset = gate ? n_out : 0;
   const int per_tile = gate ? BN / 2 : BN;
-  a.m_tiles = (tokens + BM - 1) / BM;
+  a.m_tiles = (tokens + 2 * BM - 1) / (2 * BM);
   a.n_tiles = (n_out + per_tile - 1) / per_tile;
   if ((long)a.m_tiles * a.n_tiles > 0x7fffffffL) return ODI_ERR_UNSUPPORTED;
-  // whole lines of output through TMA when its rows start on 16-byte boundaries
-  const bool f32 = epi == EPI_STORE_F32 || epi == EPI_RESIDUAL;
-  const bool tma_out = ((uintptr_t)out & 15) == 0 && ((long)ldo * (f32 ? 4 : 2)) % 16 == 0;
-  CUtensorMap mo = mx;
-  if (tma_out) {
-    rc = make_out_map(&mo, out, tokens, n_out, ldo, f32);
-    if (rc != 0) return rc;
-  }
   switch (epi) {
-    case EPI_STORE_BF16: return launch_either<EPI_STORE_BF16>(tma_out, mx, mw, mo, a, sms, stream);
-    case EPI_STORE_F32: return launch_either<EPI_STORE_F32>(tma_out, mx, mw, mo, a, sms, stream);
-    case EPI_RESIDUAL: return launch_either<EPI_RESIDUAL>(tma_out, mx, mw, mo, a, sms, stream);
-    case EPI_SWIGLU: return launch_either<EPI_SWIGLU>(tma_out, mx, mw, mo, a, sms, stream);
+    case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(mx, mw, mo, a, sms, stream);
+    case EPI_STORE_F32: return launch<EPI_STORE_F32>(mx, mw, mo, a, sms, stream);
+    case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(mx, mw, mo, a, sms, stream);
+    case EPI_SWIGLU: return launch<EPI_SWIGLU>(mx, mw, mo, a, sms, stream);
   }
   return ODI_ERR_ARGUMENT;
 }

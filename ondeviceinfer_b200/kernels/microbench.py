@@ -182,7 +182,7 @@ def main(argv=None) -> int:
     parser.add_argument("--splits", type=int, default=None)
     parser.add_argument("--swap", type=int, default=None)
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
-    parser.add_argument("--persistent", action="store_true", help="gemm: the persistent kernel for many tokens")
+    parser.add_argument("--persistent", action="store_true", help="gemm: the persistent two-CTA kernel for many tokens")
     parser.add_argument("--no-cluster", action="store_true", help="GEMM K splits through global scratch, not a cluster")
     parser.add_argument("--cluster-attention", action="store_true", help="merge decode-attention splits inside a cluster")
     parser.add_argument("--merge-in-kernel", action="store_true",

@@ -388,10 +388,18 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
            "gemm_tcgen05")
 
 
+def gemm_prefill_supported(x: torch.Tensor, w: torch.Tensor, n_out: int, out_dtype: torch.dtype) -> bool:
+    """Whether :func:`gemm_prefill_bf16` takes these operands: K a multiple of 8, 16-byte aligned operands, and
+    output rows that start on 16-byte boundaries (they leave through TMA stores)."""
+    elem = 4 if out_dtype == torch.float32 else 2
+    return gemm_bf16_supported(x, w) and (n_out * elem) % 16 == 0
+
+
 def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> None:
-    """The persistent tensor-core product for many tokens (``csrc/gemm_prefill_tcgen05.cu``): tiles of 128
-    tokens x 256 features, two accumulators in tensor memory so that a tile's epilogue runs under the next
-    tile's MMAs.  Same operands and epilogues as :func:`gemm_bf16` (without ``EPI_HEAD_PREP``)."""
+    """The persistent two-CTA tensor-core product for many tokens (``csrc/gemm_prefill_tcgen05.cu``): clusters
+    of two CTAs own tiles of 256 tokens x 256 features (tcgen05.mma.cta_group::2), two accumulators in tensor
+    memory so that a tile's epilogue runs under the next tile's MMAs, output by TMA store or fp32 reduce-add.
+    Same operands and epilogues as :func:`gemm_bf16` (without ``EPI_HEAD_PREP``)."""
     _require(x, "x", torch.bfloat16, 2)
     _require(w, "w", torch.bfloat16, 2)
     _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
@@ -402,8 +410,9 @@ def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: 
         raise KernelError(f"gemm_prefill_bf16 has no epilogue {epi}")
     if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
         raise KernelError(f"gemm sizes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    if not gemm_bf16_supported(x, w):
-        raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
+    if not gemm_prefill_supported(x, w, n_out, out.dtype):
+        raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8, 16-byte aligned operands and output rows "
+                          f"(K={K}, {n_out} {out.dtype} per row)")
     _, _, status = _gemm_buffers(w.device, 0)
     lib = load_library("gemm_prefill_tcgen05")
     _check(lib.odi_gemm_prefill_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),

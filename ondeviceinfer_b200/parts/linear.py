@@ -7,13 +7,12 @@ the kernel itself takes any number): the hand-written tcgen05 kernel
 (``csrc/gemm_tcgen05.cu``): weights streamed by TMA, fp32 accumulators in tensor memory,
 the residual add, the fp32 store of logits and the SiLU-gate product fused into its epilogue.
 
-bfloat16, more tokens (prefill): the persistent tcgen05 kernel (``csrc/gemm_prefill_tcgen05.cu``)
-where its fused epilogue beats the library's product plus the elementwise kernel it saves (gate/up
-with the SiLU gate, the output projection with the residual add; see ``PREFILL_GEMM`` below), else
-the vendor library's matrix product with fp32 accumulation, as the reference does for every
-projection through ``F.linear`` (ondeviceinfer/attention.py:149-157, ondeviceinfer/layers.py:109-113,
-ondeviceinfer/model.py:163), followed by this library's elementwise kernels.  The library also
-takes shapes the tcgen05 kernels refuse (K not a multiple of 8).
+bfloat16, more tokens (prefill): from about a thousand tokens on the persistent two-CTA tcgen05 kernel
+(``csrc/gemm_prefill_tcgen05.cu``) with the SiLU gate or the residual add in its epilogue (see
+``PREFILL_GEMM`` below); with fewer tokens the vendor library's matrix product with fp32 accumulation, as
+the reference does for every projection through ``F.linear`` (ondeviceinfer/attention.py:149-157,
+ondeviceinfer/layers.py:109-113, ondeviceinfer/model.py:163), followed by this library's elementwise
+kernels.  The library also takes shapes the tcgen05 kernels refuse (K not a multiple of 8).
 """
 
 from __future__ import annotations
@@ -32,24 +31,26 @@ import os
 OWN_KERNEL_MAX_TOKENS = int(os.environ.get("ODI_OWN_GEMM_MAX_TOKENS", "32"))
 
 
-# The projections of many tokens.  "auto": the library's product, except where the persistent tcgen05
-# kernel with a fused epilogue measured faster than the library's product plus the elementwise kernel it
-# saves (B200, Qwen3-8B sizes, 2,048 tokens: gate/up with the SiLU gate 287 against 274 + 24 us, the
-# output projection with the residual add 53 against 46 + 11 us; not the down projection, 159 against
-# 133 + 11 us, nor anything at 8,192 tokens, where the library reaches 1.5-1.6 PFLOP/s against 1.3-1.4).
-# "own" / "library" force one of them.
+# The projections of many tokens.  "auto": the persistent two-CTA tcgen05 kernel from 1,024 tokens on for
+# the products with a fused epilogue (gate/up with the SiLU gate, output and down projections with the
+# residual add) and from 2,048 on for the plain one, else the library's product followed by this library's
+# elementwise kernels.  Measured on B200 (Qwen3-8B sizes, us, own / library + elementwise): 1,024 tokens
+# gate/up 148 / 141 + 12, down 74 / 70 + 6, q/k/v 45 / 36; 2,048 tokens 273 / 274 + 24, 145 / 133 + 11,
+# 70 / 69; 8,192 tokens 1,040 / 1,031 + 96, 558 / 529 + 44, 267 / 270; with fewer tokens there are too
+# few tiles for 74 clusters (256 tokens: q/k/v 23 / 12).  "own" / "library" force one of them.
 PREFILL_GEMM = os.environ.get("ODI_PREFILL_GEMM", "auto")
-PERSISTENT_MIN_TOKENS, PERSISTENT_MAX_TOKENS = 256, 4096
+PERSISTENT_MIN_TOKENS_FUSED, PERSISTENT_MIN_TOKENS_PLAIN = 1024, 2048
 
 
 def _persistent(tokens: int, weight: torch.Tensor, x: torch.Tensor, epi: int) -> bool:
-    if PREFILL_GEMM == "library" or not ops.gemm_bf16_supported(x, weight):
+    n_out = weight.shape[0] // 2 if epi == ops.EPI_SWIGLU else weight.shape[0]
+    out_dtype = torch.float32 if epi in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL) else torch.bfloat16
+    if PREFILL_GEMM == "library" or not ops.gemm_prefill_supported(x, weight, n_out, out_dtype):
         return False
     if PREFILL_GEMM == "own":
         return True
-    if not PERSISTENT_MIN_TOKENS <= tokens <= PERSISTENT_MAX_TOKENS:
-        return False
-    return epi == ops.EPI_SWIGLU or (epi == ops.EPI_RESIDUAL and weight.shape[1] <= weight.shape[0])
+    fused = epi in (ops.EPI_SWIGLU, ops.EPI_RESIDUAL)
+    return tokens >= (PERSISTENT_MIN_TOKENS_FUSED if fused else PERSISTENT_MIN_TOKENS_PLAIN)
 
 
 class NormedRows:
@@ -142,7 +143,7 @@ def linear(x, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
     if residual is not None and _persistent(n, weight, x, ops.EPI_RESIDUAL):
         ops.gemm_prefill_bf16(x, weight, residual, ops.EPI_RESIDUAL)
         return None
-    if residual is None and PREFILL_GEMM == "own" and _persistent(n, weight, x, ops.EPI_STORE_BF16):
+    if residual is None and _persistent(n, weight, x, ops.EPI_STORE_F32 if out_dtype == torch.float32 else ops.EPI_STORE_BF16):
         wide = out_dtype == torch.float32
         out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
         ops.gemm_prefill_bf16(x, weight, out, ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16)
