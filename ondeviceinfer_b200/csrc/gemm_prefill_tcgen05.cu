@@ -26,7 +26,10 @@
 //   acc_full[b]  (each CTA's) the leader's commit reaches both: the tile's accumulator is complete
 //   acc_empty[b] (leader's) the epilogue warps of both CTAs arrive: the accumulator may be overwritten
 //
-// Epilogues: store bf16, store fp32, add into an fp32 residual, SiLU gate.  For the gate the weight rows
+// Epilogues: store bf16, store fp32, add into an fp32 residual, SiLU gate, head preparation (the rows of w
+// are query, key and value heads of 128: a tile's 256 columns are two heads, and a thread of the epilogue
+// finishes its token's row of each: per-head norm, rotation, the write to the query buffer or the cache
+// page; this one writes its rows itself, the others go through TMA).  For the gate the weight rows
 // are the gate rows followed by the up rows; the leader holds 128 gate rows and the peer the same 128 up
 // rows, a tile's 256 columns are gate | up, and silu(gate) * up gives 128 outputs.
 //
@@ -46,6 +49,7 @@
 #define EPI_STORE_F32 1
 #define EPI_RESIDUAL 2
 #define EPI_SWIGLU 3
+#define EPI_HEAD_PREP 4    // the rows of w are q, k and v heads of 128: per-head norm, rotation, cache write
 
 #define BM 128             // token rows per CTA (the lanes of its tensor memory); a tile has 2 * BM
 #define BN 256             // accumulator columns per tile
@@ -64,6 +68,7 @@ struct PrefillGemmArgs {
   int tokens, N, K, ldo;   // N: output features (for the gate: half of the weight rows)
   int up_offset;           // EPI_SWIGLU: row distance from a gate row to its up row
   int m_tiles, n_tiles;    // tiles of 256 tokens, tiles of 256 columns
+  HeadPrepArgs hp;         // EPI_HEAD_PREP
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -183,6 +188,73 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   const uint16_t both = 3;
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                ::"r"(bar), "h"(both) : "memory");
+}
+
+// One thread finishes one head of one token from the head's 128 projections in tensor memory (columns
+// taddr .. + 127 of the thread's lane): rounded to bf16 as the stored projections would be, then the
+// arithmetic of the stand-alone head preparation (per-head RMSNorm, half-split rotation), and the row goes to
+// the query buffer or to the token's place in the key / value cache.
+__device__ __forceinline__ void head_prep_row(const HeadPrepArgs& hp, int t, int h, uint32_t taddr) {
+  constexpr int d = 128, half = 64;
+  float x[d];
+#pragma unroll
+  for (int j = 0; j < d / 32; ++j) tmem_ld32(taddr + 32 * j, x + 32 * j);
+  if (t >= hp.n_tokens) return;                       // after the loads: they are warp-wide
+#pragma unroll
+  for (int i = 0; i < d; ++i) x[i] = round_to<bf16>(x[i]);
+  const int kind = h < hp.nq ? 0 : (h < hp.nq + hp.nkv ? 1 : 2);     // 0 q, 1 k, 2 v
+  const int pos = hp.tok_pos[t];
+  bf16* dst;
+  if (kind == 0) {
+    dst = (bf16*)hp.q_out + ((size_t)t * hp.nq + h) * d;
+  } else {
+    const int hk = kind == 1 ? h - hp.nq : h - hp.nq - hp.nkv;
+    const int page = hp.page_ids[hp.page_start[hp.tok_seq[t]] + page_slot_of(pos, hp.page_size, hp.ring_pages)];
+    bf16* pool = (bf16*)(kind == 1 ? hp.k_pool : hp.v_pool);
+    dst = pool + (((size_t)page * hp.nkv + hk) * hp.page_size + (pos % hp.page_size)) * d;
+  }
+  if (kind != 2) {
+    const float* w = kind == 0 ? hp.q_norm_w : hp.k_norm_w;
+    if (w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < d; ++i) ss += x[i] * x[i];
+      const float inv = rsqrtf(ss / (float)d + hp.eps);
+#pragma unroll
+      for (int i = 0; i < d; i += 4) {
+        const float4 ww = *(const float4*)(w + i);
+        x[i] = round_to<bf16>(ww.x * round_to<bf16>(x[i] * inv));
+        x[i + 1] = round_to<bf16>(ww.y * round_to<bf16>(x[i + 1] * inv));
+        x[i + 2] = round_to<bf16>(ww.z * round_to<bf16>(x[i + 2] * inv));
+        x[i + 3] = round_to<bf16>(ww.w * round_to<bf16>(x[i + 3] * inv));
+      }
+    }
+    if (hp.cos_t != nullptr) {
+      const float4* cs = (const float4*)(hp.cos_t + (size_t)t * half);
+      const float4* sn = (const float4*)(hp.sin_t + (size_t)t * half);
+#pragma unroll
+      for (int i = 0; i < half; i += 4) {
+        const float4 c = cs[i / 4], s = sn[i / 4];
+        const float cc[4] = {c.x, c.y, c.z, c.w}, ssn[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = x[i + e], hi = x[i + e + half];
+          x[i + e] = lo * cc[e] - hi * ssn[e];
+          x[i + e + half] = hi * cc[e] + lo * ssn[e];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < d; i += 8) {
+    uint32_t w4[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat162 pr = __floats2bfloat162_rn(x[i + 2 * e], x[i + 2 * e + 1]);
+      w4[e] = *(uint32_t*)&pr;
+    }
+    *(uint4*)(dst + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+  }
 }
 
 // Tile t of the walk: token tiles vary fastest inside groups of TILE_GROUP token tiles, so that the CTAs that run
@@ -306,6 +378,12 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * BN;
+      if (EPI == EPI_HEAD_PREP) {
+        // a tile's 256 columns are two heads; a thread finishes its token's row of each
+#pragma unroll 1
+        for (int hh = 0; hh < BN / 128; ++hh)
+          if (n0 + 128 * hh < a.N) head_prep_row(a.hp, tok0 + row, (n0 >> 7) + hh, taddr + 128 * hh);
+      } else
 #pragma unroll 1
       for (int c = 0; c < OUT_PER_TILE; c += COLS_PER_OP, ++op) {
         if (n0 + c >= a.N) break;
@@ -429,14 +507,25 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMa
 // x [tokens, K] bf16, w [w_rows, K] bf16 (for EPI_SWIGLU the gate rows followed by the up rows,
 // n_out = w_rows / 2), out [tokens, ldo] with rows that start on 16-byte boundaries; status: an int that
 // receives an error code if a wait gives up.
+// EPI_HEAD_PREP: out is not used; head_prep describes where the heads go (heads of 128, whole-head rotation or
+// none, keys and values written).
 extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
-                                     int ldo, int epi, int* status, cudaStream_t stream) {
+                                     int ldo, int epi, const HeadPrepArgs* head_prep, int* status, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || status == nullptr) return ODI_ERR_UNSUPPORTED;
-  const bool gate = epi == EPI_SWIGLU;
+  const bool gate = epi == EPI_SWIGLU, heads = epi == EPI_HEAD_PREP;
   if (gate ? w_rows != 2 * n_out : w_rows != n_out) return ODI_ERR_ARGUMENT;
   const bool f32 = epi == EPI_STORE_F32 || epi == EPI_RESIDUAL;
-  if (((uintptr_t)out & 15) || ((long)ldo * (f32 ? 4 : 2)) % 16 != 0) return ODI_ERR_UNSUPPORTED;
+  if (!heads && (((uintptr_t)out & 15) || ((long)ldo * (f32 ? 4 : 2)) % 16 != 0)) return ODI_ERR_UNSUPPORTED;
+  if (heads) {
+    if (head_prep == nullptr) return ODI_ERR_ARGUMENT;
+    const HeadPrepArgs& hp = *head_prep;
+    if (hp.d != 128 || n_out != (hp.nq + 2 * hp.nkv) * 128 || !hp.write_kv || hp.n_tokens != tokens ||
+        (hp.cos_t != nullptr && hp.rot_dim != hp.d) || ((uintptr_t)hp.q_out & 15) || ((uintptr_t)hp.k_pool & 15) ||
+        ((uintptr_t)hp.v_pool & 15) || ((uintptr_t)hp.cos_t & 15) || ((uintptr_t)hp.sin_t & 15) ||
+        ((uintptr_t)hp.q_norm_w & 15) || ((uintptr_t)hp.k_norm_w & 15))
+      return ODI_ERR_UNSUPPORTED;
+  }
   static int sms = 0;
   if (sms == 0) {
     int device = 0;
@@ -447,11 +536,13 @@ extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, in
   CUtensorMap mx, mw, mo;
   int rc = make_map(&mx, x, tokens, K, BM);
   if (rc == 0) rc = make_map(&mw, w, w_rows, K, BN / 2);
-  if (rc == 0) rc = make_out_map(&mo, out, tokens, n_out, ldo, f32);
+  if (rc == 0 && !heads) rc = make_out_map(&mo, out, tokens, n_out, ldo, f32);
   if (rc != 0) return rc;
+  if (heads) mo = mx;               // not used by that epilogue
   PrefillGemmArgs a;
   a.out = out; a.status = status; a.tokens = tokens; a.N = n_out; a.K = K; a.ldo = ldo;
   a.up_offset = gate ? n_out : 0;
+  a.hp = heads ? *head_prep : HeadPrepArgs{};
   const int per_tile = gate ? BN / 2 : BN;
   a.m_tiles = (tokens + 2 * BM - 1) / (2 * BM);
   a.n_tiles = (n_out + per_tile - 1) / per_tile;
@@ -461,6 +552,7 @@ extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, in
     case EPI_STORE_F32: return launch<EPI_STORE_F32>(mx, mw, mo, a, sms, stream);
     case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(mx, mw, mo, a, sms, stream);
     case EPI_SWIGLU: return launch<EPI_SWIGLU>(mx, mw, mo, a, sms, stream);
+    case EPI_HEAD_PREP: return launch<EPI_HEAD_PREP>(mx, mw, mo, a, sms, stream);
   }
   return ODI_ERR_ARGUMENT;
 }

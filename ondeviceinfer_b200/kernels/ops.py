@@ -395,28 +395,36 @@ def gemm_prefill_supported(x: torch.Tensor, w: torch.Tensor, n_out: int, out_dty
     return gemm_bf16_supported(x, w) and (n_out * elem) % 16 == 0
 
 
-def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> None:
+def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *, head_prep=None) -> None:
     """The persistent two-CTA tensor-core product for many tokens (``csrc/gemm_prefill_tcgen05.cu``): clusters
     of two CTAs own tiles of 256 tokens x 256 features (tcgen05.mma.cta_group::2), two accumulators in tensor
     memory so that a tile's epilogue runs under the next tile's MMAs, output by TMA store or fp32 reduce-add.
-    Same operands and epilogues as :func:`gemm_bf16` (without ``EPI_HEAD_PREP``)."""
+    Same operands and epilogues as :func:`gemm_bf16`; with ``EPI_HEAD_PREP`` (``out=None``, ``head_prep`` the block
+    that ``head_prep(None, ...)`` returns) a thread of the epilogue finishes a token's row of a head."""
     _require(x, "x", torch.bfloat16, 2)
     _require(w, "w", torch.bfloat16, 2)
-    _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
     tokens, K = x.shape
     w_rows = w.shape[0]
     n_out = w_rows // 2 if epi == EPI_SWIGLU else w_rows
-    if epi not in (EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU):
-        raise KernelError(f"gemm_prefill_bf16 has no epilogue {epi}")
-    if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
-        raise KernelError(f"gemm sizes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    if not gemm_prefill_supported(x, w, n_out, out.dtype):
-        raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8, 16-byte aligned operands and output rows "
-                          f"(K={K}, {n_out} {out.dtype} per row)")
+    if epi == EPI_HEAD_PREP:
+        if out is not None or head_prep is None or w.shape[1] != K:
+            raise KernelError("EPI_HEAD_PREP takes head_prep, no out, and weights as wide as x")
+        if not gemm_bf16_supported(x, w):
+            raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
+    else:
+        if epi not in (EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU):
+            raise KernelError(f"gemm_prefill_bf16 has no epilogue {epi}")
+        _require(out, "out", torch.bfloat16 if epi in (EPI_STORE_BF16, EPI_SWIGLU) else torch.float32, 2)
+        if w.shape[1] != K or out.shape != (tokens, n_out) or (epi == EPI_SWIGLU and w_rows % 2):
+            raise KernelError(f"gemm sizes disagree: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if not gemm_prefill_supported(x, w, n_out, out.dtype):
+            raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8, 16-byte aligned operands and output rows "
+                              f"(K={K}, {n_out} {out.dtype} per row)")
     _, _, status = _gemm_buffers(w.device, 0)
     lib = load_library("gemm_prefill_tcgen05")
     _check(lib.odi_gemm_prefill_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
-                                     c_int(n_out), c_int(epi), _ptr(status), _stream()), "gemm_prefill_tcgen05")
+                                     c_int(n_out), c_int(epi), byref(head_prep) if head_prep is not None else _ptr(None),
+                                     _ptr(status), _stream()), "gemm_prefill_tcgen05")
 
 
 # ------------------------------------------------------------------------------ attention

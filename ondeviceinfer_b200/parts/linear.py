@@ -160,19 +160,34 @@ def linear(x, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
     return y
 
 
+def _heads_fit(head_dim: int, rot_dim: int, rotated: bool, write_kv: bool) -> bool:
+    return head_dim == 128 and write_kv and (not rotated or rot_dim == head_dim)
+
+
 def heads_in_epilogue(x, weight_qkv: torch.Tensor, *, head_dim: int, rot_dim: int, rotated: bool, write_kv: bool) -> bool:
-    """Whether :func:`project_heads` can serve this step: the tensor-core kernel in a form whose epilogue
-    prepares the heads (bf16, decode widths, heads of 128, whole-head rotation or none, keys/values written)."""
-    return (x.dtype == torch.bfloat16 and _own(x, weight_qkv) and
-            ops.gemm_bf16_fuses_head_prep(x.shape[0], weight_qkv.shape[0], weight_qkv.shape[1], d=head_dim,
-                                          rot_dim=rot_dim, rotated=rotated, write_kv=write_kv))
+    """Whether :func:`project_heads` can serve this step: a tensor-core kernel in a form whose epilogue
+    prepares the heads (bf16, heads of 128, whole-head rotation or none, keys/values written; decode widths
+    or the many-token kernel)."""
+    if x.dtype != torch.bfloat16 or not _heads_fit(head_dim, rot_dim, rotated, write_kv):
+        return False
+    if _own(x, weight_qkv):
+        return ops.gemm_bf16_fuses_head_prep(x.shape[0], weight_qkv.shape[0], weight_qkv.shape[1], d=head_dim,
+                                             rot_dim=rot_dim, rotated=rotated, write_kv=write_kv)
+    like = x.rows if isinstance(x, NormedRows) else x
+    return (PREFILL_GEMM != "library" and x.shape[0] >= PERSISTENT_MIN_TOKENS_PLAIN and weight_qkv.shape[0] % 128 == 0
+            and ops.gemm_bf16_supported(like, weight_qkv))
 
 
 def project_heads(x, weight_qkv: torch.Tensor, head_prep) -> None:
     """The q/k/v projections of ``x`` (a tensor or :class:`NormedRows`) with per-head norm, rotation and the
     cache write done in the product's epilogue; ``head_prep`` is the block ``ops.head_prep(None, ...)`` gives."""
-    x, norm = _operand(x, weight_qkv, weight_qkv.shape[0], ops.EPI_HEAD_PREP)
-    ops.gemm_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, norm=norm, head_prep=head_prep)
+    if _own(x, weight_qkv):
+        x, norm = _operand(x, weight_qkv, weight_qkv.shape[0], ops.EPI_HEAD_PREP)
+        ops.gemm_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, norm=norm, head_prep=head_prep)
+        return
+    if isinstance(x, NormedRows):
+        x = x.materialize()
+    ops.gemm_prefill_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, head_prep=head_prep)
 
 
 def gated_linear(x, weight_gate_up: torch.Tensor) -> torch.Tensor:

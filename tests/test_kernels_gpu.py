@@ -760,3 +760,48 @@ def test_gemm_prefill_tcgen05(tokens, N, K, epi):
             close(out, expected, "bfloat16")
         else:
             assert torch.allclose(out.cpu(), expected, atol=1e-4, rtol=1e-4), float((out.cpu() - expected).abs().max())
+
+
+@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,ring", [
+    ([300, 17, 2000], [0, 50, 0], 512, 4, 2, True, True, 0),          # unequal prompts, ragged token tiles
+    ([700], [100], 1024, 6, 3, False, True, 0),                       # no norm
+    ([256, 256], [0, 0], 256, 2, 1, True, False, 0),                  # no rotation, whole tiles
+    ([130, 100], [400, 60], 768, 3, 1, True, True, 3),                # an odd number of heads, rings of three pages (no step wraps its ring)
+])
+def test_gemm_prefill_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, ring):
+    """The q/k/v product of many tokens with the head preparation in its epilogue against the product followed
+    by the head-preparation kernel: close (the two add the squares of a head in different orders), and nothing
+    written elsewhere in the cache."""
+    torch.manual_seed(41)
+    d = 128
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", ring_pages=ring, seed=42)
+    n = sum(lengths)
+    w = (torch.randn((nq + 2 * nkv) * d, K) / math.sqrt(K)).bfloat16().to(DEV)
+    x = torch.randn(n, K).bfloat16().to(DEV)
+    qw = (1 + 0.1 * torch.randn(d)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(d)).to(DEV) if norm else None
+    cos = sin = None
+    if rot:
+        inv_freq = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+        cos = torch.empty(n, d // 2, dtype=torch.float32, device=DEV)
+        sin = torch.empty_like(cos)
+        ops.rope_table(inv_freq.to(DEV), setup["tok_pos"], cos, sin)
+    common = dict(nq=nq, nkv=nkv, d=d, rot_dim=d if rot else 0, page_size=64, ring_pages=ring, write_kv=True, eps=1e-5)
+    tail = (qw, kw, cos, sin, setup["tok_seq"], setup["tok_pos"], setup["page_start"], setup["page_ids"])
+    qkv = torch.empty(n, w.shape[0], dtype=torch.bfloat16, device=DEV)
+    ops.gemm_prefill_bf16(x, w, qkv, ops.EPI_STORE_BF16)
+    q_two = torch.zeros(n, nq * d, dtype=torch.bfloat16, device=DEV)
+    k_two, v_two = torch.zeros_like(setup["k_pool"]), torch.zeros_like(setup["v_pool"])
+    ops.head_prep(qkv, q_two, k_two, v_two, *tail, **common)
+    q_one = torch.zeros_like(q_two)
+    k_one, v_one = torch.zeros_like(k_two), torch.zeros_like(v_two)
+    block = ops.head_prep(None, q_one, k_one, v_one, *tail, **common)
+    ops.gemm_prefill_bf16(x, w, None, ops.EPI_HEAD_PREP, head_prep=block)
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    assert torch.equal(v_one, v_two)
+    for one, two in ((q_one, q_two), (k_one, k_two)):
+        assert float(two.float().abs().sum()) > 0
+        assert torch.equal(one == 0, two == 0) or float(((one == 0) != (two == 0)).float().mean()) < 1e-4
+        differ = (one.float() - two.float()).abs()
+        assert float(differ.max()) <= 0.02 * float(two.float().abs().max()) and float((differ > 0).float().mean()) < 0.02
