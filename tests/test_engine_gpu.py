@@ -264,3 +264,28 @@ def test_long_context(dtype, tmp_root):
         picks.append(t)
     assert_logits_close(torch.cat(rows), expected[picks], dtype, "long context in chunks")
     cache.free(slot)
+
+
+# heads of 128 at a small width: a prompt of 2,100 tokens goes through the many-token kernels (every
+# projection, with the head preparation, the SiLU gate and the residual adds in their epilogues)
+WIDE_HEADS = dict(LARGE, num_hidden_layers=2, hidden_size=1024, num_attention_heads=8, num_key_value_heads=2,
+                  intermediate_size=2048, vocab_size=1000, tie_word_embeddings=True)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompt_through_the_many_token_kernels(dtype, tmp_path):
+    import ondeviceinfer_b200 as odi
+    from helpers import write_model_folder
+
+    weights = plain.random_weights(WIDE_HEADS, 5)
+    model = odi.load_resident_model(write_model_folder(tmp_path / "wide", WIDE_HEADS, weights), dtype=dtype)
+    tokens = plain.random_prompts(WIDE_HEADS, [2100], 6)[0]
+    expected = plain.forward_logits(weights, WIDE_HEADS, tokens)
+    cache = model.make_cache(max_tokens=2176, max_seqs=1)
+    slot = cache.alloc()
+    picks = [0, 127, 128, 1023, 1024, 2047, 2048, 2089]
+    whole = model.step(cache, [slot], [tokens[:2090]], [picks])
+    rows = [whole] + [model.step(cache, [slot], [[t]], "last") for t in tokens[2090:]]
+    assert_logits_close(torch.cat(rows), expected[picks + list(range(2090, 2100))], dtype, "long prompt", longest_sum=2048)
+    cache.free(slot)
+    cache.check()
