@@ -2,12 +2,9 @@
 //
 //     out[token, n] = sum_k X[token, k] * W[n, k]        (X and W row-major, K contiguous)
 //
-// with fp32 accumulation in tensor memory and one of four epilogues.  The weight matrix
-// Both operands are K-major, so either can be the 128-row operand of tcgen05.mma:
-//  * decode form: a tile of 128 output features on the lanes, BN = 16..256 tokens on the
-//    columns (few tokens: the step streams each weight once at HBM speed);
-//  * prefill form: a tile of 128 tokens on the lanes, BN = 64..256 features on the columns,
-//    so a thread of the epilogue owns 16 consecutive features of its token (16-byte stores).
+// with fp32 accumulation in tensor memory, for few tokens (decode, short chunks): a tile is 128 output
+// features on the lanes of the accumulator and BN = 16..256 tokens on its columns, so a step streams each
+// weight once at HBM speed whatever the number of tokens.  (Many tokens: gemm_prefill_tcgen05.cu.)
 //
 // One CTA = one (feature tile, token tile, K split).  Six warps:
 //   warp 0   TMA producer: cp.async.bulk.tensor loads of W and X tiles (64 k per stage,
@@ -37,7 +34,7 @@
 #define EPI_STORE_F32 1    // out_f32[token, n] = acc
 #define EPI_RESIDUAL 2     // out_f32[token, n] += acc
 #define EPI_SWIGLU 3       // out_bf16[token, n] = silu(acc_gate) * acc_up   (DUAL)
-#define EPI_HEAD_PREP 4    // the rows are q, k and v heads of 128: per-head norm, rotation, cache write (decode form)
+#define EPI_HEAD_PREP 4    // the rows are q, k and v heads of 128: per-head norm, rotation, cache write
 
 #define BM 128             // features per tile (UMMA M)
 #define BK 64              // k per stage: 64 bf16 = one 128-byte swizzle row
@@ -56,7 +53,7 @@ struct GemmArgs {
   int tokens, N, K, ldo;
   int dual_offset;         // DUAL: row distance between the two weight tiles
   int splits;
-  // NORM (decode form): the activation operand is rmsnorm(norm_x) * norm_w, made on the fly from the
+  // NORM: the activation operand is rmsnorm(norm_x) * norm_w, made on the fly from the
   // fp32 rows norm_x [tokens, K]; a row's sum of squares is the sum of its norm_n_parts pieces in
   // norm_parts [norm_n_parts, tokens].
   const float* norm_x;
@@ -64,7 +61,7 @@ struct GemmArgs {
   const float* norm_parts;
   int norm_n_parts;
   float norm_eps;
-  // EPI_RESIDUAL (decode form): when not null, the sums of squares of the rows it leaves, one piece
+  // EPI_RESIDUAL: when not null, the sums of squares of the rows it leaves, one piece
   // per tile of 128 features: sumsq_out [ceil(N / 128), tokens].
   float* sumsq_out;
   // EPI_HEAD_PREP: a tile of 128 features is one head (query heads, then key heads, then value heads);
@@ -230,7 +227,7 @@ __device__ __forceinline__ void head_prep_finish(const HeadPrepArgs& hp, int t, 
 
 // ------------------------------------------------------------------------------ the kernel
 
-// Features on the lanes (decode form): one value per call; the 32 lanes of a warp write 32
+// Features on the lanes: one value per call; the 32 lanes of a warp write 32
 // consecutive features of one token.
 // Returns what it left in `out` for EPI_RESIDUAL (0 outside the matrix), else 0.
 template <int EPI>
@@ -245,79 +242,38 @@ __device__ __forceinline__ float emit(const GemmArgs& a, int token, int n, float
 }
 
 
-// Tokens on the lanes (prefill form): a thread holds 16 consecutive features of its token
-// and writes them with 16-byte stores when the row is aligned for that.
-template <int EPI>
-__device__ __forceinline__ void emit_row16(const GemmArgs& a, int token, int n, const float* v, const float* u,
-                                           bool vec_ok) {
-  if (token >= a.tokens || n >= a.N) return;
-  const size_t at = (size_t)token * a.ldo + n;
-  if (vec_ok && n + 16 <= a.N) {
-    if (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU) {
-      uint32_t packed[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float lo = EPI == EPI_SWIGLU ? silu_f(v[2 * i]) * u[2 * i] : v[2 * i];
-        const float hi = EPI == EPI_SWIGLU ? silu_f(v[2 * i + 1]) * u[2 * i + 1] : v[2 * i + 1];
-        __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
-        packed[i] = *(uint32_t*)&pair;
-      }
-      uint4* dst = (uint4*)((bf16*)a.out + at);
-      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    } else {
-      float4* dst = (float4*)((float*)a.out + at);
-      float4 r[4];
-      if (EPI == EPI_RESIDUAL) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) r[i] = dst[i];
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        if (EPI == EPI_RESIDUAL) { o.x += r[i].x; o.y += r[i].y; o.z += r[i].z; o.w += r[i].w; }
-        dst[i] = o;
-      }
-    }
-    return;
-  }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) emit<EPI>(a, token, n + i, v[i], (EPI == EPI_SWIGLU) ? u[i] : 0.f);
-}
-
-// SWAP = false: the 128 lanes are features (weight rows), the BN columns are tokens.
-// SWAP = true : the 128 lanes are tokens, the BN columns are features.
-// NORM (decode form only): the four epilogue warps first serve as converters: for every k-block they
+// The 128 lanes of the accumulator are features (weight rows), its BN columns are tokens.
+// NORM: the four epilogue warps first serve as converters: for every k-block they
 // read the fp32 rows, scale them by the row's 1/rms and the norm weight with the roundings of the
 // stand-alone RMSNorm kernel, and write the bf16 operand tile in the swizzled layout that TMA would
 // have produced; the MMA thread waits for them (`ready`) as well as for the weight tile (`full`).
-template <int BN, bool DUAL, int EPI, int STAGES, bool SWAP, bool CLUSTER, bool NORM>
+template <int BN, bool DUAL, int EPI, int STAGES, bool CLUSTER, bool NORM>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs a) {
   constexpr int L_BYTES = BM * BK * 2;                    // lanes operand tile, 16 KB
   constexpr int C_BYTES = BN * BK * 2;                    // columns operand tile
-  constexpr int L_TILES = (DUAL && !SWAP) ? 2 : 1;
-  constexpr int C_TILES = (DUAL && SWAP) ? 2 : 1;
+  constexpr int L_TILES = DUAL ? 2 : 1;                   // the gate and the up tile
+  constexpr int C_TILES = 1;
   constexpr int STAGE_BYTES = L_BYTES * L_TILES + C_BYTES * C_TILES;
   constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
   constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  static_assert(!NORM || (!SWAP && BN % 16 == 0 && BN <= 64), "the norm prologue belongs to the decode form");
+  static_assert(!NORM || (BN % 16 == 0 && BN <= 64), "the norm prologue takes token tiles of 16, 32 or 64");
   // EPI_HEAD_PREP stages the finished rows behind the split partials (which peers may still be reading)
   constexpr int HP_STAGE_OFFSET = BN * BM * 4;
-  static_assert(EPI != EPI_HEAD_PREP || (!SWAP && !DUAL && BN <= 64 && 2 * BN * BM * 4 <= STAGES * STAGE_BYTES),
-                "the head-preparation epilogue belongs to the decode form");
+  static_assert(EPI != EPI_HEAD_PREP || (!DUAL && BN <= 64 && 2 * BN * BM * 4 <= STAGES * STAGE_BYTES),
+                "the head-preparation epilogue needs room behind the split partials");
   __shared__ __align__(8) uint64_t bars[3 * STAGES + 1];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ int ticket_slot;
-  __shared__ float sumsq_part[4][SWAP ? 1 : (BN <= 64 ? BN : 1)];    // per epilogue warp and token column
+  __shared__ float sumsq_part[4][BN <= 64 ? BN : 1];    // per epilogue warp and token column
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tok0 = blockIdx.x * (SWAP ? BM : BN), n0 = blockIdx.y * (SWAP ? BN : BM), split = blockIdx.z;
+  const int tok0 = blockIdx.x * BN, n0 = blockIdx.y * BM, split = blockIdx.z;
   const int total_kb = (a.K + BK - 1) / BK;
   const int kb_begin = (int)((long)total_kb * split / a.splits);
   const int kb_count = (int)((long)total_kb * (split + 1) / a.splits) - kb_begin;
@@ -340,14 +296,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      const CUtensorMap* map_l = SWAP ? &map_x : &map_w;
-      const CUtensorMap* map_c = SWAP ? &map_w : &map_x;
-      const int l_row = SWAP ? tok0 : n0, c_row = SWAP ? n0 : tok0;
-      // Weights are never written by a kernel, so in the decode form their first tiles are
+      const CUtensorMap* map_l = &map_w;       // the lanes' operand: weight rows
+      const CUtensorMap* map_c = &map_x;       // the columns' operand: token rows
+      const int l_row = n0, c_row = tok0;
+      // Weights are never written by a kernel, so their first tiles are
       // requested before this grid waits for the kernels it depends on; only the activation
       // tiles (and everything the epilogue touches, which runs after them) come after the wait.
       constexpr uint32_t TX_BYTES = NORM ? L_BYTES * L_TILES : STAGE_BYTES;   // NORM: the converters fill the rest
-      const int pre = SWAP ? 0 : min(STAGES, kb_count);
+      const int pre = min(STAGES, kb_count);
       for (int i = 0; i < pre; ++i) {
         const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
         const int k0 = (kb_begin + i) * BK;
@@ -396,7 +352,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
           // 16 k = 32 bytes further inside the swizzle row: +2 in the (address >> 4) field
           umma_bf16(tmem_base, dl + 2 * j, dc + 2 * j, idesc, acc);
-          if (DUAL) umma_bf16(tmem_base + BN, (SWAP ? dl : dl2) + 2 * j, (SWAP ? dc2 : dc) + 2 * j, idesc, acc);
+          if (DUAL) umma_bf16(tmem_base + BN, dl2 + 2 * j, dc + 2 * j, idesc, acc);
         }
         umma_commit(empty0 + 8 * s);    // the stage is free once these MMAs have read it
       }
@@ -486,20 +442,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (!ok && lane == 0) atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_EPILOGUE);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     tc_fence_after();
-    if (ok && SWAP) {
-      const int token = tok0 + row;
-      const bool vec_ok = (EPI == EPI_STORE_BF16 || EPI == EPI_SWIGLU)
-                              ? (a.ldo % 8 == 0 && ((uintptr_t)a.out & 15) == 0)
-                              : (a.ldo % 4 == 0 && ((uintptr_t)a.out & 15) == 0);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        if (n0 + c >= a.N) break;
-        float v[16], u[16];
-        tmem_ld16(taddr + c, v);
-        if (DUAL) tmem_ld16(taddr + BN + c, u);
-        emit_row16<EPI>(a, token, n0 + c, v, u, vec_ok);
-      }
-    } else if (ok && a.splits == 1) {
+    if (ok && a.splits == 1) {
       const int n = n0 + row;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
@@ -602,7 +545,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (threadIdx.x == 64) a.tickets[tile_id] = 0;    // ready for the next launch
       }
     }
-    if (!SWAP && EPI == EPI_HEAD_PREP && a.splits == 1) {
+    if (EPI == EPI_HEAD_PREP && a.splits == 1) {
       // every epilogue warp comes here, whatever happened above; then a warp per token column
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const float* stage = (const float*)(smem + HP_STAGE_OFFSET);
@@ -610,7 +553,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int c = lane_group; c < BN && tok0 + c < a.tokens; c += 4)
           head_prep_finish(a.hp, tok0 + c, blockIdx.y, stage + c * BM, lane);
     }
-    if (!SWAP && EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr && a.splits == 1) {
+    if (EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr && a.splits == 1) {
       // every epilogue warp comes here, whatever happened above: the four warps' sums, in warp order
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const int c = threadIdx.x - 64;
@@ -620,7 +563,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     tc_fence_before();
   }
-  if (CLUSTER && !SWAP && a.splits > 1) {
+  if (CLUSTER && a.splits > 1) {
     // Every thread of every CTA of the cluster takes part in both barriers, whatever happened before.
     __syncwarp();
     cluster_sync_all();
@@ -711,23 +654,23 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
 }
 
-template <int BN, bool DUAL, int EPI, bool SWAP, bool CLUSTER, bool NORM = false>
+template <int BN, bool DUAL, int EPI, bool CLUSTER, bool NORM = false>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
-  constexpr int STAGE_BYTES = BM * BK * 2 * ((DUAL && !SWAP) ? 2 : 1) + BN * BK * 2 * ((DUAL && SWAP) ? 2 : 1);
-  // The decode form takes about 72 KB (four stages of a 128 x 16 tile), so that three CTAs fit on an
+  constexpr int STAGE_BYTES = BM * BK * 2 * (DUAL ? 2 : 1) + BN * BK * 2;
+  // A CTA takes about 72 KB (four stages of a 128 x 16 tile), so that three CTAs fit on an
   // SM: several short pipelines per SM hide each other's set-up, drain and split exchange, and the
   // CTAs of the next kernel of the stream find room to move in and request their first weight tiles
   // while this one drains.  Measured on whole captured decode steps (Qwen3-8B sizes, batch 1 / 8):
   // 72-84 KB 3.39 / 3.86 ms, 56-64 KB 3.46 / 4.13 ms, 100 KB 3.50 / 4.13 ms; one CTA of 144-200 KB
-  // per SM is 1.5x slower per kernel.  The prefill form takes the SM alone.
+  // per SM is 1.5x slower per kernel.
 #ifndef ODI_GEMM_DECODE_SMEM_KB
 #define ODI_GEMM_DECODE_SMEM_KB 72
 #endif
-  constexpr int BUDGET = SWAP ? 200 * 1024 : ODI_GEMM_DECODE_SMEM_KB * 1024;
+  constexpr int BUDGET = ODI_GEMM_DECODE_SMEM_KB * 1024;
   constexpr int STAGES = BUDGET / STAGE_BYTES < 2 ? 2 : (BUDGET / STAGE_BYTES > 12 ? 12 : BUDGET / STAGE_BYTES);
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
   static_assert(!CLUSTER || (DUAL ? 2 : 1) * BN * BM * 4 <= STAGES * STAGE_BYTES, "the split partial must fit the stage memory");
-  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, SWAP, CLUSTER, NORM>;
+  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, CLUSTER, NORM>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -756,28 +699,28 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
   return launch_status();
 }
 
-template <int BN, bool SWAP, bool CLUSTER>
+template <int BN, bool CLUSTER>
 static int dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid,
                         cudaStream_t stream) {
   if (a.norm_x != nullptr) {
     // the norm prologue exists for the two products that follow a norm in a decoder layer, at decode widths
-    if constexpr (!SWAP && BN <= 32) {
-      if (epi == EPI_STORE_BF16) return launch<BN, false, EPI_STORE_BF16, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
-      if (epi == EPI_SWIGLU) return launch<BN, true, EPI_SWIGLU, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
-      if (epi == EPI_HEAD_PREP) return launch<BN, false, EPI_HEAD_PREP, SWAP, CLUSTER, true>(mw, mx, a, grid, stream);
+    if constexpr (BN <= 32) {
+      if (epi == EPI_STORE_BF16) return launch<BN, false, EPI_STORE_BF16, CLUSTER, true>(mw, mx, a, grid, stream);
+      if (epi == EPI_SWIGLU) return launch<BN, true, EPI_SWIGLU, CLUSTER, true>(mw, mx, a, grid, stream);
+      if (epi == EPI_HEAD_PREP) return launch<BN, false, EPI_HEAD_PREP, CLUSTER, true>(mw, mx, a, grid, stream);
     }
     return ODI_ERR_UNSUPPORTED;
   }
   if (epi == EPI_HEAD_PREP) {
-    if constexpr (!SWAP && BN <= 32) return launch<BN, false, EPI_HEAD_PREP, SWAP, CLUSTER>(mw, mx, a, grid, stream);
+    if constexpr (BN <= 32) return launch<BN, false, EPI_HEAD_PREP, CLUSTER>(mw, mx, a, grid, stream);
     else return ODI_ERR_UNSUPPORTED;
   }
   switch (epi) {
-    case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, SWAP, CLUSTER>(mw, mx, a, grid, stream);
-    case EPI_STORE_F32: return launch<BN, false, EPI_STORE_F32, SWAP, CLUSTER>(mw, mx, a, grid, stream);
-    case EPI_RESIDUAL: return launch<BN, false, EPI_RESIDUAL, SWAP, CLUSTER>(mw, mx, a, grid, stream);
+    case EPI_STORE_BF16: return launch<BN, false, EPI_STORE_BF16, CLUSTER>(mw, mx, a, grid, stream);
+    case EPI_STORE_F32: return launch<BN, false, EPI_STORE_F32, CLUSTER>(mw, mx, a, grid, stream);
+    case EPI_RESIDUAL: return launch<BN, false, EPI_RESIDUAL, CLUSTER>(mw, mx, a, grid, stream);
     case EPI_SWIGLU:
-      if constexpr (BN <= 128 && !(CLUSTER && BN > 64)) return launch<BN, true, EPI_SWIGLU, SWAP, CLUSTER>(mw, mx, a, grid, stream);
+      if constexpr (BN <= 128 && !(CLUSTER && BN > 64)) return launch<BN, true, EPI_SWIGLU, CLUSTER>(mw, mx, a, grid, stream);
       else return ODI_ERR_UNSUPPORTED;
   }
   return ODI_ERR_ARGUMENT;
@@ -792,11 +735,11 @@ extern "C" long odi_gemm_bf16_scratch_floats(int tokens, int n_out, int bn, int 
 
 // x [tokens, K] bf16, w [w_rows, K] bf16 (for EPI_SWIGLU w holds the gate rows followed by
 // the up rows and n_out = w_rows / 2), out [tokens, ldo].
-// swap == 0 (decode form): tiles of 128 features x bn tokens, bn in {16, 32, 64, 128, 256}, K splits allowed;
-//            cluster != 0 lets 2..8 splits (bn <= 64) exchange partials through distributed shared memory.
-// swap == 1 (prefill form): tiles of 128 tokens x bn features, bn in {64, 128, 256}, no splits.
+// Tiles of 128 features x bn tokens, bn in {16, 32, 64, 128, 256}, K splits allowed; cluster != 0 lets 2..8 splits
+// (bn <= 64) exchange partials through distributed shared memory.  Many tokens are the business of
+// gemm_prefill_tcgen05.cu; this kernel takes them too, tile by tile, but re-reads the weights for every token tile.
 extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
-                             int ldo, int epi, int bn, int splits, int swap, int cluster, float* scratch,
+                             int ldo, int epi, int bn, int splits, int cluster, float* scratch,
                              int* tickets, int* status, const float* norm_x, const float* norm_w,
                              const float* norm_parts, int norm_n_parts, float norm_eps, float* sumsq_out,
                              const HeadPrepArgs* head_prep, cudaStream_t stream) {
@@ -804,26 +747,26 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
   if (x == nullptr && norm_x == nullptr) return ODI_ERR_ARGUMENT;
   const int total_kb = (K + BK - 1) / BK;
-  if (splits < 1 || splits > total_kb || (swap && splits != 1)) return ODI_ERR_ARGUMENT;
-  const bool clustered = cluster && splits > 1 && splits <= 8 && bn <= 64 && !swap;
+  if (splits < 1 || splits > total_kb) return ODI_ERR_ARGUMENT;
+  const bool clustered = cluster && splits > 1 && splits <= 8 && bn <= 64;
   if (splits > 1 && !clustered && (scratch == nullptr || tickets == nullptr)) return ODI_ERR_ARGUMENT;
   if (status == nullptr) return ODI_ERR_ARGUMENT;
   const bool dual = epi == EPI_SWIGLU;
   if (dual && w_rows != 2 * n_out) return ODI_ERR_ARGUMENT;
   CUtensorMap mw, mx;
-  int rc = make_map(&mw, w, w_rows, K, swap ? bn : BM);
+  int rc = make_map(&mw, w, w_rows, K, BM);
   if (rc != 0) return rc;
-  rc = make_map(&mx, norm_x != nullptr ? w : x, tokens, K, swap ? BM : bn);    // with the norm prologue the map is not used
+  rc = make_map(&mx, norm_x != nullptr ? w : x, tokens, K, bn);    // with the norm prologue the map is not used
   if (rc != 0) return rc;
   GemmArgs a;
   a.out = out; a.scratch = scratch; a.tickets = tickets; a.status = status;
   a.tokens = tokens; a.N = n_out; a.K = K; a.ldo = ldo; a.dual_offset = dual ? n_out : 0; a.splits = splits;
   if (norm_x != nullptr) {
-    if (swap || bn > 32 || (epi != EPI_STORE_BF16 && epi != EPI_SWIGLU && epi != EPI_HEAD_PREP)) return ODI_ERR_UNSUPPORTED;
+    if (bn > 32 || (epi != EPI_STORE_BF16 && epi != EPI_SWIGLU && epi != EPI_HEAD_PREP)) return ODI_ERR_UNSUPPORTED;
     if (norm_w == nullptr || norm_parts == nullptr || norm_n_parts < 1) return ODI_ERR_ARGUMENT;
     if (((uintptr_t)norm_x & 15) || ((uintptr_t)norm_w & 15)) return ODI_ERR_UNSUPPORTED;
   }
-  if (sumsq_out != nullptr && (epi != EPI_RESIDUAL || swap || bn > 64 || !(clustered || splits == 1))) return ODI_ERR_UNSUPPORTED;
+  if (sumsq_out != nullptr && (epi != EPI_RESIDUAL || bn > 64 || !(clustered || splits == 1))) return ODI_ERR_UNSUPPORTED;
   a.norm_x = norm_x; a.norm_w = norm_w; a.norm_parts = norm_parts; a.norm_n_parts = norm_n_parts; a.norm_eps = norm_eps;
   a.sumsq_out = sumsq_out;
   if (epi == EPI_HEAD_PREP) {
@@ -831,37 +774,28 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
     if (head_prep == nullptr) return ODI_ERR_ARGUMENT;
     a.hp = *head_prep;
     const HeadPrepArgs& hp = a.hp;
-    if (swap || bn > 32 || !(clustered || splits == 1) || hp.d != BM || n_out != (hp.nq + 2 * hp.nkv) * BM ||
+    if (bn > 32 || !(clustered || splits == 1) || hp.d != BM || n_out != (hp.nq + 2 * hp.nkv) * BM ||
         !hp.write_kv || (hp.cos_t != nullptr && hp.rot_dim != hp.d) || hp.n_tokens != tokens)
       return ODI_ERR_UNSUPPORTED;
   } else {
     a.hp = HeadPrepArgs{};
   }
-  const int tok_tile = swap ? BM : bn, n_tile = swap ? bn : BM;
-  dim3 grid((tokens + tok_tile - 1) / tok_tile, (n_out + n_tile - 1) / n_tile, splits);
+  dim3 grid((tokens + bn - 1) / bn, (n_out + BM - 1) / BM, splits);
   if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;
-  if (swap) {
-    switch (bn) {
-      case 64: return dispatch_epi<64, true, false>(epi, mw, mx, a, grid, stream);
-      case 128: return dispatch_epi<128, true, false>(epi, mw, mx, a, grid, stream);
-      case 256: return dispatch_epi<256, true, false>(epi, mw, mx, a, grid, stream);
-    }
-    return ODI_ERR_UNSUPPORTED;
-  }
   // 2..8 splits of a token tile of up to 64 exchange their partials inside a cluster
   if (cluster && splits > 1 && splits <= 8 && bn <= 64) {
     switch (bn) {
-      case 16: return dispatch_epi<16, false, true>(epi, mw, mx, a, grid, stream);
-      case 32: return dispatch_epi<32, false, true>(epi, mw, mx, a, grid, stream);
-      case 64: return dispatch_epi<64, false, true>(epi, mw, mx, a, grid, stream);
+      case 16: return dispatch_epi<16, true>(epi, mw, mx, a, grid, stream);
+      case 32: return dispatch_epi<32, true>(epi, mw, mx, a, grid, stream);
+      case 64: return dispatch_epi<64, true>(epi, mw, mx, a, grid, stream);
     }
   }
   switch (bn) {
-    case 16: return dispatch_epi<16, false, false>(epi, mw, mx, a, grid, stream);
-    case 32: return dispatch_epi<32, false, false>(epi, mw, mx, a, grid, stream);
-    case 64: return dispatch_epi<64, false, false>(epi, mw, mx, a, grid, stream);
-    case 128: return dispatch_epi<128, false, false>(epi, mw, mx, a, grid, stream);
-    case 256: return dispatch_epi<256, false, false>(epi, mw, mx, a, grid, stream);
+    case 16: return dispatch_epi<16, false>(epi, mw, mx, a, grid, stream);
+    case 32: return dispatch_epi<32, false>(epi, mw, mx, a, grid, stream);
+    case 64: return dispatch_epi<64, false>(epi, mw, mx, a, grid, stream);
+    case 128: return dispatch_epi<128, false>(epi, mw, mx, a, grid, stream);
+    case 256: return dispatch_epi<256, false>(epi, mw, mx, a, grid, stream);
   }
   return ODI_ERR_UNSUPPORTED;
 }

@@ -93,7 +93,7 @@ def gemm_case(args) -> dict:
     elif args.persistent:
         run = lambda i: ops.gemm_prefill_bf16(x, ws[i], out, epi)
     else:
-        run = lambda i: ops.gemm_bf16(x, ws[i], out, epi, swap=args.swap, bn=args.bn, splits=args.splits,
+        run = lambda i: ops.gemm_bf16(x, ws[i], out, epi, bn=args.bn, splits=args.splits,
                                       cluster=not args.no_cluster, **extra)
     us = time_kernel(run, copies, args.reps)
     ops.raise_on_kernel_fault()
@@ -180,7 +180,6 @@ def main(argv=None) -> int:
     parser.add_argument("--sumsq", action="store_true", help="gemm --epi residual: also leave the rows' sums of squares")
     parser.add_argument("--bn", type=int, default=None)
     parser.add_argument("--splits", type=int, default=None)
-    parser.add_argument("--swap", type=int, default=None)
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
     parser.add_argument("--persistent", action="store_true", help="gemm: the persistent two-CTA kernel for many tokens")
     parser.add_argument("--no-cluster", action="store_true", help="GEMM K splits through global scratch, not a cluster")
@@ -199,8 +198,6 @@ def main(argv=None) -> int:
     parser.add_argument("--no-rotate", dest="rotate", action="store_false",
                         help="one operand set only (small captures under a profiler)")
     args = parser.parse_args(argv)
-    if args.swap is not None:
-        args.swap = bool(args.swap)
     if args.case == "attention-decode" and args.splits is None:
         args.splits = 1
     torch.manual_seed(0)

@@ -258,28 +258,16 @@ def raise_on_kernel_fault() -> None:
 
 
 def gemm_bf16_plan(tokens: int, n_out: int, K: int, epi: int):
-    """(swap, tile, splits) for a shape.
-
-    Up to 64 tokens: decode form (128 features x `tile` tokens per CTA) with enough K
-    splits for about 384 CTAs (at most 8, a cluster), each split at least four k-blocks of 64.
-    More tokens: prefill form (128 tokens x `tile` features per CTA), the largest tile
-    that still gives every SM a CTA.
-    """
+    """(tile, splits) for a shape: tiles of 128 features x `tile` tokens, with enough K splits for about
+    384 CTAs (at most 8, a cluster), each split at least four k-blocks of 64."""
     total_kb = -(-K // 64)
-    if tokens <= 64:
-        bn = next(b for b in (16, 32, 64) if tokens <= b)
-        tiles = -(-n_out // 128)
-        # measured on whole decode steps on B200: about 384 CTAs (three of 72 KB per SM) stream best,
-        # in clusters of up to 8 splits (192: +7 %, 288: +2 %, 512: +7 % step time)
-        target = 384
-        splits = max(1, min(total_kb // 4, int(target / tiles + 0.5), 8)) if tiles < target else 1
-        return False, bn, splits
-    choices = (128, 64) if epi == EPI_SWIGLU else (256, 128, 64)
-    token_tiles = -(-tokens // 128)
-    for bn in choices:
-        if token_tiles * -(-n_out // bn) >= 120:
-            return True, bn, 1
-    return True, choices[-1], 1
+    bn = next((b for b in (16, 32, 64) if tokens <= b), 64)
+    tiles = -(-n_out // 128) * -(-tokens // bn)
+    # measured on whole decode steps on B200: about 384 CTAs (three of 72 KB per SM) stream best,
+    # in clusters of up to 8 splits (192: +7 %, 288: +2 %, 512: +7 % step time)
+    target = 384
+    splits = max(1, min(total_kb // 4, int(target / tiles + 0.5), 8)) if tiles < target else 1
+    return bn, splits
 
 
 def gemm_bf16_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -294,27 +282,27 @@ def gemm_bf16_sumsq_parts(n_out: int) -> int:
 
 def gemm_bf16_fuses_norm(tokens: int, n_out: int, K: int, epi: int) -> bool:
     """Whether the planned form of this product can take its operand through the norm prologue."""
-    swap, bn, _ = gemm_bf16_plan(tokens, n_out, K, epi)
-    return not swap and bn <= 32 and epi in (EPI_STORE_BF16, EPI_SWIGLU, EPI_HEAD_PREP)
+    bn, _ = gemm_bf16_plan(tokens, n_out, K, epi)
+    return bn <= 32 and tokens <= 32 and epi in (EPI_STORE_BF16, EPI_SWIGLU, EPI_HEAD_PREP)
 
 
 def gemm_bf16_fuses_head_prep(tokens: int, n_out: int, K: int, *, d: int, rot_dim: int, rotated: bool,
                               write_kv: bool) -> bool:
     """Whether the planned form of the q/k/v product can prepare the heads in its epilogue: heads of 128
     (a tile of the product is a head), whole-head rotation or none, keys and values written, decode widths."""
-    swap, bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_STORE_BF16)
-    return (not swap and bn <= 32 and splits <= 8 and d == 128 and n_out % 128 == 0 and write_kv
+    bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_STORE_BF16)
+    return (bn <= 32 and tokens <= 32 and splits <= 8 and d == 128 and n_out % 128 == 0 and write_kv
             and (not rotated or rot_dim == d))
 
 
 def gemm_bf16_gives_sumsq(tokens: int, n_out: int, K: int) -> bool:
     """Whether the planned form of this residual product can leave the rows' sums of squares."""
-    swap, bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_RESIDUAL)
-    return not swap and bn <= 64 and splits <= 8
+    bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_RESIDUAL)
+    return bn <= 64 and splits <= 8
 
 
 def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *,
-              swap: Optional[bool] = None, bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True,
+              bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True,
               norm: Optional[tuple] = None, sumsq_out: Optional[torch.Tensor] = None, head_prep=None) -> None:
     """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
 
@@ -365,8 +353,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
             raise KernelError("sumsq_out goes with EPI_RESIDUAL and has one row per tile of 128 features")
     if not gemm_bf16_supported(x_like, w):
         raise KernelError(f"gemm_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
-    plan_swap, plan_bn, plan_splits = gemm_bf16_plan(tokens, n_out, K, epi)
-    swap = plan_swap if swap is None else swap
+    plan_bn, plan_splits = gemm_bf16_plan(tokens, n_out, K, epi)
     bn = plan_bn if bn is None else bn
     splits = plan_splits if splits is None else splits
     lib = load_library("gemm_tcgen05")
@@ -374,7 +361,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
     need = lib.odi_gemm_bf16_scratch_floats(c_int(tokens), c_int(n_out), c_int(bn), c_int(splits),
                                             c_int(1 if epi == EPI_SWIGLU else 0))
     tiles = -(-n_out // 128) * -(-tokens // bn)
-    scratch, tickets, status = _gemm_buffers(w.device, need if not swap else 0)
+    scratch, tickets, status = _gemm_buffers(w.device, need)
     if splits > 1 and tiles > tickets.numel():
         raise KernelError("too many tiles for a split product")
     if norm is not None:
@@ -382,8 +369,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
     else:
         norm_args = (_ptr(None), _ptr(None), _ptr(None), c_int(0), c_float(0.0))
     _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
-                             c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if swap else 0),
-                             c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
+                             c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
                              _ptr(sumsq_out), byref(head_prep) if head_prep is not None else _ptr(None), _stream()),
            "gemm_tcgen05")
 
