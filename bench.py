@@ -2,13 +2,15 @@
 """Serving benchmark of ondeviceinfer_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
-                    [--layers L] [--batch B] [--points / --no-points]
+                    [--layers L] [--batch B] [--no-points]
+                    [--sizes 8B|14B|32B] [--prompt-len T] [--context C]
 
 Measures the metric of BASELINE.json: decode tokens per second (and prefill tokens per
 second at 2,048 tokens) for the Qwen3-8B layer sizes in bf16 with seeded random weights
 and uniform random token ids.  A "step" is one decode step of the whole batch.  The
 default run has a batch of 8 sequences with 2,048-token prompts in a cache sized for a
-context of 4,096.  One JSON line is printed:
+context of 4,096; ``--sizes``, ``--prompt-len`` and ``--context`` give the same run at the
+layer sizes of Qwen3-14B or Qwen3-32B and at other lengths.  One JSON line is printed:
 
 * ``value``   decoded tokens per second over K steps, timed on the device with CUDA
               events (sampled tokens stay on the device);
@@ -44,6 +46,12 @@ QWEN3_8B = {
     "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
     "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "max_position_embeddings": 40960, "hidden_act": "silu",
+}
+# other layer sizes of the same architecture, for runs beside the default one (--sizes)
+OTHER_SIZES = {
+    "8B": {},
+    "14B": {"num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40, "intermediate_size": 17408},
+    "32B": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "intermediate_size": 25600},
 }
 CONTEXT, PROMPT, PREFILL_TOKENS = 4096, 2048, 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -145,6 +153,9 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--sizes", default="8B", choices=sorted(OTHER_SIZES), help="layer sizes (default: the benchmark's)")
+    parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the timed decode steps")
+    parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
     args = parser.parse_args()
     if args.impl == "reference":
         return run_reference_arm()
@@ -160,7 +171,12 @@ def main() -> int:
     from ondeviceinfer_b200.kernels import ops
     from ondeviceinfer_b200.sampling import Sampler
 
-    cfg = dict(QWEN3_8B)
+    cfg = dict(QWEN3_8B, **OTHER_SIZES[args.sizes])
+    prompt_len = args.prompt_len
+    needed = prompt_len + args.warmup + args.steps + 1
+    context = args.context or max(CONTEXT, -(-needed // 64) * 64)
+    if context < needed:
+        parser.error(f"--context {context} is below the {needed} positions that the prompt and the steps need")
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
@@ -175,14 +191,14 @@ def main() -> int:
         return torch.randint(0, cfg["vocab_size"], (batch, length), generator=gen).tolist()
 
     def decode_run(batch, steps, warmup, end_to_end):
-        """Prefill `batch` prompts of PROMPT tokens, then time `steps` decode steps.
+        """Prefill `batch` prompts of `prompt_len` tokens, then time `steps` decode steps.
 
         Device-timed: the steps replay back to back, sampled tokens stay on the device.
         End to end: the public decode call per step, which copies the step's token ids from
         pinned host memory to the device and reads the sampled tokens back to the host."""
-        cache = model.make_cache(max_tokens=batch * CONTEXT, max_seqs=batch)
+        cache = model.make_cache(max_tokens=batch * context, max_seqs=batch)
         slots = [cache.alloc() for _ in range(batch)]
-        logits = model.step(cache, slots, prompts_for(batch, PROMPT), "last")
+        logits = model.step(cache, slots, prompts_for(batch, prompt_len), "last")
         tokens = sampler(logits, range(batch), [0] * batch)
         runner = odi.api.decode_runner(model, cache, temperature=0.0, seed=0)
         runner.begin(slots, tokens, list(range(batch)), [1] * batch)
@@ -240,18 +256,18 @@ def main() -> int:
     clock_record = clocks.stop()
     e2e_run = decode_run(args.batch, args.steps, args.warmup, end_to_end=True)
     result = {
-        "metric": "decode tokens/s (Qwen3-8B layer sizes, bf16, batch %d, 2,048-token prompts)" % args.batch,
+        "metric": "decode tokens/s (Qwen3-%s layer sizes, bf16, batch %d, %s-token prompts)" % (args.sizes, args.batch, format(prompt_len, ",")),
         "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights normal(0, 0.02), uniform random token ids",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-8B layer sizes", "layers": layers, "layers_of_model": full_layers,
+            "model": "Qwen3-%s layer sizes" % args.sizes, "layers": layers, "layers_of_model": full_layers,
             "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"],
             "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False, "global_batch": args.batch,
-            "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single-gpu",
+            "seq_len": context, "prompt_len": prompt_len, "parallelism": "single-gpu",
             "l2": "inputs larger than L2: each step reads all weights and the cache",
             "peaks": peak_source},
         "e2e": {"value": e2e_run["tok_s"], "unit": "tokens/s", "ms_per_step": e2e_run["ms_per_step"],

@@ -58,12 +58,12 @@ class _DecodeContext:
 
 
 class DecodeRunner:
-    def __init__(self, model, cache, *, temperature: float = 0.0, seed: int = 0, kv_len_hint: int = 2048) -> None:
+    def __init__(self, model, cache, *, temperature: float = 0.0, seed: int = 0) -> None:
         self.model, self.cache = model, cache
         self.temperature, self.seed = float(temperature), int(seed)
-        self.kv_len_hint = kv_len_hint
         self.max_pages = cache.n_pages
-        self._graphs: Dict[int, tuple] = {}
+        self._contexts: Dict[int, _DecodeContext] = {}     # by width: the buffers that every graph of the width uses
+        self._graphs: Dict[tuple, tuple] = {}               # by (width, longest-sequence bucket)
         self.live_slots: List[int] = []
         self.ctx: Optional[_DecodeContext] = None
         self._host_pages: List[np.ndarray] = []
@@ -74,6 +74,16 @@ class DecodeRunner:
 
     def close(self) -> None:
         self._graphs.clear()
+        self._contexts.clear()
+
+    @staticmethod
+    def _bucket_for(kv_len: int) -> int:
+        """A captured graph fixes how the keys of a sequence are cut among blocks, which is chosen from
+        the longest sequence: one graph per power of two of that length, from 256 on."""
+        bucket = 256
+        while bucket < kv_len:
+            bucket *= 2
+        return bucket
 
     @staticmethod
     def _width_for(n: int) -> int:
@@ -93,9 +103,8 @@ class DecodeRunner:
         if n == 0:
             raise ValueError("a decode batch needs at least one sequence")
         width = self._width_for(n)
-        if width not in self._graphs:
-            self._graphs[width] = self._capture(width)
-        ctx, _, _ = self._graphs[width]
+        self._graph_for(width, self._bucket_for(max(self.cache.lengths[s] for s in slots) + 1))
+        ctx = self._contexts[width]
         self.ctx, self.live_slots = ctx, list(slots)
         pad = self.cache.pad_slot
         row_slots = list(slots) + [pad] * (width - n)
@@ -137,9 +146,30 @@ class DecodeRunner:
         ops.sample(logits, ctx.token_ids, self.temperature, self.seed, ctx.streams, ctx.steps,
                    advance_pos=ctx.tok_pos, advance_past=ctx.past, active=ctx.active)
 
-    def _capture(self, width: int):
-        device = self.model.device
-        ctx = _DecodeContext(self.cache, width, self.max_pages, device, self.kv_len_hint)
+    def _graph_for(self, width: int, bucket: int):
+        key = (width, bucket)
+        if key not in self._graphs:
+            ctx = self._contexts.get(width)
+            if ctx is None:
+                ctx = self._contexts[width] = _DecodeContext(self.cache, width, self.max_pages, self.model.device, bucket)
+                self._graphs[key] = self._capture(ctx, bucket)
+            else:
+                # in the middle of a batch: the capture runs on the pad slot and overwrites the buffers
+                names = ("token_ids", "tok_pos", "past", "slots", "streams", "steps", "active")
+                saved = [getattr(ctx, name).clone() for name in names]
+                pages = [ids.clone() for ids in ctx._page_ids]
+                slot_list = ctx.slot_list
+                self._graphs[key] = self._capture(ctx, bucket)
+                for name, value in zip(names, saved):
+                    getattr(ctx, name).copy_(value)
+                for ids, value in zip(ctx._page_ids, pages):
+                    ids.copy_(value)
+                ctx.slot_list = slot_list
+        return self._graphs[key]
+
+    def _capture(self, ctx: _DecodeContext, bucket: int):
+        device, width = self.model.device, ctx.width
+        ctx.max_kv_len = bucket
         pad = self.cache.pad_slot
         ctx.slots.fill_(pad)
         ctx.slot_list = [pad] * width
@@ -158,18 +188,19 @@ class DecodeRunner:
             self._run_once(ctx)
         launches = {k: ops.LAUNCHES[k] - counted[k] for k in ("own", "library")}
         ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
-        return ctx, graph, launches
+        return graph, launches
 
     # ------------------------------------------------------------------ steps
 
     def step_device(self, n_steps: int = 1) -> None:
         """Replay ``n_steps`` decode steps back to back; tokens stay on the device."""
         self._reserve_next(n_steps)
-        _, graph, launches = self._graphs[self.ctx.width]
-        for _ in range(n_steps):
+        longest = max(self.cache.lengths[s] for s in self.live_slots)
+        for i in range(n_steps):
+            graph, launches = self._graph_for(self.ctx.width, self._bucket_for(longest + i + 1))
             graph.replay()
-        ops.LAUNCHES["own"] += n_steps * launches["own"]
-        ops.LAUNCHES["library"] += n_steps * launches["library"]
+            ops.LAUNCHES["own"] += launches["own"]
+            ops.LAUNCHES["library"] += launches["library"]
         self.cache.advance(self.live_slots, [n_steps] * len(self.live_slots))
 
     def step(self, host_tokens: Optional[Sequence[int]] = None) -> List[int]:

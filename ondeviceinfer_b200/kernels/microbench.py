@@ -103,11 +103,11 @@ def gemm_case(args) -> dict:
             "us": us, "weight_GBps": weight_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
 
 
-def _cache_setup(batch: int, ctx: int, nkv: int, d: int, copies: int):
+def _cache_setup(batch: int, ctx: int, nkv: int, d: int, copies: int, in_order: bool = False):
     pages_per_seq = (ctx + 64) // 64 + 1
     n_pages = batch * pages_per_seq
     pools = [torch.randn(2, n_pages, nkv, 64, d, device="cuda").bfloat16() for _ in range(copies)]
-    order = torch.randperm(n_pages).to(torch.int32)
+    order = (torch.arange(n_pages) if in_order else torch.randperm(n_pages)).to(torch.int32)
     page_ids = order.cuda()
     page_start = (torch.arange(batch + 1, dtype=torch.int32) * pages_per_seq).cuda()
     return pools, page_start, page_ids
@@ -117,7 +117,7 @@ def attention_decode_case(args) -> dict:
     nq, nkv, d = args.heads, args.kv_heads, args.head_dim
     kv_bytes = 2 * args.batch * args.ctx * nkv * d * 2
     copies = max(1, int(math.ceil(3 * L2_BYTES / kv_bytes))) if args.rotate else 1
-    pools, page_start, page_ids = _cache_setup(args.batch, args.ctx, nkv, d, copies)
+    pools, page_start, page_ids = _cache_setup(args.batch, args.ctx, nkv, d, copies, args.pages_in_order)
     q = torch.randn(args.batch, nq, d, device="cuda").bfloat16()
     out = torch.empty(args.batch, nq * d, dtype=torch.bfloat16, device="cuda")
     cu_q = torch.arange(args.batch + 1, dtype=torch.int32, device="cuda")
@@ -188,6 +188,8 @@ def main(argv=None) -> int:
                         help="decode-attention splits merged by the block that comes last, not by a second kernel")
     parser.add_argument("--mma-sync", action="store_true", help="attention-prefill: the mma.sync kernel instead of tcgen05")
     parser.add_argument("--heads-per-cta", type=int, default=0, help="attention-prefill on tcgen05: 1, 2 or 0 (default choice)")
+    parser.add_argument("--pages-in-order", action="store_true",
+                        help="attention-decode: every sequence's pages lie one after another in the pool, as a fresh cache hands them out")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--ctx", type=int, default=2048)
     parser.add_argument("--heads", type=int, default=32)

@@ -168,3 +168,23 @@ def test_graph_replay_gives_the_tokens_of_the_plain_step_path(dtype, tmp_root):
     b = odi.generate(model, prompts, max_new_tokens=40, eos_token_id=stop, use_graphs=False)
     if dtype == "float32":
         assert a.generated_ids == b.generated_ids and a.finish_reasons == b.finish_reasons
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_while_the_longest_sequence_passes_a_power_of_two(dtype, tmp_root):
+    """A captured graph fixes how many blocks share a sequence's keys, chosen from the longest
+    sequence; when that length passes 256 in the middle of a batch another graph takes over on
+    the same buffers, and the tokens stay those of the step path."""
+    model, weights, cfg = engine_model("C", dtype, tmp_root)
+    prompts = plain.random_prompts(cfg, [200, 250, 17], 77)
+    kwargs = dict(max_new_tokens=24, temperature=0.0, eos_token_id=None)
+    stepped = odi.generate(model, prompts, use_graphs=False, **kwargs)
+    cache = model.make_cache(max_tokens=3 * 320, max_seqs=3)
+    replayed = odi.generate(model, prompts, cache=cache, use_graphs=True, **kwargs)
+    cache.check()
+    if dtype == "float32":
+        assert replayed.generated_ids == stepped.generated_ids
+        assert replayed.generated_ids[1] == plain.generate(weights, cfg, prompts[1], 24)
+    else:
+        for p, g in zip(prompts, replayed.generated_ids):
+            assert all(near_tie(weights, cfg, p + g[:t], g[t], dtype) for t in range(len(g)))
