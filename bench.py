@@ -155,6 +155,8 @@ def main() -> int:
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--sizes", default="8B", choices=sorted(OTHER_SIZES), help="layer sizes (default: the benchmark's)")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the timed decode steps")
+    parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
+                        help="unequal prompts: lengths uniform in [LOW, HIGH] from --seed instead of --prompt-len")
     parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -173,6 +175,9 @@ def main() -> int:
 
     cfg = dict(QWEN3_8B, **OTHER_SIZES[args.sizes])
     prompt_len = args.prompt_len
+    prompt_range = [int(v) for v in args.prompt_range.split(",")] if args.prompt_range else None
+    if prompt_range:
+        prompt_len = prompt_range[1]
     needed = prompt_len + args.warmup + args.steps + 1
     context = args.context or max(CONTEXT, -(-needed // 64) * 64)
     if context < needed:
@@ -188,6 +193,9 @@ def main() -> int:
     sampler = Sampler(0.0)
 
     def prompts_for(batch, length):
+        if prompt_range:
+            lengths = torch.randint(prompt_range[0], prompt_range[1] + 1, (batch,), generator=gen).tolist()
+            return [torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
         return torch.randint(0, cfg["vocab_size"], (batch, length), generator=gen).tolist()
 
     def decode_run(batch, steps, warmup, end_to_end):
@@ -206,7 +214,7 @@ def main() -> int:
             tokens = runner.step(tokens)
         torch.cuda.synchronize()
         before = dict(ops.LAUNCHES)
-        start_len = cache.length(slots[0])
+        start_len = sum(cache.length(slot) for slot in slots) / batch
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wall = time.perf_counter()
         start.record()
@@ -267,7 +275,7 @@ def main() -> int:
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"],
             "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False, "global_batch": args.batch,
-            "seq_len": context, "prompt_len": prompt_len, "parallelism": "single-gpu",
+            "seq_len": context, "prompt_len": args.prompt_range or prompt_len, "parallelism": "single-gpu",
             "l2": "inputs larger than L2: each step reads all weights and the cache",
             "peaks": peak_source},
         "e2e": {"value": e2e_run["tok_s"], "unit": "tokens/s", "ms_per_step": e2e_run["ms_per_step"],

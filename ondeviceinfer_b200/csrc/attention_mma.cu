@@ -52,6 +52,10 @@ struct MmaAttnArgs {
   int clustered;          // decode: the splits of a (sequence, kv head) form a cluster and merge in shared memory
   int* tickets;           // decode with global partials: one counter per (sequence, block row), zero before and
                           // after; the block that finishes a row of splits last merges them (null: a combine kernel does)
+  const int* tiles_per_split;   // decode with global partials and the combine kernel: when not null, one int on the
+                          // device: every block takes that many tiles of 64 keys, so a sequence of n tiles uses
+                          // its first ceil(n / that) splits and its other blocks leave at once (`splits` then only
+                          // bounds the count); null: every sequence is cut into `splits` equal ranges
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -287,6 +291,13 @@ __device__ __forceinline__ void combine_row(const float* p, bf16* out_row, int s
 #define DC_STAGES (D <= 128 ? 3 : 2)
 #endif
 
+// Tiles of 64 keys that one block of a sequence of n_tiles takes.  *wanted is written by the host before
+// the launch (no kernel writes it); whatever it holds, `splits` blocks cover the sequence.
+__device__ __forceinline__ int tiles_of_a_split(const int* wanted, int splits, int n_tiles) {
+  const int even = (n_tiles + splits - 1) / splits;
+  return wanted != nullptr ? max(*wanted, even) : even;
+}
+
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_kernel(MmaAttnArgs a) {
   pdl_launch_dependents();
@@ -303,8 +314,9 @@ attention_decode_kernel(MmaAttnArgs a) {
   const int tok = a.cu_q[seq];
   const int pos = a.past[seq];                     // the query's position; keys 0 .. pos are visible
   const int n_tiles = pos / KT + 1;
-  const int per_split = (n_tiles + a.splits - 1) / a.splits;
+  const int per_split = tiles_of_a_split(a.tiles_per_split, a.splits, n_tiles);
   const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
+  if (a.tiles_per_split != nullptr && split > 0 && tile_begin >= n_tiles) return;   // a shorter sequence needs fewer blocks
   const int* pages = a.page_ids + a.page_start[seq];
 
   auto issue = [&](int tile) {
@@ -516,11 +528,20 @@ attention_decode_kernel(MmaAttnArgs a) {
   }
 }
 
-__global__ void attention_mma_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits) {
+// One block per (token, head).  With `tiles_per_split` a row has the partials of its sequence's first
+// ceil(tiles / *tiles_per_split) splits only (one token per sequence: the token's index is the sequence's).
+__global__ void attention_mma_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits,
+                                             const int* __restrict__ past, int nq, const int* __restrict__ tiles_per_split) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;
-  combine_row(partial + row * splits * (D + 2), out + row * D, splits, threadIdx.x, blockDim.x);
+  int used = splits;
+  if (tiles_per_split != nullptr) {
+    const int n_tiles = past[row / nq] / KT + 1;
+    const int per_split = tiles_of_a_split(tiles_per_split, splits, n_tiles);
+    used = (n_tiles + per_split - 1) / per_split;
+  }
+  combine_row(partial + row * splits * (D + 2), out + row * D, used, threadIdx.x, blockDim.x);
 }
 
 extern "C" int odi_attention_mma_head_dim() { return D; }
@@ -553,6 +574,7 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   if (max_q_len != 1) return ODI_ERR_ARGUMENT;
   a.clustered = (a.clustered && a.splits > 1 && a.splits <= 8) ? 1 : 0;
   if (a.splits > 1 && !a.clustered && a.partial == nullptr) return ODI_ERR_ARGUMENT;
+  if (a.tiles_per_split != nullptr && (a.clustered || a.tickets != nullptr)) return ODI_ERR_ARGUMENT;
   a.head_chunks = (g + 15) / 16;
   dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
@@ -578,7 +600,8 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   int rc = launch_status();
   if (rc != 0 || a.splits == 1 || a.tickets != nullptr) return rc;
   const int combine_threads = D >= 128 ? 128 : 64;
-  odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream, a.partial, a.out, a.splits);
+  odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream,
+                      (const float*)a.partial, a.out, a.splits, a.past, a.nq, a.tiles_per_split);
   return launch_status();
 }
 
@@ -647,6 +670,7 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
   a.partial = noalloc_scratch_address[device];
   a.clustered = 0;      // this entry point is the global-partial form
   a.tickets = nullptr;  // ... with the combine kernel
+  a.tiles_per_split = nullptr;   // ... and every sequence cut into `splits` equal ranges
   a.head_chunks = (a.nq / a.nkv + 15) / 16;
   dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
@@ -655,6 +679,6 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
   if (rc != 0 || a.splits == 1) return rc;
   const int combine_threads = D >= 128 ? 128 : 64;
   odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream,
-                      (const float*)a.partial, a.out, a.splits);
+                      (const float*)a.partial, a.out, a.splits, a.past, a.nq, (const int*)nullptr);
   return launch_status();
 }

@@ -25,6 +25,13 @@ import torch
 from ..kernels import ops
 
 
+def _power_of_two(n: int) -> int:
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
 class _DecodeContext:
     """The fixed-buffer counterpart of :class:`~ondeviceinfer_b200.engine.step.StepContext`
     for ``width`` sequences that bring one token each."""
@@ -47,6 +54,41 @@ class _DecodeContext:
         self._page_ids = [zeros(width * max_pages) for _ in cache.kv_groups]
         self._memo: Dict[object, object] = {}
         self.slot_list: List[int] = []
+        self.kv_lens: List[int] = [kv_len_hint] * width      # host: the keys each row sees in the coming step
+        self._key_splits: Dict[int, list] = {}               # block rows -> [device int, its value, bound on the splits]
+        self._planned_tiles: tuple = ()
+        self._planned_bounds: tuple = ()
+
+    def key_splits(self, block_rows: int):
+        """``(tiles_per_split, splits)`` for a mixer whose decode kernel cuts each sequence's keys among
+        blocks.  The first is one int32 on the device that :meth:`plan_key_splits` refreshes before a
+        replay; the second, a power of two, is fixed in the graph being captured."""
+        if block_rows not in self._key_splits:
+            per, splits = ops.plan_key_splits(self.kv_lens, block_rows)
+            self._key_splits[block_rows] = [torch.tensor([per], dtype=torch.int32, device=self.token_ids.device), per,
+                                            _power_of_two(splits)]
+        entry = self._key_splits[block_rows]
+        return entry[0], entry[2]
+
+    def plan_key_splits(self, kv_lens: Sequence[int], fix_bounds: bool = False) -> tuple:
+        """Refresh the block sizes for the coming step and return the bounds on the splits that it needs,
+        as a key for the graph to replay; ``fix_bounds`` makes them the bounds of the next capture."""
+        tiles = tuple(-(-n // 64) for n in kv_lens)
+        if tiles == self._planned_tiles and not fix_bounds and len(self._planned_bounds) == len(self._key_splits):
+            return self._planned_bounds           # the plan only changes when a sequence enters another tile
+        self.kv_lens = list(kv_lens)
+        needed = []
+        for block_rows in sorted(self._key_splits):
+            entry = self._key_splits[block_rows]
+            per, splits = ops.plan_key_splits(self.kv_lens, block_rows)
+            if per != entry[1]:
+                entry[0].fill_(per)
+                entry[1] = per
+            needed.append(_power_of_two(splits))
+            if fix_bounds:
+                entry[2] = needed[-1]
+        self._planned_tiles, self._planned_bounds = tiles, tuple(needed)
+        return self._planned_bounds
 
     def page_table(self, group_index: int):
         return self._page_start, self._page_ids[group_index]
@@ -103,7 +145,7 @@ class DecodeRunner:
         if n == 0:
             raise ValueError("a decode batch needs at least one sequence")
         width = self._width_for(n)
-        self._graph_for(width, self._bucket_for(max(self.cache.lengths[s] for s in slots) + 1))
+        self._graph_for(width, [self.cache.lengths[s] + 1 for s in slots])
         ctx = self._contexts[width]
         self.ctx, self.live_slots = ctx, list(slots)
         pad = self.cache.pad_slot
@@ -146,25 +188,32 @@ class DecodeRunner:
         ops.sample(logits, ctx.token_ids, self.temperature, self.seed, ctx.streams, ctx.steps,
                    advance_pos=ctx.tok_pos, advance_past=ctx.past, active=ctx.active)
 
-    def _graph_for(self, width: int, bucket: int):
-        key = (width, bucket)
+    def _graph_for(self, width: int, kv_lens: Sequence[int]):
+        """The graph for ``width`` rows whose live sequences see ``kv_lens`` keys in the coming step: one per
+        power of two of the longest sequence and per bound on the key splits; padding rows see one key."""
+        kv_lens = list(kv_lens) + [1] * (width - len(kv_lens))
+        bucket = self._bucket_for(max(kv_lens))
+        ctx = self._contexts.get(width)
+        if ctx is None:
+            ctx = self._contexts[width] = _DecodeContext(self.cache, width, self.max_pages, self.model.device, bucket)
+            ctx.kv_lens = kv_lens
+            graph = self._capture(ctx, bucket)          # its warm-up run tells which parts cut keys
+            self._graphs[(width, bucket, ctx.plan_key_splits(kv_lens))] = graph
+            return graph
+        key = (width, bucket, ctx.plan_key_splits(kv_lens))
         if key not in self._graphs:
-            ctx = self._contexts.get(width)
-            if ctx is None:
-                ctx = self._contexts[width] = _DecodeContext(self.cache, width, self.max_pages, self.model.device, bucket)
-                self._graphs[key] = self._capture(ctx, bucket)
-            else:
-                # in the middle of a batch: the capture runs on the pad slot and overwrites the buffers
-                names = ("token_ids", "tok_pos", "past", "slots", "streams", "steps", "active")
-                saved = [getattr(ctx, name).clone() for name in names]
-                pages = [ids.clone() for ids in ctx._page_ids]
-                slot_list = ctx.slot_list
-                self._graphs[key] = self._capture(ctx, bucket)
-                for name, value in zip(names, saved):
-                    getattr(ctx, name).copy_(value)
-                for ids, value in zip(ctx._page_ids, pages):
-                    ids.copy_(value)
-                ctx.slot_list = slot_list
+            # in the middle of a batch: the capture runs on the pad slot and overwrites the buffers
+            names = ("token_ids", "tok_pos", "past", "slots", "streams", "steps", "active")
+            saved = [getattr(ctx, name).clone() for name in names]
+            pages = [ids.clone() for ids in ctx._page_ids]
+            slot_list = ctx.slot_list
+            ctx.plan_key_splits(kv_lens, fix_bounds=True)
+            self._graphs[key] = self._capture(ctx, bucket)
+            for name, value in zip(names, saved):
+                getattr(ctx, name).copy_(value)
+            for ids, value in zip(ctx._page_ids, pages):
+                ids.copy_(value)
+            ctx.slot_list = slot_list
         return self._graphs[key]
 
     def _capture(self, ctx: _DecodeContext, bucket: int):
@@ -195,9 +244,9 @@ class DecodeRunner:
     def step_device(self, n_steps: int = 1) -> None:
         """Replay ``n_steps`` decode steps back to back; tokens stay on the device."""
         self._reserve_next(n_steps)
-        longest = max(self.cache.lengths[s] for s in self.live_slots)
+        lengths = [self.cache.lengths[s] for s in self.live_slots]
         for i in range(n_steps):
-            graph, launches = self._graph_for(self.ctx.width, self._bucket_for(longest + i + 1))
+            graph, launches = self._graph_for(self.ctx.width, [n + i + 1 for n in lengths])
             graph.replay()
             ops.LAUNCHES["own"] += launches["own"]
             ops.LAUNCHES["library"] += launches["library"]

@@ -22,6 +22,8 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 import numpy as np
 import torch
 
+from ..kernels import ops
+
 Want = Union[str, Sequence[Sequence[int]]]
 
 
@@ -79,6 +81,15 @@ class StepContext:
 
     def page_table(self, group_index: int) -> Tuple[torch.Tensor, torch.Tensor]:
         return self._page_tables[group_index]
+
+    def key_splits(self, block_rows: int) -> Tuple[Optional[torch.Tensor], int]:
+        """For a mixer whose decode kernel cuts each sequence's keys among blocks (``block_rows`` blocks per
+        cut): ``(tiles_per_split, splits)`` as :func:`ondeviceinfer_b200.kernels.ops.plan_key_splits` gives
+        them for this step's sequences, the first as one int32 on the device."""
+        def make():
+            per, splits = ops.plan_key_splits([p + t for p, t in zip(self.past_lens, self.q_lens)], block_rows)
+            return torch.tensor([per], dtype=torch.int32).to(self.past.device, non_blocking=True), splits
+        return self.memo(("key_splits", block_rows), make)
 
     def memo(self, key, make: Callable[[], object]):
         """A value shared by all layers of the step (rotary tables and the like)."""

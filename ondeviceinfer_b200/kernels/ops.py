@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import POINTER, Structure, byref, c_float, c_int, c_long, c_ulonglong, c_void_p
-from typing import Optional
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -456,7 +456,8 @@ class _MmaAttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("k_pool", c_void_p), ("v_pool", c_void_p), ("out", c_void_p),
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("splits", c_int),
-                ("head_chunks", c_int), ("scale", c_float), ("clustered", c_int), ("tickets", c_void_p)]
+                ("head_chunks", c_int), ("scale", c_float), ("clustered", c_int), ("tickets", c_void_p),
+                ("tiles_per_split", c_void_p)]
 
 
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -473,11 +474,40 @@ def _attention_tickets(device, count: int) -> torch.Tensor:
     return have
 
 
+DECODE_ATTENTION_BLOCKS = 296     # blocks of the split-key decode kernel that a B200 holds at once (148 SMs x 2)
+
+
+def plan_key_splits(kv_lens: Sequence[int], block_rows: int, *, blocks: int = DECODE_ATTENTION_BLOCKS,
+                    min_tiles: int = 2, max_splits: int = 64) -> Tuple[int, int]:
+    """How the split-key decode attention cuts unequal sequences: ``(tiles_per_split, splits)``.
+
+    ``kv_lens`` are the keys that each sequence sees, ``block_rows`` the blocks that one split of one
+    sequence launches (kv heads x chunks of 16 query heads).  Every block takes ``tiles_per_split`` tiles
+    of 64 keys, so a long sequence gets more blocks than a short one and all blocks end together; the
+    size is the smallest (from ``min_tiles`` up) with which all blocks are on the GPU at once, or the
+    longest sequence whole when even that is too many.  ``splits`` is what the longest sequence needs."""
+    tiles = [max(1, -(-int(n) // 64)) for n in kv_lens]
+    longest, total = max(tiles), sum(tiles)
+    per = max(min_tiles, -(-total * block_rows // blocks), -(-longest // max_splits))
+    for _ in range(64):
+        if per >= longest or sum(-(-t // per) for t in tiles) * block_rows <= blocks:
+            break
+        per += max(1, per // 8)
+    per = min(per, longest)
+    return per, -(-longest // per)
+
+
 def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                   nq: int, nkv: int, d: int, page_size: int, scale: float, splits: int = 1,
-                  partial: Optional[torch.Tensor] = None, cluster: bool = False, merge_in_kernel: bool = False) -> None:
+                  partial: Optional[torch.Tensor] = None, cluster: bool = False, merge_in_kernel: bool = False,
+                  tiles_per_split: Optional[torch.Tensor] = None) -> None:
     """bf16 causal GQA on the tensor cores: the prefill kernel for any q_len, the split-key
     decode kernel when every sequence brings exactly one token.  No window.
+
+    Decode with ``tiles_per_split`` (one int32 on the device, written by the host; see
+    :func:`plan_key_splits`): every block takes that many tiles of 64 keys and ``splits`` only bounds the
+    count per sequence; whatever the number says, ``splits`` blocks cover every sequence.  Without it every
+    sequence is cut into ``splits`` equal ranges.
 
     Decode splits go through the fp32 ``partial`` buffer and a combine kernel.  ``merge_in_kernel=True``
     lets the block that finishes a (sequence, kv head) last merge them instead (an atomic ticket; the same
@@ -508,9 +538,13 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
     tickets = None
     if decode and splits > 1 and not clustered and merge_in_kernel:
         tickets = _attention_tickets(q.device, n_seqs * nkv * (-(-(nq // nkv) // 16)))
+    if tiles_per_split is not None:
+        if not decode or clustered or tickets is not None:
+            raise KernelError("tiles_per_split belongs to the decode kernel with the combine kernel")
+        _require(tiles_per_split, "tiles_per_split", torch.int32)
     args = _MmaAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
                         _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale, 1 if clustered else 0,
-                        _ptr(tickets))
+                        _ptr(tickets), _ptr(tiles_per_split if decode else None))
     lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(1 if decode else 0),
                                  _stream()), "attention_mma",

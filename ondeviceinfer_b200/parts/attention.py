@@ -96,12 +96,15 @@ class Attention(Part):
         token.  float32, windows, head sizes above 256: the CUDA-core kernel."""
         s = self.spec
         tensor_cores = q.dtype == torch.bfloat16 and s.window is None and s.head_dim <= 256
-        splits, partial = 1, None
+        splits, partial, tiles_per_split = 1, None, None
         if ctx.max_q_len == 1:
             # decode: cut long key ranges so that enough blocks run side by side
-            work = ctx.n_seqs * s.num_kv_heads * ((s.num_heads // s.num_kv_heads + 15) // 16)
-            tiles = (ctx.max_kv_len + PAGE_SIZE - 1) // PAGE_SIZE
-            splits = max(1, min(32, 296 // max(work, 1), tiles // 2 if tensor_cores else (ctx.max_kv_len + 255) // 256))
+            block_rows = s.num_kv_heads * ((s.num_heads // s.num_kv_heads + 15) // 16)
+            if tensor_cores:
+                # blocks of equal size, so that unequal sequences end together; the context plans it
+                tiles_per_split, splits = ctx.key_splits(block_rows)
+            else:
+                splits = max(1, min(32, 296 // max(ctx.n_seqs * block_rows, 1), (ctx.max_kv_len + 255) // 256))
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.head_dim + 2),),
                                       dtype=torch.float32, device=q.device)
@@ -114,7 +117,7 @@ class Attention(Part):
             ops.attention_mma(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                               n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
                               d=s.head_dim, page_size=PAGE_SIZE, scale=self.scale, splits=splits, partial=partial,
-                              cluster=False)
+                              tiles_per_split=tiles_per_split if ctx.max_q_len == 1 else None)
             return
         ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                            n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,

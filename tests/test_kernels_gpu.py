@@ -641,6 +641,41 @@ def test_attention_mma_finds_one_far_key():
     close(out, expected, "bfloat16")
 
 
+@pytest.mark.parametrize("wanted", [None, 1, 2, 5, 1000])
+def test_attention_mma_blocks_of_equal_size(wanted):
+    """Decode over unequal sequences with every block taking the same number of 64-key tiles: a long
+    sequence uses more of its splits than a short one.  One far key carries each answer, so a block that
+    was left out shows.  The number on the device may be anything (too small for the bound on the splits,
+    or larger than every sequence): the sequences are covered all the same."""
+    d, nq, nkv = 128, 8, 2
+    lengths, past = [1, 1, 1, 1], [1300, 10, 64, 700]
+    keys = {0: 1290, 1: 2, 2: 64, 3: 5}
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=24)
+    q = torch.randn(4, nq, d) * 0.1
+    for tok, key in keys.items():
+        q[tok] = torch.nn.functional.normalize(setup["dense"][tok][0][:, key], dim=-1).repeat_interleave(nq // nkv, 0) * 40.0
+    scale = 1.0 / math.sqrt(d)
+    per, splits = ops.plan_key_splits([p + 1 for p in past], nkv, blocks=16, max_splits=8)
+    assert per * splits >= 21 and splits > 1
+    number = per if wanted is None else wanted
+    out = torch.empty(4, nq * d, dtype=torch.bfloat16, device=DEV)
+    partial = torch.full((4 * nq * splits * (d + 2),), float("nan"), dtype=torch.float32, device=DEV)
+    ops.attention_mma(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                      setup["page_start"], setup["page_ids"], n_seqs=4, max_q_len=1, nq=nq, nkv=nkv, d=d,
+                      page_size=64, scale=scale, splits=splits, partial=partial,
+                      tiles_per_split=torch.tensor([number], dtype=torch.int32, device=DEV))
+    for tok, key in keys.items():
+        value = setup["dense"][tok][1][:, key].bfloat16().float().repeat_interleave(nq // nkv, 0).reshape(-1)
+        assert float((out[tok].float().cpu() - value).abs().max()) < 0.05, tok
+    expected = plain_attention(q, setup["dense"], lengths, past, nq, nkv, d, 0, scale, "bfloat16")
+    close(out, expected, "bfloat16")
+    with pytest.raises(ops.KernelError):
+        ops.attention_mma(q.bfloat16().to(DEV), setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"],
+                          setup["page_start"], setup["page_ids"], n_seqs=4, max_q_len=1, nq=nq, nkv=nkv, d=d,
+                          page_size=64, scale=scale, splits=4, cluster=True,
+                          tiles_per_split=torch.tensor([2], dtype=torch.int32, device=DEV))
+
+
 TC_ATTN_CASES = [
     # d, nq, nkv, lengths, past
     (128, 4, 2, [128], [0]),                      # exactly one tile of queries, two pages of keys

@@ -60,3 +60,28 @@ def test_step_context_indexes_tokens_by_sequence_and_position():
     calls = []
     assert ctx.memo("k", lambda: calls.append(1) or 7) == 7 and ctx.memo("k", lambda: calls.append(1) or 8) == 7
     assert len(calls) == 1
+
+
+def test_key_split_plan_covers_every_sequence_and_fills_the_gpu_once():
+    """Blocks of equal size for unequal sequences: the longest sequence is covered by the splits, no block
+    is smaller than asked, and all blocks are on the GPU at once when that can be had."""
+    import random
+
+    from ondeviceinfer_b200.kernels.ops import plan_key_splits
+
+    rng = random.Random(5)
+    for trial in range(200):
+        n = rng.choice([1, 2, 8, 16, 64, 200])
+        kv_lens = [rng.randint(1, rng.choice([64, 3000, 140000])) for _ in range(n)]
+        rows = rng.choice([1, 2, 8, 16])
+        per, splits = plan_key_splits(kv_lens, rows)
+        tiles = [-(-k // 64) for k in kv_lens]
+        assert per >= 1 and 1 <= splits <= 64
+        assert per * splits >= max(tiles)
+        assert per >= min(2, max(tiles))
+        blocks = sum(-(-t // per) for t in tiles) * rows
+        assert blocks <= 296 or per == max(tiles)
+    assert plan_key_splits([2049] * 8, 8) == (9, 4)          # 8 sequences of 33 tiles: four blocks each, 256 in all
+    assert plan_key_splits([2049] * 64, 8) == (33, 1)        # more sequences than the GPU holds blocks: each whole
+    per, splits = plan_key_splits([131001], 8)
+    assert splits * 8 <= 296 < (splits + 1) * 8 + 8
