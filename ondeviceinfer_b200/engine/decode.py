@@ -6,7 +6,15 @@ GPU needs.  A :class:`DecodeRunner` keeps the step's index tensors in fixed devi
 buffers, captures embedding -> layers -> head -> sampling once per batch width as a CUDA
 graph, and replays it: the sampled token is written where the next step reads its
 input, and the sampling kernel advances positions, lengths and step numbers in place.
-Per step the host only makes sure every sequence has a page for its next position.
+Per step the host only makes sure every sequence has a page for its next position and
+chooses the graph.
+
+What a graph fixes besides the width: how a mixer's decode kernel may cut a sequence's keys
+among blocks.  That follows the sequences' lengths, so there is one graph per power of two of
+the longest sequence and per bound on the number of cuts (a power of two as well); all graphs of
+a width share its buffers, and a batch that outgrows its graph in the middle goes on with
+another.  The size of the cuts themselves is one number on the device that the host refreshes
+when a sequence enters another tile of 64 keys (:meth:`_DecodeContext.plan_key_splits`).
 
 Widths are powers of two up to 32, then multiples of 16; rows beyond the live sequences are padding: they run on a
 slot outside the cache's capacity with a constant length of zero and their results are dropped, so
@@ -36,12 +44,12 @@ class _DecodeContext:
     """The fixed-buffer counterpart of :class:`~ondeviceinfer_b200.engine.step.StepContext`
     for ``width`` sequences that bring one token each."""
 
-    def __init__(self, cache, width: int, max_pages: int, device, kv_len_hint: int) -> None:
+    def __init__(self, cache, width: int, max_pages: int, device, longest: int) -> None:
         self.width = width
         self.n_seqs = self.n_tokens = self.n_want = width
         self.max_q_len = 1
         self.q_lens = [1] * width
-        self.max_kv_len = kv_len_hint
+        self.max_kv_len = longest
         self.max_pages = max_pages
         arange = torch.arange(width + 1, dtype=torch.int32, device=device)
         zeros = lambda n: torch.zeros(n, dtype=torch.int32, device=device)
@@ -54,7 +62,7 @@ class _DecodeContext:
         self._page_ids = [zeros(width * max_pages) for _ in cache.kv_groups]
         self._memo: Dict[object, object] = {}
         self.slot_list: List[int] = []
-        self.kv_lens: List[int] = [kv_len_hint] * width      # host: the keys each row sees in the coming step
+        self.kv_lens: List[int] = [longest] * width      # host: the keys each row sees in the coming step
         self._key_splits: Dict[int, list] = {}               # block rows -> [device int, its value, bound on the splits]
         self._planned_tiles: tuple = ()
         self._planned_bounds: tuple = ()
