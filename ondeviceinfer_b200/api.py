@@ -14,7 +14,6 @@ Reference                                              Here
 
 from __future__ import annotations
 
-import json
 from pathlib import Path
 from typing import List, Optional, Sequence, Union
 

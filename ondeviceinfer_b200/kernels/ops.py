@@ -9,7 +9,7 @@ without a GPU, or without the compiled libraries, these functions raise.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, byref, c_float, c_int, c_long, c_ulonglong, c_void_p
+from ctypes import Structure, byref, c_float, c_int, c_long, c_ulonglong, c_void_p
 from typing import Optional, Sequence, Tuple
 
 import torch

@@ -6,7 +6,6 @@ implementation, in 32-bit and in bfloat16."""
 
 import json
 import subprocess
-import sys
 from pathlib import Path
 
 import numpy as np
