@@ -266,20 +266,26 @@ attention_prefill_kernel(MmaAttnArgs a) {
 
 // Merge the split partials of one (token, head) row: out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s,
 // the splits in order.  `first`, `step`: which elements of the row this thread writes.
+// No load sits behind a branch, so the loads of a pass over the splits are in flight together, four splits
+// at a time: the merge costs a few round trips to L2, not one per split.  (Unrolled by eight, the common
+// case of four splits ran in the remainder loop, one load after another: 19.1 against 17.4 us at 8 x 2048.)
 __device__ __forceinline__ void combine_row(const float* p, bf16* out_row, int splits, int first, int step) {
   float M = -INFINITY;
+#pragma unroll 4
   for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(p + s * (D + 2) + D));
   float denom = 0.f;
+#pragma unroll 4
   for (int s = 0; s < splits; ++s) {
-    const float ms = __ldcg(p + s * (D + 2) + D);
-    if (ms != -INFINITY) denom += expf(ms - M) * __ldcg(p + s * (D + 2) + D + 1);
+    const float ms = __ldcg(p + s * (D + 2) + D), ls = __ldcg(p + s * (D + 2) + D + 1);
+    denom += ms != -INFINITY ? expf(ms - M) * ls : 0.f;
   }
   const float inv = denom > 0.f ? 1.f / denom : 0.f;
   for (int dd = first; dd < D; dd += step) {
     float v = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
-      const float ms = __ldcg(p + s * (D + 2) + D);
-      if (ms != -INFINITY) v += expf(ms - M) * __ldcg(p + s * (D + 2) + dd);
+      const float ms = __ldcg(p + s * (D + 2) + D), x = __ldcg(p + s * (D + 2) + dd);
+      v += ms != -INFINITY ? expf(ms - M) * x : 0.f;      // an empty split (max -inf) adds nothing, whatever it holds
     }
     out_row[dd] = __float2bfloat16_rn(v * inv);
   }

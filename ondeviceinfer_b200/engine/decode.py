@@ -210,13 +210,21 @@ class DecodeRunner:
             return graph
         key = (width, bucket, ctx.plan_key_splits(kv_lens))
         if key not in self._graphs:
+            # A graph made for sequences up to twice as long, or for up to twice the splits, serves as well (its
+            # surplus blocks leave at once): a capture costs what hundreds of steps take.
+            near = [k for k in self._graphs
+                    if k[0] == width and bucket <= k[1] <= 2 * bucket and len(k[2]) == len(key[2])
+                    and all(need <= have <= 2 * need for need, have in zip(key[2], k[2]))]
+            if near:
+                return self._graphs[min(near, key=lambda k: (k[1], k[2]))]
+        if key not in self._graphs:
             # in the middle of a batch: the capture runs on the pad slot and overwrites the buffers
             names = ("token_ids", "tok_pos", "past", "slots", "streams", "steps", "active")
             saved = [getattr(ctx, name).clone() for name in names]
             pages = [ids.clone() for ids in ctx._page_ids]
             slot_list = ctx.slot_list
             ctx.plan_key_splits(kv_lens, fix_bounds=True)
-            self._graphs[key] = self._capture(ctx, bucket)
+            self._graphs[key] = self._capture(ctx, bucket, warm_up=False)     # the width has run before
             for name, value in zip(names, saved):
                 getattr(ctx, name).copy_(value)
             for ids, value in zip(ctx._page_ids, pages):
@@ -224,7 +232,7 @@ class DecodeRunner:
             ctx.slot_list = slot_list
         return self._graphs[key]
 
-    def _capture(self, ctx: _DecodeContext, bucket: int):
+    def _capture(self, ctx: _DecodeContext, bucket: int, warm_up: bool = True):
         device, width = self.model.device, ctx.width
         ctx.max_kv_len = bucket
         pad = self.cache.pad_slot
@@ -232,11 +240,12 @@ class DecodeRunner:
         ctx.slot_list = [pad] * width
         for g, group in enumerate(self.cache.kv_groups):
             ctx._page_ids[g].fill_(group.slot_pages[pad][0])
-        side = torch.cuda.Stream(device=device)
-        side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
-            self._run_once(ctx)           # warm-up: compiles, sizes scratch, sets function attributes
-        torch.cuda.current_stream(device).wait_stream(side)
+        if warm_up:
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                self._run_once(ctx)           # compiles, sizes scratch, sets function attributes
+            torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
         counted = dict(ops.LAUNCHES)
