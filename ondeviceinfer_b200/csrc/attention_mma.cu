@@ -359,10 +359,12 @@ attention_decode_kernel(MmaAttnArgs a) {
   const float sl2 = a.scale * LOG2E;
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
+    // One barrier per tile: after it this tile's copies are visible to all warps and all warps have left
+    // the tile before, whose stage the next request overwrites.
+    cp_async_wait<DC_STAGES - 2>();
+    __syncthreads();
     if (tile + DC_STAGES - 1 < tile_end) issue(tile + DC_STAGES - 1);
     cp_async_commit();
-    cp_async_wait<DC_STAGES - 1>();
-    __syncthreads();
     const uint8_t* st = smem + (size_t)((tile - tile_begin) % DC_STAGES) * 2 * TILE_BYTES;
     const uint32_t k_smem = smem_addr(st), v_smem = k_smem + TILE_BYTES;
     const int kbase = tile * KT + warp * 16;        // this warp's 16 keys
@@ -418,7 +420,6 @@ attention_decode_kernel(MmaAttnArgs a) {
         mma_bf16(o[dp * 2 + 1], pf, b2, b3);
       }
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
