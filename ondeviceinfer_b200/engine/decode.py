@@ -224,7 +224,7 @@ class DecodeRunner:
             pages = [ids.clone() for ids in ctx._page_ids]
             slot_list = ctx.slot_list
             ctx.plan_key_splits(kv_lens, fix_bounds=True)
-            self._graphs[key] = self._capture(ctx, bucket, warm_up=False)     # the width has run before
+            self._graphs[key] = self._capture(ctx, bucket)
             for name, value in zip(names, saved):
                 getattr(ctx, name).copy_(value)
             for ids, value in zip(ctx._page_ids, pages):
@@ -232,7 +232,7 @@ class DecodeRunner:
             ctx.slot_list = slot_list
         return self._graphs[key]
 
-    def _capture(self, ctx: _DecodeContext, bucket: int, warm_up: bool = True):
+    def _capture(self, ctx: _DecodeContext, bucket: int):
         device, width = self.model.device, ctx.width
         ctx.max_kv_len = bucket
         pad = self.cache.pad_slot
@@ -240,12 +240,14 @@ class DecodeRunner:
         ctx.slot_list = [pad] * width
         for g, group in enumerate(self.cache.kv_groups):
             ctx._page_ids[g].fill_(group.slot_pages[pad][0])
-        if warm_up:
-            side = torch.cuda.Stream(device=device)
-            side.wait_stream(torch.cuda.current_stream(device))
-            with torch.cuda.stream(side):
-                self._run_once(ctx)           # compiles, sizes scratch, sets function attributes
-            torch.cuda.current_stream(device).wait_stream(side)
+        # The run before the capture compiles, sizes scratch, sets function attributes and loads every kernel
+        # that the graph will hold: a kernel's first launch is not allowed inside a capture, and a graph for
+        # more key splits may be the first to use one (the merge of the splits).
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            self._run_once(ctx)
+        torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
         ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
         counted = dict(ops.LAUNCHES)
