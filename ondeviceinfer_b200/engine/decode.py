@@ -25,6 +25,8 @@ is not marked ``graph_safe``) do not use this path.
 
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -109,7 +111,10 @@ class _DecodeContext:
 
 class DecodeRunner:
     def __init__(self, model, cache, *, temperature: float = 0.0, seed: int = 0) -> None:
-        self.model, self.cache = model, cache
+        # The cache keeps its runners (ondeviceinfer_b200.api.decode_runner); the runner must not keep the cache
+        # alive in turn, or the two, and the runner's graphs, would only go when the cycle collector runs:
+        # possibly in the middle of another capture, which a graph's destruction invalidates.
+        self.model, self._cache = model, weakref.ref(cache)
         self.temperature, self.seed = float(temperature), int(seed)
         self.max_pages = cache.n_pages
         self._contexts: Dict[int, _DecodeContext] = {}     # by width: the buffers that every graph of the width uses
@@ -119,6 +124,13 @@ class DecodeRunner:
         self._host_pages: List[np.ndarray] = []
         self._pinned_tokens: Optional[torch.Tensor] = None
         self._pinned_out: Optional[torch.Tensor] = None
+
+    @property
+    def cache(self):
+        cache = self._cache()
+        if cache is None:
+            raise RuntimeError("the cache of this decode runner is gone")
+        return cache
 
     # ------------------------------------------------------------------ set-up
 
@@ -252,8 +264,17 @@ class DecodeRunner:
         ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
         counted = dict(ops.LAUNCHES)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            self._run_once(ctx)
+        # No cycle collection while the stream captures: it could destroy a dropped graph of somebody else's,
+        # which is not allowed then and invalidates this capture.  What is garbage already goes first.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                self._run_once(ctx)
+        finally:
+            if collecting:
+                gc.enable()
         launches = {k: ops.LAUNCHES[k] - counted[k] for k in ("own", "library")}
         ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
         return graph, launches

@@ -241,6 +241,17 @@ def test_qwen3_8b_layer_sizes(sizes, dtype, tmp_path):
     for slot in slots:
         cache.free(slot)
     cache.check()
+    if sizes == "8B":
+        # 40 sequences of one or two tokens: the logits of 40 rows over the whole vocabulary in one product
+        many = plain.random_prompts(LARGE, [1 + i % 2 for i in range(40)], 4)
+        wide = model.make_cache(max_tokens=40 * 64, max_seqs=40)
+        slots = [wide.alloc() for _ in many]
+        logits = model.step(wide, slots, many, "last")
+        expected = torch.stack([plain.forward_logits(weights, LARGE, r)[-1] for r in many])
+        assert_logits_close(logits, expected, dtype, "8B sizes, 40 sequences", longest_sum=LARGE["intermediate_size"])
+        for slot in slots:
+            wide.free(slot)
+        wide.check()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

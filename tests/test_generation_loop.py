@@ -161,3 +161,31 @@ def test_decode_widths_pad_little_above_32():
     from ondeviceinfer_b200.engine.decode import DecodeRunner
     widths = {n: DecodeRunner._width_for(n) for n in (1, 2, 3, 8, 9, 17, 32, 33, 48, 49, 64, 65, 100)}
     assert widths == {1: 1, 2: 2, 3: 4, 8: 8, 9: 16, 17: 32, 32: 32, 33: 48, 48: 48, 49: 64, 64: 64, 65: 80, 100: 112}
+
+
+def test_a_dropped_cache_takes_its_decode_runner_along_at_once():
+    """The cache keeps its decode runners and a runner only a weak reference to the cache: when the last
+    reference to the cache goes, both go at that moment, not when the cycle collector next runs (which may be
+    in the middle of somebody else's graph capture, where destroying a graph is not allowed)."""
+    import gc
+    import weakref
+
+    import torch
+
+    from ondeviceinfer_b200.api import decode_runner
+    from ondeviceinfer_b200.cache import KVNeed, SequenceCache
+
+    class Model:            # what decode_runner touches before the first step
+        decoder = object()
+
+    gc.collect()
+    gc.disable()
+    try:
+        cache = SequenceCache([(KVNeed(2, 16),)], [None], dtype=torch.float32, device="cpu", max_tokens=256, max_seqs=2)
+        runner = decode_runner(Model, cache)
+        assert decode_runner(Model, cache) is runner and runner.cache is cache
+        gone = weakref.ref(runner)
+        del runner, cache
+        assert gone() is None
+    finally:
+        gc.enable()
