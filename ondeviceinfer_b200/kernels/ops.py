@@ -225,6 +225,11 @@ EPI_STORE_BF16, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU, EPI_HEAD_PREP = 0, 1, 2
 
 _gemm_state = {}
 
+# Scratch that the wrappers keep per device is handed to kernels by address, and a captured CUDA graph keeps
+# replaying with the address it saw.  So a buffer that has to grow is not freed: it is put aside here for
+# the life of the process, where a graph that still writes to it does no harm.
+_outgrown = []
+
 
 def _gemm_buffers(device, scratch_floats: int):
     """Scratch for split partials, tile tickets (kept zero between launches) and the error word."""
@@ -234,6 +239,7 @@ def _gemm_buffers(device, scratch_floats: int):
         state["status"] = torch.zeros(4, dtype=torch.int32, device=device)
         state["scratch"] = torch.empty(1 << 22, dtype=torch.float32, device=device)
     if state["scratch"].numel() < scratch_floats:
+        _outgrown.append(state["scratch"])
         state["scratch"] = torch.empty(int(scratch_floats * 1.25), dtype=torch.float32, device=device)
     return state["scratch"], state["tickets"], state["status"]
 
@@ -469,6 +475,8 @@ def _attention_tickets(device, count: int) -> torch.Tensor:
     """Counters of the split-key decode attention, one per (sequence, block row); kept zero between launches."""
     have = _attention_state.get(device)
     if have is None or have.numel() < count:
+        if have is not None:
+            _outgrown.append(have)
         have = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
         _attention_state[device] = have
     return have
@@ -595,9 +603,11 @@ def _sample_buffers(device, rows: int, chunks: int):
     """Per-chunk partial results (16 bytes each) and one ticket per row (kept zero between launches)."""
     state = _sample_state.setdefault(device, {})
     if state.get("rows", 0) < rows:
+        _outgrown.append(state.get("tickets"))
         state["tickets"] = torch.zeros(max(rows, 256), dtype=torch.int32, device=device)
         state["rows"] = state["tickets"].numel()
     if state.get("entries", 0) < rows * chunks:
+        _outgrown.append(state.get("partials"))
         state["partials"] = torch.empty(max(rows * chunks, 4096) * 4, dtype=torch.float32, device=device)
         state["entries"] = state["partials"].numel() // 4
     return state["partials"], state["tickets"]
