@@ -42,6 +42,19 @@ def _power_of_two(n: int) -> int:
     return p
 
 
+def serving_graph_key(keys, width: int, bucket: int, bounds: tuple):
+    """Which of the captured graphs ``keys`` (each ``(width, longest-sequence bucket, bounds on the key splits)``)
+    serves a step that needs ``(width, bucket, bounds)``: the very one, else the smallest made for sequences up to
+    twice as long and for up to twice the splits (its surplus blocks leave at once, and a capture costs what
+    hundreds of steps take), else None."""
+    if (width, bucket, bounds) in keys:
+        return (width, bucket, bounds)
+    near = [k for k in keys
+            if k[0] == width and bucket <= k[1] <= 2 * bucket and len(k[2]) == len(bounds)
+            and all(need <= have <= 2 * need for need, have in zip(bounds, k[2]))]
+    return min(near, key=lambda k: (k[1], k[2])) if near else None
+
+
 class _DecodeContext:
     """The fixed-buffer counterpart of :class:`~ondeviceinfer_b200.engine.step.StepContext`
     for ``width`` sequences that bring one token each."""
@@ -221,27 +234,21 @@ class DecodeRunner:
             self._graphs[(width, bucket, ctx.plan_key_splits(kv_lens))] = graph
             return graph
         key = (width, bucket, ctx.plan_key_splits(kv_lens))
-        if key not in self._graphs:
-            # A graph made for sequences up to twice as long, or for up to twice the splits, serves as well (its
-            # surplus blocks leave at once): a capture costs what hundreds of steps take.
-            near = [k for k in self._graphs
-                    if k[0] == width and bucket <= k[1] <= 2 * bucket and len(k[2]) == len(key[2])
-                    and all(need <= have <= 2 * need for need, have in zip(key[2], k[2]))]
-            if near:
-                return self._graphs[min(near, key=lambda k: (k[1], k[2]))]
-        if key not in self._graphs:
-            # in the middle of a batch: the capture runs on the pad slot and overwrites the buffers
-            names = ("token_ids", "tok_pos", "past", "slots", "streams", "steps", "active")
-            saved = [getattr(ctx, name).clone() for name in names]
-            pages = [ids.clone() for ids in ctx._page_ids]
-            slot_list = ctx.slot_list
-            ctx.plan_key_splits(kv_lens, fix_bounds=True)
-            self._graphs[key] = self._capture(ctx, bucket)
-            for name, value in zip(names, saved):
-                getattr(ctx, name).copy_(value)
-            for ids, value in zip(ctx._page_ids, pages):
-                ids.copy_(value)
-            ctx.slot_list = slot_list
+        have = serving_graph_key(self._graphs, *key)
+        if have is not None:
+            return self._graphs[have]
+        # in the middle of a batch: the capture runs on the pad slot and overwrites the buffers
+        names = ("token_ids", "tok_pos", "past", "slots", "streams", "steps", "active")
+        saved = [getattr(ctx, name).clone() for name in names]
+        pages = [ids.clone() for ids in ctx._page_ids]
+        slot_list = ctx.slot_list
+        ctx.plan_key_splits(kv_lens, fix_bounds=True)
+        self._graphs[key] = self._capture(ctx, bucket)
+        for name, value in zip(names, saved):
+            getattr(ctx, name).copy_(value)
+        for ids, value in zip(ctx._page_ids, pages):
+            ids.copy_(value)
+        ctx.slot_list = slot_list
         return self._graphs[key]
 
     def _capture(self, ctx: _DecodeContext, bucket: int):

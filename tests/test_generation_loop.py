@@ -189,3 +189,24 @@ def test_a_dropped_cache_takes_its_decode_runner_along_at_once():
         assert gone() is None
     finally:
         gc.enable()
+
+
+def test_which_captured_graph_serves_a_step():
+    """The decode runner replays the graph made for the step's width, length bucket and split bounds, or one
+    made for up to twice the length and twice the splits; anything else needs a capture."""
+    from ondeviceinfer_b200.engine.decode import DecodeRunner, serving_graph_key
+
+    keys = {(8, 4096, (4,)): "a", (8, 8192, (8,)): "b", (16, 4096, (4,)): "c", (8, 4096, ()): "d"}
+    assert serving_graph_key(keys, 8, 4096, (4,)) == (8, 4096, (4,))
+    assert serving_graph_key(keys, 8, 4096, (2,)) == (8, 4096, (4,))        # twice the splits: serves
+    assert serving_graph_key(keys, 8, 4096, (1,)) is None                    # four times: a graph of its own
+    assert serving_graph_key(keys, 8, 4096, (8,)) == (8, 8192, (8,))        # twice the length: serves
+    assert serving_graph_key(keys, 8, 2048, (4,)) == (8, 4096, (4,))
+    assert serving_graph_key(keys, 8, 1024, (4,)) is None
+    assert serving_graph_key(keys, 8, 8192, (4,)) == (8, 8192, (8,))
+    assert serving_graph_key(keys, 8, 16384, (8,)) is None                   # longer than any graph was made for
+    assert serving_graph_key(keys, 8, 4096, (16,)) is None                   # more splits than any graph has
+    assert serving_graph_key(keys, 4, 4096, (4,)) is None                    # another width
+    assert serving_graph_key(keys, 8, 4096, ()) == (8, 4096, ())             # a model whose parts cut no keys
+    assert serving_graph_key(keys, 8, 4096, (4, 4)) is None
+    assert [DecodeRunner._bucket_for(n) for n in (1, 256, 257, 4096, 4097)] == [256, 256, 512, 4096, 8192]
