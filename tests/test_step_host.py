@@ -84,3 +84,30 @@ def test_key_split_plan_covers_every_sequence_and_fills_the_gpu_once():
     assert plan_key_splits([2049] * 8, 8) == (9, 4)          # 8 sequences of 33 tiles: four blocks each, 256 in all
     assert plan_key_splits([2049] * 64, 8) == (33, 1)        # more sequences than the GPU holds blocks: each whole
     assert plan_key_splits([131001], 8) == (64, 32)          # one long sequence: the most splits there are
+
+
+def test_a_kernel_that_gave_up_waiting_is_reported_once_by_name():
+    """Every wait inside the tensor-core kernels is bounded; a kernel whose wait ran out writes a code into
+    an error word and returns.  Here the word is set by hand (no GPU is made to wait): the host check names
+    the kernel and the role that gave up, clears the word, and is silent afterwards."""
+    import pytest
+    import torch
+
+    from ondeviceinfer_b200.kernels import ops
+
+    saved = dict(ops._gemm_state)
+    try:
+        ops._gemm_state.clear()
+        ops._gemm_state["test-device"] = {"status": torch.zeros(4, dtype=torch.int32)}
+        ops.raise_on_kernel_fault()                                  # nothing happened: no error
+        for code, words in ((2, "gemm_tcgen05: the MMA issuer"), (21, "gemm_prefill_tcgen05: the TMA producer"),
+                            (13, "attention_tcgen05: the softmax warps")):
+            ops._gemm_state["test-device"]["status"][0] = code
+            assert ops.gemm_status() == code
+            with pytest.raises(ops.KernelError, match=words):
+                ops.raise_on_kernel_fault()
+            assert ops.gemm_status() == 0
+            ops.raise_on_kernel_fault()
+    finally:
+        ops._gemm_state.clear()
+        ops._gemm_state.update(saved)
