@@ -1,0 +1,43 @@
+"""The arithmetic behind bench.py's roofline and prefill fractions, and its refusals (no GPU)."""
+
+import importlib.util
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+spec = importlib.util.spec_from_file_location("odi_bench", ROOT / "bench.py")
+bench = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(bench)
+
+
+def test_bytes_of_a_decode_step_and_flops_of_a_prefill_at_qwen3_8b_sizes():
+    cfg = dict(bench.QWEN3_8B)
+    per_layer, weight_bytes, kv_bytes_per_token = bench.model_figures(cfg, 36)
+    # every weight a step uses once: 36 layers and the output head in bf16 (the embedding is only gathered),
+    # the norm weights in fp32
+    assert per_layer == 6144 * 4096 + 4096 * 4096 + 3 * 12288 * 4096
+    assert abs(weight_bytes - 15.137e9) < 0.01e9
+    assert kv_bytes_per_token == 147456                     # keys and values of 8 heads of 128 in 36 layers, bf16
+    flops = bench.prefill_flops(cfg, 36, 2048)
+    assert abs(flops - 29.69e12) < 0.02e12                  # linear 28.45, causal attention 1.24, one row of logits
+    # fewer layers scale the per-layer terms only
+    assert bench.model_figures(cfg, 2)[2] == 147456 // 18
+
+
+def test_other_sizes_are_the_named_ones():
+    assert bench.OTHER_SIZES["8B"] == {}
+    cfg = dict(bench.QWEN3_8B, **bench.OTHER_SIZES["32B"])
+    sizes = (cfg["num_hidden_layers"], cfg["hidden_size"], cfg["num_attention_heads"], cfg["intermediate_size"])
+    assert sizes == (64, 5120, 64, 25600)
+    _, weight_bytes, kv = bench.model_figures(cfg, 64)
+    assert abs(weight_bytes - 63.97e9) < 0.05e9 and kv == 262144
+
+
+def test_more_than_one_gpu_is_refused_and_the_reference_arm_says_why_it_is_absent():
+    many = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--gpus", "2"], capture_output=True, text=True)
+    assert many.returncode == 2 and "one GPU" in many.stdout
+    ref = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference"], capture_output=True, text=True)
+    line = json.loads(ref.stdout.strip().splitlines()[-1])
+    assert ref.returncode == 0 and line["impl"] == "reference" and line["unavailable"]
