@@ -40,6 +40,11 @@ it says ``takes_lazy_norm = True`` and the norm has ``lazy(x, parts)``, a
 ``gated_linear`` turn into the normed operand inside the tensor-core kernel (``.materialize()`` gives
 the tensor).  A part that passes ``track`` must not touch ``residual`` after that product.
 
+Also optional: a mixer whose single-token kernel cuts each sequence's keys among several blocks may ask the
+context how (``ctx.key_splits(blocks_per_cut) -> (tiles_per_split, splits)``): the number of 64-key tiles
+that a block takes, as one int32 on the device that follows the step's sequences (also under graph replay,
+where the host refreshes it), and a bound on the cuts of one sequence, which is what a captured graph fixes.
+
 Parts are chosen by the *type* of their spec.  ``register_part(SpecType, PartClass)``
 adds a kind; nothing else in the library has to change for it.
 """
