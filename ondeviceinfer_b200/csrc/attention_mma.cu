@@ -7,15 +7,17 @@
 //  * attention_decode: one query token per sequence.  A block owns one (sequence, kv head,
 //    key split); the rows of its MMA are the query heads that share the kv head (up to 16
 //    per block), its 4 warps take 16 keys each of every 64-key page and their partial
-//    results are merged in shared memory.  With 2..8 splits the blocks of a (sequence, kv
-//    head) form a thread-block cluster: each leaves its merged (acc[d], max, sum) in its own
-//    shared memory and, after a cluster barrier, block r finishes the heads r, r + splits, ...
-//    by adding all blocks' partials in rank order through distributed shared memory.  With
-//    more splits (or when asked to) the block writes the partial to global memory for the
-//    combine kernel below.
+//    results are merged in shared memory.  With several splits the block writes its merged
+//    (acc[d], max, sum) to global memory and the combine kernel below adds the splits of a
+//    (token, head) in order.  Either every sequence is cut into `splits` equal ranges, or every
+//    block takes the same number of tiles (read from the device), so that a long sequence has
+//    more blocks than a short one and all blocks end together.  Two other ways to merge are
+//    kept as options and measured slower on B200: 2..8 splits as a thread-block cluster that
+//    adds the partials in rank order through distributed shared memory, and the block that
+//    finishes a (sequence, kv head) last (an atomic ticket) merging them.
 //
 // Key/value pages (64 positions x head_dim, contiguous) are copied to shared memory with
-// cp.async, double or triple buffered; rows are padded by 16 bytes so that ldmatrix reads
+// cp.async, double or triple buffered, one block barrier per tile; rows are padded by 16 bytes so that ldmatrix reads
 // are free of bank conflicts for every head size that is a multiple of 16.
 //
 // Compile with -DODI_HEAD_DIM=<d>, d a multiple of 16 up to 256.  No window, no ring:
