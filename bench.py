@@ -62,12 +62,19 @@ def load_peaks():
     if path.exists():
         try:
             raw = json.loads(path.read_text())
-            peaks = dict(FALLBACK_PEAKS)
+            tables = [raw] + [v for v in raw.values() if isinstance(v, dict)]     # flat, or one level down
+            peaks, found = dict(FALLBACK_PEAKS), 0
             for key in peaks:
-                if key in raw:
-                    peaks[key] = float(raw[key])
-            return peaks, "measured"
-        except (ValueError, TypeError):
+                for table in tables:
+                    value = table.get(key)
+                    if isinstance(value, dict):
+                        value = value.get("value")
+                    if isinstance(value, (int, float)) and value > 0:
+                        peaks[key], found = float(value), found + 1
+                        break
+            if found:
+                return peaks, "measured" if found == len(peaks) else "measured where given, else fallback"
+        except (ValueError, TypeError, AttributeError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
 

@@ -41,3 +41,17 @@ def test_more_than_one_gpu_is_refused_and_the_reference_arm_says_why_it_is_absen
     ref = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference"], capture_output=True, text=True)
     line = json.loads(ref.stdout.strip().splitlines()[-1])
     assert ref.returncode == 0 and line["impl"] == "reference" and line["unavailable"]
+
+
+def test_measured_peaks_are_read_flat_or_one_level_down_and_absent_ones_fall_back(tmp_path, monkeypatch):
+    monkeypatch.setattr(bench, "ROOT", tmp_path)
+    assert bench.load_peaks() == (bench.FALLBACK_PEAKS, "fallback")
+    (tmp_path / "MEASURED_PEAKS.json").write_text(json.dumps(
+        {"hbm_gbs": 7000.0, "bf16_tflops": 1600, "bf16_tflops_sustained": 1450.5, "clocks": {"sm_mhz": 1965}}))
+    assert bench.load_peaks() == ({"hbm_gbs": 7000.0, "bf16_tflops": 1600.0, "bf16_tflops_sustained": 1450.5}, "measured")
+    (tmp_path / "MEASURED_PEAKS.json").write_text(json.dumps({"peaks": {"hbm_gbs": {"value": 6900.0, "unit": "GB/s"}}}))
+    peaks, source = bench.load_peaks()
+    assert peaks["hbm_gbs"] == 6900.0 and peaks["bf16_tflops"] == bench.FALLBACK_PEAKS["bf16_tflops"]
+    assert source.startswith("measured where given")
+    (tmp_path / "MEASURED_PEAKS.json").write_text("not json")
+    assert bench.load_peaks()[1] == "fallback"
