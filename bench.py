@@ -1,27 +1,42 @@
 #!/usr/bin/env python3
-"""Serving benchmark of ondeviceinfer_b200 on one B200.
+"""Serving benchmark of ondeviceinfer_b200 on one B200, and the same run of the reference.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
-                    [--layers L] [--batch B] [--no-points]
-                    [--sizes 8B|14B|32B] [--prompt-len T] [--context C]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--layers L] [--batch B] [--no-points] [--temperature T]
+                    [--sizes 8B|14B|32B] [--prompt-len T | --prompt-range LOW,HIGH] [--context C]
 
 Measures the metric of BASELINE.json: decode tokens per second (and prefill tokens per
 second at 2,048 tokens) for the Qwen3-8B layer sizes in bf16 with seeded random weights
 and uniform random token ids.  A "step" is one decode step of the whole batch.  The
 default run has a batch of 8 sequences with 2,048-token prompts in a cache sized for a
-context of 4,096; ``--sizes``, ``--prompt-len`` and ``--context`` give the same run at the
-layer sizes of Qwen3-14B or Qwen3-32B and at other lengths.  One JSON line is printed:
+context of 4,096; ``--sizes``, ``--prompt-len``, ``--prompt-range``, ``--temperature`` and
+``--context`` give the same run at the layer sizes of Qwen3-14B or Qwen3-32B, at other
+lengths and with temperature sampling.  One JSON line is printed:
 
 * ``value``   decoded tokens per second over K steps, timed on the device with CUDA
               events (sampled tokens stay on the device);
-* ``e2e``     the same through the Python entry point: every step copies the step's
-              token ids from pinned host memory to the device and reads the sampled
-              tokens back to the host;
-* ``prefill`` one 2,048-token prompt: tokens/s, ms, and the fraction of the measured
-              bf16 tensor-core peak its flops reach;
+* ``e2e``     the same through the Python entry point ``generate()``: host token lists in,
+              host token lists out; every decode step copies the step's token ids from
+              pinned host memory to the device and reads the sampled tokens back;
+* ``prefill`` one 2,048-token prompt: tokens/s, ms (median of three after a warm-up), and
+              the fraction of the measured bf16 tensor-core peak its flops reach;
 * ``roofline`` the decode step against HBM: bytes it must read (every weight it uses
               once, plus the cached keys and values of the live requests) / its time;
-* ``points``  decode tokens/s at batch 1 and 64.
+* ``points``  decode tokens/s at batch 1 and 64, and (default run, own arm) the two other
+              configurations of the benchmark: Qwen3-14B sizes with 16 unequal prompts of
+              128 to 4,096 tokens, Qwen3-32B sizes with 8 prompts of 8,192 tokens and
+              temperature 0.7, each with its HBM fraction and prefill rate.
+
+``--impl reference`` runs the unmodified reference (UESlubei/ondeviceinfer, plain PyTorch) from
+``baseline/_ref`` through its own public path -- ``Qwen3ForCausalLM(config, device=, dtype=)``,
+``make_resident_cache``, ``model(ids, cache=, logits_to_keep=1)``, ``greedy_generate`` for batch 1 --
+on the same configuration, and prints the same line with ``"impl": "reference"``.  Nothing of
+this library is imported in that arm.
+
+Untimed steps before the timed ones: max(W, 32), in both arms and for every decode figure.  The first decode
+steps after a prefill run at the SM clock that the prefill left (the power cap pulls it down and it comes
+back within about a tenth of a second: measured here 4.29 ms a step for the first 26 steps, then 3.56), so a
+timed region of 20 steps that starts 5 steps after the prefill measures that transient, not decoding.
 
 Every step reads all weights (16 GB) and the cache, far more than the 126 MB L2, so no
 explicit L2 flush is needed between timed steps.  The work runs on one GPU only; for
@@ -32,6 +47,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import shutil
 import subprocess
 import sys
 import threading
@@ -54,7 +70,15 @@ OTHER_SIZES = {
     "32B": {"num_hidden_layers": 64, "hidden_size": 5120, "num_attention_heads": 64, "intermediate_size": 25600},
 }
 CONTEXT, PROMPT, PREFILL_TOKENS = 4096, 2048, 2048
+SETTLE_STEPS = 32          # the least number of untimed decode steps before a timed region (see the module text)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# The two further configurations of the benchmark, appended to the default run's points.
+EXTRA_POINTS = (
+    {"name": "qwen3_14b_b16_unequal", "sizes": "14B", "batch": 16, "prompt_range": (128, 4096), "seed": 3,
+     "steps": 128, "temperature": 0.0},
+    {"name": "qwen3_32b_b8_8192_t0.7", "sizes": "32B", "batch": 8, "prompt_len": 8192, "seed": 0,
+     "steps": 128, "temperature": 0.7},
+)
 
 
 def load_peaks():
@@ -131,61 +155,29 @@ def model_figures(cfg, layers):
     return per_layer, weight_bytes, kv_bytes_per_token
 
 
-def prefill_flops(cfg, layers, tokens):
+def prefill_flops(cfg, layers, tokens, prompts=1):
+    """Flops of one prefill step of ``prompts`` prompts of ``tokens`` tokens each (causal attention: half of
+    4 T^2 per head and lane), with one row of logits per prompt."""
     per_layer, _, _ = model_figures(cfg, layers)
-    linear = 2 * tokens * layers * per_layer
-    attention = 2 * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * tokens * layers  # causal half of 4*T^2
-    head = 2 * cfg["vocab_size"] * cfg["hidden_size"]
+    linear = 2 * prompts * tokens * layers * per_layer
+    attention = 2 * cfg["num_attention_heads"] * cfg["head_dim"] * tokens * tokens * layers * prompts
+    head = 2 * cfg["vocab_size"] * cfg["hidden_size"] * prompts
     return linear + attention + head
 
 
-def run_reference_arm():
-    ref = ROOT / "baseline" / "_ref"
-    if not (ref / "ondeviceinfer").exists():
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference has neither setup.py nor pyproject.toml, so the offline pip install into "
-                          "baseline/_ref fails ('Directory is not installable')"}))
-        return 0
-    print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref exists but no reference arm is wired"}))
-    return 0
+def median(values):
+    ordered = sorted(values)
+    return ordered[len(ordered) // 2]
 
 
-def main() -> int:
-    parser = argparse.ArgumentParser()
-    parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
-    parser.add_argument("--warmup", type=int, default=8)
-    parser.add_argument("--impl", default="ours")
-    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    parser.add_argument("--seed", type=int, default=0)
-    parser.add_argument("--sizes", default="8B", choices=sorted(OTHER_SIZES), help="layer sizes (default: the benchmark's)")
-    parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the timed decode steps")
-    parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
-                        help="unequal prompts: lengths uniform in [LOW, HIGH] from --seed instead of --prompt-len")
-    parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
-    args = parser.parse_args()
-    if args.impl == "reference":
-        return run_reference_arm()
-    if args.gpus != 1:
-        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported (use --gpus 1)")
-        return 2
-    if args.warmup < 3:
-        args.warmup = 3
-
-    import torch
-
-    import ondeviceinfer_b200 as odi
-    from ondeviceinfer_b200.kernels import ops
-    from ondeviceinfer_b200.sampling import Sampler
-
+def plan_run(args, parser):
+    """What both arms need to agree on: layer sizes, lengths, the ``config`` record."""
     cfg = dict(QWEN3_8B, **OTHER_SIZES[args.sizes])
     prompt_len = args.prompt_len
     prompt_range = [int(v) for v in args.prompt_range.split(",")] if args.prompt_range else None
     if prompt_range:
         prompt_len = prompt_range[1]
-    needed = prompt_len + args.warmup + args.steps + 1
+    needed = prompt_len + max(args.warmup, SETTLE_STEPS) + args.steps + 1
     context = args.context or max(CONTEXT, -(-needed // 64) * 64)
     if context < needed:
         parser.error(f"--context {context} is below the {needed} positions that the prompt and the steps need")
@@ -193,116 +185,401 @@ def main() -> int:
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
     peaks, peak_source = load_peaks()
+    record = {
+        "model": "Qwen3-%s layer sizes" % args.sizes, "layers": layers, "layers_of_model": full_layers,
+        "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+        "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+        "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"],
+        "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False, "global_batch": args.batch,
+        "seq_len": context, "prompt_len": args.prompt_range or prompt_len, "temperature": args.temperature,
+        "untimed_steps": max(args.warmup, SETTLE_STEPS),
+        "parallelism": "single-gpu",
+        "l2": "inputs larger than L2: each step reads all weights and the cache",
+        "peaks": peak_source}
+    metric = "decode tokens/s (Qwen3-%s layer sizes, bf16, batch %d, %s-token prompts)" % (
+        args.sizes, args.batch, format(prompt_len, ","))
+    return cfg, layers, prompt_len, prompt_range, context, peaks, record, metric
+
+
+def result_line(args, impl, metric, record, main_run, e2e_run, clock_record, peaks):
+    result = {
+        "metric": metric, "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights normal(0, 0.02), uniform random token ids",
+        "impl": impl, "config": record,
+        "e2e": {"value": e2e_run["tok_s"], "unit": "tokens/s", "ms_per_step": e2e_run["ms_per_step"],
+                "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch,
+                "through": e2e_run["through"]},
+        "clocks": clock_record,
+        "roofline": {"bound": "hbm", "achieved": main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1000.0) / 1e9,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s"},
+    }
+    result["roofline"]["frac"] = result["roofline"]["achieved"] / result["roofline"]["peak"]
+    return result
+
+
+# ------------------------------------------------------------------------------ the reference arm
+
+
+def reference_package(ref: Path):
+    """The folder to import the reference from, or (None, why not).
+
+    The reference has neither setup.py nor pyproject.toml, so ``pip install --target baseline/_ref`` refuses it
+    ("Directory is not installable"); it is plain Python, so a verbatim copy of its package folder under
+    ``baseline/_ref`` is the install.  The copy is made here when the checkout named by BASELINE.json is at hand."""
+    if (ref / "ondeviceinfer" / "model.py").exists():
+        return ref, None
+    try:
+        source = Path(json.loads((ROOT / "BASELINE.json").read_text()).get("reference_path", "")) / "ondeviceinfer"
+    except (OSError, ValueError):
+        source = Path("")
+    if not (source / "model.py").exists():
+        return None, ("the reference cannot be pip-installed (neither setup.py nor pyproject.toml), baseline/_ref holds "
+                      "no copy of its package and its checkout is not on this machine")
+    try:
+        ref.mkdir(parents=True, exist_ok=True)
+        shutil.copytree(source, ref / "ondeviceinfer", dirs_exist_ok=True,
+                        ignore=shutil.ignore_patterns("__pycache__", "*.pyc"))
+    except OSError as err:
+        return None, f"copying the reference's package into baseline/_ref failed: {err}"
+    return ref, None
+
+
+def run_reference_arm(args, parser) -> int:
+    ref, why = reference_package(ROOT / "baseline" / "_ref")
+    if ref is None:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "this machine has no CUDA device to run the reference on"}))
+        return 0
+    try:
+        sys.path.insert(0, str(ref))
+        from ondeviceinfer.config import Qwen3Config
+        from ondeviceinfer.generation import greedy_generate
+        from ondeviceinfer.model import Qwen3ForCausalLM
+    except Exception as err:                                  # noqa: BLE001  (any import failure is the answer)
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference does not import here: {err}"[:300]}))
+        return 0
+    if args.prompt_range or args.temperature > 0:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference decodes equal-length batches greedily only "
+                          "(ondeviceinfer/cache.py:54, ondeviceinfer/generation.py:47)"}))
+        return 0
+    if args.warmup < 3:
+        args.warmup = 3
+    cfg, layers, prompt_len, _, context, peaks, record, metric = plan_run(args, parser)
+    device = torch.device("cuda:0")
     torch.cuda.set_device(0)
-    model = odi.random_resident_model(cfg, args.seed, device="cuda:0", dtype="bfloat16")
+    config = Qwen3Config(
+        vocab_size=cfg["vocab_size"], hidden_size=cfg["hidden_size"], intermediate_size=cfg["intermediate_size"],
+        num_hidden_layers=layers, num_attention_heads=cfg["num_attention_heads"],
+        num_key_value_heads=cfg["num_key_value_heads"], head_dim=cfg["head_dim"],
+        max_position_embeddings=cfg["max_position_embeddings"], rms_norm_eps=cfg["rms_norm_eps"],
+        rope_theta=cfg["rope_theta"], tie_word_embeddings=False)
+    model = Qwen3ForCausalLM(config, device=device, dtype=torch.bfloat16).eval().requires_grad_(False)
+    fill = torch.Generator(device=device).manual_seed(args.seed)
+    with torch.no_grad():
+        for name, parameter in model.named_parameters():
+            if parameter.ndim == 1:                           # norm weights: 1 + normal(0, 0.01)
+                parameter.copy_(1.0 + 0.01 * torch.randn(parameter.shape, generator=fill, device=device))
+            else:
+                parameter.normal_(0.0, 0.02, generator=fill)
     _, weight_bytes, kv_bytes_per_token = model_figures(cfg, layers)
     gen = torch.Generator().manual_seed(args.seed)
-    sampler = Sampler(0.0)
 
     def prompts_for(batch, length):
-        if prompt_range:
-            lengths = torch.randint(prompt_range[0], prompt_range[1] + 1, (batch,), generator=gen).tolist()
-            return [torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
-        return torch.randint(0, cfg["vocab_size"], (batch, length), generator=gen).tolist()
+        return torch.randint(0, cfg["vocab_size"], (batch, length), generator=gen)
 
+    @torch.inference_mode()
     def decode_run(batch, steps, warmup, end_to_end):
-        """Prefill `batch` prompts of `prompt_len` tokens, then time `steps` decode steps.
+        """Prefill a [batch, prompt_len] block, then ``steps`` times argmax -> one-token forward, as
+        ondeviceinfer/generation.py:46-59 does (its own function refuses batches, so the loop is written out
+        here as benchmarks/benchmark_kv_offload.py:277-520 does).  End to end: every step's tokens come from
+        pinned host memory and go back to the host."""
+        cache = model.make_resident_cache(batch_size=batch, max_seq_len=context)
+        ids = prompts_for(batch, prompt_len).to(device)
+        next_token = model(ids, cache=cache, logits_to_keep=1).logits[:, -1].argmax(dim=-1, keepdim=True)
+        pinned_in = torch.empty((batch, 1), dtype=torch.int64).pin_memory()
+        pinned_out = torch.empty((batch, 1), dtype=torch.int64).pin_memory()
+        pinned_in.copy_(next_token)
 
-        Device-timed: the steps replay back to back, sampled tokens stay on the device.
-        End to end: the public decode call per step, which copies the step's token ids from
-        pinned host memory to the device and reads the sampled tokens back to the host."""
-        cache = model.make_cache(max_tokens=batch * context, max_seqs=batch)
-        slots = [cache.alloc() for _ in range(batch)]
-        logits = model.step(cache, slots, prompts_for(batch, prompt_len), "last")
-        tokens = sampler(logits, range(batch), [0] * batch)
-        runner = odi.api.decode_runner(model, cache, temperature=0.0, seed=0)
-        runner.begin(slots, tokens, list(range(batch)), [1] * batch)
-        for _ in range(warmup):
-            tokens = runner.step(tokens)
+        def one_step(token):
+            if end_to_end:
+                token = pinned_in.to(device, non_blocking=True)
+            token = model(token, cache=cache, logits_to_keep=1).logits[:, -1].argmax(dim=-1, keepdim=True)
+            if end_to_end:
+                pinned_out.copy_(token, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                pinned_in.copy_(pinned_out)
+            return token
+
+        for _ in range(max(warmup, SETTLE_STEPS)):
+            next_token = one_step(next_token)
         torch.cuda.synchronize()
-        before = dict(ops.LAUNCHES)
-        start_len = sum(cache.length(slot) for slot in slots) / batch
+        start_len = cache.get_seq_length(0)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         wall = time.perf_counter()
         start.record()
-        if end_to_end:
-            for _ in range(steps):
-                tokens = runner.step(tokens)
-        else:
-            runner.step_device(steps)
+        for _ in range(steps):
+            next_token = one_step(next_token)
         stop.record()
         torch.cuda.synchronize()
         wall = time.perf_counter() - wall
-        ms = start.elapsed_time(stop)
-        launches = {k: ops.LAUNCHES[k] - before[k] for k in before}
-        mean_ctx = start_len + (steps - 1) / 2.0
-        for slot in slots:
-            cache.free(slot)
-        runner.close()
-        del cache, runner
+        seconds = wall if end_to_end else start.elapsed_time(stop) / 1000.0
+        del cache
         torch.cuda.empty_cache()
-        seconds = wall if end_to_end else ms / 1000.0
-        return {"tok_s": batch * steps / seconds, "ms_per_step": seconds * 1000.0 / steps, "launches": launches,
-                "bytes_per_step": weight_bytes + batch * mean_ctx * kv_bytes_per_token}
+        return {"tok_s": batch * steps / seconds, "ms_per_step": seconds * 1000.0 / steps,
+                "bytes_per_step": weight_bytes + batch * (start_len + (steps - 1) / 2.0) * kv_bytes_per_token,
+                "through": "model(ids[B,1], cache=, logits_to_keep=1) per step"}
 
+    @torch.inference_mode()
     def prefill_run(repeats=3):
-        cache = model.make_cache(max_tokens=PREFILL_TOKENS, max_seqs=1)
-        prompt = prompts_for(1, PREFILL_TOKENS)
-        best = None
+        ids = prompts_for(1, PREFILL_TOKENS).to(device)
+        times = []
         for i in range(repeats + 1):
-            slot = cache.alloc()
+            cache = model.make_resident_cache(batch_size=1, max_seq_len=PREFILL_TOKENS)
             torch.cuda.synchronize()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
-            model.step(cache, [slot], prompt, "last")
+            model(ids, cache=cache, logits_to_keep=1)
             stop.record()
             torch.cuda.synchronize()
-            ms = start.elapsed_time(stop)
-            cache.free(slot)
             if i > 0:
-                best = ms if best is None else min(best, ms)
+                times.append(start.elapsed_time(stop))
+            del cache
+        ms = median(times)
         flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
-        return {"value": PREFILL_TOKENS / (best / 1000.0), "tokens": PREFILL_TOKENS, "ms": best,
-                "frac": flops / (best / 1000.0) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / best / 1e9}
+        return {"value": PREFILL_TOKENS / (ms / 1000.0), "tokens": PREFILL_TOKENS, "ms": ms,
+                "frac": flops / (ms / 1000.0) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / ms / 1e9}
+
+    @torch.inference_mode()
+    def single_request_point(steps):
+        """Batch 1 through the reference's own loop (ondeviceinfer/generation.py:28-70)."""
+        ids = prompts_for(1, prompt_len).to(device)
+        for tokens in (SETTLE_STEPS, steps + 1):               # a warm-up call, then the timed one
+            cache = model.make_resident_cache(batch_size=1, max_seq_len=context)
+            result = greedy_generate(model, ids, max_new_tokens=tokens, cache=cache, eos_token_id=None)
+            del cache
+        return result.decode_tokens_per_second
 
     clocks = ClockSampler()
     clocks.start()
     main_run = decode_run(args.batch, args.steps, args.warmup, end_to_end=False)
     clock_record = clocks.stop()
     e2e_run = decode_run(args.batch, args.steps, args.warmup, end_to_end=True)
-    result = {
-        "metric": "decode tokens/s (Qwen3-%s layer sizes, bf16, batch %d, %s-token prompts)" % (args.sizes, args.batch, format(prompt_len, ",")),
-        "value": main_run["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": main_run["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: seeded random weights normal(0, 0.02), uniform random token ids",
-        "impl": "ours",
-        "config": {
-            "model": "Qwen3-%s layer sizes" % args.sizes, "layers": layers, "layers_of_model": full_layers,
-            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
-            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"],
-            "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False, "global_batch": args.batch,
-            "seq_len": context, "prompt_len": args.prompt_range or prompt_len, "parallelism": "single-gpu",
-            "l2": "inputs larger than L2: each step reads all weights and the cache",
-            "peaks": peak_source},
-        "e2e": {"value": e2e_run["tok_s"], "unit": "tokens/s", "ms_per_step": e2e_run["ms_per_step"],
-                "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch},
-        "gpu_launches": main_run["launches"]["own"], "library_gemm_launches": main_run["launches"]["library"],
-        "clocks": clock_record,
-        "roofline": {"bound": "hbm", "achieved": main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1000.0) / 1e9,
-                     "peak": peaks["hbm_gbs"], "unit": "GB/s"},
-    }
-    result["roofline"]["frac"] = result["roofline"]["achieved"] / result["roofline"]["peak"]
+    result = result_line(args, "reference", metric, record, main_run, e2e_run, clock_record, peaks)
+    result["gpu_launches"] = 0           # none of this library's kernels: PyTorch's own (cuBLAS, SDPA, ATen)
     if not args.no_points:
         result["prefill"] = prefill_run()
         points = {}
-        for batch in (1, 64):
-            run = decode_run(batch, min(args.steps, 64), 3, end_to_end=False)
-            points[f"decode_b{batch}"] = run["tok_s"]
-            points[f"decode_b{batch}_hbm_frac"] = run["bytes_per_step"] / (run["ms_per_step"] / 1000.0) / 1e9 / peaks["hbm_gbs"]
+        steps = min(args.steps, 64)
+        b1 = single_request_point(steps)
+        points["decode_b1"] = b1
+        ctx = prompt_len + steps / 2.0
+        points["decode_b1_hbm_frac"] = (weight_bytes + ctx * kv_bytes_per_token) * b1 / 1e9 / peaks["hbm_gbs"]
+        run = decode_run(64, steps, 3, end_to_end=False)
+        points["decode_b64"] = run["tok_s"]
+        points["decode_b64_hbm_frac"] = run["bytes_per_step"] / (run["ms_per_step"] / 1000.0) / 1e9 / peaks["hbm_gbs"]
         result["points"] = points
     print(json.dumps(result))
     return 0
+
+
+# ------------------------------------------------------------------------------ this library's arm
+
+
+def run_own_arm(args, parser) -> int:
+    if args.warmup < 3:
+        args.warmup = 3
+    import torch
+
+    import ondeviceinfer_b200 as odi
+    from ondeviceinfer_b200.kernels import ops
+    from ondeviceinfer_b200.sampling import Sampler
+
+    cfg, layers, prompt_len, prompt_range, context, peaks, record, metric = plan_run(args, parser)
+    torch.cuda.set_device(0)
+
+    class Workload:
+        """One model with its prompts: the timed runs of one configuration."""
+
+        def __init__(self, cfg, layers, *, seed, prompt_len, prompt_range, context, temperature):
+            self.cfg, self.layers, self.context, self.temperature = cfg, layers, context, float(temperature)
+            self.prompt_len, self.prompt_range, self.seed = prompt_len, prompt_range, seed
+            self.model = odi.random_resident_model(cfg, seed, device="cuda:0", dtype="bfloat16")
+            _, self.weight_bytes, self.kv_bytes_per_token = model_figures(cfg, layers)
+            self.gen = torch.Generator().manual_seed(seed)
+            self.sampler = Sampler(self.temperature, seed)
+
+        def prompts_for(self, batch, length):
+            vocab = self.cfg["vocab_size"]
+            if self.prompt_range:
+                lengths = torch.randint(self.prompt_range[0], self.prompt_range[1] + 1, (batch,), generator=self.gen).tolist()
+                return [torch.randint(0, vocab, (n,), generator=self.gen).tolist() for n in lengths]
+            return torch.randint(0, vocab, (batch, length), generator=self.gen).tolist()
+
+        def decode_run(self, batch, steps, warmup, time_prefill=False):
+            """Prefill ``batch`` prompts, then time ``steps`` decode steps on the device: the steps replay back
+            to back, sampled tokens stay on the device."""
+            model = self.model
+            cache = model.make_cache(max_tokens=batch * self.context, max_seqs=batch)
+            slots = [cache.alloc() for _ in range(batch)]
+            prompts = self.prompts_for(batch, self.prompt_len)
+            torch.cuda.synchronize()
+            begun = time.perf_counter()
+            logits = model.step(cache, slots, prompts, "last")
+            tokens = self.sampler(logits, range(batch), [0] * batch)
+            torch.cuda.synchronize()
+            prefill_seconds = time.perf_counter() - begun
+            runner = odi.api.decode_runner(model, cache, temperature=self.temperature, seed=self.seed)
+            runner.begin(slots, tokens, list(range(batch)), [1] * batch)
+            for _ in range(max(warmup, SETTLE_STEPS)):
+                tokens = runner.step(tokens)
+            torch.cuda.synchronize()
+            before = dict(ops.LAUNCHES)
+            start_len = sum(cache.length(slot) for slot in slots) / batch
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step_device(steps)
+            stop.record()
+            torch.cuda.synchronize()
+            ops.raise_on_kernel_fault()
+            seconds = start.elapsed_time(stop) / 1000.0
+            launches = {k: ops.LAUNCHES[k] - before[k] for k in before}
+            mean_ctx = start_len + (steps - 1) / 2.0
+            for slot in slots:
+                cache.free(slot)
+            runner.close()
+            del cache, runner
+            torch.cuda.empty_cache()
+            run = {"tok_s": batch * steps / seconds, "ms_per_step": seconds * 1000.0 / steps, "launches": launches,
+                   "bytes_per_step": self.weight_bytes + batch * mean_ctx * self.kv_bytes_per_token}
+            if time_prefill:
+                total = sum(len(p) for p in prompts)
+                run["prefill_tok_s"] = total / prefill_seconds
+            return run
+
+        def generate_run(self, batch, steps, warmup):
+            """The same through ``generate()``: host token lists in and out; every decode step uploads the
+            step's tokens from pinned host memory and reads the sampled ones back, and the loop's own work
+            (stop test, bookkeeping) is inside the time.  A first, short call captures the graphs; the timed
+            steps are the last ``steps`` of one call, taken from the per-step times that the result carries."""
+            model = self.model
+            settle = max(warmup, SETTLE_STEPS)
+            cache = model.make_cache(max_tokens=batch * self.context, max_seqs=batch)
+            prompts = self.prompts_for(batch, self.prompt_len)
+            odi.generate(model, prompts, max_new_tokens=4, cache=cache, temperature=self.temperature,
+                         seed=self.seed, eos_token_id=None)
+            result = odi.generate(model, prompts, max_new_tokens=settle + steps + 1, cache=cache,
+                                  temperature=self.temperature, seed=self.seed, eos_token_id=None)
+            assert result.decode_steps == settle + steps and all(len(g) == settle + steps + 1 for g in result.generated_ids)
+            seconds = sum(result.step_seconds[settle:])
+            del cache
+            torch.cuda.empty_cache()
+            return {"tok_s": batch * steps / seconds, "ms_per_step": seconds * 1000.0 / steps,
+                    "through": "ondeviceinfer_b200.generate(): the last `steps` decode steps of one call"}
+
+        def prefill_run(self, repeats=3):
+            model = self.model
+            cache = model.make_cache(max_tokens=PREFILL_TOKENS, max_seqs=1)
+            prompt = torch.randint(0, self.cfg["vocab_size"], (1, PREFILL_TOKENS), generator=self.gen).tolist()
+            times = []
+            for i in range(repeats + 1):
+                slot = cache.alloc()
+                torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                model.step(cache, [slot], prompt, "last")
+                stop.record()
+                torch.cuda.synchronize()
+                cache.free(slot)
+                if i > 0:
+                    times.append(start.elapsed_time(stop))
+            ops.raise_on_kernel_fault()
+            ms = median(times)
+            flops = prefill_flops(self.cfg, self.layers, PREFILL_TOKENS)
+            return {"value": PREFILL_TOKENS / (ms / 1000.0), "tokens": PREFILL_TOKENS, "ms": ms,
+                    "frac": flops / (ms / 1000.0) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / ms / 1e9}
+
+        def hbm_frac(self, run):
+            return run["bytes_per_step"] / (run["ms_per_step"] / 1000.0) / 1e9 / peaks["hbm_gbs"]
+
+    work = Workload(cfg, layers, seed=args.seed, prompt_len=prompt_len, prompt_range=prompt_range, context=context,
+                    temperature=args.temperature)
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = work.decode_run(args.batch, args.steps, args.warmup)
+    clock_record = clocks.stop()
+    e2e_run = work.generate_run(args.batch, args.steps, args.warmup)
+    result = result_line(args, "ours", metric, record, main_run, e2e_run, clock_record, peaks)
+    result["gpu_launches"] = main_run["launches"]["own"]
+    result["library_gemm_launches"] = main_run["launches"]["library"]
+    if not args.no_points:
+        result["prefill"] = work.prefill_run()
+        points = {}
+        for batch in (1, 64):
+            run = work.decode_run(batch, min(args.steps, 64), 3)
+            points[f"decode_b{batch}"] = run["tok_s"]
+            points[f"decode_b{batch}_hbm_frac"] = work.hbm_frac(run)
+        default_run = (args.sizes == "8B" and args.layers is None and not args.prompt_range
+                       and args.prompt_len == PROMPT and args.batch == 8 and args.temperature == 0.0)
+        if default_run and not args.no_extra:
+            del work
+            torch.cuda.empty_cache()
+            free_bytes = torch.cuda.mem_get_info()[0]
+            for extra in EXTRA_POINTS:
+                big = dict(QWEN3_8B, **OTHER_SIZES[extra["sizes"]])
+                n_layers = big["num_hidden_layers"]
+                longest = extra.get("prompt_len") or extra["prompt_range"][1]
+                steps = min(args.steps, extra["steps"])
+                room = -(-(longest + steps + 8) // 64) * 64
+                _, w_bytes, kv_bytes = model_figures(big, n_layers)
+                if w_bytes + extra["batch"] * room * kv_bytes + (24 << 30) > free_bytes:
+                    points[extra["name"] + "_skipped"] = "not enough free device memory"
+                    continue
+                other = Workload(big, n_layers, seed=extra["seed"], prompt_len=extra.get("prompt_len", longest),
+                                 prompt_range=extra.get("prompt_range"), context=room,
+                                 temperature=extra["temperature"])
+                run = other.decode_run(extra["batch"], steps, 3, time_prefill=True)
+                points[extra["name"]] = run["tok_s"]
+                points[extra["name"] + "_ms_per_step"] = run["ms_per_step"]
+                points[extra["name"] + "_hbm_frac"] = other.hbm_frac(run)
+                points[extra["name"] + "_prefill_tok_s"] = run["prefill_tok_s"]
+                del other
+                torch.cuda.empty_cache()
+        result["points"] = points
+    print(json.dumps(result))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=255,
+                        help="timed decode steps (default 255: 256 new tokens per sequence, the prompt's one included)")
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    parser.add_argument("--no-extra", action="store_true", help="skip the Qwen3-14B / Qwen3-32B points of the default run")
+    parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--temperature", type=float, default=0.0, help="0: greedy; above: temperature sampling")
+    parser.add_argument("--sizes", default="8B", choices=sorted(OTHER_SIZES), help="layer sizes (default: the benchmark's)")
+    parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the timed decode steps")
+    parser.add_argument("--prompt-range", default=None, metavar="LOW,HIGH",
+                        help="unequal prompts: lengths uniform in [LOW, HIGH] from --seed instead of --prompt-len")
+    parser.add_argument("--context", type=int, default=None, help="cache positions per sequence (default 4096, or what the prompt needs)")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    if args.impl == "reference":
+        return run_reference_arm(args, parser)
+    return run_own_arm(args, parser)
 
 
 if __name__ == "__main__":

@@ -25,6 +25,7 @@ from .engine.decode import DecodeRunner
 from .engine.generate import GenerationResult, generate_requests, plan_batches
 from .engine.model import DecoderModel
 from .engine.step import run_step
+from .kernels import ops
 from .registry import config_from_dict, config_from_folder
 from .sampling import Sampler
 from .weights import RandomSource, SafetensorsSource
@@ -131,6 +132,12 @@ def generate(model: ResidentModel, prompts, *, max_new_tokens: int, cache: Optio
     batches = plan_batches([len(p) for p in prompts], max_new_tokens, max_seqs=cache.max_seqs,
                            max_tokens=cache.max_tokens, page_size=PAGE_SIZE)
     sampler = Sampler(temperature, seed)
+
+    def synchronize() -> None:
+        # where the loop waits for the device anyway, it also learns whether a kernel gave up on a barrier
+        torch.cuda.synchronize(model.device)
+        ops.raise_on_kernel_fault()
+
     decoder = None
     if use_graphs and model.decoder.graph_safe:
         decoder = decode_runner(model, cache, temperature=temperature, seed=seed)
@@ -138,7 +145,7 @@ def generate(model: ResidentModel, prompts, *, max_new_tokens: int, cache: Optio
         prompts, max_new_tokens=max_new_tokens, alloc=cache.alloc, free=cache.free,
         step=lambda slots, runs: model.step(cache, slots, runs, "last"),
         sample=sampler, batches=batches, stop_token_ids=stop,
-        synchronize=lambda: torch.cuda.synchronize(model.device), decoder=decoder)
+        synchronize=synchronize, decoder=decoder)
 
 
 def decode_runner(model: ResidentModel, cache: SequenceCache, *, temperature: float = 0.0, seed: int = 0) -> DecodeRunner:

@@ -9,9 +9,11 @@ UESlubei/ondeviceinfer.  Two deliberate differences:
   Qwen3-32B has a query width of 8192 against a hidden size of 5120, so the rule is
   not carried;
 * keys that the reference ignores but that would change the mathematics if honoured
-  (``hidden_act``, ``rope_scaling``, ``use_sliding_window``, ``attention_bias``) are
-  checked, so that a checkpoint that needs them fails with a clear error instead of
-  computing something else.
+  (``hidden_act``, ``rope_scaling``, ``use_sliding_window``) are checked, so that a
+  checkpoint that needs them fails with a clear error instead of computing something else.
+
+``attention_bias`` gives the four attention projections a bias each, as the reference's
+modules do (ondeviceinfer/attention.py:106-129: ``bias=config.attention_bias``).
 """
 
 from __future__ import annotations
@@ -112,8 +114,6 @@ class Qwen3Config:
             raise ValueError("RoPE requires an even head dimension")
         if self.hidden_act != "silu":
             raise ValueError(f"hidden_act={self.hidden_act!r}: the Qwen3 feed-forward uses silu")
-        if self.attention_bias:
-            raise NotImplementedError("attention_bias=true: projection biases are not implemented")
         if self.rms_norm_eps <= 0 or self.rope_theta <= 0:
             raise ValueError("rms_norm_eps and rope_theta must be positive")
 
@@ -153,7 +153,9 @@ class Qwen3Config:
                 position=RotarySpec(head_dim=self.head_dim, theta=self.rope_theta),
                 prefix=p + "self_attn.",
                 names=names(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight",
-                            q_norm="q_norm.weight", k_norm="k_norm.weight"),
+                            q_norm="q_norm.weight", k_norm="k_norm.weight",
+                            **({"q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+                                "o_bias": "o_proj.bias"} if self.attention_bias else {})),
                 qk_norm_eps=self.rms_norm_eps, window=None, scale=None)
             mlp = GatedMLPSpec(
                 hidden_size=self.hidden_size, intermediate_size=self.intermediate_size,

@@ -54,7 +54,8 @@ class AttentionSpec:
     ``qk_norm_eps`` not None adds an RMSNorm over each query and key head (one [head_dim]
     weight shared by the heads) before the position encoding.  ``window`` not None keeps
     only the last ``window`` keys visible (the query's own position included).
-    ``names`` maps the roles q, k, v, o, q_norm, k_norm to tensor names below ``prefix``.
+    ``names`` maps the roles q, k, v, o, q_norm, k_norm to tensor names below ``prefix``; when it also
+    names q_bias, k_bias, v_bias or o_bias, that projection adds the [out] bias of that name.
     """
 
     hidden_size: int
@@ -70,6 +71,9 @@ class AttentionSpec:
 
     def name(self, role: str) -> str:
         return self.prefix + dict(self.names)[role]
+
+    def has(self, role: str) -> bool:
+        return role in dict(self.names)
 
 
 @dataclass(frozen=True)

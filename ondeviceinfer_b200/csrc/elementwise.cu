@@ -422,6 +422,28 @@ extern "C" int odi_widen(const void* x, float* out, long n, cudaStream_t stream)
 }
 
 // ---------------------------------------------------------------------------------
+// y[t, n] += bias[n] in place, one rounding to the dtype of y (after a product that the vendor
+// library computed: the tensor-core kernels of this library add their bias themselves).
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void bias_add_kernel(T* __restrict__ y, const float* __restrict__ bias, long rows, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < rows * N) y[idx] = from_f<T>(to_f<T>(y[idx]) + bias[idx % N]);
+}
+
+extern "C" int odi_bias_add(void* y, const float* bias, long rows, int N, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0) return 0;
+  const long n = rows * N;
+  if ((n + 255) / 256 > 0x7fffffffL) return ODI_ERR_UNSUPPORTED;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (dtype == 0) odi_rc = launch_pdl((bias_add_kernel<float>), grid, dim3(256), 0, stream, (float*)y, bias, rows, N);
+  else odi_rc = launch_pdl((bias_add_kernel<bf16>), grid, dim3(256), 0, stream, (bf16*)y, bias, rows, N);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
 // Rotary tables of a step: cos/sin[t, i] of position[t] * inv_freq[i], evaluated in
 // fp32 with the full-range sincosf.  One table serves every layer of the step.
 // ---------------------------------------------------------------------------------

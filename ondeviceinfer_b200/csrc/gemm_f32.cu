@@ -1,4 +1,4 @@
-// True 32-bit matrix product for the float32 path: C[M,N] = A[M,K] * W[N,K]^T (+ R).
+// True 32-bit matrix product for the float32 path: C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ R).
 //
 // Plain FMA on the CUDA cores: no tensor cores, no TF32, no split of the K loop.  Each
 // output element is accumulated over k = 0..K-1 in that order whatever M is, so a row's
@@ -17,7 +17,7 @@
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* C,
-                const float* R, int M, int N, int K, int lda, int ldw, int ldc, int ldr) {
+                const float* R, const float* __restrict__ bias, int M, int N, int K, int lda, int ldw, int ldc, int ldr) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ __align__(16) float As[TK][TM + 4];
@@ -66,6 +66,7 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       float v = acc[i][j];
+      if (bias != nullptr) v += bias[n];
       if (R != nullptr) v += R[(size_t)m * ldr + n];
       C[(size_t)m * ldc + n] = v;
     }
@@ -73,8 +74,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
 }
 
 // R may be null (no residual) or alias C (in-place add: each element is read and then
-// written by the same thread).
-extern "C" int odi_gemm_f32(const float* A, const float* W, float* C, const float* R, int M, int N,
+// written by the same thread).  bias may be null; it is added to the product before the residual.
+extern "C" int odi_gemm_f32(const float* A, const float* W, float* C, const float* R, const float* bias, int M, int N,
                             int K, int lda, int ldw, int ldc, int ldr, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return ODI_ERR_ARGUMENT;
@@ -82,7 +83,7 @@ extern "C" int odi_gemm_f32(const float* A, const float* W, float* C, const floa
   if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
   const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) &&
                    ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
-  if (vec) odi_rc = launch_pdl((gemm_f32_kernel<true>), dim3(grid), dim3(256), 0, stream, A, W, C, R, M, N, K, lda, ldw, ldc, ldr);
-  else odi_rc = launch_pdl((gemm_f32_kernel<false>), dim3(grid), dim3(256), 0, stream, A, W, C, R, M, N, K, lda, ldw, ldc, ldr);
+  if (vec) odi_rc = launch_pdl((gemm_f32_kernel<true>), dim3(grid), dim3(256), 0, stream, A, W, C, R, bias, M, N, K, lda, ldw, ldc, ldr);
+  else odi_rc = launch_pdl((gemm_f32_kernel<false>), dim3(grid), dim3(256), 0, stream, A, W, C, R, bias, M, N, K, lda, ldw, ldc, ldr);
   return launch_status();
 }

@@ -68,6 +68,7 @@ struct PrefillGemmArgs {
   int tokens, N, K, ldo;   // N: output features (for the gate: half of the weight rows)
   int up_offset;           // EPI_SWIGLU: row distance from a gate row to its up row
   int m_tiles, n_tiles;    // tiles of 256 tokens, tiles of 256 columns
+  const float* bias;       // null, or fp32 [weight rows]: added to the product before the epilogue's own work
   HeadPrepArgs hp;         // EPI_HEAD_PREP
 };
 
@@ -194,12 +195,20 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 // taddr .. + 127 of the thread's lane): rounded to bf16 as the stored projections would be, then the
 // arithmetic of the stand-alone head preparation (per-head RMSNorm, half-split rotation), and the row goes to
 // the query buffer or to the token's place in the key / value cache.
-__device__ __forceinline__ void head_prep_row(const HeadPrepArgs& hp, int t, int h, uint32_t taddr) {
+__device__ __forceinline__ void head_prep_row(const HeadPrepArgs& hp, int t, int h, uint32_t taddr, const float* bias) {
   constexpr int d = 128, half = 64;
   float x[d];
 #pragma unroll
   for (int j = 0; j < d / 32; ++j) tmem_ld32(taddr + 32 * j, x + 32 * j);
   if (t >= hp.n_tokens) return;                       // after the loads: they are warp-wide
+  if (bias != nullptr) {
+    const float4* b4 = (const float4*)(bias + (size_t)h * d);       // the launcher checked its alignment
+#pragma unroll
+    for (int i = 0; i < d; i += 4) {
+      const float4 b = b4[i / 4];
+      x[i] += b.x; x[i + 1] += b.y; x[i + 2] += b.z; x[i + 3] += b.w;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < d; ++i) x[i] = round_to<bf16>(x[i]);
   const int kind = h < hp.nq ? 0 : (h < hp.nq + hp.nkv ? 1 : 2);     // 0 q, 1 k, 2 v
@@ -382,7 +391,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // a tile's 256 columns are two heads; a thread finishes its token's row of each
 #pragma unroll 1
         for (int hh = 0; hh < BN / 128; ++hh)
-          if (n0 + 128 * hh < a.N) head_prep_row(a.hp, tok0 + row, (n0 >> 7) + hh, taddr + 128 * hh);
+          if (n0 + 128 * hh < a.N) head_prep_row(a.hp, tok0 + row, (n0 >> 7) + hh, taddr + 128 * hh, a.bias);
       } else
 #pragma unroll 1
       for (int c = 0; c < OUT_PER_TILE; c += COLS_PER_OP, ++op) {
@@ -395,6 +404,17 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           float v[32], u[32];
           tmem_ld32(taddr + c + 32 * part, v);
           if (GATE) tmem_ld32(taddr + BN / 2 + c + 32 * part, u);
+          if (a.bias != nullptr) {
+            // a column is a feature: the same 32 biases for every thread (a broadcast read); columns beyond
+            // the matrix are clipped by the TMA store, their bias is taken as zero
+            const int nb = n0 + c + 32 * part;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const bool in = nb + j < a.N;
+              v[j] += in ? __ldg(a.bias + nb + j) : 0.f;
+              if (GATE) u[j] += in ? __ldg(a.bias + a.up_offset + nb + j) : 0.f;
+            }
+          }
           if (OUT32) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
@@ -509,14 +529,17 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMa
 // receives an error code if a wait gives up.
 // EPI_HEAD_PREP: out is not used; head_prep describes where the heads go (heads of 128, whole-head rotation or
 // none, keys and values written).
+// bias: null, or fp32 [w_rows] (16-byte aligned), added to the product.
 extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
-                                     int ldo, int epi, const HeadPrepArgs* head_prep, int* status, cudaStream_t stream) {
+                                     int ldo, int epi, const HeadPrepArgs* head_prep, const float* bias, int* status,
+                                     cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || status == nullptr) return ODI_ERR_UNSUPPORTED;
   const bool gate = epi == EPI_SWIGLU, heads = epi == EPI_HEAD_PREP;
   if (gate ? w_rows != 2 * n_out : w_rows != n_out) return ODI_ERR_ARGUMENT;
   const bool f32 = epi == EPI_STORE_F32 || epi == EPI_RESIDUAL;
   if (!heads && (((uintptr_t)out & 15) || ((long)ldo * (f32 ? 4 : 2)) % 16 != 0)) return ODI_ERR_UNSUPPORTED;
+  if ((uintptr_t)bias & 15) return ODI_ERR_UNSUPPORTED;
   if (heads) {
     if (head_prep == nullptr) return ODI_ERR_ARGUMENT;
     const HeadPrepArgs& hp = *head_prep;
@@ -542,6 +565,7 @@ extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, in
   PrefillGemmArgs a;
   a.out = out; a.status = status; a.tokens = tokens; a.N = n_out; a.K = K; a.ldo = ldo;
   a.up_offset = gate ? n_out : 0;
+  a.bias = bias;
   a.hp = heads ? *head_prep : HeadPrepArgs{};
   const int per_tile = gate ? BN / 2 : BN;
   a.m_tiles = (tokens + 2 * BM - 1) / (2 * BM);

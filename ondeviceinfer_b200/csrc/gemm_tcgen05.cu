@@ -64,6 +64,9 @@ struct GemmArgs {
   // EPI_RESIDUAL: when not null, the sums of squares of the rows it leaves, one piece
   // per tile of 128 features: sumsq_out [ceil(N / 128), tokens].
   float* sumsq_out;
+  // When not null: bias [weight rows], added to the finished product (after the K splits are summed) before
+  // anything else the epilogue does with it.
+  const float* bias;
   // EPI_HEAD_PREP: a tile of 128 features is one head (query heads, then key heads, then value heads);
   // what the stand-alone head preparation would do with the bf16 projections happens in the epilogue.
   HeadPrepArgs hp;
@@ -442,6 +445,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (!ok && lane == 0) atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_EPILOGUE);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     tc_fence_after();
+    // this thread's feature row has one bias for every token (weights: no kernel writes them)
+    const bool biased = a.bias != nullptr && n0 + row < a.N;
+    const float bias_v = biased ? a.bias[n0 + row] : 0.f;
+    const float bias_u = (DUAL && biased) ? a.bias[n0 + row + a.dual_offset] : 0.f;
     if (ok && a.splits == 1) {
       const int n = n0 + row;
 #pragma unroll 1
@@ -450,6 +457,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         float v[16], u[16];
         tmem_ld16(taddr + c, v);
         if (DUAL) tmem_ld16(taddr + BN + c, u);
+        if (a.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { v[i] += bias_v; if (DUAL) u[i] += bias_u; }
+        }
         if (EPI == EPI_RESIDUAL) {
           // read the 16 residual values first: the adds must not wait on one another
           float r[16];
@@ -529,6 +540,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
             for (int i = 0; i < 8; ++i) { v[i] += pv[i]; if (DUAL) u[i] += pu[i]; }
           }
+          if (a.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { v[i] += bias_v; if (DUAL) u[i] += bias_u; }
+          }
           if (EPI == EPI_RESIDUAL) {
             float r[8];
 #pragma unroll
@@ -573,6 +588,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const float* red = (const float*)smem;
       const uint32_t rank = cluster_rank();
       const bool sums = EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr;
+      const bool biased = a.bias != nullptr && n < a.N;
+      const float bias_v = biased ? a.bias[n] : 0.f;
+      const float bias_u = (DUAL && biased) ? a.bias[n + a.dual_offset] : 0.f;
       int slot = 0;
       if (live)
         for (int c = (int)rank; c < BN && tok0 + c < a.tokens; c += a.splits, ++slot) {   // the token columns this CTA owns
@@ -592,6 +610,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           for (int p = 0; p < 8; ++p) {
             if (p < a.splits) { v += pv[p]; if (DUAL) u += pu[p]; }
           }
+          if (a.bias != nullptr) { v += bias_v; if (DUAL) u += bias_u; }
           if (EPI == EPI_HEAD_PREP) ((float*)(smem + HP_STAGE_OFFSET))[slot * BM + row] = round_to<bf16>(v);
           float left = 0.f;
           if (EPI == EPI_RESIDUAL) { left = inside ? res + v : 0.f; if (inside) *res_at = left; }
@@ -734,7 +753,7 @@ extern "C" long odi_gemm_bf16_scratch_floats(int tokens, int n_out, int bn, int 
 }
 
 // x [tokens, K] bf16, w [w_rows, K] bf16 (for EPI_SWIGLU w holds the gate rows followed by
-// the up rows and n_out = w_rows / 2), out [tokens, ldo].
+// the up rows and n_out = w_rows / 2), out [tokens, ldo]; bias: null or fp32 [w_rows], added to the product.
 // Tiles of 128 features x bn tokens, bn in {16, 32, 64, 128, 256}, K splits allowed; cluster != 0 lets 2..8 splits
 // (bn <= 64) exchange partials through distributed shared memory.  Many tokens are the business of
 // gemm_prefill_tcgen05.cu; this kernel takes them too, tile by tile, but re-reads the weights for every token tile.
@@ -742,7 +761,7 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
                              int ldo, int epi, int bn, int splits, int cluster, float* scratch,
                              int* tickets, int* status, const float* norm_x, const float* norm_w,
                              const float* norm_parts, int norm_n_parts, float norm_eps, float* sumsq_out,
-                             const HeadPrepArgs* head_prep, cudaStream_t stream) {
+                             const HeadPrepArgs* head_prep, const float* bias, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
   if (x == nullptr && norm_x == nullptr) return ODI_ERR_ARGUMENT;
@@ -769,6 +788,7 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   if (sumsq_out != nullptr && (epi != EPI_RESIDUAL || bn > 64 || !(clustered || splits == 1))) return ODI_ERR_UNSUPPORTED;
   a.norm_x = norm_x; a.norm_w = norm_w; a.norm_parts = norm_parts; a.norm_n_parts = norm_n_parts; a.norm_eps = norm_eps;
   a.sumsq_out = sumsq_out;
+  a.bias = bias;
   if (epi == EPI_HEAD_PREP) {
     // heads of 128 (a tile is a head), whole-head rotation or none, keys and values written, tokens in columns
     if (head_prep == nullptr) return ODI_ERR_ARGUMENT;

@@ -26,6 +26,7 @@ is not marked ``graph_safe``) do not use this path.
 from __future__ import annotations
 
 import gc
+import time
 import weakref
 from typing import Dict, List, Optional, Sequence
 
@@ -33,6 +34,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
+from .step import StepDescription
 
 
 def _power_of_two(n: int) -> int:
@@ -55,11 +57,16 @@ def serving_graph_key(keys, width: int, bucket: int, bounds: tuple):
     return min(near, key=lambda k: (k[1], k[2])) if near else None
 
 
-class _DecodeContext:
+class _DecodeContext(StepDescription):
     """The fixed-buffer counterpart of :class:`~ondeviceinfer_b200.engine.step.StepContext`
-    for ``width`` sequences that bring one token each."""
+    for ``width`` sequences that bring one token each: the same names for a part
+    (:class:`~ondeviceinfer_b200.engine.step.StepDescription`), plus what only the runner uses
+    (``REPLAY_ONLY``)."""
+
+    REPLAY_ONLY = ("width", "max_pages", "streams", "steps", "active", "plan_key_splits")
 
     def __init__(self, cache, width: int, max_pages: int, device, longest: int) -> None:
+        super().__init__()
         self.width = width
         self.n_seqs = self.n_tokens = self.n_want = width
         self.max_q_len = 1
@@ -73,14 +80,26 @@ class _DecodeContext:
         self.tok_seq = arange[:width].clone()
         self.want_rows = arange[:width].clone()
         self.cu_q = arange.clone()
-        self._page_start = (arange * max_pages).contiguous()
+        page_start = (arange * max_pages).contiguous()
         self._page_ids = [zeros(width * max_pages) for _ in cache.kv_groups]
-        self._memo: Dict[object, object] = {}
+        self._page_tables = [(page_start, ids) for ids in self._page_ids]
         self.slot_list: List[int] = []
-        self.kv_lens: List[int] = [longest] * width      # host: the keys each row sees in the coming step
+        self._kv_lens: List[int] = [longest] * width         # host: the keys each row sees in the coming step
         self._key_splits: Dict[int, list] = {}               # block rows -> [device int, its value, bound on the splits]
         self._planned_tiles: tuple = ()
         self._planned_bounds: tuple = ()
+
+    @property
+    def kv_lens(self) -> List[int]:
+        return self._kv_lens
+
+    @kv_lens.setter
+    def kv_lens(self, values: Sequence[int]) -> None:
+        self._kv_lens = list(values)
+
+    @property
+    def past_lens(self) -> List[int]:
+        return [n - 1 for n in self._kv_lens]
 
     def key_splits(self, block_rows: int):
         """``(tiles_per_split, splits)`` for a mixer whose decode kernel cuts each sequence's keys among
@@ -113,14 +132,6 @@ class _DecodeContext:
         self._planned_tiles, self._planned_bounds = tiles, tuple(needed)
         return self._planned_bounds
 
-    def page_table(self, group_index: int):
-        return self._page_start, self._page_ids[group_index]
-
-    def memo(self, key, make):
-        if key not in self._memo:
-            self._memo[key] = make()
-        return self._memo[key]
-
 
 class DecodeRunner:
     def __init__(self, model, cache, *, temperature: float = 0.0, seed: int = 0) -> None:
@@ -131,7 +142,9 @@ class DecodeRunner:
         self.temperature, self.seed = float(temperature), int(seed)
         self.max_pages = cache.n_pages
         self._contexts: Dict[int, _DecodeContext] = {}     # by width: the buffers that every graph of the width uses
-        self._graphs: Dict[tuple, tuple] = {}               # by (width, longest-sequence bucket)
+        self._graphs: Dict[tuple, tuple] = {}               # by (width, longest-sequence bucket, split bounds)
+        self._last_key: Optional[tuple] = None              # the graph that the last step replayed
+        self.capture_seconds = 0.0                          # wall time spent capturing graphs so far
         self.live_slots: List[int] = []
         self.ctx: Optional[_DecodeContext] = None
         self._host_pages: List[np.ndarray] = []
@@ -215,11 +228,13 @@ class DecodeRunner:
 
     # ------------------------------------------------------------------ capture
 
-    def _run_once(self, ctx: _DecodeContext) -> None:
+    def _run_once(self, ctx: _DecodeContext) -> torch.Tensor:
         ctx._memo.clear()
+        ctx.residual_sumsq = None
         logits = self.model.forward(ctx, self.cache)
         ops.sample(logits, ctx.token_ids, self.temperature, self.seed, ctx.streams, ctx.steps,
                    advance_pos=ctx.tok_pos, advance_past=ctx.past, active=ctx.active)
+        return logits
 
     def _graph_for(self, width: int, kv_lens: Sequence[int]):
         """The graph for ``width`` rows whose live sequences see ``kv_lens`` keys in the coming step: one per
@@ -231,11 +246,13 @@ class DecodeRunner:
             ctx = self._contexts[width] = _DecodeContext(self.cache, width, self.max_pages, self.model.device, bucket)
             ctx.kv_lens = kv_lens
             graph = self._capture(ctx, bucket)          # its warm-up run tells which parts cut keys
-            self._graphs[(width, bucket, ctx.plan_key_splits(kv_lens))] = graph
+            self._last_key = (width, bucket, ctx.plan_key_splits(kv_lens))
+            self._graphs[self._last_key] = graph
             return graph
         key = (width, bucket, ctx.plan_key_splits(kv_lens))
         have = serving_graph_key(self._graphs, *key)
         if have is not None:
+            self._last_key = have
             return self._graphs[have]
         # in the middle of a batch: the capture runs on the pad slot and overwrites the buffers
         names = ("token_ids", "tok_pos", "past", "slots", "streams", "steps", "active")
@@ -249,10 +266,13 @@ class DecodeRunner:
         for ids, value in zip(ctx._page_ids, pages):
             ids.copy_(value)
         ctx.slot_list = slot_list
+        self._last_key = key
         return self._graphs[key]
 
     def _capture(self, ctx: _DecodeContext, bucket: int):
         device, width = self.model.device, ctx.width
+        torch.cuda.synchronize(device)
+        began = time.perf_counter()
         ctx.max_kv_len = bucket
         pad = self.cache.pad_slot
         ctx.slots.fill_(pad)
@@ -278,13 +298,16 @@ class DecodeRunner:
         gc.disable()
         try:
             with torch.cuda.graph(graph):
-                self._run_once(ctx)
+                logits = self._run_once(ctx)
         finally:
             if collecting:
                 gc.enable()
         launches = {k: ops.LAUNCHES[k] - counted[k] for k in ("own", "library")}
         ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
-        return graph, launches
+        torch.cuda.synchronize(device)
+        self.capture_seconds += time.perf_counter() - began
+        # `logits` lives in the graph's own memory: every replay of this graph leaves the step's logits there
+        return graph, launches, logits
 
     # ------------------------------------------------------------------ steps
 
@@ -293,7 +316,7 @@ class DecodeRunner:
         self._reserve_next(n_steps)
         lengths = [self.cache.lengths[s] for s in self.live_slots]
         for i in range(n_steps):
-            graph, launches = self._graph_for(self.ctx.width, [n + i + 1 for n in lengths])
+            graph, launches, _ = self._graph_for(self.ctx.width, [n + i + 1 for n in lengths])
             graph.replay()
             ops.LAUNCHES["own"] += launches["own"]
             ops.LAUNCHES["library"] += launches["library"]
@@ -309,12 +332,23 @@ class DecodeRunner:
             self._pinned_tokens[:n] = torch.as_tensor(host_tokens, dtype=torch.int32)
             self.ctx.token_ids[:n].copy_(self._pinned_tokens[:n], non_blocking=True)
         self.step_device(1)
-        # the sampled tokens back through pinned memory: one asynchronous copy, one wait on the stream
-        if self._pinned_out is None or self._pinned_out.numel() < n:
-            self._pinned_out = torch.empty(max(n, 64), dtype=torch.int32).pin_memory()
+        # the sampled tokens back through pinned memory, and with them the kernels' error word: two asynchronous
+        # copies, one wait on the stream
+        if self._pinned_out is None or self._pinned_out.numel() < n + 1:
+            self._pinned_out = torch.empty(max(n, 64) + 1, dtype=torch.int32).pin_memory()
         self._pinned_out[:n].copy_(self.ctx.token_ids[:n], non_blocking=True)
+        self._pinned_out[n:n + 1].copy_(ops.kernel_status_word(self.model.device), non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if int(self._pinned_out[n]) != 0:
+            ops.raise_on_kernel_fault()
         return self._pinned_out[:n].tolist()
+
+    def last_logits(self) -> torch.Tensor:
+        """fp32 logits ``[live sequences, vocab]`` of the step replayed last, on the device: a view of the
+        memory the replayed graph writes them to, valid until the next step."""
+        if self._last_key is None:
+            raise RuntimeError("no decode step has run yet")
+        return self._graphs[self._last_key][2][:len(self.live_slots)]
 
     def drop(self, finished_rows: Sequence[int], streams: Sequence[int], steps: Sequence[int]) -> None:
         """Remove rows (indices into the live set) and continue with the others; ``streams``

@@ -34,6 +34,10 @@ class GenerationResult:
     decode_seconds: float
     decode_steps: int = 0
     batches: List[List[int]] = field(default_factory=list)
+    capture_seconds: float = 0.0    # one-off set-up of a fused decoder (graph captures), not part of decode_seconds
+    # wall seconds of every decode step in the order they ran (all batches), from the loop's stop tests to the
+    # step's tokens on the host, without set-up: sum(step_seconds) is decode_seconds but for the batches' ends
+    step_seconds: List[float] = field(default_factory=list)
 
     @property
     def decode_tokens(self) -> int:
@@ -83,14 +87,22 @@ def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
 
     ``decoder`` (optional) fuses step and sampling for the one-token steps: an object with
     ``begin(slots, last_tokens, request_indices, step_numbers)`` (called whenever the live
-    set changed) and ``step() -> tokens`` (one decode step of the live set, in order)."""
+    set changed) and ``step(last_tokens) -> tokens`` (one decode step of the live set, in order;
+    the host's record of each sequence's last token is what the step is fed).  If it has a
+    ``capture_seconds`` counter, what it adds during a batch (one-off set-up such as graph captures)
+    is taken out of ``decode_seconds`` and reported apart.
+
+    ``synchronize`` is called where the loop has to wait for the device anyway (around the prompts'
+    step and at the end of a batch); it may raise, which ends the generation."""
     if max_new_tokens <= 0:
         raise ValueError("max_new_tokens must be positive")
     stop = set(int(t) for t in stop_token_ids)
     generated: List[List[int]] = [[] for _ in prompts]
     reasons = ["" for _ in prompts]
-    prefill_seconds = decode_seconds = 0.0
+    prefill_seconds = decode_seconds = capture_seconds = 0.0
     decode_steps = 0
+    step_seconds: List[float] = []
+    set_up_so_far = lambda: getattr(decoder, "capture_seconds", 0.0)
     for batch in batches:
         live = list(batch)
         slots = {r: alloc() for r in live}
@@ -102,8 +114,10 @@ def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
             synchronize()
             prefill_seconds += time.perf_counter() - start
             start = time.perf_counter()
+            set_up = set_up_so_far()
             changed = True
             while True:
+                step_start, step_set_up = time.perf_counter(), set_up_so_far()
                 still = []
                 for r, tok in zip(live, tokens):
                     generated[r].append(int(tok))
@@ -127,14 +141,18 @@ def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
                         decoder.begin([slots[r] for r in live], [generated[r][-1] for r in live], live,
                                       [len(generated[r]) for r in live])
                         changed = False
-                    tokens = decoder.step()
+                    tokens = decoder.step([generated[r][-1] for r in live])
                 decode_steps += 1
+                step_seconds.append(time.perf_counter() - step_start - (set_up_so_far() - step_set_up))
             synchronize()
-            decode_seconds += time.perf_counter() - start
+            set_up = set_up_so_far() - set_up
+            capture_seconds += set_up
+            decode_seconds += time.perf_counter() - start - set_up
         finally:
             for slot in slots.values():
                 free(slot)
     return GenerationResult(
         token_ids=[list(p) + g for p, g in zip(prompts, generated)], generated_ids=generated,
         finish_reasons=reasons, prefill_seconds=prefill_seconds, decode_seconds=decode_seconds,
-        decode_steps=decode_steps, batches=[list(b) for b in batches])
+        decode_steps=decode_steps, batches=[list(b) for b in batches], capture_seconds=capture_seconds,
+        step_seconds=step_seconds)

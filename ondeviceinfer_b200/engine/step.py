@@ -27,8 +27,13 @@ from ..kernels import ops
 Want = Union[str, Sequence[Sequence[int]]]
 
 
-class StepContext:
-    """Device-side description of a step.  All index tensors are int32.
+class StepDescription:
+    """What a part may read from the context of a step, whoever built it.
+
+    Two classes build it: :class:`StepContext` (the host describes a step of any shape and uploads
+    it once) and the fixed-buffer context of :mod:`ondeviceinfer_b200.engine.decode` (one token per
+    sequence, replayed as a CUDA graph).  ``INTERFACE`` names everything both give; a part written
+    against these names runs under either (a test holds the two to it).  All index tensors are int32.
 
     ``token_ids [n_tokens]``  the packed tokens;
     ``tok_seq [n_tokens]``    index (within the batch) of each token's sequence;
@@ -37,14 +42,51 @@ class StepContext:
     ``past [n_seqs]``         cached length of each sequence before the step;
     ``slots [n_seqs]``        cache slot of each sequence (row of the state tensors);
     ``want_rows [n_want]``    packed token indices whose logits are returned;
-    ``page_table(g)``         ``(page_start [n_seqs + 1], page_ids)`` of key/value group g.
+    ``page_table(g)``         ``(page_start [n_seqs + 1], page_ids)`` of key/value group g;
+    ``key_splits(rows)``      how a split-key decode kernel may cut the sequences' keys;
+    ``memo(key, make)``       a value shared by all layers of the step (rotary tables and the like);
+    ``residual_sumsq``        the note a residual product leaves for the norm that follows it.
 
-    Host mirrors: ``n_seqs``, ``n_tokens``, ``q_lens``, ``past_lens``, ``max_q_len``,
-    ``max_kv_len`` (longest key range after the step), ``slot_list``.
+    Host mirrors: ``n_seqs``, ``n_tokens``, ``n_want``, ``q_lens``, ``past_lens``, ``kv_lens`` (keys each
+    sequence sees after the step), ``max_q_len``, ``max_kv_len``, ``slot_list``.  Under graph replay the host
+    code of a part runs at capture only: a part that is marked ``graph_safe`` lets the mirrors decide sizes
+    and kernel forms (which a graph fixes, and for which the runner keeps one graph per width and length
+    bucket), never values.
     """
+
+    INTERFACE = ("token_ids", "tok_seq", "tok_pos", "cu_q", "past", "slots", "want_rows",
+                 "n_seqs", "n_tokens", "n_want", "q_lens", "past_lens", "kv_lens", "max_q_len", "max_kv_len",
+                 "slot_list", "residual_sumsq", "page_table", "key_splits", "memo")
+
+    def __init__(self) -> None:
+        self._memo: Dict[object, object] = {}
+        self._page_tables: List[Tuple[torch.Tensor, torch.Tensor]] = []
+        self.residual_sumsq = None
+
+    def page_table(self, group_index: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        return self._page_tables[group_index]
+
+    def memo(self, key, make: Callable[[], object]):
+        """A value shared by all layers of the step (rotary tables and the like)."""
+        if key not in self._memo:
+            self._memo[key] = make()
+        return self._memo[key]
+
+    @property
+    def kv_lens(self) -> List[int]:
+        return [p + t for p, t in zip(self.past_lens, self.q_lens)]
+
+    def key_splits(self, block_rows: int) -> Tuple[Optional[torch.Tensor], int]:
+        raise NotImplementedError
+
+
+class StepContext(StepDescription):
+    """Device-side description of a step, built on the host and uploaded in one copy
+    (fields: see :class:`StepDescription`)."""
 
     def __init__(self, cache, slots: Sequence[int], tokens: Sequence[Sequence[int]],
                  want_rows: Sequence[int], device) -> None:
+        super().__init__()
         self.n_seqs = len(slots)
         self.slot_list = list(slots)
         self.q_lens = [len(t) for t in tokens]
@@ -53,7 +95,6 @@ class StepContext:
         self.max_q_len = max(self.q_lens)
         self.max_kv_len = max(p + t for p, t in zip(self.past_lens, self.q_lens))
         self.n_want = len(want_rows)
-        self._memo: Dict[object, object] = {}
 
         q = np.asarray(self.q_lens, dtype=np.int64)
         cu = np.zeros(self.n_seqs + 1, dtype=np.int64)
@@ -71,31 +112,22 @@ class StepContext:
             pieces += [start, np.fromiter((p for l in lists for p in l), dtype=np.int64, count=int(start[-1]))]
         sizes = [len(p) for p in pieces]
         packed = np.concatenate(pieces).astype(np.int32)
-        self.meta = torch.from_numpy(packed).to(device)
+        self._meta = torch.from_numpy(packed).to(device)
         views, offset = [], 0
         for size in sizes:
-            views.append(self.meta[offset:offset + size])
+            views.append(self._meta[offset:offset + size])
             offset += size
         (self.token_ids, self.tok_seq, self.tok_pos, self.cu_q, self.past, self.slots, self.want_rows) = views[:7]
         self._page_tables = [(views[7 + 2 * g], views[8 + 2 * g]) for g in range(len(cache.kv_groups))]
-
-    def page_table(self, group_index: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        return self._page_tables[group_index]
 
     def key_splits(self, block_rows: int) -> Tuple[Optional[torch.Tensor], int]:
         """For a mixer whose decode kernel cuts each sequence's keys among blocks (``block_rows`` blocks per
         cut): ``(tiles_per_split, splits)`` as :func:`ondeviceinfer_b200.kernels.ops.plan_key_splits` gives
         them for this step's sequences, the first as one int32 on the device."""
         def make():
-            per, splits = ops.plan_key_splits([p + t for p, t in zip(self.past_lens, self.q_lens)], block_rows)
+            per, splits = ops.plan_key_splits(self.kv_lens, block_rows)
             return torch.tensor([per], dtype=torch.int32).to(self.past.device, non_blocking=True), splits
         return self.memo(("key_splits", block_rows), make)
-
-    def memo(self, key, make: Callable[[], object]):
-        """A value shared by all layers of the step (rotary tables and the like)."""
-        if key not in self._memo:
-            self._memo[key] = make()
-        return self._memo[key]
 
 
 def resolve_want(want: Want, q_lens: Sequence[int]) -> List[List[int]]:

@@ -58,7 +58,7 @@ def build_dir() -> Path:
     for folder in candidates:
         try:
             folder.mkdir(parents=True, exist_ok=True)
-            probe = folder / f".probe-{os.getpid()}"
+            probe = folder / f".probe-{os.getpid()}-{threading.get_ident()}"      # threads may probe side by side
             probe.write_text("")
             probe.unlink()
             return folder

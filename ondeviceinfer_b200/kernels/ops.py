@@ -193,6 +193,16 @@ def residual_add(hidden: torch.Tensor, y: torch.Tensor) -> None:
            "residual_add")
 
 
+def bias_add(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """y[t, n] += bias[n] in place (y bf16 or fp32, bias fp32), rounded once to the dtype of y.  For the
+    products that the tensor-core kernels refuse and the vendor library computes."""
+    _require(y, "y", ndim=2)
+    _require_bias(bias, y.shape[1])
+    lib = load_library("elementwise")
+    _check(lib.odi_bias_add(_ptr(y), _ptr(bias), c_long(y.shape[0]), c_int(y.shape[1]), c_int(dtype_code(y.dtype)),
+                            _stream()), "bias_add")
+
+
 def widen(x: torch.Tensor, out: torch.Tensor) -> None:
     _require(x, "x", torch.bfloat16)
     _require(out, "out", torch.float32)
@@ -203,8 +213,16 @@ def widen(x: torch.Tensor, out: torch.Tensor) -> None:
 # ------------------------------------------------------------------------------ matrix products
 
 
-def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> None:
-    """out[M,N] = a[M,K] w[N,K]^T (+ residual) in true fp32; residual may be ``out`` itself."""
+def _require_bias(bias: Optional[torch.Tensor], rows: int) -> None:
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+        if bias.numel() != rows:
+            raise KernelError(f"bias has {bias.numel()} entries, the weight has {rows} rows")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+             bias: Optional[torch.Tensor] = None) -> None:
+    """out[M,N] = a[M,K] w[N,K]^T (+ bias[N]) (+ residual) in true fp32; residual may be ``out`` itself."""
     _require(a, "a", torch.float32, 2)
     _require(w, "w", torch.float32, 2)
     _require(out, "out", torch.float32, 2)
@@ -216,8 +234,9 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Opti
         _require(residual, "residual", torch.float32, 2)
         if residual.shape != out.shape:
             raise KernelError("residual and out disagree")
+    _require_bias(bias, N)
     lib = load_library("gemm_f32")
-    _check(lib.odi_gemm_f32(_ptr(a), _ptr(w), _ptr(out), _ptr(residual), c_int(M), c_int(N), c_int(K),
+    _check(lib.odi_gemm_f32(_ptr(a), _ptr(w), _ptr(out), _ptr(residual), _ptr(bias), c_int(M), c_int(N), c_int(K),
                             c_int(K), c_int(K), c_int(N), c_int(N), _stream()), "gemm_f32")
 
 
@@ -233,6 +252,9 @@ _outgrown = []
 
 def _gemm_buffers(device, scratch_floats: int):
     """Scratch for split partials, tile tickets (kept zero between launches) and the error word."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     state = _gemm_state.setdefault(device, {})
     if "tickets" not in state:
         state["tickets"] = torch.zeros(16384, dtype=torch.int32, device=device)
@@ -242,6 +264,14 @@ def _gemm_buffers(device, scratch_floats: int):
         _outgrown.append(state["scratch"])
         state["scratch"] = torch.empty(int(scratch_floats * 1.25), dtype=torch.float32, device=device)
     return state["scratch"], state["tickets"], state["status"]
+
+
+def kernel_status_word(device) -> torch.Tensor:
+    """The error word of the kernels that wait on barriers, as a one-element int32 tensor on ``device``
+    (0 = fine).  Whoever already copies a step's result to the host can take it along and call
+    :func:`raise_on_kernel_fault` when it is not zero."""
+    _, _, status = _gemm_buffers(torch.device(device), 0)
+    return status[:1]
 
 
 def gemm_status(device=None) -> int:
@@ -309,7 +339,8 @@ def gemm_bf16_gives_sumsq(tokens: int, n_out: int, K: int) -> bool:
 
 def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *,
               bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True,
-              norm: Optional[tuple] = None, sumsq_out: Optional[torch.Tensor] = None, head_prep=None) -> None:
+              norm: Optional[tuple] = None, sumsq_out: Optional[torch.Tensor] = None, head_prep=None,
+              bias: Optional[torch.Tensor] = None) -> None:
     """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
 
     ``EPI_STORE_BF16`` / ``EPI_STORE_F32``: out [tokens, rows]; ``EPI_RESIDUAL``: out (fp32) += product;
@@ -325,6 +356,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
     ``EPI_HEAD_PREP`` with ``head_prep`` (the block that ``head_prep(None, ...)`` returns) and ``out=None``:
     w holds query, key and value heads of 128 rows each; the epilogue rounds the projections to bf16 and
     does what :func:`head_prep` does with them (``gemm_bf16_fuses_head_prep`` says when).
+    ``bias`` (fp32, one per row of w): added to the fp32 product before the epilogue's own work and rounding.
     """
     if norm is not None:
         if x is not None:
@@ -359,6 +391,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
             raise KernelError("sumsq_out goes with EPI_RESIDUAL and has one row per tile of 128 features")
     if not gemm_bf16_supported(x_like, w):
         raise KernelError(f"gemm_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
+    _require_bias(bias, w_rows)
     plan_bn, plan_splits = gemm_bf16_plan(tokens, n_out, K, epi)
     bn = plan_bn if bn is None else bn
     splits = plan_splits if splits is None else splits
@@ -376,7 +409,8 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
         norm_args = (_ptr(None), _ptr(None), _ptr(None), c_int(0), c_float(0.0))
     _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
                              c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
-                             _ptr(sumsq_out), byref(head_prep) if head_prep is not None else _ptr(None), _stream()),
+                             _ptr(sumsq_out), byref(head_prep) if head_prep is not None else _ptr(None), _ptr(bias),
+                             _stream()),
            "gemm_tcgen05")
 
 
@@ -387,7 +421,8 @@ def gemm_prefill_supported(x: torch.Tensor, w: torch.Tensor, n_out: int, out_dty
     return gemm_bf16_supported(x, w) and (n_out * elem) % 16 == 0
 
 
-def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *, head_prep=None) -> None:
+def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *, head_prep=None,
+                      bias: Optional[torch.Tensor] = None) -> None:
     """The persistent two-CTA tensor-core product for many tokens (``csrc/gemm_prefill_tcgen05.cu``): clusters
     of two CTAs own tiles of 256 tokens x 256 features (tcgen05.mma.cta_group::2), two accumulators in tensor
     memory so that a tile's epilogue runs under the next tile's MMAs, output by TMA store or fp32 reduce-add.
@@ -412,11 +447,12 @@ def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tens
         if not gemm_prefill_supported(x, w, n_out, out.dtype):
             raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8, 16-byte aligned operands and output rows "
                               f"(K={K}, {n_out} {out.dtype} per row)")
+    _require_bias(bias, w_rows)
     _, _, status = _gemm_buffers(w.device, 0)
     lib = load_library("gemm_prefill_tcgen05")
     _check(lib.odi_gemm_prefill_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
                                      c_int(n_out), c_int(epi), byref(head_prep) if head_prep is not None else _ptr(None),
-                                     _ptr(status), _stream()), "gemm_prefill_tcgen05")
+                                     _ptr(bias), _ptr(status), _stream()), "gemm_prefill_tcgen05")
 
 
 # ------------------------------------------------------------------------------ attention

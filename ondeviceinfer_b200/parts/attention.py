@@ -1,7 +1,8 @@
 """Grouped-query causal attention over the paged cache
 (ondeviceinfer/attention.py:88-177 of UESlubei/ondeviceinfer).
 
-Steps of ``forward``: one matrix product for the concatenated q, k, v projections; the
+Steps of ``forward``: one matrix product for the concatenated q, k, v projections (with their
+biases, if the spec names any: ondeviceinfer/attention.py:106-123); the
 per-head Q/K RMSNorm, the rotary embedding and the cache write (a fused kernel of their own,
 or, at decode widths with heads of 128, the epilogue of that product); attention over the
 cache pages of each sequence; the output projection with the residual add.  Head counts,
@@ -50,6 +51,8 @@ class Attention(Part):
         if s.qk_norm_eps is not None:
             decls += [TensorDecl(s.name("q_norm"), (s.head_dim,), "one_plus_normal"),
                       TensorDecl(s.name("k_norm"), (s.head_dim,), "one_plus_normal")]
+        decls += [TensorDecl(s.name(role), (size,)) for role, size in
+                  (("q_bias", q), ("k_bias", kv), ("v_bias", kv), ("o_bias", s.hidden_size)) if s.has(role)]
         return decls + self.position.tensor_decls()
 
     def load(self, fetch, runtime) -> None:
@@ -60,6 +63,14 @@ class Attention(Part):
         self.w_o = fetch.matrix(s.name("o"))
         self.q_norm = fetch.vector(s.name("q_norm")) if s.qk_norm_eps is not None else None
         self.k_norm = fetch.vector(s.name("k_norm")) if s.qk_norm_eps is not None else None
+        # biases (fp32), those of q, k and v concatenated like their weights; a projection without one adds zero
+        q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        self.b_qkv = None
+        if any(s.has(role) for role in ("q_bias", "k_bias", "v_bias")):
+            zeros = lambda size: torch.zeros(size, dtype=torch.float32, device=runtime.device)
+            self.b_qkv = torch.cat([fetch.vector(s.name(role)) if s.has(role) else zeros(size)
+                                    for role, size in (("q_bias", q), ("k_bias", kv), ("v_bias", kv))])
+        self.b_o = fetch.vector(s.name("o_bias")) if s.has("o_bias") else None
         self.position.load(fetch, runtime)
 
     def cache_needs(self):
@@ -77,17 +88,17 @@ class Attention(Part):
         cos, sin = tables if tables is not None else (None, None)
         # with heads of 128 at decode widths the product's epilogue prepares the heads itself
         fused = heads_in_epilogue(x, self.w_qkv, head_dim=s.head_dim, rot_dim=self.position.rot_dim,
-                                  rotated=cos is not None, write_kv=view.writes_kv)
-        prepared = ops.head_prep(None if fused else linear(x, self.w_qkv), q, view.keys, view.values,
+                                  rotated=cos is not None, write_kv=view.writes_kv, biased=self.b_qkv is not None)
+        prepared = ops.head_prep(None if fused else linear(x, self.w_qkv, bias=self.b_qkv), q, view.keys, view.values,
                                  self.q_norm, self.k_norm, cos, sin, ctx.tok_seq, ctx.tok_pos, page_start, page_ids,
                                  nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim, rot_dim=self.position.rot_dim,
                                  page_size=PAGE_SIZE, ring_pages=group.ring_pages, write_kv=view.writes_kv,
                                  eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0)
         if fused:
-            project_heads(x, self.w_qkv, prepared)
+            project_heads(x, self.w_qkv, prepared, bias=self.b_qkv)
         o = torch.empty_like(q)
         self.attend(q, o, ctx, view, page_start, page_ids)
-        linear(o, self.w_o, residual=residual, track=ctx)
+        linear(o, self.w_o, bias=self.b_o, residual=residual, track=ctx)
 
     def attend(self, q, o, ctx, view, page_start, page_ids) -> None:
         """bf16 without a window: the tensor-core kernels -- tcgen05 flash attention for steps that

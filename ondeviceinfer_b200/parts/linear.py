@@ -42,14 +42,14 @@ PREFILL_GEMM = os.environ.get("ODI_PREFILL_GEMM", "auto")
 PERSISTENT_MIN_TOKENS_FUSED, PERSISTENT_MIN_TOKENS_PLAIN = 1024, 2048
 
 
-def _persistent(tokens: int, weight: torch.Tensor, x: torch.Tensor, epi: int) -> bool:
+def _persistent(tokens: int, weight: torch.Tensor, x: torch.Tensor, epi: int, biased: bool = False) -> bool:
     n_out = weight.shape[0] // 2 if epi == ops.EPI_SWIGLU else weight.shape[0]
     out_dtype = torch.float32 if epi in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL) else torch.bfloat16
     if PREFILL_GEMM == "library" or not ops.gemm_prefill_supported(x, weight, n_out, out_dtype):
         return False
     if PREFILL_GEMM == "own":
         return True
-    fused = epi in (ops.EPI_SWIGLU, ops.EPI_RESIDUAL)
+    fused = biased or epi in (ops.EPI_SWIGLU, ops.EPI_RESIDUAL)      # a bias is a fused epilogue too
     return tokens >= (PERSISTENT_MIN_TOKENS_FUSED if fused else PERSISTENT_MIN_TOKENS_PLAIN)
 
 
@@ -89,11 +89,16 @@ class NormedRows:
 TALL_PRODUCT_FEATURES, TALL_PRODUCT_MAX_TOKENS = 32768, 64
 
 
-def _own(x, weight: torch.Tensor) -> bool:
+def _own(x, weight: torch.Tensor, biased: bool = False) -> bool:
+    """Whether the few-token tensor-core kernel serves this product.  A product with a bias stays with this
+    library's kernels at every width (the bias joins the fp32 product before its one rounding, which a
+    library product that returns bf16 cannot offer): this kernel up to where the many-token one takes over."""
     like = x.rows if isinstance(x, NormedRows) else x
     limit = OWN_KERNEL_MAX_TOKENS
     if weight.shape[0] >= TALL_PRODUCT_FEATURES and limit >= 32:
         limit = max(limit, TALL_PRODUCT_MAX_TOKENS)
+    if biased and PREFILL_GEMM != "library":
+        limit = max(limit, PERSISTENT_MIN_TOKENS_FUSED - 1)
     return x.shape[0] <= limit and ops.gemm_bf16_supported(like, weight)
 
 
@@ -106,9 +111,10 @@ def _operand(x, weight: torch.Tensor, n_out: int, epi: int):
     return x.materialize(), None
 
 
-def linear(x, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
+def linear(x, weight: torch.Tensor, *, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, track=None) -> Optional[torch.Tensor]:
-    """``x`` [tokens, in] (a tensor or :class:`NormedRows`), ``weight`` [out, in].
+    """``x`` [tokens, in] (a tensor or :class:`NormedRows`), ``weight`` [out, in], ``bias`` None or fp32 [out]
+    (added to the fp32 product before it is rounded or added to the residual).
 
     With ``residual`` (fp32 [tokens, out]) the product is added to it in place and
     nothing is returned; otherwise a new [tokens, out] tensor in ``out_dtype`` (default:
@@ -122,24 +128,25 @@ def linear(x, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
     n, N = x.shape[0], weight.shape[0]
     if track is not None:
         track.residual_sumsq = None
-    if isinstance(x, NormedRows) and not (x.dtype == torch.bfloat16 and _own(x, weight)):
+    biased = bias is not None
+    if isinstance(x, NormedRows) and not (x.dtype == torch.bfloat16 and _own(x, weight, biased)):
         x = x.materialize()
     if x.dtype == torch.float32:
         if residual is not None:
-            ops.gemm_f32(x, weight, residual, residual)
+            ops.gemm_f32(x, weight, residual, residual, bias=bias)
             return None
         out = torch.empty((n, N), dtype=torch.float32, device=x.device)
-        ops.gemm_f32(x, weight, out)
+        ops.gemm_f32(x, weight, out, bias=bias)
         return out
     if x.dtype != torch.bfloat16:
         raise ops.KernelError(f"linear takes float32 or bfloat16 activations, not {x.dtype}")
-    if _own(x, weight):
+    if _own(x, weight, biased):
         if residual is not None:
             x, norm = _operand(x, weight, N, ops.EPI_RESIDUAL)
             parts = None
             if track is not None and ops.gemm_bf16_gives_sumsq(n, N, weight.shape[1]):
                 parts = torch.empty((ops.gemm_bf16_sumsq_parts(N), n), dtype=torch.float32, device=residual.device)
-            ops.gemm_bf16(x, weight, residual, ops.EPI_RESIDUAL, norm=norm, sumsq_out=parts)
+            ops.gemm_bf16(x, weight, residual, ops.EPI_RESIDUAL, norm=norm, sumsq_out=parts, bias=bias)
             if parts is not None:
                 track.residual_sumsq = (residual, parts)
             return None
@@ -147,56 +154,79 @@ def linear(x, weight: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
         epi = ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16
         x, norm = _operand(x, weight, N, epi)
         out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=weight.device)
-        ops.gemm_bf16(x, weight, out, epi, norm=norm)
+        ops.gemm_bf16(x, weight, out, epi, norm=norm, bias=bias)
         return out
-    if residual is not None and _persistent(n, weight, x, ops.EPI_RESIDUAL):
-        ops.gemm_prefill_bf16(x, weight, residual, ops.EPI_RESIDUAL)
+    if residual is not None and _persistent(n, weight, x, ops.EPI_RESIDUAL, biased):
+        ops.gemm_prefill_bf16(x, weight, residual, ops.EPI_RESIDUAL, bias=bias)
         return None
-    if residual is None and _persistent(n, weight, x, ops.EPI_STORE_F32 if out_dtype == torch.float32 else ops.EPI_STORE_BF16):
+    if residual is None and _persistent(n, weight, x, ops.EPI_STORE_F32 if out_dtype == torch.float32 else ops.EPI_STORE_BF16, biased):
         wide = out_dtype == torch.float32
         out = torch.empty((n, N), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
-        ops.gemm_prefill_bf16(x, weight, out, ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16)
+        ops.gemm_prefill_bf16(x, weight, out, ops.EPI_STORE_F32 if wide else ops.EPI_STORE_BF16, bias=bias)
         return out
+    if residual is None and out_dtype == torch.float32:
+        return _wide_product(x, weight, bias)
     y = torch.matmul(x, weight.t())
     ops.LAUNCHES["library"] += 1
+    if biased:
+        ops.bias_add(y, bias)          # after the library's rounding: only shapes the own kernels refuse come here
     if residual is not None:
         ops.residual_add(residual, y)
         return None
-    if out_dtype == torch.float32:
-        out = torch.empty((n, N), dtype=torch.float32, device=x.device)
-        ops.widen(y, out)
-        return out
     return y
+
+
+# fp32 results of bf16 operands (the logits) are never rounded to bf16 on the way, whatever the number of rows:
+# a vocabulary of 150,000 logits rounded to 8 bits of mantissa ties often, and the first-index argmax would
+# then choose by the batch's width.  So beyond the few-token limit they stay with this library's kernels:
+# the many-token kernel from WIDE_PERSISTENT_MIN_ROWS rows on, the few-token kernel tile by tile below
+# (token tiles of one feature tile run side by side and share the weight tile in L2), and for a K that the
+# tensor-core kernels refuse the fp32 kernel on widened operands.
+WIDE_PERSISTENT_MIN_ROWS = 256
+
+
+def _wide_product(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    n, N = x.shape[0], weight.shape[0]
+    out = torch.empty((n, N), dtype=torch.float32, device=x.device)
+    if n >= WIDE_PERSISTENT_MIN_ROWS and PREFILL_GEMM != "library" and ops.gemm_prefill_supported(x, weight, N, torch.float32):
+        ops.gemm_prefill_bf16(x, weight, out, ops.EPI_STORE_F32, bias=bias)
+    elif ops.gemm_bf16_supported(x, weight):
+        ops.gemm_bf16(x, weight, out, ops.EPI_STORE_F32, bias=bias)
+    else:
+        ops.gemm_f32(x.float(), weight.float(), out, bias=bias)
+    return out
 
 
 def _heads_fit(head_dim: int, rot_dim: int, rotated: bool, write_kv: bool) -> bool:
     return head_dim == 128 and write_kv and (not rotated or rot_dim == head_dim)
 
 
-def heads_in_epilogue(x, weight_qkv: torch.Tensor, *, head_dim: int, rot_dim: int, rotated: bool, write_kv: bool) -> bool:
+def heads_in_epilogue(x, weight_qkv: torch.Tensor, *, head_dim: int, rot_dim: int, rotated: bool, write_kv: bool,
+                      biased: bool = False) -> bool:
     """Whether :func:`project_heads` can serve this step: a tensor-core kernel in a form whose epilogue
     prepares the heads (bf16, heads of 128, whole-head rotation or none, keys/values written; decode widths
     or the many-token kernel)."""
     if x.dtype != torch.bfloat16 or not _heads_fit(head_dim, rot_dim, rotated, write_kv):
         return False
-    if _own(x, weight_qkv):
+    if _own(x, weight_qkv, biased):
         return ops.gemm_bf16_fuses_head_prep(x.shape[0], weight_qkv.shape[0], weight_qkv.shape[1], d=head_dim,
                                              rot_dim=rot_dim, rotated=rotated, write_kv=write_kv)
     like = x.rows if isinstance(x, NormedRows) else x
-    return (PREFILL_GEMM != "library" and x.shape[0] >= PERSISTENT_MIN_TOKENS_PLAIN and weight_qkv.shape[0] % 128 == 0
+    least = PERSISTENT_MIN_TOKENS_FUSED if biased else PERSISTENT_MIN_TOKENS_PLAIN
+    return (PREFILL_GEMM != "library" and x.shape[0] >= least and weight_qkv.shape[0] % 128 == 0
             and ops.gemm_bf16_supported(like, weight_qkv))
 
 
-def project_heads(x, weight_qkv: torch.Tensor, head_prep) -> None:
+def project_heads(x, weight_qkv: torch.Tensor, head_prep, bias: Optional[torch.Tensor] = None) -> None:
     """The q/k/v projections of ``x`` (a tensor or :class:`NormedRows`) with per-head norm, rotation and the
     cache write done in the product's epilogue; ``head_prep`` is the block ``ops.head_prep(None, ...)`` gives."""
-    if _own(x, weight_qkv):
+    if _own(x, weight_qkv, bias is not None):
         x, norm = _operand(x, weight_qkv, weight_qkv.shape[0], ops.EPI_HEAD_PREP)
-        ops.gemm_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, norm=norm, head_prep=head_prep)
+        ops.gemm_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, norm=norm, head_prep=head_prep, bias=bias)
         return
     if isinstance(x, NormedRows):
         x = x.materialize()
-    ops.gemm_prefill_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, head_prep=head_prep)
+    ops.gemm_prefill_bf16(x, weight_qkv, None, ops.EPI_HEAD_PREP, head_prep=head_prep, bias=bias)
 
 
 def gated_linear(x, weight_gate_up: torch.Tensor) -> torch.Tensor:

@@ -5,7 +5,7 @@ Run once, on the CPU, with the UESlubei/ondeviceinfer checkout importable:
 
     python tests/golden/make_golden.py /path/to/ondeviceinfer-checkout
 
-For the tiny random models A and B it builds the reference's ``Qwen3ForCausalLM``
+For the tiny random models A and B, and A with biases on the attention projections, it builds the reference's ``Qwen3ForCausalLM``
 (ondeviceinfer/model.py:121-163) in fp32, loads the tests' seeded weights into it by
 their checkpoint names, runs every prompt alone and whole, and also prefill + token by
 token through the reference's resident cache.  It asserts that the plain implementation
@@ -32,6 +32,7 @@ import plain_qwen3 as plain  # noqa: E402
 CASES = {
     "tiny_a": (plain.TINY_A, 0, [5, 11, 17], 8),
     "tiny_b": (plain.TINY_B, 1, [1, 7, 30, 64], 16),
+    "tiny_a_bias": (plain.TINY_A_BIAS, 10, [5, 11, 17], 8),
 }
 
 
@@ -46,7 +47,7 @@ def reference_model(ref_root, cfg, weights):
         num_attention_heads=cfg["num_attention_heads"], num_key_value_heads=cfg["num_key_value_heads"],
         head_dim=cfg["head_dim"], max_position_embeddings=cfg["max_position_embeddings"],
         rms_norm_eps=cfg["rms_norm_eps"], rope_theta=cfg["rope_theta"],
-        tie_word_embeddings=cfg["tie_word_embeddings"])
+        tie_word_embeddings=cfg["tie_word_embeddings"], attention_bias=cfg.get("attention_bias", False))
     model = Qwen3ForCausalLM(config, dtype=torch.float32).eval()
     state = {k: v.float() for k, v in weights.items()}
     if cfg["tie_word_embeddings"]:
@@ -58,7 +59,9 @@ def reference_model(ref_root, cfg, weights):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    ref_root = Path(sys.argv[1])
     for name, (cfg, seed, lengths, new_tokens) in CASES.items():
         weights = plain.random_weights(cfg, seed)
         prompts = plain.random_prompts(cfg, lengths, seed)
@@ -95,7 +98,13 @@ def main():
                 out[f"positions_{r}"] = np.asarray(picks, dtype=np.int32)
                 out[f"logits_{r}"] = whole[picks].numpy().astype(np.float32)
                 out[f"greedy_{r}"] = np.asarray(ref_tokens, dtype=np.int32)
-        np.savez_compressed(HERE / f"{name}.npz", **out)
+        target = HERE / f"{name}.npz"
+        if target.exists():
+            old = np.load(target)
+            if sorted(old.files) == sorted(out) and all(np.array_equal(old[k], out[k]) for k in out):
+                print(f"{name}: the committed file already holds these outputs")
+                continue
+        np.savez_compressed(target, **out)
         print(f"{name}: plain vs reference max |dlogit| = {worst:.3e} (fp32), "
               f"{worst_bf16:.3e} (bf16 arithmetic); wrote {name}.npz")
 

@@ -49,6 +49,10 @@ CASES = {
     "A": (plain.TINY_A, 0),
     "B": (plain.TINY_B, 1),
     "C": (plain.TINY_C, 2),
+    # with projection biases
+    "Ab": (plain.TINY_A_BIAS, 10),
+    "Bb": (plain.TINY_B_BIAS, 11),
+    "Cb": (plain.TINY_C_BIAS, 12),
 }
 
 

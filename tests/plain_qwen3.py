@@ -86,9 +86,11 @@ def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> t
     return (probs @ vv.float()).to(q.dtype)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """y = x W^T for an [out, in] weight (ondeviceinfer/attention.py:106-129: nn.Linear, no bias)."""
-    return x @ weight.t()
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x W^T (+ b) for an [out, in] weight (nn.Linear; the four attention projections carry a bias
+    when ``attention_bias`` is set, ondeviceinfer/attention.py:106-129; no other product has one)."""
+    y = x @ weight.t()
+    return y if bias is None else y + bias
 
 
 def attention_block(x, w, prefix, cfg, cos, sin):
@@ -102,9 +104,9 @@ def attention_block(x, w, prefix, cfg, cos, sin):
     T = x.shape[0]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], head_dim_of(cfg)
     eps = cfg["rms_norm_eps"]
-    q = linear(x, w[prefix + "q_proj.weight"]).view(T, nq, d)
-    k = linear(x, w[prefix + "k_proj.weight"]).view(T, nkv, d)
-    v = linear(x, w[prefix + "v_proj.weight"]).view(T, nkv, d)
+    q = linear(x, w[prefix + "q_proj.weight"], w.get(prefix + "q_proj.bias")).view(T, nq, d)
+    k = linear(x, w[prefix + "k_proj.weight"], w.get(prefix + "k_proj.bias")).view(T, nkv, d)
+    v = linear(x, w[prefix + "v_proj.weight"], w.get(prefix + "v_proj.bias")).view(T, nkv, d)
     q = rms_norm(q, w[prefix + "q_norm.weight"], eps).transpose(0, 1)
     k = rms_norm(k, w[prefix + "k_norm.weight"], eps).transpose(0, 1)
     v = v.transpose(0, 1)
@@ -112,7 +114,7 @@ def attention_block(x, w, prefix, cfg, cos, sin):
     k = apply_rope(k, cos, sin)
     o = causal_gqa_attention(q, k, v)
     o = o.transpose(0, 1).reshape(T, nq * d)
-    return linear(o, w[prefix + "o_proj.weight"])
+    return linear(o, w[prefix + "o_proj.weight"], w.get(prefix + "o_proj.bias"))
 
 
 def swiglu(x, w, prefix):
@@ -240,6 +242,13 @@ TINY_C = {
 }
 
 
+# The same three with a bias on the four attention projections (``attention_bias``,
+# ondeviceinfer/config.py:59 and ondeviceinfer/attention.py:106-129), under seeds of their own.
+TINY_A_BIAS = dict(TINY_A, attention_bias=True)
+TINY_B_BIAS = dict(TINY_B, attention_bias=True)
+TINY_C_BIAS = dict(TINY_C, attention_bias=True)
+
+
 def tensor_shapes(cfg):
     """Checkpoint tensor names and shapes, in file order (module tree of
     ondeviceinfer/model.py:27-38,77-89,137-144)."""
@@ -253,6 +262,11 @@ def tensor_shapes(cfg):
         shapes[p + "self_attn.k_proj.weight"] = (nkv * d, H)
         shapes[p + "self_attn.v_proj.weight"] = (nkv * d, H)
         shapes[p + "self_attn.o_proj.weight"] = (H, nq * d)
+        if cfg.get("attention_bias", False):          # bias=config.attention_bias, ondeviceinfer/attention.py:106-129
+            shapes[p + "self_attn.q_proj.bias"] = (nq * d,)
+            shapes[p + "self_attn.k_proj.bias"] = (nkv * d,)
+            shapes[p + "self_attn.v_proj.bias"] = (nkv * d,)
+            shapes[p + "self_attn.o_proj.bias"] = (H,)
         shapes[p + "self_attn.q_norm.weight"] = (d,)
         shapes[p + "self_attn.k_norm.weight"] = (d,)
         shapes[p + "post_attention_layernorm.weight"] = (H,)
@@ -272,7 +286,7 @@ def random_weights(cfg, seed, std=0.02, norm_std=0.01):
     out = {}
     for name, shape in tensor_shapes(cfg).items():
         t = torch.randn(shape, generator=gen, dtype=torch.float32)
-        t = 1.0 + norm_std * t if len(shape) == 1 else std * t
+        t = 1.0 + norm_std * t if len(shape) == 1 and not name.endswith(".bias") else std * t
         out[name] = t.to(torch.bfloat16)
     return out
 

@@ -35,12 +35,32 @@ def test_other_sizes_are_the_named_ones():
     assert abs(weight_bytes - 63.97e9) < 0.05e9 and kv == 262144
 
 
-def test_more_than_one_gpu_is_refused_and_the_reference_arm_says_why_it_is_absent():
+def test_more_than_one_gpu_is_refused():
     many = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--gpus", "2"], capture_output=True, text=True)
     assert many.returncode == 2 and "one GPU" in many.stdout
-    ref = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference"], capture_output=True, text=True)
-    line = json.loads(ref.stdout.strip().splitlines()[-1])
-    assert ref.returncode == 0 and line["impl"] == "reference" and line["unavailable"]
+
+
+def test_the_reference_arm_imports_a_verbatim_copy_of_the_reference_or_says_why_not(tmp_path):
+    """The reference is plain Python without an installer: its arm runs from a copy of its package folder.
+    Without such a copy and without the checkout the arm is unavailable and says so; with a copy it is found;
+    and the two arms describe one run with the same ``config`` record."""
+    folder, why = bench.reference_package(tmp_path / "nothing_here")
+    if folder is None:
+        assert "cannot be pip-installed" in why
+    else:                                                   # the checkout is on this machine: it was copied
+        assert (folder / "ondeviceinfer" / "model.py").exists() and why is None
+    made = tmp_path / "ref" / "ondeviceinfer"
+    made.mkdir(parents=True)
+    (made / "model.py").write_text("")
+    assert bench.reference_package(tmp_path / "ref") == (tmp_path / "ref", None)
+
+    import argparse
+    args = argparse.Namespace(sizes="8B", prompt_len=2048, prompt_range=None, warmup=5, steps=20, context=None,
+                              layers=None, batch=8, temperature=0.0)
+    cfg, layers, prompt_len, _, context, _, record, metric = bench.plan_run(args, argparse.ArgumentParser())
+    assert (layers, prompt_len, context) == (36, 2048, 4096) and "batch 8" in metric
+    assert record["untimed_steps"] == 32 and record["layers"] == record["layers_of_model"] == 36
+    assert len(record) <= 20 and all(not isinstance(v, (dict, list)) for v in record.values())
 
 
 def test_measured_peaks_are_read_flat_or_one_level_down_and_absent_ones_fall_back(tmp_path, monkeypatch):

@@ -55,7 +55,6 @@ def test_missing_keys_are_named_together():
     ({"hidden_act": "gelu"}, ValueError),
     ({"rope_scaling": {"type": "yarn", "factor": 4}}, ValueError),
     ({"use_sliding_window": True, "sliding_window": 4096}, ValueError),
-    ({"attention_bias": True}, NotImplementedError),
     ({"model_type": "llama"}, ValueError),
     ({"num_hidden_layers": 0}, ValueError),
 ])
@@ -123,3 +122,22 @@ def test_plan_order_is_checked():
     ok = ModelPlan(plan.embedding, plan.layers, (OrderEntry(0), OrderEntry(1), OrderEntry(0), OrderEntry(1, cache_from=1)),
                    plan.final_norm, plan.head)
     ok.validate()
+
+
+def test_attention_bias_gives_the_four_projections_a_bias_each():
+    """ondeviceinfer/attention.py:106-129 builds q, k, v and o projections with bias=config.attention_bias."""
+    from ondeviceinfer_b200.engine.model import DecoderModel
+
+    plain_plan = config_from_dict(RAW_8B).to_plan()
+    biased_plan = config_from_dict(dict(RAW_8B, attention_bias=True)).to_plan()
+    assert not any(plain_plan.layers[0].mixer.has(role) for role in ("q_bias", "k_bias", "v_bias", "o_bias"))
+    mixer = biased_plan.layers[3].mixer
+    assert mixer.name("q_bias") == "model.layers.3.self_attn.q_proj.bias"
+    assert mixer.name("o_bias") == "model.layers.3.self_attn.o_proj.bias"
+    small = dict(RAW_8B, attention_bias=True, num_hidden_layers=1)
+    shapes = {d.name: d.shape for d in DecoderModel(config_from_dict(small).to_plan()).tensor_decls()}
+    assert shapes["model.layers.0.self_attn.q_proj.bias"] == (4096,)
+    assert shapes["model.layers.0.self_attn.k_proj.bias"] == (1024,)
+    assert shapes["model.layers.0.self_attn.v_proj.bias"] == (1024,)
+    assert shapes["model.layers.0.self_attn.o_proj.bias"] == (4096,)
+    assert config_from_dict(small).to_dict()["attention_bias"] is True

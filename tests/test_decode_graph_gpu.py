@@ -1,0 +1,160 @@
+"""The decode path that generation really runs, compared at the level of logits.
+
+``generate()`` does not decode through the generic step function: its one-token steps replay CUDA graphs
+on fixed buffers (``engine/decode.py``): rows of a fixed width with padding rows on a slot outside the
+cache, page tables of fixed stride, key splits bounded by the graph, counters advanced by the sampling
+kernel.  Here given tokens are fed through exactly that path (each step's inputs copied from the host, as
+``generate()`` does) and the logits that each replay leaves are compared, per request and position, with
+the plain implementation: a wrong page-table row, a padding row that leaks, a dropped key split or a
+stale position in one sequence fails these tests, where a comparison of sampled tokens might not.
+"""
+
+import pytest
+import torch
+
+import ondeviceinfer_b200 as odi
+import plain_qwen3 as plain
+from helpers import CASES, assert_logits_close, engine_model, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="session")
+def tmp_root(tmp_path_factory):
+    return tmp_path_factory.mktemp("models")
+
+
+def replay_batches(model, cache, requests, batches, tails, *, drop=False):
+    """Feed ``requests`` (token lists) batch by batch: all but the last ``tails[r]`` tokens of each request in
+    one prompt step, then one token per live request per graph replay; a request that has been fed whole
+    leaves and gives its slot back.  Returns, per request, the logits at positions ``cut - 1 .. len - 1``."""
+    got = {}
+    runner = odi.api.decode_runner(model, cache)
+    for batch in batches:
+        slots = {r: cache.alloc() for r in batch}
+        fed = {r: len(requests[r]) - tails[r] for r in batch}
+        assert all(n >= 1 for n in fed.values())
+        logits = model.step(cache, [slots[r] for r in batch], [requests[r][:fed[r]] for r in batch], "last")
+        for i, r in enumerate(batch):
+            got[r] = [logits[i:i + 1].clone()]
+        live = [r for r in batch]
+        begun = False          # whether the runner's live set is this batch's
+        changed = True
+        while True:
+            done = [i for i, r in enumerate(live) if fed[r] == len(requests[r])]
+            if done:
+                for i in done:
+                    cache.free(slots.pop(live[i]))
+                stay = [r for i, r in enumerate(live) if i not in done]
+                if stay and drop and begun:
+                    runner.drop(done, stay, [fed[r] for r in stay])      # the runner narrows its own live set
+                else:
+                    changed = True
+                live = stay
+            if not live:
+                break
+            feed = [requests[r][fed[r]] for r in live]
+            if changed:
+                runner.begin([slots[r] for r in live], feed, live, [fed[r] for r in live])
+                changed, begun = False, True
+            runner.step(feed)
+            rows = runner.last_logits()
+            assert rows.shape == (len(live), model.vocab_size) and rows.dtype == torch.float32
+            for i, r in enumerate(live):
+                got[r].append(rows[i:i + 1].clone())
+                fed[r] += 1
+        cache.check()
+    return {r: torch.cat(rows) for r, rows in got.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["A", "B", "C", "Cb"])
+def test_graph_replay_logits_of_unequal_batches_that_shrink_and_reuse_slots(case, dtype, tmp_root):
+    """Seven requests in batches of three on a cache of three slots; in each batch the tails are unequal, so the
+    batch narrows (widths 4, 2, 1 with padding rows) while it runs; the second and third batch run in the
+    slots and pages the first gave back."""
+    model, _, cfg = engine_model(case, dtype, tmp_root)
+    lengths = [70, 9, 33, 130, 64, 65, 20]
+    requests = plain.random_prompts(cfg, lengths, CASES[case][1] + 200)
+    tails = {r: min(len(requests[r]) - 1, [3, 8, 5][r % 3]) for r in range(len(requests))}
+    cache = model.make_cache(max_tokens=3 * 192, max_seqs=3)
+    for drop in (False, True):
+        got = replay_batches(model, cache, requests, [[0, 1, 2], [3, 4, 5], [6]], tails, drop=drop)
+        assert cache.slots.held_count == 0
+        for r, tokens in enumerate(requests):
+            expected = plain_logits(case, tokens)[len(tokens) - tails[r] - 1:]
+            assert_logits_close(got[r], expected, dtype, f"{case} request {r} through graph replay (drop={drop})")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case,count", [("B", 40), ("C", 64), ("Cb", 37)])
+def test_graph_replay_logits_at_wide_batches(case, count, dtype, tmp_root):
+    """37, 40 and 64 live sequences: the captured widths 48 and 64 (multiples of 16, with 11 and 8 padding rows
+    or none), whose products go other ways than those of narrow batches; unequal lengths and tails, so the
+    batch also passes through narrower widths while it empties."""
+    model, _, cfg = engine_model(case, dtype, tmp_root)
+    lengths = [2 + (7 * i) % 45 for i in range(count)]
+    requests = plain.random_prompts(cfg, lengths, CASES[case][1] + 300)
+    tails = {r: min(len(requests[r]) - 1, 1 + r % 4) for r in range(count)}
+    cache = model.make_cache(max_tokens=count * 64, max_seqs=count)
+    got = replay_batches(model, cache, requests, [list(range(count))], tails)
+    runner = odi.api.decode_runner(model, cache)
+    assert {key[0] for key in runner._graphs} >= {DecodeRunner_width(count)}
+    for r, tokens in enumerate(requests):
+        expected = plain_logits(case, tokens)[len(tokens) - tails[r] - 1:]
+        assert_logits_close(got[r], expected, dtype, f"{case} request {r} of {count} through graph replay")
+
+
+def DecodeRunner_width(n):
+    from ondeviceinfer_b200.engine.decode import DecodeRunner
+    return DecodeRunner._width_for(n)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_replay_matches_the_step_path_row_by_row(dtype, tmp_root):
+    """The same steps through the generic step function and through graph replay: 32-bit logits are the
+    same bits (the same kernels on the same values; only the launch differs), bfloat16 logits as close as
+    two runs of different kernel forms may be (the replayed width pads the batch, which may choose another
+    token tile)."""
+    model, _, cfg = engine_model("C", dtype, tmp_root)
+    requests = plain.random_prompts(cfg, [100, 3, 64, 190, 31], 401)
+    tails = {r: 6 for r in range(5)}
+    cache = model.make_cache(max_tokens=5 * 256, max_seqs=5)
+    replayed = replay_batches(model, cache, requests, [[0, 1, 2, 3, 4]], tails)
+    slots = [cache.alloc() for _ in requests]
+    stepped = [model.step(cache, slots, [r[:-6] for r in requests], "last")]
+    for t in range(6):
+        stepped.append(model.step(cache, slots, [[r[len(r) - 6 + t]] for r in requests], "last"))
+    for slot in slots:
+        cache.free(slot)
+    for r in range(5):
+        mine = torch.stack([rows[r] for rows in stepped])
+        if dtype == "float32":
+            assert torch.equal(mine, replayed[r]), r
+        else:
+            assert_logits_close(replayed[r], mine, dtype, f"request {r}: replay against stepping")
+
+
+@pytest.mark.parametrize("V,K", [(389, 96), (1000, 4096), (40000, 256), (523, 84)])
+def test_logits_keep_fp32_at_every_number_of_rows(V, K):
+    """The head product returns fp32 from fp32 accumulators whether 1, 64, 65 or 300 rows are wanted (the kernel
+    form changes with the count, the precision does not): a row's logits in a wide batch equal its logits in
+    a narrow one far below bf16's spacing, and they are not bf16 numbers.  K = 84 is a width that the
+    tensor-core kernels refuse."""
+    import math
+
+    from ondeviceinfer_b200.parts.linear import linear
+
+    torch.manual_seed(3)
+    x = torch.randn(300, K).bfloat16().cuda()
+    w = (torch.randn(V, K) / math.sqrt(K)).bfloat16().cuda()
+    exact = x.double().cpu() @ w.double().cpu().t()
+    outs = {n: linear(x[:n], w, out_dtype=torch.float32) for n in (1, 64, 65, 255, 300)}
+    for n, out in outs.items():
+        assert out.dtype == torch.float32 and out.shape == (n, V)
+        assert float((out.double().cpu() - exact[:n]).abs().max()) < 2e-5 * math.sqrt(K), n
+        assert not torch.equal(out.bfloat16().float(), out), f"{n} rows: the logits were rounded to bf16 on the way"
+    assert float((outs[65][:64] - outs[64]).abs().max()) < 1e-4
+    assert float((outs[300][:64] - outs[64]).abs().max()) < 1e-4

@@ -108,9 +108,13 @@ def cpu_graphs(monkeypatch):
     original = DecodeRunner._capture
 
     def capture(self, ctx, bucket):
-        graph, launches = original(self, ctx, bucket)
-        graph.run = lambda: self._run_once(ctx)
-        return graph, launches
+        graph, launches, logits = original(self, ctx, bucket)
+
+        def run():
+            logits.copy_(self._run_once(ctx))      # a replay leaves the step's logits where the capture saw them
+
+        graph.run = run
+        return graph, launches, logits
 
     monkeypatch.setattr(DecodeRunner, "_capture", capture)
 
@@ -143,7 +147,9 @@ def test_runner_follows_the_sequences_through_graphs_captures_and_dropped_rows(c
         tokens, lengths = expect(tokens, lengths), [n + 1 for n in lengths]
         assert runner.ctx.token_ids[:3].tolist() == tokens, step
         assert [cache.lengths[s] for s in slots] == lengths
-        graph, _ = runner._graph_for(4, [n + 1 for n in lengths])
+        # the logits of the replayed step stay readable: the token each live row chose is their argmax
+        assert runner.last_logits().shape == (3, VOCAB) and runner.last_logits().argmax(-1).tolist() == tokens
+        graph, _, _ = runner._graph_for(4, [n + 1 for n in lengths])
         per = runner.ctx._key_splits[BLOCK_ROWS][1]
         assert math.ceil(max(-(-(n + 1) // 64) for n in lengths) / per) <= graph.bound
     assert any(key[1] == 512 for key in runner._graphs) and first_keys < set(runner._graphs)

@@ -12,6 +12,8 @@ pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 # request lengths: one token, a page minus / exactly / plus one, several pages, odd sizes
 LENGTHS = {"A": [5, 11, 17, 64, 33, 100], "B": [1, 7, 30, 64, 65, 130, 63, 2], "C": [3, 200, 77, 129, 64, 31]}
+LENGTHS.update({"Ab": LENGTHS["A"], "Bb": LENGTHS["B"], "Cb": LENGTHS["C"]})      # the same with projection biases
+ALL_CASES = ["A", "B", "C", "Ab", "Bb", "Cb"]
 
 
 @pytest.fixture(scope="session")
@@ -25,7 +27,7 @@ def requests_of(case):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ALL_CASES)
 def test_each_request_alone_and_whole(case, dtype, tmp_root):
     model, _, _ = engine_model(case, dtype, tmp_root)
     cache = model.make_cache(max_tokens=256, max_seqs=1)
@@ -40,7 +42,7 @@ def test_each_request_alone_and_whole(case, dtype, tmp_root):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ALL_CASES)
 def test_last_32_tokens_one_by_one(case, dtype, tmp_root):
     model, _, _ = engine_model(case, dtype, tmp_root)
     cache = model.make_cache(max_tokens=256, max_seqs=1)
@@ -56,7 +58,7 @@ def test_last_32_tokens_one_by_one(case, dtype, tmp_root):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ALL_CASES)
 def test_batches_of_unequal_lengths_reuse_slots(case, dtype, tmp_root):
     """Batches of three requests on a cache with three slots, one batch after another: the
     prompts (all but the last d_i tokens, d_i unequal) in one step, then one token per live

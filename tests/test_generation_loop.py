@@ -58,6 +58,7 @@ def test_unequal_prompts_shrinking_batch_and_stop_token_kept():
     assert script.steps[1][1] == [[10], [20], [30]]
     assert script.steps[2][1] == [[11], [30 + 1]] and len(script.steps[2][0]) == 2
     assert len(script.steps) == 4 and result.decode_steps == 3
+    assert len(result.step_seconds) == 3 and all(t >= 0 for t in result.step_seconds)
     assert result.decode_tokens == 3 + 1 + 3
 
 
@@ -138,7 +139,9 @@ def test_fused_decoder_is_told_when_the_live_set_changes():
             self.live = list(requests)
             self.position = dict(zip(requests, steps))
 
-        def step(self):
+        def step(self, last_tokens):
+            # the loop feeds each live sequence's last token from its own record
+            assert last_tokens == [scripts[r][self.position[r] - 1] for r in self.live]
             out = [scripts[r][self.position[r]] for r in self.live]
             for r in self.live:
                 self.position[r] += 1

@@ -305,6 +305,11 @@ def test_gemm_f32_is_true_fp32_and_row_independent(M, N, K):
     r = res.clone().to(DEV)
     ops.gemm_f32(a.to(DEV), w.to(DEV), r, r)
     assert torch.allclose(r.cpu(), res + out.cpu(), atol=1e-6, rtol=1e-6)
+    # a bias joins the product before the residual
+    bias = torch.randn(N)
+    r = res.clone().to(DEV)
+    ops.gemm_f32(a.to(DEV), w.to(DEV), r, r, bias=bias.to(DEV))
+    assert torch.equal(r.cpu(), (out.cpu() + bias) + res)
 
 
 def test_sample_greedy_ties_and_temperature_against_plain():
@@ -388,11 +393,13 @@ GEMM_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("biased", [False, True])
 @pytest.mark.parametrize("epi", ["store_bf16", "store_f32", "residual", "swiglu"])
 @pytest.mark.parametrize("tokens,N,K,tile,splits", GEMM_SHAPES)
-def test_gemm_tcgen05(tokens, N, K, tile, splits, epi):
+def test_gemm_tcgen05(tokens, N, K, tile, splits, epi, biased):
     """The tensor-core product and its four epilogues against fp32 torch on the same bf16
-    inputs: every tile width, K splits, several token tiles, ragged edges in all three sizes."""
+    inputs: every tile width, K splits, several token tiles, ragged edges in all three sizes;
+    with and without a bias per weight row."""
     code = {"store_bf16": ops.EPI_STORE_BF16, "store_f32": ops.EPI_STORE_F32, "residual": ops.EPI_RESIDUAL,
             "swiglu": ops.EPI_SWIGLU}[epi]
     if epi == "swiglu" and tile == 256:
@@ -401,7 +408,10 @@ def test_gemm_tcgen05(tokens, N, K, tile, splits, epi):
     x = torch.randn(tokens, K).bfloat16().to(DEV)
     rows = 2 * N if epi == "swiglu" else N
     w = (torch.randn(rows, K) / math.sqrt(K)).bfloat16().to(DEV)
+    bias = torch.randn(rows).to(DEV) if biased else None
     ref = (x.float() @ w.float().t()).cpu()
+    if biased:
+        ref = ref + bias.cpu()
     if epi == "store_bf16":
         out, expected = torch.empty(tokens, N, dtype=torch.bfloat16, device=DEV), ref
     elif epi == "store_f32":
@@ -412,13 +422,13 @@ def test_gemm_tcgen05(tokens, N, K, tile, splits, epi):
     else:
         out = torch.empty(tokens, N, dtype=torch.bfloat16, device=DEV)
         expected = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
-    ops.gemm_bf16(x, w, out, code, bn=tile, splits=splits)
+    ops.gemm_bf16(x, w, out, code, bn=tile, splits=splits, bias=bias)
     torch.cuda.synchronize()
     ops.raise_on_kernel_fault()
     if epi == "store_f32":
         # K splits through a cluster and through global scratch add in the same order: same bits
         other = torch.empty_like(out)
-        ops.gemm_bf16(x, w, other, code, bn=tile, splits=splits, cluster=False)
+        ops.gemm_bf16(x, w, other, code, bn=tile, splits=splits, cluster=False, bias=bias)
         assert torch.equal(other, out)
     if out.dtype == torch.bfloat16:
         close(out, expected, "bfloat16")
@@ -427,7 +437,7 @@ def test_gemm_tcgen05(tokens, N, K, tile, splits, epi):
     # launched again, the split tickets must have been left at zero
     if epi == "store_f32":
         again = torch.empty_like(out)
-        ops.gemm_bf16(x, w, again, code, bn=tile, splits=splits)
+        ops.gemm_bf16(x, w, again, code, bn=tile, splits=splits, bias=bias)
         assert torch.equal(again, out)
 
 
@@ -486,16 +496,16 @@ def test_gemm_tcgen05_norm_prologue_and_sums_of_squares(tokens, H, N, tile, spli
     close(fused, expected, "bfloat16")
 
 
-@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,lazy,ring", [
-    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, True, 0),     # a decode step, a cluster per head
-    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, False, 0),
-    ([3, 1, 16], [0, 200, 10], 256, 4, 2, True, True, False, 0),                          # a short K: one split, 32 columns
-    ([3, 1, 16], [0, 200, 10], 256, 4, 2, False, False, True, 0),                         # neither norm nor rotation
-    ([1, 1, 1], [70, 2, 900], 1024, 6, 3, True, False, True, 0),
-    ([5, 6], [0, 64], 2048, 2, 1, False, True, False, 0),
-    ([1, 1, 2], [500, 130, 62], 512, 4, 2, True, True, True, 2),                          # a ring of two pages per sequence
+@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,lazy,ring,biased", [
+    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, True, 0, False),     # a decode step, a cluster per head
+    ([1] * 8, [300, 64, 63, 1000, 0, 5, 127, 128], 4096, 32, 8, True, True, False, 0, True),
+    ([3, 1, 16], [0, 200, 10], 256, 4, 2, True, True, False, 0, False),                          # a short K: one split, 32 columns
+    ([3, 1, 16], [0, 200, 10], 256, 4, 2, False, False, True, 0, True),                          # neither norm nor rotation
+    ([1, 1, 1], [70, 2, 900], 1024, 6, 3, True, False, True, 0, True),
+    ([5, 6], [0, 64], 2048, 2, 1, False, True, False, 0, False),
+    ([1, 1, 2], [500, 130, 62], 512, 4, 2, True, True, True, 2, False),                          # a ring of two pages per sequence
 ])
-def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, lazy, ring):
+def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, lazy, ring, biased):
     """The q/k/v product with the head preparation in its epilogue against the product followed by the
     head-preparation kernel: the same bits in the queries and in the cache, nothing written elsewhere."""
     torch.manual_seed(23)
@@ -522,11 +532,15 @@ def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, 
     common = dict(nq=nq, nkv=nkv, d=d, rot_dim=d if rot else 0, page_size=64, ring_pages=ring, write_kv=True, eps=1e-5)
     tail = (qw, kw, cos, sin, setup["tok_seq"], setup["tok_pos"], setup["page_start"], setup["page_ids"])
 
+    bias = torch.randn(w.shape[0]).to(DEV) if biased else None
     qkv = torch.empty(n, w.shape[0], dtype=torch.bfloat16, device=DEV)
     if lazy:
-        ops.gemm_bf16(None, w, qkv, ops.EPI_STORE_BF16, norm=(rows, g, parts, 1e-6))
+        ops.gemm_bf16(None, w, qkv, ops.EPI_STORE_BF16, norm=(rows, g, parts, 1e-6), bias=bias)
     else:
-        ops.gemm_bf16(x, w, qkv, ops.EPI_STORE_BF16)
+        ops.gemm_bf16(x, w, qkv, ops.EPI_STORE_BF16, bias=bias)
+    if biased:      # the bias is in the projections that the two forms share
+        plain_qkv = x.float() @ w.float().t() + bias
+        assert float((qkv.float() - plain_qkv).abs().max()) <= 0.02 * float(plain_qkv.abs().max())
     q_two = torch.zeros(n, nq * d, dtype=torch.bfloat16, device=DEV)
     k_two, v_two = torch.zeros_like(setup["k_pool"]), torch.zeros_like(setup["v_pool"])
     ops.head_prep(qkv, q_two, k_two, v_two, *tail, **common)
@@ -536,7 +550,7 @@ def test_gemm_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, 
     k_one, v_one = torch.zeros_like(k_two), torch.zeros_like(v_two)
     block = ops.head_prep(None, q_one, k_one, v_one, *tail, **common)
     ops.gemm_bf16(None if lazy else x, w, None, ops.EPI_HEAD_PREP, head_prep=block,
-                  norm=(rows, g, parts, 1e-6) if lazy else None)
+                  norm=(rows, g, parts, 1e-6) if lazy else None, bias=bias)
     torch.cuda.synchronize()
     ops.raise_on_kernel_fault()
     assert float(q_two.float().abs().sum()) > 0 and float(k_two.float().abs().sum()) > 0
@@ -759,20 +773,36 @@ PREFILL_GEMM_SHAPES = [
     (128, 256, 64), (2048, 4096, 4096), (300, 520, 200), (33, 1000, 1000), (1030, 1024, 512), (130, 6144, 72),
     (5000, 389, 96), (4500, 776, 136),
 ]
+# the shapes of a 2,048-token prefill at Qwen3-8B and Qwen3-14B layer sizes: the down projection's long K with
+# the reduce-add epilogue, the gate/up product's 2 x 12,288 features, a ragged token count at the long K
+PREFILL_GEMM_MODEL_SHAPES = [
+    (2048, 4096, 12288, "residual", False), (2048, 4096, 12288, "store_bf16", True),
+    (2048, 12288, 4096, "swiglu", False), (2048, 5120, 17408, "residual", True),
+    (1900, 4096, 12288, "residual", False), (2100, 6144, 4096, "store_bf16", True),
+]
 
 
+@pytest.mark.parametrize("tokens,N,K,epi,biased", PREFILL_GEMM_MODEL_SHAPES)
+def test_gemm_prefill_tcgen05_at_model_sizes(tokens, N, K, epi, biased):
+    test_gemm_prefill_tcgen05(tokens, N, K, epi, biased)
+
+
+@pytest.mark.parametrize("biased", [False, True])
 @pytest.mark.parametrize("epi", ["store_bf16", "store_f32", "residual", "swiglu"])
 @pytest.mark.parametrize("tokens,N,K", PREFILL_GEMM_SHAPES)
-def test_gemm_prefill_tcgen05(tokens, N, K, epi):
+def test_gemm_prefill_tcgen05(tokens, N, K, epi, biased):
     """The persistent product for many tokens and its four epilogues against fp32 torch on the same
-    bf16 inputs; twice, so that a second launch finds the same result."""
+    bf16 inputs; twice, so that a second launch finds the same result; with and without a bias."""
     code = {"store_bf16": ops.EPI_STORE_BF16, "store_f32": ops.EPI_STORE_F32, "residual": ops.EPI_RESIDUAL,
             "swiglu": ops.EPI_SWIGLU}[epi]
     torch.manual_seed(31)
     x = torch.randn(tokens, K).bfloat16().to(DEV)
     rows = 2 * N if epi == "swiglu" else N
     w = (torch.randn(rows, K) / math.sqrt(K)).bfloat16().to(DEV)
+    bias = torch.randn(rows).to(DEV) if biased else None
     ref = (x.float() @ w.float().t()).cpu()
+    if biased:
+        ref = ref + bias.cpu()
     res = torch.randn(tokens, N)
     for _ in range(2):
         if epi == "store_bf16":
@@ -786,9 +816,9 @@ def test_gemm_prefill_tcgen05(tokens, N, K, epi):
             expected = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
         if not ops.gemm_prefill_supported(x, w, N, out.dtype):
             with pytest.raises(ops.KernelError):        # rows of the output that do not start on 16 bytes are refused
-                ops.gemm_prefill_bf16(x, w, out, code)
+                ops.gemm_prefill_bf16(x, w, out, code, bias=bias)
             return
-        ops.gemm_prefill_bf16(x, w, out, code)
+        ops.gemm_prefill_bf16(x, w, out, code, bias=bias)
         torch.cuda.synchronize()
         ops.raise_on_kernel_fault()
         if out.dtype == torch.bfloat16:
@@ -797,13 +827,14 @@ def test_gemm_prefill_tcgen05(tokens, N, K, epi):
             assert torch.allclose(out.cpu(), expected, atol=1e-4, rtol=1e-4), float((out.cpu() - expected).abs().max())
 
 
-@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,ring", [
-    ([300, 17, 2000], [0, 50, 0], 512, 4, 2, True, True, 0),          # unequal prompts, ragged token tiles
-    ([700], [100], 1024, 6, 3, False, True, 0),                       # no norm
-    ([256, 256], [0, 0], 256, 2, 1, True, False, 0),                  # no rotation, whole tiles
-    ([130, 100], [400, 60], 768, 3, 1, True, True, 3),                # an odd number of heads, rings of three pages (no step wraps its ring)
+@pytest.mark.parametrize("lengths,past,K,nq,nkv,norm,rot,ring,biased", [
+    ([300, 17, 2000], [0, 50, 0], 512, 4, 2, True, True, 0, False),          # unequal prompts, ragged token tiles
+    ([300, 17, 2000], [0, 50, 0], 512, 4, 2, True, True, 0, True),
+    ([700], [100], 1024, 6, 3, False, True, 0, True),                        # no norm
+    ([256, 256], [0, 0], 256, 2, 1, True, False, 0, False),                  # no rotation, whole tiles
+    ([130, 100], [400, 60], 768, 3, 1, True, True, 3, False),                # an odd number of heads, rings of three pages (no step wraps its ring)
 ])
-def test_gemm_prefill_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, ring):
+def test_gemm_prefill_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, nq, nkv, norm, rot, ring, biased):
     """The q/k/v product of many tokens with the head preparation in its epilogue against the product followed
     by the head-preparation kernel: close (the two add the squares of a head in different orders), and nothing
     written elsewhere in the cache."""
@@ -823,15 +854,19 @@ def test_gemm_prefill_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, n
         ops.rope_table(inv_freq.to(DEV), setup["tok_pos"], cos, sin)
     common = dict(nq=nq, nkv=nkv, d=d, rot_dim=d if rot else 0, page_size=64, ring_pages=ring, write_kv=True, eps=1e-5)
     tail = (qw, kw, cos, sin, setup["tok_seq"], setup["tok_pos"], setup["page_start"], setup["page_ids"])
+    bias = torch.randn(w.shape[0]).to(DEV) if biased else None
     qkv = torch.empty(n, w.shape[0], dtype=torch.bfloat16, device=DEV)
-    ops.gemm_prefill_bf16(x, w, qkv, ops.EPI_STORE_BF16)
+    ops.gemm_prefill_bf16(x, w, qkv, ops.EPI_STORE_BF16, bias=bias)
+    if biased:
+        plain_qkv = x.float() @ w.float().t() + bias
+        assert float((qkv.float() - plain_qkv).abs().max()) <= 0.02 * float(plain_qkv.abs().max())
     q_two = torch.zeros(n, nq * d, dtype=torch.bfloat16, device=DEV)
     k_two, v_two = torch.zeros_like(setup["k_pool"]), torch.zeros_like(setup["v_pool"])
     ops.head_prep(qkv, q_two, k_two, v_two, *tail, **common)
     q_one = torch.zeros_like(q_two)
     k_one, v_one = torch.zeros_like(k_two), torch.zeros_like(v_two)
     block = ops.head_prep(None, q_one, k_one, v_one, *tail, **common)
-    ops.gemm_prefill_bf16(x, w, None, ops.EPI_HEAD_PREP, head_prep=block)
+    ops.gemm_prefill_bf16(x, w, None, ops.EPI_HEAD_PREP, head_prep=block, bias=bias)
     torch.cuda.synchronize()
     ops.raise_on_kernel_fault()
     assert torch.equal(v_one, v_two)

@@ -13,7 +13,8 @@ import plain_qwen3 as plain
 GOLDEN = Path(__file__).parent / "golden"
 
 
-@pytest.mark.parametrize("name,cfg,seed", [("tiny_a", plain.TINY_A, 0), ("tiny_b", plain.TINY_B, 1)])
+@pytest.mark.parametrize("name,cfg,seed", [("tiny_a", plain.TINY_A, 0), ("tiny_b", plain.TINY_B, 1),
+                                           ("tiny_a_bias", plain.TINY_A_BIAS, 10)])
 def test_plain_matches_reference_outputs(name, cfg, seed):
     data = np.load(GOLDEN / f"{name}.npz")
     weights = plain.random_weights(cfg, seed)

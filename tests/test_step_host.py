@@ -111,3 +111,66 @@ def test_a_kernel_that_gave_up_waiting_is_reported_once_by_name():
     finally:
         ops._gemm_state.clear()
         ops._gemm_state.update(saved)
+
+
+def test_the_two_step_contexts_give_a_part_the_same_names():
+    """A part reads a step through StepDescription.INTERFACE.  The context of the generic step and the
+    fixed-buffer context of graph replay both give every one of those names, the generic one gives a part
+    nothing else, and what the replay context has beyond them is the runner's own (REPLAY_ONLY): so a part
+    written and tested under one cannot break only under the other."""
+    from ondeviceinfer_b200.engine.decode import _DecodeContext
+    from ondeviceinfer_b200.engine.step import StepDescription
+
+    cache = make_cache()
+    a, b = cache.alloc(), cache.alloc()
+    cache.reserve([a, b], [3, 1])
+    generic = StepContext(cache, [a, b], [[1, 2, 3], [4]], [2, 3], "cpu")
+    replay = _DecodeContext(cache, 2, cache.n_pages, "cpu", 256)
+    public = lambda obj: {name for name in dir(obj) if not name.startswith("_") and name != "INTERFACE"}
+    interface = set(StepDescription.INTERFACE)
+    assert interface <= public(generic) and interface <= public(replay) | {"slot_list"}
+    assert public(generic) == interface
+    assert public(replay) - interface == set(_DecodeContext.REPLAY_ONLY) | {"REPLAY_ONLY"}
+    # the mirrors agree in kind: lists of ints per sequence, counts as ints
+    for ctx in (generic, replay):
+        assert len(ctx.q_lens) == len(ctx.past_lens) == len(ctx.kv_lens) == ctx.n_seqs
+        assert [p + q for p, q in zip(ctx.past_lens, ctx.q_lens)] == list(ctx.kv_lens)
+        start, ids = ctx.page_table(1)
+        assert start.dtype == ids.dtype == torch.int32 and start.numel() == ctx.n_seqs + 1
+        assert ctx.memo("k", lambda: 7) == 7 and ctx.memo("k", lambda: 8) == 7
+        assert ctx.residual_sumsq is None
+
+
+def test_generation_stops_with_an_error_when_a_kernel_gave_up_waiting():
+    """The generation loop synchronises around the prompts' step and at a batch's end; the entry point's
+    synchronise also reads the kernels' error word there.  With the word set by hand during a step the loop
+    raises (and gives its slots back) instead of returning tokens computed from an invalid result."""
+    from ondeviceinfer_b200.engine.generate import generate_requests
+    from ondeviceinfer_b200.kernels import ops
+
+    saved = dict(ops._gemm_state)
+    held, steps = set(), []
+
+    def alloc():
+        slot = len(held)
+        held.add(slot)
+        return slot
+
+    def step(slots, runs):
+        steps.append(len(steps))
+        if len(steps) == 3:                              # a kernel of the third step gives up on a barrier
+            ops._gemm_state["test-device"]["status"][0] = 2
+        return None
+
+    try:
+        ops._gemm_state.clear()
+        ops._gemm_state["test-device"] = {"status": torch.zeros(4, dtype=torch.int32)}
+        with pytest.raises(ops.KernelError, match="gave up waiting"):
+            generate_requests([[1, 2], [3]], max_new_tokens=6, alloc=alloc, free=held.remove, step=step,
+                              sample=lambda logits, requests, numbers: [5] * len(requests), batches=[[0, 1]],
+                              synchronize=ops.raise_on_kernel_fault)
+        assert not held and len(steps) == 6              # the batch ran to its end, then the check refused it
+        assert ops.gemm_status() == 0                    # reported once
+    finally:
+        ops._gemm_state.clear()
+        ops._gemm_state.update(saved)
