@@ -555,6 +555,14 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, 
 
 extern "C" int odi_attention_mma_head_dim() { return D; }
 
+// Dynamic shared memory of the decode kernel: the ring of K/V stages, or, if larger, the four warps'
+// partials plus the block's merged one.  Every launcher of the kernel takes it from here.
+static inline int decode_smem_bytes() {
+  const int ring = DC_STAGES * 2 * TILE_BYTES;
+  const int merge = (DC_WARPS + 1) * 16 * (D + 2) * 4;
+  return ring > merge ? ring : merge;
+}
+
 // decode != 0 requires q_len == 1 for every sequence (max_q_len == 1).
 extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_tokens, int decode,
                                  cudaStream_t stream) {
@@ -564,8 +572,7 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   const int g = a.nq / a.nkv;
   static bool configured = false;
   const int pf_smem = PF_STAGES * 2 * TILE_BYTES;
-  const int dc_merge = (DC_WARPS + 1) * 16 * (D + 2) * 4;    // the four warps' partials and the block's merged one
-  const int dc_smem = DC_STAGES * 2 * TILE_BYTES > dc_merge ? DC_STAGES * 2 * TILE_BYTES : dc_merge;
+  const int dc_smem = decode_smem_bytes();
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem);
     if (e == cudaSuccess)
@@ -621,13 +628,18 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
 // the fixed array below instead of a caller-provided buffer.
 #include <stdio.h>
 
+#include <atomic>
+
 #include "attention_noalloc.h"
 
 static __device__ __align__(256) float odi_noalloc_scratch[ODI_NOALLOC_SCRATCH_FLOATS];
 
 #define ODI_NOALLOC_MAX_DEVICES 64
-static float* noalloc_scratch_address[ODI_NOALLOC_MAX_DEVICES];   // device addresses, looked up once per device
-static bool noalloc_configured[ODI_NOALLOC_MAX_DEVICES];
+// Device address of the array on each device; null until that device's set-up has completed.  Threads may make
+// their first calls side by side: whoever finishes the set-up publishes the address with release order, a
+// reader that sees it (acquire) also sees the set-up done; two threads that both find null both do the
+// set-up, which gives the same address and sets the same attribute.
+static std::atomic<float*> noalloc_scratch_address[ODI_NOALLOC_MAX_DEVICES];
 static thread_local char noalloc_error_text[256] = "";
 
 extern "C" long odi_attention_decode_noalloc_need(int n_tokens, int nq, int splits) {
@@ -640,8 +652,18 @@ extern "C" const char* odi_attention_decode_noalloc_error() { return noalloc_err
 
 extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_tokens, cudaStream_t stream) {
   noalloc_error_text[0] = 0;
+  if (args == nullptr) {
+    snprintf(noalloc_error_text, sizeof(noalloc_error_text), "args is null");
+    return ODI_ERR_ARGUMENT;
+  }
   MmaAttnArgs a = *args;
   if (a.n_seqs <= 0 || n_tokens <= 0) return 0;
+  if (a.q == nullptr || a.k_pool == nullptr || a.v_pool == nullptr || a.out == nullptr || a.cu_q == nullptr ||
+      a.past == nullptr || a.page_start == nullptr || a.page_ids == nullptr) {
+    snprintf(noalloc_error_text, sizeof(noalloc_error_text),
+             "q, k_pool, v_pool, out, cu_q, past, page_start and page_ids must all be device pointers, one is null");
+    return ODI_ERR_ARGUMENT;
+  }
   if (a.nq % a.nkv != 0 || a.n_seqs > 65535 || a.splits < 1 || n_tokens != a.n_seqs) {
     snprintf(noalloc_error_text, sizeof(noalloc_error_text),
              "decode attention needs one token per sequence (n_tokens=%d, n_seqs=%d), nq a multiple of nkv, splits >= 1",
@@ -660,12 +682,11 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
   if (device < 0 || device >= ODI_NOALLOC_MAX_DEVICES) return ODI_ERR_UNSUPPORTED;
-  const int dc_merge = DC_WARPS * 16 * (D + 2) * 4;
-  const int dc_smem = DC_STAGES * 2 * TILE_BYTES > dc_merge ? DC_STAGES * 2 * TILE_BYTES : dc_merge;
-  if (!noalloc_configured[device]) {
+  const int dc_smem = decode_smem_bytes();
+  float* address = noalloc_scratch_address[device].load(std::memory_order_acquire);
+  if (address == nullptr) {
     // Set-up, once per device with that device current: the array's name is a host-side
     // handle; the address a kernel can use comes from cudaGetSymbolAddress.
-    float* address = nullptr;
     e = cudaGetSymbolAddress((void**)&address, odi_noalloc_scratch);
     if (e != cudaSuccess || address == nullptr) {
       snprintf(noalloc_error_text, sizeof(noalloc_error_text), "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
@@ -673,10 +694,9 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
     }
     e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dc_smem);
     if (e != cudaSuccess) return (int)e;
-    noalloc_scratch_address[device] = address;
-    noalloc_configured[device] = true;
+    noalloc_scratch_address[device].store(address, std::memory_order_release);
   }
-  a.partial = noalloc_scratch_address[device];
+  a.partial = address;
   a.clustered = 0;      // this entry point is the global-partial form
   a.tickets = nullptr;  // ... with the combine kernel
   a.tiles_per_split = nullptr;   // ... and every sequence cut into `splits` equal ranges

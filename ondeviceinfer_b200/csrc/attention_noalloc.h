@@ -33,6 +33,12 @@
 //    by that same call first, so stale contents are never seen.  Two calls whose kernels may
 //    overlap on the GPU (different streams without an ordering between them) race on the
 //    array; order them, or use odi_attention_mma with separate buffers.
+//  * Threads: the entry point may be called from several host threads.  The per-device set-up is published
+//    atomically, so first calls that run side by side are safe (each may do the look-up; they agree), and
+//    the refusal text is kept per thread.  What threads cannot share without ordering is the array itself:
+//    the rule above on overlapping kernels holds whichever threads launched them.
+//  * A null args, or a null q, k_pool, v_pool, out, cu_q, past, page_start or page_ids, is refused with
+//    ODI_ERR_ARGUMENT and a message; nothing is launched.
 //  * The entry point calls no cudaMalloc, cudaFree or any other allocating routine.
 #pragma once
 

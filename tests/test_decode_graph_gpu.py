@@ -119,7 +119,7 @@ def test_graph_replay_matches_the_step_path_row_by_row(dtype, tmp_root):
     two runs of different kernel forms may be (the replayed width pads the batch, which may choose another
     token tile)."""
     model, _, cfg = engine_model("C", dtype, tmp_root)
-    requests = plain.random_prompts(cfg, [100, 3, 64, 190, 31], 401)
+    requests = plain.random_prompts(cfg, [100, 7, 64, 190, 31], 401)
     tails = {r: 6 for r in range(5)}
     cache = model.make_cache(max_tokens=5 * 256, max_seqs=5)
     replayed = replay_batches(model, cache, requests, [[0, 1, 2, 3, 4]], tails)
@@ -158,3 +158,101 @@ def test_logits_keep_fp32_at_every_number_of_rows(V, K):
         assert not torch.equal(out.bfloat16().float(), out), f"{n} rows: the logits were rounded to bf16 on the way"
     assert float((outs[65][:64] - outs[64]).abs().max()) < 1e-4
     assert float((outs[300][:64] - outs[64]).abs().max()) < 1e-4
+
+
+# ----------------------------------------------------------------------------- a windowed model under graph replay
+#
+# Graph replay is only exercised by the Qwen3 plan's full attention otherwise.  This plan, defined here and made of
+# the library's graph-safe parts only, has a windowed attention layer beside a full one: under replay its
+# CUDA-core decode kernel runs with ring page tables, splits fixed from the graph's length bucket, padding rows
+# on the pad slot, and captures in the middle of a batch.
+
+WINDOW = 40
+WINDOWED = {"architectures": ["WindowedForCausalLM"], "vocab_size": 173, "hidden_size": 64, "eps": 1e-5}
+
+
+class WindowedConfig:
+    def __init__(self, raw):
+        self.raw = dict(raw)
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw)
+
+    def to_dict(self):
+        return dict(self.raw)
+
+    def to_plan(self):
+        from ondeviceinfer_b200.config import (AttentionSpec, EmbeddingSpec, GatedMLPSpec, HeadSpec, ModelPlan, OrderEntry,
+                                               PreNormBlockSpec, RMSNormSpec, RotarySpec, names)
+        H, V, eps = self.raw["hidden_size"], self.raw["vocab_size"], self.raw["eps"]
+
+        def block(i, window, nq, nkv, d):
+            attention = AttentionSpec(H, nq, nkv, d, RotarySpec(d, 3000.0), f"l{i}.attn.",
+                                      names(q="q", k="k", v="v", o="o", q_norm="qn", k_norm="kn"),
+                                      qk_norm_eps=eps, window=window)
+            return PreNormBlockSpec(RMSNormSpec(H, eps, f"l{i}.n1"), attention, RMSNormSpec(H, eps, f"l{i}.n2"),
+                                    GatedMLPSpec(H, 2 * H, "silu", f"l{i}.ff.", names(gate="g", up="u", down="d")))
+
+        layers = (block(0, None, 4, 2, 16), block(1, WINDOW, 2, 1, 32))
+        return ModelPlan(EmbeddingSpec(V, H, "emb"), layers, (OrderEntry(0), OrderEntry(1)), RMSNormSpec(H, eps, "nf"),
+                         HeadSpec(V, H, None))
+
+
+def windowed_plain_logits(w, ids):
+    import math
+    H, eps, T = WINDOWED["hidden_size"], WINDOWED["eps"], len(ids)
+    h = w["emb"][torch.tensor(ids)]
+    pos = torch.arange(T)
+    for i, (window, nq, nkv, d) in enumerate(((None, 4, 2, 16), (WINDOW, 2, 1, 32))):
+        p = f"l{i}.attn."
+        x = plain.rms_norm(h, w[f"l{i}.n1"], eps)
+        q = plain.rms_norm(plain.linear(x, w[p + "q"]).view(T, nq, d), w[p + "qn"], eps).transpose(0, 1)
+        k = plain.rms_norm(plain.linear(x, w[p + "k"]).view(T, nkv, d), w[p + "kn"], eps).transpose(0, 1)
+        v = plain.linear(x, w[p + "v"]).view(T, nkv, d).transpose(0, 1)
+        cos, sin = plain.rope_tables(pos, d, 3000.0, torch.float32)
+        q, k = plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin)
+        g = nq // nkv
+        scores = q @ k.repeat_interleave(g, 0).transpose(-1, -2) / math.sqrt(d)
+        visible = pos[None, :] <= pos[:, None]
+        if window:
+            visible = visible & (pos[None, :] > pos[:, None] - window)
+        o = torch.softmax(scores.masked_fill(~visible, float("-inf")), -1) @ v.repeat_interleave(g, 0)
+        h = h + plain.linear(o.transpose(0, 1).reshape(T, -1), w[p + "o"])
+        m = plain.rms_norm(h, w[f"l{i}.n2"], eps)
+        h = h + plain.linear(torch.nn.functional.silu(plain.linear(m, w[f"l{i}.ff.g"])) * plain.linear(m, w[f"l{i}.ff.u"]),
+                             w[f"l{i}.ff.d"])
+    return plain.linear(plain.rms_norm(h, w["nf"], eps), w["emb"])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_replay_of_a_windowed_layer_past_the_rings_wrap_and_across_a_bucket(dtype, tmp_path):
+    from ondeviceinfer_b200 import load_resident_model, register_architecture, write_random_model
+    from ondeviceinfer_b200.weights import SafetensorsSource
+
+    register_architecture("WindowedForCausalLM", WindowedConfig)
+    folder = write_random_model(tmp_path / "windowed", WINDOWED, seed=6)
+    source = SafetensorsSource(folder)
+    weights = {n: source.fetch(n).float() for n in source.stored()}
+    model = load_resident_model(folder, dtype=dtype)
+    assert model.decoder.graph_safe
+    gen = torch.Generator().manual_seed(10)
+    # request 0 decodes positions 380 .. 419 (its ring of 6 pages wraps at 384), request 1 decodes 240 .. 269 alone
+    # (the longest sequence passes 256 in the middle of the batch: another graph is captured), request 2 is short
+    lengths, tails = [420, 270, 100], {0: 40, 1: 30, 2: 10}
+    requests = [torch.randint(0, WINDOWED["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
+    cache = model.make_cache(max_tokens=2 * 448, max_seqs=2)
+    windowed = next(g for g in cache.kv_groups if g.need.window == WINDOW)
+    assert windowed.ring_pages == 6
+    got = replay_batches(model, cache, requests, [[0, 2], [1]], tails)
+    runner = odi.api.decode_runner(model, cache)
+    assert {key[1] for key in runner._graphs} >= {256, 512}, "the batch of request 1 should have crossed a length bucket"
+    for r, tokens in enumerate(requests):
+        expected = windowed_plain_logits(weights, tokens)[len(tokens) - tails[r] - 1:]
+        assert_logits_close(got[r], expected, dtype, f"windowed request {r} through graph replay")
+    # and the same tokens from generate() with and without graphs
+    prompts = [r[:-8] for r in requests[:2]]
+    with_graphs = odi.generate(model, prompts, max_new_tokens=12, use_graphs=True)
+    without = odi.generate(model, prompts, max_new_tokens=12, use_graphs=False)
+    if dtype == "float32":
+        assert with_graphs.generated_ids == without.generated_ids

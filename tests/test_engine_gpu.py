@@ -302,3 +302,40 @@ def test_long_prompt_through_the_many_token_kernels(dtype, tmp_path):
     assert_logits_close(torch.cat(rows), expected[picks + list(range(2090, 2100))], dtype, "long prompt", longest_sum=2048)
     cache.free(slot)
     cache.check()
+
+
+# One layer with the sizes of Qwen3-8B (a small vocabulary keeps the plain implementation affordable) and a
+# prompt of 2,100 tokens: every projection goes through the many-token tensor-core kernel at the shapes the
+# prefill benchmark stands on (q/k/v 6,144 x 4,096 with the head preparation, output projection, gate/up
+# 2 x 12,288 x 4,096 with the SiLU gate, down 4,096 x 12,288 with the reduce-add), attention through the
+# tcgen05 kernel at 32 query and 8 key/value heads.
+LARGE_PREFILL = dict(LARGE, vocab_size=1000)
+_LARGE_PREFILL_EXPECTED = {}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompt_at_qwen3_8b_layer_sizes(dtype, tmp_path):
+    import ondeviceinfer_b200 as odi
+    from helpers import write_model_folder
+    from ondeviceinfer_b200.kernels import ops
+
+    weights = plain.random_weights(LARGE_PREFILL, 8)
+    tokens = plain.random_prompts(LARGE_PREFILL, [2100], 9)[0]
+    if "logits" not in _LARGE_PREFILL_EXPECTED:
+        _LARGE_PREFILL_EXPECTED["logits"] = plain.forward_logits(weights, LARGE_PREFILL, tokens)
+    expected = _LARGE_PREFILL_EXPECTED["logits"]
+    model = odi.load_resident_model(write_model_folder(tmp_path / "large_prefill", LARGE_PREFILL, weights), dtype=dtype)
+    cache = model.make_cache(max_tokens=2112, max_seqs=1)
+    slot = cache.alloc()
+    picks = [0, 63, 64, 255, 256, 1000, 2047, 2048, 2095]
+    before = dict(ops.LAUNCHES)
+    whole = model.step(cache, [slot], [tokens[:2096]], [picks])
+    if dtype == "bfloat16":
+        assert ops.LAUNCHES["library"] == before["library"], "a projection of the long prompt went to the vendor library"
+    rows = [whole] + [model.step(cache, [slot], [[t]], "last") for t in tokens[2096:]]
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    assert_logits_close(torch.cat(rows), expected[picks + list(range(2096, 2100))], dtype, "2,100 tokens at 8B layer sizes",
+                        longest_sum=LARGE_PREFILL["intermediate_size"])
+    cache.free(slot)
+    cache.check()

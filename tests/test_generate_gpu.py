@@ -10,7 +10,7 @@ import torch
 
 import ondeviceinfer_b200 as odi
 import plain_qwen3 as plain
-from helpers import CASES, engine_model, write_model_folder
+from helpers import BF16_CDF, BF16_TIE, CASES, engine_model, write_model_folder
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -24,7 +24,7 @@ def tmp_root(tmp_path_factory):
 def near_tie(weights, cfg, prefix, token, dtype):
     """True if `token` is the plain argmax after `prefix`, or within the bf16 tolerance of it."""
     logits = plain.forward_logits(weights, cfg, prefix)[-1]
-    return float(logits.max() - logits[token]) <= (0.0 if dtype == "float32" else 3e-2)
+    return float(logits.max() - logits[token]) <= (0.0 if dtype == "float32" else BF16_TIE)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -75,7 +75,7 @@ def test_temperature_sampling_of_model_b_does_not_depend_on_the_batch(dtype, tmp
                 cdf = torch.softmax(logits / 0.8, 0).cumsum(0)
                 u = plain.uniform_draw(1, r, t)
                 lo = float(cdf[token - 1]) if token > 0 else 0.0
-                assert lo - 2e-2 <= u <= float(cdf[token]) + 2e-2, (r, t)
+                assert lo - BF16_CDF <= u <= float(cdf[token]) + BF16_CDF, (r, t)
     other_seed = odi.generate(model, prompts, max_new_tokens=16, temperature=0.8, seed=2)
     assert other_seed.generated_ids != together.generated_ids
 
@@ -158,9 +158,12 @@ def test_graph_replay_gives_the_tokens_of_the_plain_step_path(dtype, tmp_root):
         if dtype == "float32":
             assert replayed.generated_ids == stepped.generated_ids
             assert again.generated_ids == stepped.generated_ids[:3]
-        else:
-            same = sum(a == b for a, b in zip(replayed.generated_ids, stepped.generated_ids))
-            assert same >= 4, "bf16 graph replay and stepping should agree except for rare near-ties"
+        elif temperature == 0.0:
+            # bf16: the logits of graph replay are compared row by row elsewhere (test_decode_graph_gpu.py); here
+            # every token either run chose must be the plain argmax after the same prefix, or within a near-tie of it
+            for run in (replayed, stepped, again):
+                for p, g in zip(prompts, run.generated_ids):
+                    assert all(near_tie(weights, cfg, p + g[:t], g[t], dtype) for t in range(len(g)))
     # sequences that stop at different times: the batch narrows and the runner re-begins
     free_run = odi.generate(model, prompts, max_new_tokens=40, use_graphs=False)
     stop = free_run.generated_ids[1][10]

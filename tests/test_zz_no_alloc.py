@@ -94,3 +94,19 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
     assert "2097152" in message and str(n * nq * splits * (D + 2)) in message
     torch.cuda.synchronize()
     assert float(out.float().min()) == 7.0, "a refused call must not launch anything"
+
+
+def test_no_alloc_entry_point_refuses_null_pointers():
+    lib = load_library("attention_mma", {"ODI_HEAD_DIM": D})
+    lib.odi_attention_decode_noalloc_error.restype = ctypes.c_char_p
+    setup = paged_setup([1] * 2, [10, 20], 2, D, "bfloat16", seed=44)
+    out = torch.full((2, 4 * D), 7.0, dtype=torch.bfloat16, device=DEV)
+    args = ops._MmaAttnArgs(0, setup["k_pool"].data_ptr(), setup["v_pool"].data_ptr(), out.data_ptr(),
+                            0, setup["cu_q"].data_ptr(), setup["past"].data_ptr(), setup["page_start"].data_ptr(),
+                            setup["page_ids"].data_ptr(), 2, 4, 2, 2, 0, 1.0)       # q is null
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.odi_attention_decode_noalloc(ctypes.byref(args), ctypes.c_int(2), stream) == ops.ODI_ERR_ARGUMENT
+    assert "null" in lib.odi_attention_decode_noalloc_error().decode()
+    assert lib.odi_attention_decode_noalloc(None, ctypes.c_int(2), stream) == ops.ODI_ERR_ARGUMENT
+    torch.cuda.synchronize()
+    assert float(out.float().min()) == 7.0
