@@ -39,7 +39,10 @@
 #define BM 128             // features per tile (UMMA M)
 #define BK 64              // k per stage: 64 bf16 = one 128-byte swizzle row
 #define GEMM_THREADS 192
-#define WAIT_CYCLES 4000000000ll   // about two seconds of SM clock
+#ifndef ODI_WAIT_CYCLES
+#define ODI_WAIT_CYCLES 4000000000ll   // about two seconds of SM clock; a self-test build makes it milliseconds
+#endif
+#define WAIT_CYCLES ((long long)ODI_WAIT_CYCLES)
 
 #define GEMM_ERR_TIMEOUT_PRODUCER 1
 #define GEMM_ERR_TIMEOUT_MMA 2
@@ -67,6 +70,10 @@ struct GemmArgs {
   // When not null: bias [weight rows], added to the finished product (after the K splits are summed) before
   // anything else the epilogue does with it.
   const float* bias;
+  // Self-test of the bounded waits: when set, the producer announces and requests nothing, so no copy is ever
+  // in flight and the MMA role's first wait runs out; the kernel must record that, free its tensor memory and
+  // return.  Never set on the product path.
+  int no_loads;
   // EPI_HEAD_PREP: a tile of 128 features is one head (query heads, then key heads, then value heads);
   // what the stand-alone head preparation would do with the bf16 projections happens in the epilogue.
   HeadPrepArgs hp;
@@ -94,8 +101,10 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when it gave up or when another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait.  Returns false when it gave up or when another role already gave up.  The role whose own wait
+// ran out records its code in `status` before it raises the abort flag, so the word names the role that
+// waited in vain and not one that merely left after it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   const long long start = clock64();
   for (uint32_t i = 0;; ++i) {
     if (mbar_test(bar, parity)) return true;
@@ -105,6 +114,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (clock64() - start > WAIT_CYCLES) break;
     }
   }
+  atomicCAS(status, 0, code);
+  __threadfence_block();
   *abort_flag = 1;
   return false;
 }
@@ -298,7 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   pdl_launch_dependents();      // the next kernel may be scheduled; it waits for this grid before it reads
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && !a.no_loads) {
       const CUtensorMap* map_l = &map_w;       // the lanes' operand: weight rows
       const CUtensorMap* map_c = &map_x;       // the columns' operand: token rows
       const int l_row = n0, c_row = tok0;
@@ -324,7 +335,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int i = pre; i < kb_count; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
-        if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_ptr)) { atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_PRODUCER); break; }
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, abort_ptr, a.status, GEMM_ERR_TIMEOUT_PRODUCER)) break;
         const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
         const int k0 = (kb_begin + i) * BK;
         mbar_expect_tx(full0 + 8 * s, TX_BYTES);
@@ -341,8 +352,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       for (int i = 0; i < kb_count && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
-        if (!mbar_wait(full0 + 8 * s, phase, abort_ptr) || (NORM && !mbar_wait(ready0 + 8 * s, phase, abort_ptr))) {
-          atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_MMA); ok = false; break;
+        if (!mbar_wait(full0 + 8 * s, phase, abort_ptr, a.status, GEMM_ERR_TIMEOUT_MMA) ||
+            (NORM && !mbar_wait(ready0 + 8 * s, phase, abort_ptr, a.status, GEMM_ERR_TIMEOUT_MMA))) {
+          ok = false; break;
         }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -421,7 +433,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const int i = base + j;
           if (i >= kb_count) break;
           const int s = i % STAGES;
-          if (i >= STAGES && !mbar_wait(empty0 + 8 * s, (((uint32_t)(i / STAGES) & 1u) ^ 1u), abort_ptr)) { conv_ok = false; break; }
+          if (i >= STAGES && !mbar_wait(empty0 + 8 * s, (((uint32_t)(i / STAGES) & 1u) ^ 1u), abort_ptr, a.status, GEMM_ERR_TIMEOUT_EPILOGUE)) { conv_ok = false; break; }
           const float4 g0 = ring[j].g[0], g1 = ring[j].g[1];
           uint8_t* tile = smem + (size_t)s * STAGE_BYTES + L_BYTES * L_TILES;
 #pragma unroll
@@ -439,16 +451,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           fetch_x(ring[j], i + DEPTH);
         }
       }
-      if (!conv_ok && lane == 0) atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_EPILOGUE);
     }
-    bool ok = mbar_wait(acc_bar, 0, abort_ptr);
-    if (!ok && lane == 0) atomicCAS(a.status, 0, GEMM_ERR_TIMEOUT_EPILOGUE);
+    bool ok = mbar_wait(acc_bar, 0, abort_ptr, a.status, GEMM_ERR_TIMEOUT_EPILOGUE);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     tc_fence_after();
-    // this thread's feature row has one bias for every token (weights: no kernel writes them)
-    const bool biased = a.bias != nullptr && n0 + row < a.N;
-    const float bias_v = biased ? a.bias[n0 + row] : 0.f;
-    const float bias_u = (DUAL && biased) ? a.bias[n0 + row + a.dual_offset] : 0.f;
     if (ok && a.splits == 1) {
       const int n = n0 + row;
 #pragma unroll 1
@@ -457,7 +463,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         float v[16], u[16];
         tmem_ld16(taddr + c, v);
         if (DUAL) tmem_ld16(taddr + BN + c, u);
-        if (a.bias != nullptr) {
+        if (a.bias != nullptr && n < a.N) {
+          // this thread's feature row has one bias for every token (a weight: no kernel writes it)
+          const float bias_v = a.bias[n], bias_u = DUAL ? a.bias[n + a.dual_offset] : 0.f;
 #pragma unroll
           for (int i = 0; i < 16; ++i) { v[i] += bias_v; if (DUAL) u[i] += bias_u; }
         }
@@ -540,7 +548,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
             for (int i = 0; i < 8; ++i) { v[i] += pv[i]; if (DUAL) u[i] += pu[i]; }
           }
-          if (a.bias != nullptr) {
+          if (a.bias != nullptr && n < a.N) {
+            const float bias_v = a.bias[n], bias_u = DUAL ? a.bias[n + a.dual_offset] : 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) { v[i] += bias_v; if (DUAL) u[i] += bias_u; }
           }
@@ -588,9 +597,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const float* red = (const float*)smem;
       const uint32_t rank = cluster_rank();
       const bool sums = EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr;
-      const bool biased = a.bias != nullptr && n < a.N;
-      const float bias_v = biased ? a.bias[n] : 0.f;
-      const float bias_u = (DUAL && biased) ? a.bias[n + a.dual_offset] : 0.f;
       int slot = 0;
       if (live)
         for (int c = (int)rank; c < BN && tok0 + c < a.tokens; c += a.splits, ++slot) {   // the token columns this CTA owns
@@ -610,7 +616,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           for (int p = 0; p < 8; ++p) {
             if (p < a.splits) { v += pv[p]; if (DUAL) u += pu[p]; }
           }
-          if (a.bias != nullptr) { v += bias_v; if (DUAL) u += bias_u; }
+          if (a.bias != nullptr && n < a.N) { v += a.bias[n]; if (DUAL) u += a.bias[n + a.dual_offset]; }
           if (EPI == EPI_HEAD_PREP) ((float*)(smem + HP_STAGE_OFFSET))[slot * BM + row] = round_to<bf16>(v);
           float left = 0.f;
           if (EPI == EPI_RESIDUAL) { left = inside ? res + v : 0.f; if (inside) *res_at = left; }
@@ -754,6 +760,7 @@ extern "C" long odi_gemm_bf16_scratch_floats(int tokens, int n_out, int bn, int 
 
 // x [tokens, K] bf16, w [w_rows, K] bf16 (for EPI_SWIGLU w holds the gate rows followed by
 // the up rows and n_out = w_rows / 2), out [tokens, ldo]; bias: null or fp32 [w_rows], added to the product.
+// no_loads != 0: the self-test of the bounded waits (see GemmArgs); the result is invalid by design.
 // Tiles of 128 features x bn tokens, bn in {16, 32, 64, 128, 256}, K splits allowed; cluster != 0 lets 2..8 splits
 // (bn <= 64) exchange partials through distributed shared memory.  Many tokens are the business of
 // gemm_prefill_tcgen05.cu; this kernel takes them too, tile by tile, but re-reads the weights for every token tile.
@@ -761,7 +768,7 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
                              int ldo, int epi, int bn, int splits, int cluster, float* scratch,
                              int* tickets, int* status, const float* norm_x, const float* norm_w,
                              const float* norm_parts, int norm_n_parts, float norm_eps, float* sumsq_out,
-                             const HeadPrepArgs* head_prep, const float* bias, cudaStream_t stream) {
+                             const HeadPrepArgs* head_prep, const float* bias, int no_loads, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
   if (x == nullptr && norm_x == nullptr) return ODI_ERR_ARGUMENT;
@@ -789,6 +796,8 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   a.norm_x = norm_x; a.norm_w = norm_w; a.norm_parts = norm_parts; a.norm_n_parts = norm_n_parts; a.norm_eps = norm_eps;
   a.sumsq_out = sumsq_out;
   a.bias = bias;
+  a.no_loads = no_loads;
+  if (no_loads && (norm_x != nullptr || splits != 1)) return ODI_ERR_ARGUMENT;     // the self-test is one plain tile
   if (epi == EPI_HEAD_PREP) {
     // heads of 128 (a tile is a head), whole-head rotation or none, keys and values written, tokens in columns
     if (head_prep == nullptr) return ODI_ERR_ARGUMENT;

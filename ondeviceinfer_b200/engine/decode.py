@@ -34,6 +34,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
+from ..profiling import nvtx_range
 from .step import StepDescription
 
 
@@ -273,6 +274,10 @@ class DecodeRunner:
         device, width = self.model.device, ctx.width
         torch.cuda.synchronize(device)
         began = time.perf_counter()
+        with nvtx_range(f"capture[{width} rows, up to {bucket} keys]"):
+            return self._capture_now(ctx, bucket, device, width, began)
+
+    def _capture_now(self, ctx: _DecodeContext, bucket: int, device, width: int, began: float):
         ctx.max_kv_len = bucket
         pad = self.cache.pad_slot
         ctx.slots.fill_(pad)
@@ -317,7 +322,8 @@ class DecodeRunner:
         lengths = [self.cache.lengths[s] for s in self.live_slots]
         for i in range(n_steps):
             graph, launches, _ = self._graph_for(self.ctx.width, [n + i + 1 for n in lengths])
-            graph.replay()
+            with nvtx_range(f"decode_step[{self.ctx.width} rows]"):
+                graph.replay()
             ops.LAUNCHES["own"] += launches["own"]
             ops.LAUNCHES["library"] += launches["library"]
         self.cache.advance(self.live_slots, [n_steps] * len(self.live_slots))

@@ -19,6 +19,8 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Sequence
 
+from ..profiling import nvtx_range
+
 
 @dataclass
 class GenerationResult:
@@ -109,9 +111,10 @@ def generate_requests(prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
         try:
             synchronize()
             start = time.perf_counter()
-            logits = step([slots[r] for r in live], [list(prompts[r]) for r in live])
-            tokens = sample(logits, live, [0] * len(live))
-            synchronize()
+            with nvtx_range(f"prefill[{len(live)} requests]"):
+                logits = step([slots[r] for r in live], [list(prompts[r]) for r in live])
+                tokens = sample(logits, live, [0] * len(live))
+                synchronize()
             prefill_seconds += time.perf_counter() - start
             start = time.perf_counter()
             set_up = set_up_so_far()

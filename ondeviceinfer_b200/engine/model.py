@@ -16,6 +16,7 @@ from ..cache import SequenceCache
 from ..config.specs import ModelPlan
 from ..kernels import ops
 from ..parts import Runtime, build_part, linear
+from ..profiling import nvtx_range
 from ..weights import loader
 from ..weights.tensors import TensorDecl
 
@@ -102,11 +103,14 @@ class DecoderModel:
     def forward(self, ctx, cache) -> torch.Tensor:
         """Run the step described by ``ctx``; return fp32 logits at ``ctx.want_rows``."""
         hidden = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.runtime.device)
-        ops.embed(self.embedding, ctx.token_ids, hidden)
+        with nvtx_range("embed"):
+            ops.embed(self.embedding, ctx.token_ids, hidden)
         ctx.residual_sumsq = None          # nothing is known about the rows of `hidden` yet
         for index, entry in enumerate(self.plan.order):
-            self.layers[entry.layer].forward(hidden, ctx, cache.view(index))
+            with nvtx_range(f"layer_{entry.layer}"):
+                self.layers[entry.layer].forward(hidden, ctx, cache.view(index))
         if ctx.n_want == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.runtime.device)
-        final = self.final_norm(hidden, rows=ctx.want_rows)
-        return linear(final, self.head, out_dtype=torch.float32)
+        with nvtx_range("head"):
+            final = self.final_norm(hidden, rows=ctx.want_rows)
+            return linear(final, self.head, out_dtype=torch.float32)

@@ -23,6 +23,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
+from ..profiling import nvtx_range
 
 Want = Union[str, Sequence[Sequence[int]]]
 
@@ -211,7 +212,8 @@ def _run_chunk(model, cache, slots, tokens, places) -> torch.Tensor:
     cache.reserve(slots, q_lens)
     starts = np.concatenate(([0], np.cumsum(q_lens)[:-1])) if q_lens else []
     want_rows = [int(starts[i]) + p for i, seq in enumerate(places) for p in seq]
-    ctx = StepContext(cache, slots, tokens, want_rows, model.device)
-    logits = model.forward(ctx, cache)
+    with nvtx_range(f"step[{len(slots)} seqs, {sum(q_lens)} tokens]"):
+        ctx = StepContext(cache, slots, tokens, want_rows, model.device)
+        logits = model.forward(ctx, cache)
     cache.advance(slots, q_lens)
     return logits

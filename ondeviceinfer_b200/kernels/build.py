@@ -147,7 +147,7 @@ ALL_SOURCES = {
     "elementwise": [{}],
     "gemm_f32": [{}],
     "sampling": [{}],
-    "gemm_tcgen05": [{}],
+    "gemm_tcgen05": [{}, {"ODI_WAIT_CYCLES": 20_000_000}],      # the second: ops.selftest_bounded_wait
     "gemm_prefill_tcgen05": [{}],
     "attention_simt": [{"ODI_HEAD_DIM": 128}],
     "attention_mma": [{"ODI_HEAD_DIM": 128}],

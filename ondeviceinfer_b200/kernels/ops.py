@@ -410,8 +410,35 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
     _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
                              c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
                              _ptr(sumsq_out), byref(head_prep) if head_prep is not None else _ptr(None), _ptr(bias),
-                             _stream()),
+                             c_int(0), _stream()),
            "gemm_tcgen05")
+
+
+SELFTEST_WAIT_CYCLES = 20_000_000        # about ten milliseconds of SM clock
+
+
+def selftest_bounded_wait(device="cuda:0") -> int:
+    """Make one wait of the tensor-core GEMM run out, safely, and return the code the kernel recorded.
+
+    One tile is launched from a build of ``gemm_tcgen05.cu`` whose waits last about ten milliseconds
+    (``ODI_WAIT_CYCLES``) with a producer that requests no copy at all, so nothing is in flight: the MMA role
+    gives up on its first wait, every role leaves its loop, tensor memory is freed and the kernel returns.
+    The error word then holds the MMA role's code (2) and :func:`raise_on_kernel_fault` raises naming it.
+    The product's own build and its two-second limit are not involved."""
+    device = torch.device(device)
+    x = torch.zeros((16, 256), dtype=torch.bfloat16, device=device)
+    w = torch.zeros((128, 256), dtype=torch.bfloat16, device=device)
+    out = torch.zeros((16, 128), dtype=torch.float32, device=device)
+    scratch, tickets, status = _gemm_buffers(device, 0)
+    lib = load_library("gemm_tcgen05", {"ODI_WAIT_CYCLES": SELFTEST_WAIT_CYCLES})
+    none = _ptr(None)
+    with torch.cuda.device(device):
+        _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(16), c_int(128), c_int(256), c_int(128), c_int(128),
+                                 c_int(EPI_STORE_F32), c_int(16), c_int(1), c_int(0), _ptr(scratch), _ptr(tickets),
+                                 _ptr(status), none, none, none, c_int(0), c_float(0.0), none, none, none, c_int(1),
+                                 _stream()), "gemm_tcgen05 (bounded-wait self-test)")
+        torch.cuda.synchronize(device)
+    return int(status[0].item())
 
 
 def gemm_prefill_supported(x: torch.Tensor, w: torch.Tensor, n_out: int, out_dtype: torch.dtype) -> bool:

@@ -237,14 +237,15 @@ def test_graph_replay_of_a_windowed_layer_past_the_rings_wrap_and_across_a_bucke
     model = load_resident_model(folder, dtype=dtype)
     assert model.decoder.graph_safe
     gen = torch.Generator().manual_seed(10)
-    # request 0 decodes positions 380 .. 419 (its ring of 6 pages wraps at 384), request 1 decodes 240 .. 269 alone
-    # (the longest sequence passes 256 in the middle of the batch: another graph is captured), request 2 is short
+    # request 1 decodes 240 .. 269 alone and first (the sequence passes 256 in the middle of the batch: another
+    # graph is captured there), request 0 decodes positions 380 .. 419 (its ring of 6 pages wraps at 384),
+    # request 2 is short and leaves the second batch early
     lengths, tails = [420, 270, 100], {0: 40, 1: 30, 2: 10}
     requests = [torch.randint(0, WINDOWED["vocab_size"], (n,), generator=gen).tolist() for n in lengths]
     cache = model.make_cache(max_tokens=2 * 448, max_seqs=2)
     windowed = next(g for g in cache.kv_groups if g.need.window == WINDOW)
     assert windowed.ring_pages == 6
-    got = replay_batches(model, cache, requests, [[0, 2], [1]], tails)
+    got = replay_batches(model, cache, requests, [[1], [0, 2]], tails)
     runner = odi.api.decode_runner(model, cache)
     assert {key[1] for key in runner._graphs} >= {256, 512}, "the batch of request 1 should have crossed a length bucket"
     for r, tokens in enumerate(requests):

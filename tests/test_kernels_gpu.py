@@ -875,3 +875,24 @@ def test_gemm_prefill_tcgen05_prepares_heads_in_its_epilogue(lengths, past, K, n
         assert torch.equal(one == 0, two == 0) or float(((one == 0) != (two == 0)).float().mean()) < 1e-4
         differ = (one.float() - two.float()).abs()
         assert float(differ.max()) <= 0.02 * float(two.float().abs().max()) and float((differ > 0).float().mean()) < 0.02
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_gpu_usable():
+    """Every barrier wait of the tensor-core kernels is bounded.  Here one runs out for real, safely: one tile of
+    a build whose waits last about ten milliseconds, with a producer that requests no copy (nothing is in
+    flight).  The MMA role gives up, the kernel frees its tensor memory and returns, the error word names that
+    role, the host check raises once, and the next product on the same device is right."""
+    ops.raise_on_kernel_fault()                      # start from a clean word
+    code = ops.selftest_bounded_wait(DEV)
+    assert code == 2, f"the MMA role's wait should have run out first (code 2), the word holds {code}"
+    with pytest.raises(ops.KernelError, match="gemm_tcgen05: the MMA issuer"):
+        ops.raise_on_kernel_fault()
+    ops.raise_on_kernel_fault()                      # reported once
+    torch.manual_seed(50)
+    x = torch.randn(8, 512).bfloat16().to(DEV)
+    w = (torch.randn(256, 512) / math.sqrt(512)).bfloat16().to(DEV)
+    out = torch.empty(8, 256, dtype=torch.float32, device=DEV)
+    ops.gemm_bf16(x, w, out, ops.EPI_STORE_F32)
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    assert torch.allclose(out.cpu(), (x.float() @ w.float().t()).cpu(), atol=1e-4, rtol=1e-4)

@@ -239,9 +239,9 @@ def test_two_blocks_decode_through_the_fused_products(monkeypatch):
             seen["lazy"] += isinstance(x, linear_module.NormedRows)
             return real_operand(x, *args)
 
-        def counting_heads(*args):
+        def counting_heads(*args, **kwargs):
             seen["heads"] += 1
-            return real_heads(*args)
+            return real_heads(*args, **kwargs)
 
         monkeypatch.setattr(linear_module, "_operand", counting_operand)
         monkeypatch.setattr("ondeviceinfer_b200.parts.attention.project_heads", counting_heads)

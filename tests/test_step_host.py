@@ -174,3 +174,34 @@ def test_generation_stops_with_an_error_when_a_kernel_gave_up_waiting():
     finally:
         ops._gemm_state.clear()
         ops._gemm_state.update(saved)
+
+
+def test_nvtx_ranges_are_off_unless_the_environment_switches_them_on():
+    """ONDEVICEINFER_NVTX, read once at import (ondeviceinfer/profiling.py:17-49 of the reference): off, a range
+    is the shared do-nothing context; on, it pushes and pops a named range."""
+    import subprocess
+    import sys
+
+    from ondeviceinfer_b200 import profiling
+
+    assert not profiling.nvtx_enabled()
+    assert profiling.nvtx_range("a") is profiling.nvtx_range("b")
+    with profiling.nvtx_range("nothing happens"):
+        pass
+    script = (
+        "import torch\n"
+        "seen = []\n"
+        "torch.cuda.nvtx.range_push = lambda name: seen.append(('push', name))\n"
+        "torch.cuda.nvtx.range_pop = lambda: seen.append(('pop',))\n"
+        "from ondeviceinfer_b200 import profiling\n"
+        "assert profiling.nvtx_enabled()\n"
+        "with profiling.nvtx_range('layer_3'):\n"
+        "    seen.append(('inside',))\n"
+        "assert seen == [('push', 'layer_3'), ('inside',), ('pop',)], seen\n"
+        "print('ok')\n")
+    import os
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    done = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, cwd=root,
+                          env=dict(os.environ, ONDEVICEINFER_NVTX="yes", PYTHONPATH=root))
+    assert done.returncode == 0 and done.stdout.strip() == "ok", done.stderr
