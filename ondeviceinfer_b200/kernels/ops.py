@@ -9,6 +9,7 @@ without a GPU, or without the compiled libraries, these functions raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import Structure, byref, c_float, c_int, c_long, c_ulonglong, c_void_p
 from typing import Optional, Sequence, Tuple
 
@@ -293,11 +294,16 @@ def raise_on_kernel_fault() -> None:
         raise KernelError(f"a kernel gave up waiting on a barrier ({names.get(code, code)}); its result is invalid")
 
 
+# Token tile for 33 to 64 tokens: 64 (one tile), or 32 (two tiles side by side, which keep the norm prologue,
+# the head preparation and the sums of squares that only tiles up to 32 have).
+TILE_ABOVE_32 = int(os.environ.get("ODI_GEMM_TILE_ABOVE_32", "64"))
+
+
 def gemm_bf16_plan(tokens: int, n_out: int, K: int, epi: int):
     """(tile, splits) for a shape: tiles of 128 features x `tile` tokens, with enough K splits for about
     384 CTAs (at most 8, a cluster), each split at least four k-blocks of 64."""
     total_kb = -(-K // 64)
-    bn = next((b for b in (16, 32, 64) if tokens <= b), 64)
+    bn = next((b for b in (16, 32) if tokens <= b), TILE_ABOVE_32 if tokens <= 64 else 64)
     tiles = -(-n_out // 128) * -(-tokens // bn)
     # measured on whole decode steps on B200: about 384 CTAs (three of 72 KB per SM) stream best,
     # in clusters of up to 8 splits (192: +7 %, 288: +2 %, 512: +7 % step time)
@@ -319,7 +325,7 @@ def gemm_bf16_sumsq_parts(n_out: int) -> int:
 def gemm_bf16_fuses_norm(tokens: int, n_out: int, K: int, epi: int) -> bool:
     """Whether the planned form of this product can take its operand through the norm prologue."""
     bn, _ = gemm_bf16_plan(tokens, n_out, K, epi)
-    return bn <= 32 and tokens <= 32 and epi in (EPI_STORE_BF16, EPI_SWIGLU, EPI_HEAD_PREP)
+    return bn <= 32 and tokens <= 64 and epi in (EPI_STORE_BF16, EPI_SWIGLU, EPI_HEAD_PREP)
 
 
 def gemm_bf16_fuses_head_prep(tokens: int, n_out: int, K: int, *, d: int, rot_dim: int, rotated: bool,
@@ -327,7 +333,7 @@ def gemm_bf16_fuses_head_prep(tokens: int, n_out: int, K: int, *, d: int, rot_di
     """Whether the planned form of the q/k/v product can prepare the heads in its epilogue: heads of 128
     (a tile of the product is a head), whole-head rotation or none, keys and values written, decode widths."""
     bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_STORE_BF16)
-    return (bn <= 32 and tokens <= 32 and splits <= 8 and d == 128 and n_out % 128 == 0 and write_kv
+    return (bn <= 32 and tokens <= 64 and splits <= 8 and d == 128 and n_out % 128 == 0 and write_kv
             and (not rotated or rot_dim == d))
 
 
