@@ -116,6 +116,8 @@ class OrderEntry:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
+    """Token embedding: hidden[t] = table[token[t]], no scaling, nothing added."""
+
     vocab_size: int
     hidden_size: int
     weight_name: str
@@ -123,20 +125,27 @@ class EmbeddingSpec:
 
 @dataclass(frozen=True)
 class HeadSpec:
-    """Output head: logits = norm(h) W^T; ``weight_name`` None ties it to the embedding table."""
+    """Output head: logits = rows W^T on the rows the final norm gives it.  ``weight_name`` None ties it to the
+    embedding table (the model then fills in that tensor's name and sets ``tied``); with ``tied`` the head
+    binds ``weight_name`` without declaring it, because another part already does."""
 
     vocab_size: int
     hidden_size: int
     weight_name: Optional[str]
+    tied: bool = False
 
 
 @dataclass(frozen=True)
 class ModelPlan:
-    embedding: EmbeddingSpec
+    """``embedding`` and ``head`` are specs of registered parts like the layers' (any spec whose part has
+    ``forward(ctx) -> hidden`` resp. ``forward(rows, ctx) -> logits`` and the sizes ``vocab_size`` /
+    ``hidden_size``); :class:`EmbeddingSpec` and :class:`HeadSpec` are the plain ones."""
+
+    embedding: object
     layers: Tuple[object, ...]
     order: Tuple[OrderEntry, ...]
     final_norm: object
-    head: HeadSpec
+    head: object
     # tensors that may be present in a checkpoint and are deliberately not used
     ignored_tensors: Tuple[str, ...] = field(default_factory=tuple)
 

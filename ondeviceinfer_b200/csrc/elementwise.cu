@@ -65,15 +65,26 @@ template <> struct Pack4<bf16> {
   }
 };
 
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *(const float4*)p; }
+template <> __device__ __forceinline__ float4 load4<bf16>(const bf16* p) {
+  const uint2 raw = *(const uint2*)p;
+  const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x), hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
 // H a multiple of 4 and at most 4 * NV * blockDim.x: one read of the row, kept in registers.
+// add != null (then rows == null): the row becomes x + add first, is written back to x, and that sum is normed:
+// the residual add of a product that a library computed, fused with the norm that follows it.
 template <typename T, int NV>
-__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                   T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ w,
+                                   T* __restrict__ out, const int* __restrict__ rows, const T* __restrict__ add,
+                                   int H, float eps) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
-  const float4* xr = (const float4*)(x + (size_t)(rows ? rows[r] : r) * H);
+  float4* xr = (float4*)(x + (size_t)(rows ? rows[r] : r) * H);
   const int nvec = H >> 2;
   float4 v[NV];
   float ss = 0.f;
@@ -81,6 +92,11 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   for (int j = 0; j < NV; ++j) {
     const int i = threadIdx.x + j * blockDim.x;
     v[j] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (add != nullptr && i < nvec) {
+      const float4 y = load4<T>(add + (size_t)r * H + 4 * i);
+      v[j].x += y.x; v[j].y += y.y; v[j].z += y.z; v[j].w += y.w;
+      xr[i] = v[j];
+    }
     ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
   }
   ss = block_sum(ss, scratch);
@@ -97,23 +113,31 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
-extern "C" int odi_rmsnorm(const float* x, const float* w, void* out, const int* rows, int n, int H,
+// add: null, or [n, H] in the dtype of out: x += add in place before the norm (vector form only: the caller asks
+// odi_rmsnorm_adds first).
+extern "C" int odi_rmsnorm_adds(const float* x, const float* w, const void* out, const void* add, int H) {
+  return H % 4 == 0 && H <= 4 * 4 * 512 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+         ((uintptr_t)out % 16 == 0) && ((uintptr_t)add % 8 == 0);
+}
+
+extern "C" int odi_rmsnorm(float* x, const float* w, void* out, const int* rows, const void* add, int n, int H,
                            float eps, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   const bool aligned = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  if (add != nullptr && (rows != nullptr || !odi_rmsnorm_adds(x, w, out, add, H))) return ODI_ERR_UNSUPPORTED;
   if (aligned && H <= 4 * 4 * 512) {
     const int nvec = H / 4;
     const int threads = nvec >= 1024 ? 512 : (nvec >= 256 ? 256 : 128);
     const int nv = (nvec + threads - 1) / threads;   // 1..4
-#define ODI_NORM(T, NV) rmsnorm_vec_kernel<T, NV><<<n, threads, 0, stream>>>(x, w, (T*)out, rows, H, eps)
+#define ODI_NORM(T, NV) rmsnorm_vec_kernel<T, NV><<<n, threads, 0, stream>>>(x, w, (T*)out, rows, (const T*)add, H, eps)
     if (dtype == 0) { if (nv <= 1) ODI_NORM(float, 1); else if (nv <= 2) ODI_NORM(float, 2); else ODI_NORM(float, 4); }
     else { if (nv <= 1) ODI_NORM(bf16, 1); else if (nv <= 2) ODI_NORM(bf16, 2); else ODI_NORM(bf16, 4); }
 #undef ODI_NORM
     return launch_status();
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  if (dtype == 0) odi_rc = launch_pdl((rmsnorm_kernel<float>), dim3(n), dim3(threads), 0, stream, x, w, (float*)out, rows, H, eps);
-  else odi_rc = launch_pdl((rmsnorm_kernel<bf16>), dim3(n), dim3(threads), 0, stream, x, w, (bf16*)out, rows, H, eps);
+  if (dtype == 0) odi_rc = launch_pdl((rmsnorm_kernel<float>), dim3(n), dim3(threads), 0, stream, (const float*)x, w, (float*)out, rows, H, eps);
+  else odi_rc = launch_pdl((rmsnorm_kernel<bf16>), dim3(n), dim3(threads), 0, stream, (const float*)x, w, (bf16*)out, rows, H, eps);
   return launch_status();
 }
 

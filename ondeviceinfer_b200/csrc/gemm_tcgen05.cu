@@ -325,6 +325,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tma_load_2d(dst, map_l, k0, l_row, full0 + 8 * i);
         if (L_TILES == 2) tma_load_2d(dst + L_BYTES, map_l, k0, l_row + a.dual_offset, full0 + 8 * i);
       }
+      // (Asking the rest of this CTA's weights into L2 here as well, with cp.async.bulk.prefetch.tensor, measured
+      // no gain for two k-blocks beyond the ring (3.46 against 3.49 ms a step at batch 8) and a loss beyond that:
+      // 3.55 with four, 3.67 with eight, 4.16 with all.)
       if (!NORM) {
         pdl_wait();
         for (int i = 0; i < pre; ++i) {

@@ -1,21 +1,22 @@
 """A decoder built from a :class:`~ondeviceinfer_b200.config.specs.ModelPlan`.
 
-The model is the embedding, a tuple of layers (blocks built from the plan through the
-part registries), the order in which layers run (data: it may name a layer twice, or let
-an execution read the cache of an earlier one), the final norm and the output head.
-It does not know which architecture it is.
+The model is an embedding part, a tuple of layers (blocks), the order in which layers run
+(data: it may name a layer twice, or let an execution read the cache of an earlier one), a
+final norm and a head part, every one of them built from its spec through the part
+registries.  It does not know which architecture it is, nor what its ends do.
 """
 
 from __future__ import annotations
 
+from dataclasses import replace
 from typing import List, Optional
 
 import torch
 
 from ..cache import SequenceCache
 from ..config.specs import ModelPlan
-from ..kernels import ops
-from ..parts import Runtime, build_part, linear
+from ..parts import Runtime, build_part
+from ..parts.linear import flush_residual_add
 from ..profiling import nvtx_range
 from ..weights import loader
 from ..weights.tensors import TensorDecl
@@ -25,9 +26,15 @@ class DecoderModel:
     def __init__(self, plan: ModelPlan) -> None:
         plan.validate()
         self.plan = plan
+        self.embedding = build_part(plan.embedding)
         self.layers = [build_part(spec) for spec in plan.layers]
         self.final_norm = build_part(plan.final_norm)
-        self.vocab_size = plan.embedding.vocab_size
+        head = plan.head
+        if getattr(head, "weight_name", "") is None:        # tied: the head binds the embedding's tensor
+            head = replace(head, weight_name=plan.embedding.weight_name, tied=True)
+        self.head = build_part(head)
+        self.vocab_size = plan.embedding.vocab_size          # token ids a step may bring
+        self.logits_size = head.vocab_size                   # width of the logits the head returns
         self.hidden_size = plan.embedding.hidden_size
         self.runtime: Optional[Runtime] = None
         for i, entry in enumerate(plan.order):
@@ -41,14 +48,10 @@ class DecoderModel:
     # ------------------------------------------------------------------ weights
 
     def tensor_decls(self) -> List[TensorDecl]:
-        e, h = self.plan.embedding, self.plan.head
-        decls = [TensorDecl(e.weight_name, (e.vocab_size, e.hidden_size))]
+        decls = list(self.embedding.tensor_decls())
         for layer in self.layers:
             decls += layer.tensor_decls()
-        decls += self.final_norm.tensor_decls()
-        if h.weight_name is not None:
-            decls.append(TensorDecl(h.weight_name, (h.vocab_size, h.hidden_size)))
-        return decls
+        return decls + list(self.final_norm.tensor_decls()) + list(self.head.tensor_decls())
 
     def load(self, source, *, dtype: torch.dtype, device) -> "DecoderModel":
         """Check the source against the declarations (one error for everything that does
@@ -61,12 +64,11 @@ class DecoderModel:
         loader.check(self.tensor_decls(), source.stored(), self.plan.ignored_tensors)
         self.runtime = Runtime(dtype=dtype, device=device)
         fetch = loader.Fetcher(source, dtype, device)
-        self.embedding = fetch.matrix(self.plan.embedding.weight_name)
+        self.embedding.load(fetch, self.runtime)
         for layer in self.layers:
             layer.load(fetch, self.runtime)
         self.final_norm.load(fetch, self.runtime)
-        head_name = self.plan.head.weight_name
-        self.head = self.embedding if head_name is None else fetch.matrix(head_name)
+        self.head.load(fetch, self.runtime)
         return self
 
     @property
@@ -86,8 +88,8 @@ class DecoderModel:
     @property
     def graph_safe(self) -> bool:
         """True if every part may be captured in a CUDA graph (no host work per step)."""
-        return all(getattr(layer, "graph_safe", False) for layer in self.layers) and \
-            getattr(self.final_norm, "graph_safe", False)
+        return all(getattr(part, "graph_safe", False)
+                   for part in (self.embedding, *self.layers, self.final_norm, self.head))
 
     # ------------------------------------------------------------------ cache
 
@@ -102,15 +104,21 @@ class DecoderModel:
 
     def forward(self, ctx, cache) -> torch.Tensor:
         """Run the step described by ``ctx``; return fp32 logits at ``ctx.want_rows``."""
-        hidden = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.runtime.device)
         with nvtx_range("embed"):
-            ops.embed(self.embedding, ctx.token_ids, hidden)
+            hidden = self.embedding.forward(ctx)           # the fp32 residual stream [tokens, hidden]
         ctx.residual_sumsq = None          # nothing is known about the rows of `hidden` yet
+        ctx.pending_residual_add = None
         for index, entry in enumerate(self.plan.order):
+            layer = self.layers[entry.layer]
+            # A block that finishes deferred residual adds (parts/block.py) sets the flag for its own parts and
+            # takes over an add that the block before left; any other block finds the stream complete.
+            ctx.defers_residual_add = False
+            if not getattr(layer, "finishes_residual_adds", False):
+                flush_residual_add(ctx)
             with nvtx_range(f"layer_{entry.layer}"):
-                self.layers[entry.layer].forward(hidden, ctx, cache.view(index))
+                layer.forward(hidden, ctx, cache.view(index))
+        flush_residual_add(ctx)                # the last block's last product
         if ctx.n_want == 0:
-            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.runtime.device)
+            return torch.empty((0, self.logits_size), dtype=torch.float32, device=self.runtime.device)
         with nvtx_range("head"):
-            final = self.final_norm(hidden, rows=ctx.want_rows)
-            return linear(final, self.head, out_dtype=torch.float32)
+            return self.head.forward(self.final_norm(hidden, rows=ctx.want_rows), ctx)

@@ -46,7 +46,9 @@ class StepDescription:
     ``page_table(g)``         ``(page_start [n_seqs + 1], page_ids)`` of key/value group g;
     ``key_splits(rows)``      how a split-key decode kernel may cut the sequences' keys;
     ``memo(key, make)``       a value shared by all layers of the step (rotary tables and the like);
-    ``residual_sumsq``        the note a residual product leaves for the norm that follows it.
+    ``residual_sumsq``        the note a residual product leaves for the norm that follows it;
+    ``pending_residual_add``, ``defers_residual_add``  a residual add left to the next norm, and the flag of a block
+                              that finishes such adds (``parts/linear.py``, ``parts/block.py``).
 
     Host mirrors: ``n_seqs``, ``n_tokens``, ``n_want``, ``q_lens``, ``past_lens``, ``kv_lens`` (keys each
     sequence sees after the step), ``max_q_len``, ``max_kv_len``, ``slot_list``.  Under graph replay the host
@@ -57,12 +59,15 @@ class StepDescription:
 
     INTERFACE = ("token_ids", "tok_seq", "tok_pos", "cu_q", "past", "slots", "want_rows",
                  "n_seqs", "n_tokens", "n_want", "q_lens", "past_lens", "kv_lens", "max_q_len", "max_kv_len",
-                 "slot_list", "residual_sumsq", "page_table", "key_splits", "memo")
+                 "slot_list", "residual_sumsq", "pending_residual_add", "defers_residual_add",
+                 "page_table", "key_splits", "memo")
 
     def __init__(self) -> None:
         self._memo: Dict[object, object] = {}
         self._page_tables: List[Tuple[torch.Tensor, torch.Tensor]] = []
         self.residual_sumsq = None
+        self.pending_residual_add = None       # (residual, product) that a block left to the next norm
+        self.defers_residual_add = False       # set by a block that finishes such adds
 
     def page_table(self, group_index: int) -> Tuple[torch.Tensor, torch.Tensor]:
         return self._page_tables[group_index]
@@ -203,7 +208,7 @@ def run_step(model, cache, slots: Sequence[int], tokens: Sequence[Sequence[int]]
         offset += limit
     rows = [r for seq in outputs for r in seq]
     if not rows:
-        return torch.empty((0, model.vocab_size), dtype=torch.float32, device=model.device)
+        return torch.empty((0, getattr(model, "logits_size", model.vocab_size)), dtype=torch.float32, device=model.device)
     return torch.stack(rows)
 
 

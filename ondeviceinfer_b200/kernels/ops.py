@@ -91,9 +91,21 @@ def embed(table: torch.Tensor, ids: torch.Tensor, hidden: torch.Tensor) -> None:
                          c_int(dtype_code(table.dtype)), _stream()), "embed")
 
 
+def rmsnorm_adds(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: torch.Tensor) -> bool:
+    """Whether :func:`rmsnorm` can take ``add`` for these tensors (the vector form: a width that is a multiple of 4
+    and at most 8,192, aligned tensors, ``add`` in the dtype of ``out``)."""
+    if add.dtype != out.dtype or add.shape != x.shape or not add.is_contiguous():
+        return False
+    lib = load_library("elementwise")
+    return bool(lib.odi_rmsnorm_adds(_ptr(x), _ptr(weight), _ptr(out), _ptr(add), c_int(x.shape[1])))
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None) -> None:
-    """out[i] = weight * cast(x[r_i] * rsqrt(mean(x[r_i]^2) + eps)), r_i = rows[i] or i."""
+            rows: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> None:
+    """out[i] = weight * cast(x[r_i] * rsqrt(mean(x[r_i]^2) + eps)), r_i = rows[i] or i.
+
+    ``add`` ([tokens, H] in the dtype of ``out``, without ``rows``; see :func:`rmsnorm_adds`): first x += add, in
+    place, then the norm of the sum: the residual add of a product and the norm after it in one pass."""
     _require(x, "x", torch.float32, 2)
     _require(weight, "weight", torch.float32, 1)
     _require(out, "out", ndim=2)
@@ -107,8 +119,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
             raise KernelError("rows and out disagree")
     elif x.shape[0] != n:
         raise KernelError("x and out disagree")
+    if add is not None:
+        _require(add, "add", out.dtype, 2)
+        if rows is not None or add.shape != x.shape:
+            raise KernelError("rmsnorm: add goes without rows and has the shape of x")
     lib = load_library("elementwise")
-    _check(lib.odi_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), _ptr(rows), c_int(n), c_int(H), c_float(eps),
+    _check(lib.odi_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), _ptr(rows), _ptr(add), c_int(n), c_int(H), c_float(eps),
                            c_int(dtype_code(out.dtype)), _stream()), "rmsnorm")
 
 

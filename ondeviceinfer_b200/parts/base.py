@@ -40,6 +40,13 @@ it says ``takes_lazy_norm = True`` and the norm has ``lazy(x, parts)``, a
 ``gated_linear`` turn into the normed operand inside the tensor-core kernel (``.materialize()`` gives
 the tensor).  A part that passes ``track`` must not touch ``residual`` after that product.
 
+Also optional, between a block and the model: a block with ``finishes_residual_adds = True`` may set
+``ctx.defers_residual_add`` while its parts run; a product that the vendor library computed then leaves its
+residual add pending (``ctx.pending_residual_add``) and the block's next norm does it in its own pass
+(``norm(x, add=product)`` for a norm with ``adds = True``), the add after its last product being taken over by
+the next such block or by the model.  Whoever calls such a block directly finishes with
+``parts.linear.flush_residual_add(ctx)``.  A block that knows nothing of this never sees a pending add.
+
 Also optional: a mixer whose single-token kernel cuts each sequence's keys among several blocks may ask the
 context how (``ctx.key_splits(blocks_per_cut) -> (tiles_per_split, splits)``): the number of 64-key tiles
 that a block takes, as one int32 on the device that follows the step's sequences (also under graph replay,

@@ -4,10 +4,18 @@ from __future__ import annotations
 
 from ..config.specs import PreNormBlockSpec
 from .base import Part, build_part, register_part
+from .linear import flush_residual_add
+
+
+def ops_residual_add(residual, product) -> None:
+    from ..kernels import ops
+    ops.residual_add(residual, product)
 
 
 class PreNormBlock(Part):
     """h += mixer(norm(h)); h += feed_forward(norm(h))  (ondeviceinfer/model.py:49-63)."""
+
+    finishes_residual_adds = True     # its norms take over a residual add that a product left pending
 
     def __init__(self, spec: PreNormBlockSpec) -> None:
         super().__init__(spec)
@@ -40,11 +48,22 @@ class PreNormBlock(Part):
         has left the rows' sums of squares in ``ctx.residual_sumsq`` and both sides know how."""
         known = getattr(ctx, "residual_sumsq", None)
         ctx.residual_sumsq = None
+        pending = getattr(ctx, "pending_residual_add", None)
+        if pending is not None:
+            # a product of the part before is still to be added to the stream: in this norm's pass if it is
+            # this stream and the norm knows how, else now
+            ctx.pending_residual_add = None
+            if pending[0] is hidden and getattr(norm, "adds", False):
+                return norm(hidden, add=pending[1])
+            ops_residual_add(*pending)
         if known is not None and known[0] is hidden and hasattr(norm, "lazy") and getattr(consumer, "takes_lazy_norm", False):
             return norm.lazy(hidden, known[1])
         return norm(hidden)
 
     def forward(self, hidden, ctx, view) -> None:
+        # This block finishes residual adds that its parts' last products leave pending (in the norm that follows,
+        # here or in the next block; the model flushes the last one): it says so, and only then is an add deferred.
+        ctx.defers_residual_add = True
         self.mixer.forward(self._normed(self.mixer_norm, self.mixer, hidden, ctx), ctx, view, hidden)
         self.ffn.forward(self._normed(self.ffn_norm, self.ffn, hidden, ctx), ctx, hidden)
 

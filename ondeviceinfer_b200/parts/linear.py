@@ -123,7 +123,10 @@ def linear(x, weight: torch.Tensor, *, bias: Optional[torch.Tensor] = None, resi
     ``track`` (the step context) with ``residual``: if the kernel can, it also leaves the sums of
     squares of the rows it wrote, and ``track.residual_sumsq = (residual, parts)`` says so to the
     next norm; otherwise ``track.residual_sumsq`` is set to None.  Whoever passes ``track`` promises
-    not to change ``residual`` afterwards.
+    not to change ``residual`` afterwards.  If ``track.defers_residual_add`` is set (by a block that
+    knows how to finish it: see :func:`flush_residual_add`) and the product came from the vendor
+    library, the add itself is left to the norm that follows: ``track.pending_residual_add =
+    (residual, product)``.
     """
     n, N = x.shape[0], weight.shape[0]
     if track is not None:
@@ -171,9 +174,21 @@ def linear(x, weight: torch.Tensor, *, bias: Optional[torch.Tensor] = None, resi
     if biased:
         ops.bias_add(y, bias)          # after the library's rounding: only shapes the own kernels refuse come here
     if residual is not None:
-        ops.residual_add(residual, y)
+        if track is not None and getattr(track, "defers_residual_add", False):
+            # the block that set the flag adds `y` in the norm that follows (one pass instead of two)
+            track.pending_residual_add = (residual, y)
+        else:
+            ops.residual_add(residual, y)
         return None
     return y
+
+
+def flush_residual_add(ctx) -> None:
+    """Do a residual add that :func:`linear` left pending on ``ctx`` (nothing if there is none)."""
+    pending = getattr(ctx, "pending_residual_add", None)
+    if pending is not None:
+        ctx.pending_residual_add = None
+        ops.residual_add(*pending)
 
 
 # fp32 results of bf16 operands (the logits) are never rounded to bf16 on the way, whatever the number of rows:

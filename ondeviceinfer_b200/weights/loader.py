@@ -17,6 +17,7 @@ What is kept in which precision:
 
 from __future__ import annotations
 
+import weakref
 from typing import Dict, Iterable, List
 
 import torch
@@ -62,13 +63,22 @@ class Fetcher:
 
     def __init__(self, source, compute_dtype: torch.dtype, device) -> None:
         self.source, self.compute_dtype, self.device = source, compute_dtype, torch.device(device)
+        # One tensor per name for as long as somebody holds it: two parts that bind the same matrix (a head tied
+        # to the embedding table) share its storage; a matrix that its part only concatenates into another is
+        # not kept alive by this table.
+        self._matrices = weakref.WeakValueDictionary()
 
     def matrix(self, name: str) -> torch.Tensor:
-        """A matrix or table in the compute dtype."""
+        """A matrix or table in the compute dtype (the same tensor for the same name while it is held)."""
+        held = self._matrices.get(name)
+        if held is not None:
+            return held
         t = self.source.fetch(name)
         if not t.is_floating_point():
             raise TypeError(f"tensor {name!r} is stored as {t.dtype}, a floating matrix was expected")
-        return t.to(device=self.device, dtype=self.compute_dtype, non_blocking=False).contiguous()
+        t = t.to(device=self.device, dtype=self.compute_dtype, non_blocking=False).contiguous()
+        self._matrices[name] = t
+        return t
 
     def vector(self, name: str) -> torch.Tensor:
         """A small floating tensor, held in float32."""

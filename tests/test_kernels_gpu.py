@@ -52,6 +52,27 @@ def test_rmsnorm_and_row_gather(dtype, H, eps):
     assert torch.equal(picked, out[rows.long()])
 
 
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("H", [80, 4096, 5120])
+def test_rmsnorm_with_a_pending_residual_add(dtype, H):
+    """x += add in place and the norm of the sum in one pass: the same bits as the add followed by the norm."""
+    torch.manual_seed(12)
+    x = torch.randn(5, H)
+    add = torch.randn(5, H).to(DT[dtype])
+    w = (1 + 0.1 * torch.randn(H)).to(DEV)
+    two_x, one_x = x.clone().to(DEV), x.clone().to(DEV)
+    two, one = torch.empty(5, H, dtype=DT[dtype], device=DEV), torch.empty(5, H, dtype=DT[dtype], device=DEV)
+    ops.residual_add(two_x, add.to(DEV))
+    ops.rmsnorm(two_x, w, 1e-6, two)
+    assert ops.rmsnorm_adds(one_x, w, one, add.to(DEV))
+    ops.rmsnorm(one_x, w, 1e-6, one, add=add.to(DEV))
+    assert torch.equal(one_x, two_x) and torch.equal(one, two)
+    assert torch.equal(one_x.cpu(), x + add.float())
+    assert not ops.rmsnorm_adds(one_x, w, one, add.to(DEV).float() if dtype == "bfloat16" else add.to(DEV).bfloat16())
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(one_x, w, 1e-6, one, rows=torch.arange(5, dtype=torch.int32, device=DEV), add=add.to(DEV))
+
+
 def test_rope_table_matches_host_angles():
     theta, dim = 1e6, 128
     inv_freq = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))

@@ -1,10 +1,11 @@
 """The framework is open: a mixer with state of its own, a feed-forward with routing, a position
-encoding and a whole architecture are defined HERE, registered, built, loaded from a random model
-folder and stepped without touching the library's files.  The architecture mixes what the Qwen3
-plan never does: a stateful mixer, a windowed attention layer beside full ones (two cache groups
-plus a state group), a layer that runs twice, a layer execution that reads the cache of an earlier
-one, and a layer whose attention rotates by half positions and whose feed-forward sends each token
-to one of three experts.  It is a toy for this test only."""
+encoding, an embedding, an output head and a whole architecture are defined HERE, registered, built,
+loaded from a random model folder and stepped without touching the library's files.  The architecture
+mixes what the Qwen3 plan never does: a scaled embedding with learned absolute positions added, a
+stateful mixer, a windowed attention layer beside full ones (two cache groups plus a state group), a
+layer that runs twice, a layer execution that reads the cache of an earlier one, a layer whose
+attention rotates by half positions and whose feed-forward sends each token to one of three experts,
+and a head whose logits are soft-capped.  It is a toy for this test only."""
 
 import json
 import math
@@ -139,6 +140,63 @@ class RoutedFeedForward:
                 residual[rows] += weight[rows, None] * y
 
 
+# ----------------------------------------------------------------------------- toy ends: embedding and head
+
+
+@dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    weight_name: str
+    positions_name: str
+    max_positions: int
+    scale: float
+
+
+class ScaledEmbedding:
+    """hidden[t] = scale * table[token[t]] + learned[position[t]]."""
+
+    def __init__(self, spec):
+        self.spec = spec
+
+    def tensor_decls(self):
+        s = self.spec
+        return [TensorDecl(s.weight_name, (s.vocab_size, s.hidden_size)),
+                TensorDecl(s.positions_name, (s.max_positions, s.hidden_size))]
+
+    def load(self, fetch, runtime):
+        self.table = fetch.matrix(self.spec.weight_name)
+        self.learned = fetch.matrix(self.spec.positions_name)
+
+    def forward(self, ctx):
+        return self.spec.scale * self.table[ctx.token_ids.long()].float() + self.learned[ctx.tok_pos.long()].float()
+
+
+@dataclass(frozen=True)
+class SoftCapHeadSpec:
+    vocab_size: int
+    hidden_size: int
+    weight_name: str
+    cap: float
+    tied: bool = True          # binds the embedding's table, declares nothing
+
+
+class SoftCapHead:
+    """logits = cap * tanh((rows W^T) / cap)."""
+
+    def __init__(self, spec):
+        self.spec = spec
+
+    def tensor_decls(self):
+        return []
+
+    def load(self, fetch, runtime):
+        self.weight = fetch.matrix(self.spec.weight_name)
+
+    def forward(self, rows, ctx):
+        return self.spec.cap * torch.tanh(rows.float() @ self.weight.float().t() / self.spec.cap)
+
+
 # ----------------------------------------------------------------------------- a toy architecture
 
 
@@ -176,10 +234,11 @@ class ToyConfig:
         layers = (block(0, attention(0, None, 4, 2, 16)), block(1, DecaySpec(H, 0.9, "l1.mix")),
                   block(2, attention(2, WINDOW, 2, 1, 32)), routed)
         order = (OrderEntry(0), OrderEntry(1), OrderEntry(2), OrderEntry(0), OrderEntry(2, cache_from=2), OrderEntry(3))
-        return ModelPlan(EmbeddingSpec(self.vocab_size, H, "emb"), layers, order, RMSNormSpec(H, self.eps, "nf"),
-                         HeadSpec(self.vocab_size, H, None))
+        return ModelPlan(ScaledEmbeddingSpec(self.vocab_size, H, "emb", "pos", MAX_POSITIONS, EMB_SCALE), layers, order,
+                         RMSNormSpec(H, self.eps, "nf"), SoftCapHeadSpec(self.vocab_size, H, "emb", LOGIT_CAP))
 
 
+MAX_POSITIONS, EMB_SCALE, LOGIT_CAP = 640, 3.0, 0.25
 TOY = {"architectures": ["ToyForCausalLM"], "vocab_size": 211, "hidden_size": 48, "eps": 1e-5}
 
 
@@ -187,8 +246,8 @@ def toy_plain_logits(w, ids):
     """Whole sequence, no cache, from the plain functions plus the toy's own rules."""
     H, eps = TOY["hidden_size"], TOY["eps"]
     T = len(ids)
-    h = w["emb"][torch.tensor(ids)]
     pos = torch.arange(T)
+    h = EMB_SCALE * w["emb"][torch.tensor(ids)] + w["pos"][pos]
 
     def qkv(i, x, nq, nkv, d, theta=3000.0, step=1.0):
         p = f"l{i}.attn."
@@ -244,7 +303,7 @@ def toy_plain_logits(w, ids):
                          plain.linear(m[t:t + 1], w[f"l3.moe.{e}.u"]), w[f"l3.moe.{e}.d"])
         routed[t] = weight[t] * y[0]
     h = h + routed
-    return plain.linear(plain.rms_norm(h, w["nf"], eps), w["emb"])
+    return LOGIT_CAP * torch.tanh(plain.linear(plain.rms_norm(h, w["nf"], eps), w["emb"]) / LOGIT_CAP)
 
 
 @pytest.fixture(scope="module")
@@ -252,6 +311,8 @@ def toy(tmp_path_factory):
     register_part(DecaySpec, DecayMixer)
     register_part(HalfStepRotarySpec, HalfStepRotary)
     register_part(RoutedSpec, RoutedFeedForward)
+    register_part(ScaledEmbeddingSpec, ScaledEmbedding)
+    register_part(SoftCapHeadSpec, SoftCapHead)
     register_architecture("ToyForCausalLM", ToyConfig)
     folder = write_random_model(tmp_path_factory.mktemp("toy"), TOY, seed=5)
     source = SafetensorsSource(folder)
@@ -263,6 +324,7 @@ def test_registered_toy_is_built_with_its_cache_groups(toy):
     folder, weights = toy
     assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
     assert "l1.mix" in weights and "l2.attn.kn" in weights and "l3.moe.router" in weights and "l3.moe.2.d" in weights
+    assert weights["pos"].shape == (MAX_POSITIONS, TOY["hidden_size"]) and "head" not in weights
     model = load_resident_model(folder, dtype="float32")
     cache = model.make_cache(max_tokens=1024, max_seqs=2)
     assert len(cache.kv_groups) == 3 and len(cache.state_groups) == 1
