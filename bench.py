@@ -18,8 +18,9 @@ lengths and with temperature sampling.  One JSON line is printed:
 * ``e2e``     the same through the Python entry point ``generate()``: host token lists in,
               host token lists out; every decode step copies the step's token ids from
               pinned host memory to the device and reads the sampled tokens back;
-* ``prefill`` one 2,048-token prompt: tokens/s, ms (median of three after a warm-up), and
-              the fraction of the measured bf16 tensor-core peak its flops reach;
+* ``prefill`` one 2,048-token prompt: tokens/s, ms (median of three after a warm-up, each from a GPU
+              idle for a quarter of a second), and the fraction of the measured bf16 tensor-core
+              peak (the burst figure) its flops reach;
 * ``roofline`` the decode step against HBM: bytes it must read (every weight it uses
               once, plus the cached keys and values of the live requests) / its time;
 * ``points``  decode tokens/s at batch 1 and 64, and (default run, own arm) the two other
@@ -71,6 +72,10 @@ OTHER_SIZES = {
 }
 CONTEXT, PROMPT, PREFILL_TOKENS = 4096, 2048, 2048
 SETTLE_STEPS = 32          # the least number of untimed decode steps before a timed region (see the module text)
+# Each timed prefill starts from a GPU that has been idle this long, in both arms: one prompt arriving, not a loop of
+# prompts back to back (whose second and later rounds run at the clocks the power cap leaves after the first; the
+# measured peak that the fraction is taken of is a burst figure as well).
+PREFILL_PAUSE_SECONDS = 0.25
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # The two further configurations of the benchmark, appended to the default run's points.
 EXTRA_POINTS = (
@@ -342,6 +347,7 @@ def run_reference_arm(args, parser) -> int:
         for i in range(repeats + 1):
             cache = model.make_resident_cache(batch_size=1, max_seq_len=PREFILL_TOKENS)
             torch.cuda.synchronize()
+            time.sleep(PREFILL_PAUSE_SECONDS)
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
             model(ids, cache=cache, logits_to_keep=1)
@@ -495,6 +501,7 @@ def run_own_arm(args, parser) -> int:
             for i in range(repeats + 1):
                 slot = cache.alloc()
                 torch.cuda.synchronize()
+                time.sleep(PREFILL_PAUSE_SECONDS)
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record()
                 model.step(cache, [slot], prompt, "last")

@@ -249,8 +249,18 @@ def test_qwen3_8b_layer_sizes(sizes, dtype, tmp_path):
         wide = model.make_cache(max_tokens=40 * 64, max_seqs=40)
         slots = [wide.alloc() for _ in many]
         logits = model.step(wide, slots, many, "last")
-        expected = torch.stack([plain.forward_logits(weights, LARGE, r)[-1] for r in many])
+        follow = plain.random_prompts(LARGE, [1] * 40, 5)              # one more token each, fed through graph replay
+        whole = [plain.forward_logits(weights, LARGE, r + f) for r, f in zip(many, follow)]
+        expected = torch.stack([w[len(r) - 1] for w, r in zip(whole, many)])
         assert_logits_close(logits, expected, dtype, "8B sizes, 40 sequences", longest_sum=LARGE["intermediate_size"])
+        # the same 40 rows one step on through the decode path of generate(): a captured graph of width 48
+        runner = odi.api.decode_runner(model, wide)
+        feed = [f[0] for f in follow]
+        runner.begin(slots, feed, list(range(40)), [1] * 40)
+        runner.step(feed)
+        assert runner.ctx.width == 48
+        assert_logits_close(runner.last_logits(), torch.stack([w[-1] for w in whole]), dtype,
+                            "8B sizes, 40 sequences, graph replay", longest_sum=LARGE["intermediate_size"])
         for slot in slots:
             wide.free(slot)
         wide.check()
