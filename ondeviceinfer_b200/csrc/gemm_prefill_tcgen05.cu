@@ -69,6 +69,10 @@ struct PrefillGemmArgs {
   int up_offset;           // EPI_SWIGLU: row distance from a gate row to its up row
   int m_tiles, n_tiles;    // tiles of 256 tokens, tiles of 256 columns
   const float* bias;       // null, or fp32 [weight rows]: added to the product before the epilogue's own work
+  // EPI_RESIDUAL: every tile's k-blocks in `parts` ranges that different pairs add into the residual one after the
+  // other (see segment_of); flags: two counters per tile, zero on entry and left zero.
+  int parts;
+  int* flags;
   HeadPrepArgs hp;         // EPI_HEAD_PREP
 };
 
@@ -278,6 +282,32 @@ __device__ __forceinline__ void tile_of(int t, int m_tiles, int n_tiles, int& m,
   n = r / rows;
 }
 
+// The idx-th piece of work of a pair: a tile and a range of its k-blocks.
+//
+// Walking whole tiles, 128 tiles on 74 pairs take two rounds of which the second is a quarter empty (the down
+// projection of a 2,048-token prompt; 160 tiles take three rounds at the sizes of Qwen3-14B).  With `parts` > 1
+// every tile's k-blocks are cut into that many equal ranges and the pairs walk the (part, tile) units instead,
+// all tiles' first parts before all second parts, so that the pairs that run side by side still stream the same
+// k-blocks of a few weight tiles and activation rows through L2.  A tile is then finished by `parts` adds into
+// the fp32 residual (the reduce-add epilogue needs no fix-up pass), by different pairs at different times.  The
+// adds are ordered, so that the sum does not depend on timing: part q adds after a counter says that part q - 1's
+// add of the same token rows is complete, and then raises it (the last part puts it back to zero).  A unit only
+// ever waits for a unit that comes earlier in the walk, and a pair takes its units in the walk's order: nobody
+// waits for somebody who waits for him.
+struct Segment { int tile, kb0, kb1, part; bool last; };
+__device__ __forceinline__ bool segment_of(const PrefillGemmArgs& a, int pair, int n_pairs, int total_tiles, int total_kb,
+                                           int idx, Segment& sg) {
+  const int parts = a.parts < 1 ? 1 : a.parts;
+  const long unit = (long)idx * n_pairs + pair;
+  if (unit >= (long)total_tiles * parts) return false;
+  sg.part = (int)(unit / total_tiles);
+  sg.tile = (int)(unit - (long)sg.part * total_tiles);
+  sg.kb0 = (int)((long)total_kb * sg.part / parts);
+  sg.kb1 = (int)((long)total_kb * (sg.part + 1) / parts);
+  sg.last = sg.part == parts - 1;
+  return true;
+}
+
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -323,13 +353,14 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       pdl_wait();                     // the activations come from the kernel before
       int it = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+      Segment sg;
+      for (int idx = 0; ok && segment_of(a, pair, n_pairs, total_tiles, total_kb, idx, sg); ++idx) {
         int tm, tn;
-        tile_of(tile, a.m_tiles, a.n_tiles, tm, tn);
+        tile_of(sg.tile, a.m_tiles, a.n_tiles, tm, tn);
         const int tok0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * OUT_PER_TILE;
         // this CTA's weight rows: its half of the 256 columns (for the gate: gate rows in the leader, up rows in the peer)
         const int w_row = GATE ? n0 + (int)rank * a.up_offset : n0 + (int)rank * (BN / 2);
-        for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty0 + 8 * s, (((uint32_t)(it / STAGES) & 1u) ^ 1u), abort_ptr)) { ok = false; break; }
           const uint32_t dst = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -345,11 +376,12 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       constexpr uint32_t idesc = instr_desc_bf16(2 * BM, BN);
       int it = 0, local = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
+      Segment sg;
+      for (; ok && segment_of(a, pair, n_pairs, total_tiles, total_kb, local, sg); ++local) {
         const int buf = local & 1;
         if (local >= 2 && !mbar_wait(acc_empty0 + 8 * buf, (((uint32_t)(local >> 1) & 1u) ^ 1u), abort_ptr)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(full0 + 8 * s, (uint32_t)(it / STAGES) & 1u, abort_ptr)) { ok = false; break; }
           tc_fence_after();
@@ -357,7 +389,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           const uint64_t da = smem_desc_k_sw128(sa), db = smem_desc_k_sw128(sa + A_BYTES);
 #pragma unroll
           for (int j = 0; j < BK / 16; ++j)
-            umma_pair_bf16(tmem_base + buf * BN, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            umma_pair_bf16(tmem_base + buf * BN, da + 2 * j, db + 2 * j, idesc, (kb > sg.kb0 || j > 0) ? 1u : 0u);
           umma_commit_pair(empty0 + 8 * s);         // both CTAs may refill the stage
         }
         if (ok) umma_commit_pair(acc_full0 + 8 * buf);
@@ -372,13 +404,26 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     uint8_t* stage_out = smem + STAGES * STAGE_BYTES;
     int local = 0, op = 0;
     bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++local) {
+    Segment sg;
+    for (; ok && segment_of(a, pair, n_pairs, total_tiles, total_kb, local, sg); ++local) {
       const int buf = local & 1;
       int tm, tn;
-      tile_of(tile, a.m_tiles, a.n_tiles, tm, tn);
+      tile_of(sg.tile, a.m_tiles, a.n_tiles, tm, tn);
       const int tok0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * OUT_PER_TILE;
       if (warp == 2) {
-        const bool got = mbar_wait(acc_full0 + 8 * buf, (uint32_t)(local >> 1) & 1u, abort_ptr);
+        bool got = mbar_wait(acc_full0 + 8 * buf, (uint32_t)(local >> 1) & 1u, abort_ptr);
+        if (got && EPI == EPI_RESIDUAL && sg.part > 0 && lane == 0) {
+          // a later part of a tile: add once the part before has added to these token rows (it ran a round
+          // earlier as a rule, so this seldom waits; the wait is bounded like every other)
+          volatile int* flag = a.flags + 2 * sg.tile + (int)rank;
+          const long long start = clock64();
+          while (*flag != sg.part) {
+            if (*abort_ptr || clock64() - start > WAIT_CYCLES) { *abort_ptr = 1; got = false; break; }
+            __nanosleep(64);
+          }
+          if (got) { __threadfence(); if (sg.last) *flag = 0; }      // the last part leaves it zero for the next launch
+        }
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
         if (lane == 0) epilogue_ok = got ? 1 : 0;
       }
       epilogue_sync();
@@ -404,9 +449,9 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           float v[32], u[32];
           tmem_ld32(taddr + c + 32 * part, v);
           if (GATE) tmem_ld32(taddr + BN / 2 + c + 32 * part, u);
-          if (a.bias != nullptr) {
+          if (a.bias != nullptr && sg.part == 0) {
             // a column is a feature: the same 32 biases for every thread (a broadcast read); columns beyond
-            // the matrix are clipped by the TMA store, their bias is taken as zero
+            // the matrix are clipped by the TMA store, their bias is taken as zero; a tile's first part adds it
             const int nb = n0 + c + 32 * part;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -447,6 +492,12 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8 * buf);
+      if (EPI == EPI_RESIDUAL && !sg.last && threadIdx.x == 64) {
+        // not the tile's last part: once this CTA's adds have completed, let the next part add
+        bulk_wait_all();
+        __threadfence();
+        atomicExch(a.flags + 2 * sg.tile + (int)rank, sg.part + 1);
+      }
     }
     if (threadIdx.x == 64) bulk_wait_all();
     if (!ok && lane == 0) atomicCAS(a.status, 0, ERR_EPILOGUE);
@@ -530,9 +581,10 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMa
 // EPI_HEAD_PREP: out is not used; head_prep describes where the heads go (heads of 128, whole-head rotation or
 // none, keys and values written).
 // bias: null, or fp32 [w_rows] (16-byte aligned), added to the product.
+// flags: n_flags ints, zero on entry and left zero (two per tile are used when the work is balanced).
 extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, int tokens, int n_out, int K, int w_rows,
                                      int ldo, int epi, const HeadPrepArgs* head_prep, const float* bias, int* status,
-                                     cudaStream_t stream) {
+                                     int* flags, int n_flags, int balance, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || status == nullptr) return ODI_ERR_UNSUPPORTED;
   const bool gate = epi == EPI_SWIGLU, heads = epi == EPI_HEAD_PREP;
@@ -571,6 +623,35 @@ extern "C" int odi_gemm_prefill_bf16(const void* x, const void* w, void* out, in
   a.m_tiles = (tokens + 2 * BM - 1) / (2 * BM);
   a.n_tiles = (n_out + per_tile - 1) / per_tile;
   if ((long)a.m_tiles * a.n_tiles > 0x7fffffffL) return ODI_ERR_UNSUPPORTED;
+  // Parts per tile (see segment_of), for the residual epilogue: the count up to 4 that makes the walk shortest, as
+  // long as a part keeps at least 32 k-blocks (its epilogue hides under the next unit's products) and the walk gets
+  // at least 15 % shorter; balance: 0 whole tiles always, 1 the choice described, 2..4 that many parts whatever the
+  // gain.  Measured on B200, 2,048 tokens, TFLOP/s whole / in parts: 5,120 x 17,408 (160 tiles, three rounds whole,
+  // 2.25 in quarters) 1,285 / 1,380; 5,120 x 8,192 (halves: 2.5 rounds) 1,264 / 1,308; 4,096 x 12,288 (128 tiles,
+  // two rounds whole, 1.75 in quarters) 1,378 / 1,366: there the whole-tile walk already runs at the rate the power
+  // cap sustains (its idle SMs let the busy ones clock higher), so a shorter walk gains nothing and the extra
+  // epilogues cost a little; hence the threshold.
+  {
+    const long tiles = (long)a.m_tiles * a.n_tiles;
+    const int pairs = tiles < sms / 2 ? (int)tiles : sms / 2;
+    const int total_kb = (K + BK - 1) / BK;
+    int parts = 1;
+    if (epi == EPI_RESIDUAL && flags != nullptr && 2 * tiles <= n_flags && balance > 0) {
+      if (balance >= 2) {
+        parts = balance > 4 ? 4 : balance;
+      } else {
+        const double whole = (double)((tiles + pairs - 1) / pairs);
+        double best = whole;
+        for (int p = 2; p <= 4 && total_kb / p >= 32; ++p) {
+          const double rounds = (double)((tiles * p + pairs - 1) / pairs) / p;
+          if (rounds < best * 0.97 && rounds <= whole * 0.85) { best = rounds; parts = p; }
+        }
+      }
+      if (parts > total_kb) parts = total_kb;
+    }
+    a.parts = parts;
+    a.flags = flags;
+  }
   switch (epi) {
     case EPI_STORE_BF16: return launch<EPI_STORE_BF16>(mx, mw, mo, a, sms, stream);
     case EPI_STORE_F32: return launch<EPI_STORE_F32>(mx, mw, mo, a, sms, stream);

@@ -17,6 +17,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import shlex
 import shutil
 import subprocess
 import sys
@@ -77,8 +78,13 @@ def _key(source: Path, defines: Mapping[str, object], extra: list) -> str:
     return h.hexdigest()[:16]
 
 
+def _extra_flags(name: str, extra: Optional[list]) -> list:
+    """The source's own extra flags plus what ``ODI_NVCC_FLAGS_<NAME>`` adds (for sweeps of build-time constants)."""
+    return list(extra or []) + shlex.split(os.environ.get(f"ODI_NVCC_FLAGS_{name.upper()}", ""))
+
+
 def library_path(name: str, defines: Optional[Mapping[str, object]] = None, extra: Optional[list] = None) -> Path:
-    defines, extra = dict(defines or {}), list(extra or [])
+    defines, extra = dict(defines or {}), _extra_flags(name, extra)
     source = CSRC / f"{name}.cu"
     if not source.exists():
         raise KernelBuildError(f"no kernel source {source}")
@@ -89,8 +95,9 @@ def library_path(name: str, defines: Optional[Mapping[str, object]] = None, extr
 def compile_library(name: str, defines: Optional[Mapping[str, object]] = None, extra: Optional[list] = None,
                     verbose: bool = True) -> Path:
     """Build ``csrc/<name>.cu`` unless an up-to-date build exists; return the library's path."""
-    defines, extra = dict(defines or {}), list(extra or [])
+    defines = dict(defines or {})
     out = library_path(name, defines, extra)
+    extra = _extra_flags(name, extra)
     if out.exists():
         return out
     source = CSRC / f"{name}.cu"

@@ -470,11 +470,17 @@ def gemm_prefill_supported(x: torch.Tensor, w: torch.Tensor, n_out: int, out_dty
     return gemm_bf16_supported(x, w) and (n_out * elem) % 16 == 0
 
 
+PREFILL_BALANCE = int(os.environ.get("ODI_PREFILL_BALANCE", "1"))     # 0 whole tiles, 1 parts when they pay, 2..4 that many
+
+
 def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *, head_prep=None,
-                      bias: Optional[torch.Tensor] = None) -> None:
+                      bias: Optional[torch.Tensor] = None, balance: Optional[int] = None) -> None:
     """The persistent two-CTA tensor-core product for many tokens (``csrc/gemm_prefill_tcgen05.cu``): clusters
     of two CTAs own tiles of 256 tokens x 256 features (tcgen05.mma.cta_group::2), two accumulators in tensor
     memory so that a tile's epilogue runs under the next tile's MMAs, output by TMA store or fp32 reduce-add.
+    ``balance`` (default ``ODI_PREFILL_BALANCE``, 1): with ``EPI_RESIDUAL``, cut every tile's k-blocks into up to four
+    parts that different CTA pairs add into the residual, in a fixed order, when that shortens the walk (128 tiles
+    on 74 pairs: two rounds whole, 1.75 in quarters); 0 whole tiles always, 2..4 that many parts.
     Same operands and epilogues as :func:`gemm_bf16`; with ``EPI_HEAD_PREP`` (``out=None``, ``head_prep`` the block
     that ``head_prep(None, ...)`` returns) a thread of the epilogue finishes a token's row of a head."""
     _require(x, "x", torch.bfloat16, 2)
@@ -497,11 +503,15 @@ def gemm_prefill_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tens
             raise KernelError(f"gemm_prefill_tcgen05 needs K a multiple of 8, 16-byte aligned operands and output rows "
                               f"(K={K}, {n_out} {out.dtype} per row)")
     _require_bias(bias, w_rows)
-    _, _, status = _gemm_buffers(w.device, 0)
+    _, tickets, status = _gemm_buffers(w.device, 0)
+    # the upper half of the ticket array serves as the tiles' flags (the few-token kernel counts tiles in the lower)
+    flags = tickets[tickets.numel() // 2:]
     lib = load_library("gemm_prefill_tcgen05")
     _check(lib.odi_gemm_prefill_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
                                      c_int(n_out), c_int(epi), byref(head_prep) if head_prep is not None else _ptr(None),
-                                     _ptr(bias), _ptr(status), _stream()), "gemm_prefill_tcgen05")
+                                     _ptr(bias), _ptr(status), _ptr(flags), c_int(flags.numel()),
+                                     c_int(PREFILL_BALANCE if balance is None else balance), _stream()),
+           "gemm_prefill_tcgen05")
 
 
 # ------------------------------------------------------------------------------ attention

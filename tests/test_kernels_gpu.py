@@ -917,3 +917,30 @@ def test_a_wait_that_runs_out_is_reported_and_leaves_the_gpu_usable():
     torch.cuda.synchronize()
     ops.raise_on_kernel_fault()
     assert torch.allclose(out.cpu(), (x.float() @ w.float().t()).cpu(), atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("tokens,N,K", [(2048, 4096, 4096), (2048, 4096, 12288), (5000, 1024, 136), (2100, 5120, 1000),
+                                        (4500, 776, 72), (19000, 256, 64)])
+def test_gemm_prefill_tcgen05_adds_a_tile_in_ordered_parts(tokens, N, K):
+    """The residual product with every tile's k-blocks cut into parts that different CTA pairs add one after the
+    other: the same result as whole tiles up to fp32 rounding, against fp32 torch, and the same bits every time
+    (the order of a tile's adds is fixed); the counters are left zero."""
+    torch.manual_seed(61)
+    x = torch.randn(tokens, K).bfloat16().to(DEV)
+    w = (torch.randn(N, K) / math.sqrt(K)).bfloat16().to(DEV)
+    res = torch.randn(tokens, N)
+    expected = res + (x.float() @ w.float().t()).cpu()
+    outs = []
+    bias = torch.randn(N).to(DEV)
+    expected = expected + bias.cpu()
+    for balance in (0, 4, 4, 1, 2, 3):
+        out = res.clone().to(DEV)
+        ops.gemm_prefill_bf16(x, w, out, ops.EPI_RESIDUAL, balance=balance, bias=bias)
+        torch.cuda.synchronize()
+        ops.raise_on_kernel_fault()
+        assert torch.allclose(out.cpu(), expected, atol=1e-4, rtol=1e-4), (balance, float((out.cpu() - expected).abs().max()))
+        outs.append(out)
+    assert torch.equal(outs[1], outs[2]), "two runs in four parts differ: the order of a tile's adds is not fixed"
+    assert float((outs[0] - outs[1]).abs().max()) <= 2e-5 * math.sqrt(K)
+    _, tickets, _ = ops._gemm_buffers(torch.device(DEV), 0)
+    assert int(tickets.abs().sum()) == 0, "a flag or ticket was left set"
