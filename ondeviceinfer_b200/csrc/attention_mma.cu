@@ -539,6 +539,11 @@ attention_decode_kernel(MmaAttnArgs a) {
 
 // One block per (token, head).  With `tiles_per_split` a row has the partials of its sequence's first
 // ceil(tiles / *tiles_per_split) splits only (one token per sequence: the token's index is the sequence's).
+// Up to 32 splits: the first warp reads every split's maximum and sum in one round trip and leaves the weights
+// in shared memory, then every thread requests its element of all splits at once and adds them in split order:
+// two round trips to L2 whatever the number of splits, and the arithmetic, its order and so its bits are those
+// of combine_row (which walks the splits three times, four loads at a time: with the 17 splits of one sequence
+// of 2,048 keys that kernel took as long as the attention itself).
 __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits,
                                              const int* __restrict__ past, int nq, const int* __restrict__ tiles_per_split) {
   pdl_launch_dependents();
@@ -550,7 +555,38 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, 
     const int per_split = tiles_of_a_split(tiles_per_split, splits, n_tiles);
     used = (n_tiles + per_split - 1) / per_split;
   }
-  combine_row(partial + row * splits * (D + 2), out + row * D, used, threadIdx.x, blockDim.x);
+  constexpr int RS = D + 2;
+  const float* p = partial + row * splits * RS;
+  if (used > 32) {
+    combine_row(p, out + row * D, used, threadIdx.x, blockDim.x);
+    return;
+  }
+  __shared__ float weight[32];
+  __shared__ float inv_denom;
+  if (threadIdx.x < 32) {
+    const int s = threadIdx.x;
+    const float ms = s < used ? __ldcg(p + s * RS + D) : -INFINITY;
+    const float ls = s < used ? __ldcg(p + s * RS + D + 1) : 0.f;
+    const float M = warp_max(ms);
+    const float w = ms != -INFINITY ? expf(ms - M) : 0.f;       // an empty split (max -inf) adds nothing
+    const float wl = ms != -INFINITY ? w * ls : 0.f;
+    float denom = 0.f;
+    for (int i = 0; i < used; ++i) denom += __shfl_sync(0xffffffffu, wl, i);     // in split order, as combine_row adds
+    weight[s] = w;
+    if (s == 0) inv_denom = denom > 0.f ? 1.f / denom : 0.f;
+  }
+  __syncthreads();
+  const float inv = inv_denom;
+  for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+    float x[32];
+#pragma unroll
+    for (int s = 0; s < 32; ++s) x[s] = s < used ? __ldcg(p + s * RS + dd) : 0.f;
+    float v = 0.f;
+#pragma unroll
+    for (int s = 0; s < 32; ++s)
+      if (s < used && weight[s] > 0.f) v += weight[s] * x[s];      // whatever an empty split's slot holds, it is not read into the sum
+    out[row * D + dd] = __float2bfloat16_rn(v * inv);
+  }
 }
 
 extern "C" int odi_attention_mma_head_dim() { return D; }

@@ -206,15 +206,12 @@ __device__ __forceinline__ void head_prep_row(const HeadPrepArgs& hp, int t, int
   for (int j = 0; j < d / 32; ++j) tmem_ld32(taddr + 32 * j, x + 32 * j);
   if (t >= hp.n_tokens) return;                       // after the loads: they are warp-wide
   if (bias != nullptr) {
-    const float4* b4 = (const float4*)(bias + (size_t)h * d);       // the launcher checked its alignment
 #pragma unroll
-    for (int i = 0; i < d; i += 4) {
-      const float4 b = b4[i / 4];
-      x[i] += b.x; x[i + 1] += b.y; x[i + 2] += b.z; x[i + 3] += b.w;
-    }
+    for (int i = 0; i < d; ++i) x[i] = round_to<bf16>(x[i] + __ldg(bias + h * d + i));   // the same for every thread: a broadcast read
+  } else {
+#pragma unroll
+    for (int i = 0; i < d; ++i) x[i] = round_to<bf16>(x[i]);
   }
-#pragma unroll
-  for (int i = 0; i < d; ++i) x[i] = round_to<bf16>(x[i]);
   const int kind = h < hp.nq ? 0 : (h < hp.nq + hp.nkv ? 1 : 2);     // 0 q, 1 k, 2 v
   const int pos = hp.tok_pos[t];
   bf16* dst;
