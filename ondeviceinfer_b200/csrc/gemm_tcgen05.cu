@@ -199,16 +199,17 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 // One warp finishes one head of one token: `vals` holds the head's 128 projections (already rounded
 // to bf16), lane i takes elements 4i .. 4i+3, whose rotation partners sit in lane i ^ 16.  The
 // arithmetic, its order and its roundings are those of head_prep_vec_kernel<4> (elementwise.cu).
-__device__ __forceinline__ void head_prep_finish(const HeadPrepArgs& hp, int t, int h, const float* vals, int lane) {
+// `pos` and `page` (the token's position and, for key and value heads, the cache page that holds it) come from
+// head_prep_lookup, which the warp ran long before: the three dependent index loads do not sit behind the product.
+__device__ __forceinline__ void head_prep_finish(const HeadPrepArgs& hp, int t, int h, const float* vals, int lane,
+                                                 int pos, int page) {
   constexpr int d = 128, half = 64;
   const int kind = h < hp.nq ? 0 : (h < hp.nq + hp.nkv ? 1 : 2);     // 0 q, 1 k, 2 v
-  const int pos = hp.tok_pos[t];
   bf16* dst;
   if (kind == 0) {
     dst = (bf16*)hp.q_out + ((size_t)t * hp.nq + h) * d;
   } else {
     const int hk = kind == 1 ? h - hp.nq : h - hp.nq - hp.nkv;
-    const int page = hp.page_ids[hp.page_start[hp.tok_seq[t]] + page_slot_of(pos, hp.page_size, hp.ring_pages)];
     bf16* pool = (bf16*)(kind == 1 ? hp.k_pool : hp.v_pool);
     dst = pool + (((size_t)page * hp.nkv + hk) * hp.page_size + (pos % hp.page_size)) * d;
   }
@@ -237,6 +238,15 @@ __device__ __forceinline__ void head_prep_finish(const HeadPrepArgs& hp, int t, 
   }
   __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
   *(uint2*)(dst + 4 * lane) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+}
+
+// Position and cache page of token t for head h (the page only for key and value heads).  The step's index arrays
+// are written by the host, or by the sampling kernel of the step before: nothing of this step, so they may be
+// read before the dependency wait.
+__device__ __forceinline__ void head_prep_lookup(const HeadPrepArgs& hp, int t, int h, int& pos, int& page) {
+  pos = hp.tok_pos[t];
+  page = 0;
+  if (h >= hp.nq) page = hp.page_ids[hp.page_start[hp.tok_seq[t]] + page_slot_of(pos, hp.page_size, hp.ring_pages)];
 }
 
 // ------------------------------------------------------------------------------ the kernel
@@ -307,6 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abort_ptr = &abort_flag;
   pdl_launch_dependents();      // the next kernel may be scheduled; it waits for this grid before it reads
+  int hp_pos = 0, hp_page = 0;  // EPI_HEAD_PREP, epilogue warps: what head_prep_lookup found for the lane's token column
 
   if (warp == 0) {
     if (lane == 0 && !a.no_loads) {
@@ -382,6 +393,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int row = lane_group * 32 + lane;              // lane of the accumulator
     const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
     const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    // EPI_HEAD_PREP: lane j looks up, now, the j-th token column that this warp will finish at the very end (one
+    // split: columns lane_group, lane_group + 4, ...; a cluster: the columns this CTA owns, rank + splits * (lane_group + 4 j))
+    if (EPI == EPI_HEAD_PREP) {
+      const int nth = lane_group + 4 * lane;
+      const int c = a.splits == 1 ? nth : (int)cluster_rank() + nth * a.splits;
+      if (c < BN && tok0 + c < a.tokens) head_prep_lookup(a.hp, tok0 + c, blockIdx.y, hp_pos, hp_page);
+    }
     if (NORM) {
       constexpr int ITEMS = BN / 16;                  // token rows per thread: trow, trow + 16, ...
       constexpr int WANT = ITEMS == 1 ? 4 : 2;        // k-blocks in flight per thread, as registers allow (three CTAs per SM)
@@ -577,8 +595,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const float* stage = (const float*)(smem + HP_STAGE_OFFSET);
       if (ok)
-        for (int c = lane_group; c < BN && tok0 + c < a.tokens; c += 4)
-          head_prep_finish(a.hp, tok0 + c, blockIdx.y, stage + c * BM, lane);
+        for (int c = lane_group, j = 0; c < BN && tok0 + c < a.tokens; c += 4, ++j)
+          head_prep_finish(a.hp, tok0 + c, blockIdx.y, stage + c * BM, lane, __shfl_sync(0xffffffffu, hp_pos, j),
+                           __shfl_sync(0xffffffffu, hp_page, j));
     }
     if (EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr && a.splits == 1) {
       // every epilogue warp comes here, whatever happened above: the four warps' sums, in warp order
@@ -632,8 +651,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       if (EPI == EPI_HEAD_PREP) {
         asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps: the owned columns are staged
         if (live)
-          for (int sl = warp & 3; sl < slot; sl += 4)       // a warp per owned token column
-            head_prep_finish(a.hp, tok0 + (int)rank + sl * a.splits, blockIdx.y, (const float*)(smem + HP_STAGE_OFFSET) + sl * BM, lane);
+          for (int sl = warp & 3, j = 0; sl < slot; sl += 4, ++j)       // a warp per owned token column
+            head_prep_finish(a.hp, tok0 + (int)rank + sl * a.splits, blockIdx.y, (const float*)(smem + HP_STAGE_OFFSET) + sl * BM, lane,
+                             __shfl_sync(0xffffffffu, hp_pos, j), __shfl_sync(0xffffffffu, hp_page, j));
       }
       if (sums) {
         asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
