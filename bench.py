@@ -365,16 +365,18 @@ def run_reference_arm(args, parser) -> int:
     def single_request_point(steps):
         """Batch 1 through the reference's own loop (ondeviceinfer/generation.py:28-70)."""
         ids = prompts_for(1, prompt_len).to(device)
-        for tokens in (SETTLE_STEPS, steps + 1):               # a warm-up call, then the timed one
+        for tokens in (steps + 1, steps + 1):                  # an untimed call over the same lengths, then the timed one
             cache = model.make_resident_cache(batch_size=1, max_seq_len=context)
             result = greedy_generate(model, ids, max_new_tokens=tokens, cache=cache, eos_token_id=None)
             del cache
         return result.decode_tokens_per_second
 
-    # One whole untimed pass first, as the reference's own benchmark does (benchmarks/benchmark_resident.py:30-31,
-    # --warmup-runs 1): measured here, the first decode loop of a process runs at 58 ms a step, every later one
-    # at 18 ms, however many steps the first had behind it.
-    decode_run(args.batch, 4, 0, end_to_end=False)
+    # One whole untimed pass over the same lengths first, as the reference's own benchmark does
+    # (benchmarks/benchmark_resident.py:30-31, --warmup-runs 1, then repeats of the same prompt): measured here, a
+    # decode step at a key length that the process has not seen before takes 58 to 73 ms, at a length it has seen
+    # 18 ms (whatever PyTorch's attention call prepares per shape is kept), so the timed passes below repeat the
+    # lengths of an untimed one and show the reference at its best.
+    decode_run(args.batch, args.steps, args.warmup, end_to_end=False)
     clocks = ClockSampler()
     clocks.start()
     main_run = decode_run(args.batch, args.steps, args.warmup, end_to_end=False)
@@ -390,7 +392,7 @@ def run_reference_arm(args, parser) -> int:
         points["decode_b1"] = b1
         ctx = prompt_len + steps / 2.0
         points["decode_b1_hbm_frac"] = (weight_bytes + ctx * kv_bytes_per_token) * b1 / 1e9 / peaks["hbm_gbs"]
-        decode_run(64, 4, 0, end_to_end=False)                 # the untimed pass at this batch size
+        decode_run(64, steps, 3, end_to_end=False)             # the untimed pass at this batch size, same lengths
         run = decode_run(64, steps, 3, end_to_end=False)
         points["decode_b64"] = run["tok_s"]
         points["decode_b64_hbm_frac"] = run["bytes_per_step"] / (run["ms_per_step"] / 1000.0) / 1e9 / peaks["hbm_gbs"]
