@@ -178,6 +178,17 @@ def test_chunks_of_a_few_tokens_and_chosen_places(dtype, tmp_root):
     cache.free(sb)
 
 
+def test_a_tied_head_shares_the_embedding_table(tmp_root):
+    """Model A ties its head to the embedding: the two parts bind the same tensor (the loader hands out one tensor per
+    name), so the table is on the device once; model B has a head of its own."""
+    tied, _, _ = engine_model("A", "bfloat16", tmp_root)
+    assert tied.decoder.head.weight.data_ptr() == tied.decoder.embedding.table.data_ptr()
+    assert tied.decoder.head.tensor_decls() == []
+    own, _, _ = engine_model("B", "bfloat16", tmp_root)
+    assert own.decoder.head.weight.data_ptr() != own.decoder.embedding.table.data_ptr()
+    assert [d.name for d in own.decoder.head.tensor_decls()] == ["lm_head.weight"]
+
+
 def test_capacity_and_misuse_are_host_errors(tmp_root):
     from ondeviceinfer_b200 import CacheCapacityError
 
