@@ -62,6 +62,8 @@ CASES = {
     "Ab": (plain.TINY_A_BIAS, 10),
     "Bb": (plain.TINY_B_BIAS, 11),
     "Cb": (plain.TINY_C_BIAS, 12),
+    # a width that is no multiple of 8, heads of 48, biases
+    "D": (plain.TINY_D, 13),
 }
 
 

@@ -249,6 +249,18 @@ TINY_B_BIAS = dict(TINY_B, attention_bias=True)
 TINY_C_BIAS = dict(TINY_C, attention_bias=True)
 
 
+# A shape that the tensor-core kernels refuse in places: a width of 100 (no multiple of 8, so its products go to the
+# vendor library and its logits through the fp32 kernel), heads of 48, as many key/value heads as query heads,
+# biases on the attention projections.
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5,
+    "num_key_value_heads": 5, "head_dim": 48, "intermediate_size": 136, "vocab_size": 301,
+    "rope_theta": 20000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 512, "hidden_act": "silu", "attention_bias": True,
+}
+
+
 def tensor_shapes(cfg):
     """Checkpoint tensor names and shapes, in file order (module tree of
     ondeviceinfer/model.py:27-38,77-89,137-144)."""

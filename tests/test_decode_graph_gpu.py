@@ -70,7 +70,7 @@ def replay_batches(model, cache, requests, batches, tails, *, drop=False):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("case", ["A", "B", "C", "Cb"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "Cb", "D"])
 def test_graph_replay_logits_of_unequal_batches_that_shrink_and_reuse_slots(case, dtype, tmp_root):
     """Seven requests in batches of three on a cache of three slots; in each batch the tails are unequal, so the
     batch narrows (widths 4, 2, 1 with padding rows) while it runs; the second and third batch run in the

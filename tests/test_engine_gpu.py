@@ -13,7 +13,8 @@ DTYPES = ["float32", "bfloat16"]
 # request lengths: one token, a page minus / exactly / plus one, several pages, odd sizes
 LENGTHS = {"A": [5, 11, 17, 64, 33, 100], "B": [1, 7, 30, 64, 65, 130, 63, 2], "C": [3, 200, 77, 129, 64, 31]}
 LENGTHS.update({"Ab": LENGTHS["A"], "Bb": LENGTHS["B"], "Cb": LENGTHS["C"]})      # the same with projection biases
-ALL_CASES = ["A", "B", "C", "Ab", "Bb", "Cb"]
+LENGTHS["D"] = [2, 40, 65, 9, 128, 33]
+ALL_CASES = ["A", "B", "C", "Ab", "Bb", "Cb", "D"]
 
 
 @pytest.fixture(scope="session")
