@@ -80,9 +80,14 @@ def test_key_split_plan_covers_every_sequence_and_fills_the_gpu_once():
         assert per * splits >= max(tiles)
         assert per >= min(2, max(tiles))
         blocks = sum(-(-t // per) for t in tiles) * rows
-        assert blocks <= 296 or per == max(tiles)
+        # all blocks on the GPU at once when that can be had; when even whole sequences are too many for that,
+        # whole sequences or a few cuts each (which fill the rounds better)
+        assert blocks <= 296 or len(tiles) * rows > 296
+        if blocks > 296:
+            assert per == max(tiles) or splits <= 6
     assert plan_key_splits([2049] * 8, 8) == (9, 4)          # 8 sequences of 33 tiles: four blocks each, 256 in all
     assert plan_key_splits([2049] * 64, 8) == (33, 1)        # more sequences than the GPU holds blocks: each whole
+    assert plan_key_splits([2049] * 40, 8) == (11, 3)        # 320 whole sequences would run two rounds for 1.08: three cuts each
     assert plan_key_splits([131001], 8) == (64, 32)          # one long sequence: the most splits there are
 
 
