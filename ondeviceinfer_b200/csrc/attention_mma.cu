@@ -58,6 +58,12 @@ struct MmaAttnArgs {
                           // device: every block takes that many tiles of 64 keys, so a sequence of n tiles uses
                           // its first ceil(n / that) splits and its other blocks leave at once (`splits` then only
                           // bounds the count); null: every sequence is cut into `splits` equal ranges
+  long pool_rows;         // rows of D in each pool (pages * nkv * 64): the TMA-fed decode kernel maps the pools with it
+  int* status;            // error word of the TMA-fed decode kernel's bounded waits (0 = fine); null: that kernel is not used
+  int items;              // decode with tiles_per_split: when > 0, tiles_per_split[1] is a count n <= items and
+                          // tiles_per_split[2 .. 2 + n) the host's list of the blocks that have keys, one entry per
+                          // (sequence, split): sequence << 8 | 128 if it is the sequence's last split | split.  The grid
+                          // is then `items` wide and has no block without work among those with work.
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -306,6 +312,106 @@ __device__ __forceinline__ int tiles_of_a_split(const int* wanted, int splits, i
   return wanted != nullptr ? max(*wanted, even) : even;
 }
 
+// Which (sequence, split) a decode block works on; false if it has nothing to do.  Without a list the grid has
+// one block per sequence and split up to the bound, and a short sequence's surplus blocks leave at once.  Those
+// blocks are not free: each takes a place on an SM for about a microsecond, and a place beside a block that
+// streams keys took only about three of them before it stayed empty until that block ended (16 sequences of 128
+// to 4,096 keys, 8 kv heads, 15 tiles a block: blocks of the last splits started up to 23 us late behind them, 32 us
+// for the whole kernel against 27 us).  With the host's list every block in front of the grid has keys.
+#define DC_ERR_PLAN 33
+__device__ __forceinline__ bool decode_block_item(const MmaAttnArgs& a, int& seq, int& split, bool& last_listed) {
+  last_listed = false;
+  if (a.items > 0) {
+    if ((int)blockIdx.x >= a.tiles_per_split[1]) return false;
+    const int packed = a.tiles_per_split[2 + blockIdx.x];
+    seq = packed >> 8;
+    split = packed & 127;
+    last_listed = (packed & 128) != 0;
+    return true;
+  }
+  // launched sequence by sequence for a cluster (its members must be neighbours in x), split by split otherwise
+  seq = a.clustered ? blockIdx.z : blockIdx.x;
+  split = a.clustered ? blockIdx.x : blockIdx.z;
+  return true;
+}
+// The host's list must cover what the device's lengths ask for: a sequence whose last listed block ends before
+// its keys do would lose keys, so that block reports it instead (the step's status word; the host raises).
+__device__ __forceinline__ void decode_check_plan(const MmaAttnArgs& a, bool last_listed, int tile_end, int n_tiles) {
+  if (last_listed && tile_end < n_tiles && a.status != nullptr && threadIdx.x == 0) atomicCAS(a.status, 0, DC_ERR_PLAN);
+}
+
+// The end of a decode block: the four warps (each saw a quarter of the keys of every tile) merge their running
+// (acc, max, sum) through shared memory, and the block's result goes out: the final bf16 rows when the block saw
+// the whole sequence, its partial (in the natural-log domain of the combine kernel) otherwise, or stays in shared
+// memory for a cluster.  `smem` must be free of tiles: every copy has landed and every warp has left the last tile.
+__device__ __forceinline__ void decode_merge_warps(const MmaAttnArgs& a, uint8_t* smem, float (&o)[DTILES][4],
+                                                   float m_lo, float m_hi, float l_lo, float l_hi, int warp, int lane,
+                                                   int tok, int head0, int heads_here, int split) {
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+  // Merge the four warps (each saw a quarter of the keys): [warp][row][D + 2] floats in shared memory.
+  float* mg = (float*)smem;
+  constexpr int RS = D + 2;
+  asm volatile("bar.sync 1, 128;" ::: "memory");      // the four compute warps
+  {
+    const int c = (lane & 3) * 2;
+    float* lo = mg + ((size_t)warp * 16 + r_lo) * RS;
+    float* hi = mg + ((size_t)warp * 16 + r_hi) * RS;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+      lo[i * 8 + c] = o[i][0]; lo[i * 8 + c + 1] = o[i][1];
+      hi[i * 8 + c] = o[i][2]; hi[i * 8 + c + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) { lo[D] = m_lo; lo[D + 1] = l_lo; hi[D] = m_hi; hi[D + 1] = l_hi; }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");      // the four compute warps
+  for (int row = warp; row < heads_here; row += DC_WARPS) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) M = fmaxf(M, mg[((size_t)w * 16 + row) * RS + D]);
+    float wgt[DC_WARPS], L = 0.f;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) {
+      const float mw = mg[((size_t)w * 16 + row) * RS + D];
+      wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += wgt[w] * mg[((size_t)w * 16 + row) * RS + D + 1];
+    }
+    const int head = head0 + row;
+    if (a.clustered) {
+      // this split's merged partial stays in shared memory, behind the four warps' area
+      float* fin = mg + (size_t)DC_WARPS * 16 * RS + (size_t)row * RS;
+      for (int dd = lane; dd < D; dd += 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
+        fin[dd] = v;
+      }
+      if (lane == 0) { fin[D] = M; fin[D + 1] = L; }
+    } else if (a.splits == 1) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      bf16* dst = a.out + ((size_t)tok * a.nq + head) * D;
+      for (int dd = lane; dd < D; dd += 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
+        dst[dd] = __float2bfloat16_rn(v * inv);
+      }
+    } else {
+      // partial in the natural-log domain of the combine kernel: max * ln 2
+      float* dst = a.partial + (((size_t)tok * a.nq + head) * a.splits + split) * RS;
+      for (int dd = lane; dd < D; dd += 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
+        dst[dd] = v;
+      }
+      if (lane == 0) { dst[D] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f; dst[D + 1] = L; }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_kernel(MmaAttnArgs a) {
   pdl_launch_dependents();
@@ -314,7 +420,9 @@ attention_decode_kernel(MmaAttnArgs a) {
   // position is written by the kernel before this one, so it is never requested ahead of the wait.
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int seq = blockIdx.z, split = blockIdx.x;
+  int seq, split;
+  bool last_listed;
+  if (!decode_block_item(a, seq, split, last_listed)) return;
   const int hk = blockIdx.y / a.head_chunks, chunk = blockIdx.y % a.head_chunks;
   const int g = a.nq / a.nkv;
   const int heads_here = min(16, g - chunk * 16);
@@ -325,6 +433,7 @@ attention_decode_kernel(MmaAttnArgs a) {
   const int per_split = tiles_of_a_split(a.tiles_per_split, a.splits, n_tiles);
   const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
   if (a.tiles_per_split != nullptr && split > 0 && tile_begin >= n_tiles) return;   // a shorter sequence needs fewer blocks
+  decode_check_plan(a, last_listed, tile_end, n_tiles);
   const int* pages = a.page_ids + a.page_start[seq];
 
   auto issue = [&](int tile) {
@@ -424,68 +533,9 @@ attention_decode_kernel(MmaAttnArgs a) {
     }
   }
   cp_async_wait<0>();
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-
-  // Merge the four warps (each saw a quarter of the keys): [warp][row][D + 2] floats in shared memory.
+  decode_merge_warps(a, smem, o, m_lo, m_hi, l_lo, l_hi, warp, lane, tok, head0, heads_here, split);
   float* mg = (float*)smem;
   constexpr int RS = D + 2;
-  __syncthreads();
-  {
-    const int c = (lane & 3) * 2;
-    float* lo = mg + ((size_t)warp * 16 + r_lo) * RS;
-    float* hi = mg + ((size_t)warp * 16 + r_hi) * RS;
-#pragma unroll
-    for (int i = 0; i < DTILES; ++i) {
-      lo[i * 8 + c] = o[i][0]; lo[i * 8 + c + 1] = o[i][1];
-      hi[i * 8 + c] = o[i][2]; hi[i * 8 + c + 1] = o[i][3];
-    }
-    if ((lane & 3) == 0) { lo[D] = m_lo; lo[D + 1] = l_lo; hi[D] = m_hi; hi[D + 1] = l_hi; }
-  }
-  __syncthreads();
-  for (int row = warp; row < heads_here; row += DC_WARPS) {
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < DC_WARPS; ++w) M = fmaxf(M, mg[((size_t)w * 16 + row) * RS + D]);
-    float wgt[DC_WARPS], L = 0.f;
-#pragma unroll
-    for (int w = 0; w < DC_WARPS; ++w) {
-      const float mw = mg[((size_t)w * 16 + row) * RS + D];
-      wgt[w] = mw == -INFINITY ? 0.f : exp2f(mw - M);
-      L += wgt[w] * mg[((size_t)w * 16 + row) * RS + D + 1];
-    }
-    const int head = head0 + row;
-    if (a.clustered) {
-      // this split's merged partial stays in shared memory, behind the four warps' area
-      float* fin = mg + (size_t)DC_WARPS * 16 * RS + (size_t)row * RS;
-      for (int dd = lane; dd < D; dd += 32) {
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
-        fin[dd] = v;
-      }
-      if (lane == 0) { fin[D] = M; fin[D + 1] = L; }
-    } else if (a.splits == 1) {
-      const float inv = L > 0.f ? 1.f / L : 0.f;
-      bf16* dst = a.out + ((size_t)tok * a.nq + head) * D;
-      for (int dd = lane; dd < D; dd += 32) {
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
-        dst[dd] = __float2bfloat16_rn(v * inv);
-      }
-    } else {
-      // partial in the natural-log domain of the combine kernel: max * ln 2
-      float* dst = a.partial + (((size_t)tok * a.nq + head) * a.splits + split) * RS;
-      for (int dd = lane; dd < D; dd += 32) {
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < DC_WARPS; ++w) v += wgt[w] * mg[((size_t)w * 16 + row) * RS + dd];
-        dst[dd] = v;
-      }
-      if (lane == 0) { dst[D] = M == -INFINITY ? -INFINITY : M * 0.6931471805599453f; dst[D + 1] = L; }
-    }
-  }
   if (a.splits > 1 && !a.clustered && a.tickets != nullptr) {
     // Whoever publishes the last partial of this (sequence, block row) merges them: nobody waits, and the
     // merge reads the splits in order, so the result does not depend on who came last.
@@ -536,6 +586,239 @@ attention_decode_kernel(MmaAttnArgs a) {
     cluster_sync_all();     // nobody leaves while its shared memory may still be read
   }
 }
+
+// ------------------------------------------------------------------------------ decode, TMA-fed
+//
+// The same split-key decode block with its key/value tiles brought by the tensor-memory accelerator instead of by
+// the compute warps: a fifth warp's one thread issues cp.async.bulk.tensor loads (boxes of 64 positions x 64 lanes
+// of the head, 128-byte swizzle, no multicast) into a ring of TD_SLOTS slots, a slot being the 64 x D keys or the
+// 64 x D values of one page; each slot has a `full` barrier (the copy's bytes) and an `empty` barrier (the four
+// compute warps, each when it has read the slot).  Against the cp.async form: up to TD_SLOTS - 1 slots of a
+// block are in flight instead of two stages (at head size 128: 80 KB instead of 64 KB, in 96 KB of shared memory
+// instead of 104 KB), a key slot is free again as soon as the scores exist, the warps meet at no block barrier per
+// tile, and the compute warps issue no copies.  Pages that earlier steps filled are requested before the
+// dependency wait; the page of the query's own position after it.  Every wait is bounded (about two seconds), after
+// which the block records who gave up in `status`, skips its work and leaves.  Head sizes 64 and 128.
+#if D == 64 || D == 128
+#include <cuda.h>
+
+#define TD_SLOTS 6
+#define TD_BOXES (D / 64)                 // boxes of 64 lanes (128 bytes) per row of the head
+#define TD_BOX_BYTES (KT * 128)           // 64 rows of 128 bytes
+#define TD_SLOT_BYTES (TD_BOXES * TD_BOX_BYTES)
+#define TD_THREADS (DC_WARPS * 32 + 32)
+#define TD_WAIT_CYCLES 4000000000ll
+#define TD_ERR_PRODUCER 31
+#define TD_ERR_CONSUMER 32
+
+__device__ __forceinline__ void td_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void td_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void td_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool td_mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait; false when it gave up (it then records `code`) or when somebody else already has.
+__device__ __forceinline__ bool td_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  const long long start = clock64();
+  for (uint32_t i = 0;; ++i) {
+    if (td_mbar_test(bar, parity)) return true;
+    if ((i & 0xf) == 0xf) {
+      if (*abort_flag) return false;
+      if (clock64() - start > TD_WAIT_CYCLES) break;
+    }
+  }
+  atomicCAS(status, 0, code);
+  __threadfence_block();
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void td_tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// Address of the 16-byte chunk `chunk` (8 lanes of the head) of row `row` in a slot written by TMA with the
+// 128-byte swizzle: boxes of 64 lanes, rows of 128 bytes, the chunk index within a row XOR the row's low bits.
+__device__ __forceinline__ uint32_t td_chunk_addr(uint32_t slot, int row, int chunk) {
+  return slot + (uint32_t)(chunk >> 3) * TD_BOX_BYTES + (uint32_t)row * 128u + (uint32_t)(((chunk & 7) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(TD_THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            MmaAttnArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t bars[2 * TD_SLOTS];
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int seq, split;
+  bool last_listed;
+  if (!decode_block_item(a, seq, split, last_listed)) return;
+  const int hk = blockIdx.y / a.head_chunks, chunk = blockIdx.y % a.head_chunks;
+  const int g = a.nq / a.nkv;
+  const int heads_here = min(16, g - chunk * 16);
+  const int head0 = hk * g + chunk * 16;
+  const int tok = a.cu_q[seq];
+  const int pos = a.past[seq];                     // the query's position; keys 0 .. pos are visible
+  const int n_tiles = pos / KT + 1;
+  const int per_split = tiles_of_a_split(a.tiles_per_split, a.splits, n_tiles);
+  const int tile_begin = split * per_split, tile_end = min(n_tiles, tile_begin + per_split);
+  if (a.tiles_per_split != nullptr && split > 0 && tile_begin >= n_tiles) return;   // a shorter sequence needs fewer blocks
+  decode_check_plan(a, last_listed, tile_end, n_tiles);
+  const int* pages = a.page_ids + a.page_start[seq];
+  const int my_tiles = max(tile_end - tile_begin, 0);
+  const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[TD_SLOTS]);
+  const uint32_t ring = smem_addr(smem);
+  if (tid == 0) {
+    for (int s = 0; s < TD_SLOTS; ++s) { td_mbar_init(full0 + 8 * s, 1); td_mbar_init(empty0 + 8 * s, DC_WARPS); }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  volatile int* abort_ptr = &abort_flag;
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+  if (warp == DC_WARPS) {
+    // producer: item 2 t is the key slot of the block's t-th tile, item 2 t + 1 its value slot.  The warp reads
+    // the page numbers of 32 tiles at a time in one round trip; one thread issues the copies.
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
+    bool waited = false, ok = true;
+    for (int base = 0; base < my_tiles && ok; base += 32) {
+      const int my_page = base + lane < my_tiles ? pages[tile_begin + base + lane] : 0;
+      const int here = min(32, my_tiles - base);
+      for (int j = 0; j < here && ok; ++j) {
+        const int page = __shfl_sync(0xffffffffu, my_page, j);
+        if (lane == 0) {
+          const int tile = tile_begin + base + j;
+          if (tile == n_tiles - 1 && !waited) { pdl_wait(); waited = true; }     // the page written in this step
+          const int row = (page * a.nkv + hk) * KT;
+#pragma unroll
+          for (int kv = 0; kv < 2; ++kv) {
+            const int item = 2 * (base + j) + kv, s = item % TD_SLOTS;
+            if (item >= TD_SLOTS &&
+                !td_mbar_wait(empty0 + 8 * s, ((uint32_t)(item / TD_SLOTS) & 1u) ^ 1u, abort_ptr, a.status, TD_ERR_PRODUCER)) {
+              ok = false;
+              break;
+            }
+            const uint32_t dst = ring + (uint32_t)s * TD_SLOT_BYTES;
+            td_mbar_expect_tx(full0 + 8 * s, TD_SLOT_BYTES);
+#pragma unroll
+            for (int b = 0; b < TD_BOXES; ++b)
+              td_tma_load_2d(dst + b * TD_BOX_BYTES, kv ? &map_v : &map_k, 64 * b, row, full0 + 8 * s);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+    }
+  } else {
+    pdl_wait();                                     // the query comes from the kernel before
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;    // rows of the MMA tile are query heads
+    const bf16* q_lo = r_lo < heads_here ? a.q + ((size_t)tok * a.nq + head0 + r_lo) * D : nullptr;
+    const bf16* q_hi = r_hi < heads_here ? a.q + ((size_t)tok * a.nq + head0 + r_hi) * D : nullptr;
+    uint32_t qf[KSTEPS][4];
+    load_q_frags(qf, q_lo, q_hi, lane);
+    const float sl2 = a.scale * LOG2E;
+    bool ok = true;
+    for (int t = 0; t < my_tiles && ok; ++t) {
+      const int tile = tile_begin + t;
+      const int ik = 2 * t, iv = 2 * t + 1;
+      const int sk = ik % TD_SLOTS, sv = iv % TD_SLOTS;
+      const int kbase = tile * KT + warp * 16;      // this warp's 16 keys
+      const bool mine = kbase <= pos;               // some of them are visible
+      uint32_t pf[4];
+      if (!td_mbar_wait(full0 + 8 * sk, (uint32_t)(ik / TD_SLOTS) & 1u, abort_ptr, a.status, TD_ERR_CONSUMER)) { ok = false; break; }
+      if (mine) {
+        const uint32_t k_slot = ring + (uint32_t)sk * TD_SLOT_BYTES;
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          const int m = lane >> 3, r = lane & 7;
+          const int key = warp * 16 + (m >> 1) * 8 + r, ch = ks * 2 + (m & 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(td_chunk_addr(k_slot, key, ch), b0, b1, b2, b3);
+          mma_bf16(s[0], qf[ks], b0, b1);
+          mma_bf16(s[1], qf[ks], b2, b3);
+        }
+        __syncwarp();
+        if (lane == 0) td_mbar_arrive(empty0 + 8 * sk);          // the scores exist: the key slot may be refilled
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int kj = kbase + i * 8 + (lane & 3) * 2;
+          s[i][0] = (kj <= pos) ? s[i][0] * sl2 : -INFINITY;
+          s[i][1] = (kj + 1 <= pos) ? s[i][1] * sl2 : -INFINITY;
+          s[i][2] = (kj <= pos) ? s[i][2] * sl2 : -INFINITY;
+          s[i][3] = (kj + 1 <= pos) ? s[i][3] * sl2 : -INFINITY;
+          mx_lo = fmaxf(mx_lo, fmaxf(s[i][0], s[i][1]));
+          mx_hi = fmaxf(mx_hi, fmaxf(s[i][2], s[i][3]));
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);   // finite: key kbase is visible
+        const float al_lo = exp2f(m_lo - mn_lo), al_hi = exp2f(m_hi - mn_hi);
+        m_lo = mn_lo; m_hi = mn_hi;
+        float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float p0 = exp2f(s[i][0] - mn_lo), p1 = exp2f(s[i][1] - mn_lo);
+          const float p2 = exp2f(s[i][2] - mn_hi), p3 = exp2f(s[i][3] - mn_hi);
+          sum_lo += p0 + p1; sum_hi += p2 + p3;
+          pf[i * 2] = pack_bf16(p0, p1);
+          pf[i * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_lo = l_lo * al_lo + sum_lo; l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+        for (int i = 0; i < DTILES; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+      } else {
+        __syncwarp();
+        if (lane == 0) td_mbar_arrive(empty0 + 8 * sk);
+      }
+      if (!td_mbar_wait(full0 + 8 * sv, (uint32_t)(iv / TD_SLOTS) & 1u, abort_ptr, a.status, TD_ERR_CONSUMER)) { ok = false; break; }
+      if (mine) {
+        const uint32_t v_slot = ring + (uint32_t)sv * TD_SLOT_BYTES;
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+          const int m = lane >> 3, r = lane & 7;
+          const int key = warp * 16 + (m & 1) * 8 + r, ch = dp * 2 + (m >> 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(td_chunk_addr(v_slot, key, ch), b0, b1, b2, b3);
+          mma_bf16(o[dp * 2], pf, b0, b1);
+          mma_bf16(o[dp * 2 + 1], pf, b2, b3);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) td_mbar_arrive(empty0 + 8 * sv);
+    }
+  }
+  // Every copy that was requested has landed (each was waited for) unless somebody gave up; then nothing is
+  // written.  The ring is free for the merge of the warps.
+  __syncthreads();
+  if (abort_flag || warp == DC_WARPS) return;
+  decode_merge_warps(a, smem, o, m_lo, m_hi, l_lo, l_hi, warp, lane, tok, head0, heads_here, split);
+}
+#endif
 
 // One block per (token, head).  With `tiles_per_split` a row has the partials of its sequence's first
 // ceil(tiles / *tiles_per_split) splits only (one token per sequence: the token's index is the sequence's).
@@ -599,6 +882,43 @@ static inline int decode_smem_bytes() {
   return ring > merge ? ring : merge;
 }
 
+#if D == 64 || D == 128
+typedef CUresult (*TdEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A pool as a [rows, D] row-major bf16 matrix cut into boxes of 64 rows x 64 lanes (128 bytes) with the 128-byte swizzle.
+static int td_make_map(CUtensorMap* map, const void* base, long rows) {
+  static TdEncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (TdEncodeTiledFn)p;
+  }
+  if (fn == nullptr || ((uintptr_t)base & 15)) return ODI_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  cuuint32_t box[2] = {64, KT};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
+}
+
+// ODI_DECODE_ATTENTION=cp keeps the cp.async form (for comparisons); anything else, or nothing: the TMA-fed form.
+static bool decode_by_tma() {
+  static int choice = -1;
+  if (choice < 0) {
+    const char* e = getenv("ODI_DECODE_ATTENTION");
+    choice = (e != nullptr && e[0] == 'c') ? 0 : 1;
+  }
+  return choice == 1;
+}
+#endif
+
 // decode != 0 requires q_len == 1 for every sequence (max_q_len == 1).
 extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_tokens, int decode,
                                  cudaStream_t stream) {
@@ -627,9 +947,12 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
   a.clustered = (a.clustered && a.splits > 1 && a.splits <= 8) ? 1 : 0;
   if (a.splits > 1 && !a.clustered && a.partial == nullptr) return ODI_ERR_ARGUMENT;
   if (a.tiles_per_split != nullptr && (a.clustered || a.tickets != nullptr)) return ODI_ERR_ARGUMENT;
+  if (a.items < 0 || (a.items > 0 && a.tiles_per_split == nullptr)) return ODI_ERR_ARGUMENT;
   a.head_chunks = (g + 15) / 16;
   dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
-  if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+  if (!a.clustered) grid = dim3(a.n_seqs, a.nkv * a.head_chunks, a.splits);      // see decode_block_item
+  if (a.items > 0) grid = dim3(a.items, a.nkv * a.head_chunks, 1);
+  if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;
   if (a.clustered) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -648,6 +971,24 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
     odi_rc = (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel, a);
     return launch_status();
   }
+#if D == 64 || D == 128
+  if (a.tickets == nullptr && a.status != nullptr && a.pool_rows > 0 && decode_by_tma()) {
+    // the TMA-fed form: the pools as [pool_rows, D] matrices cut into boxes of 64 rows x 64 lanes
+    CUtensorMap map_k, map_v;
+    int rc = td_make_map(&map_k, a.k_pool, a.pool_rows);
+    if (rc == 0) rc = td_make_map(&map_v, a.v_pool, a.pool_rows);
+    if (rc != 0) return rc;
+    constexpr int TD_SMEM = TD_SLOTS * TD_SLOT_BYTES + 1024;
+    static_assert(TD_SLOTS * TD_SLOT_BYTES >= (DC_WARPS + 1) * 16 * (D + 2) * 4, "the merge of the warps reuses the ring");
+    static bool td_configured = false;
+    if (!td_configured) {
+      cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TD_SMEM);
+      if (e != cudaSuccess) return (int)e;
+      td_configured = true;
+    }
+    odi_rc = launch_pdl((attention_decode_tma_kernel), dim3(grid), dim3(TD_THREADS), TD_SMEM, stream, map_k, map_v, a);
+  } else
+#endif
   odi_rc = launch_pdl((attention_decode_kernel), dim3(grid), dim3(DC_WARPS * 32), dc_smem, stream, a);
   int rc = launch_status();
   if (rc != 0 || a.splits == 1 || a.tickets != nullptr) return rc;
@@ -736,9 +1077,10 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
   a.clustered = 0;      // this entry point is the global-partial form
   a.tickets = nullptr;  // ... with the combine kernel
   a.tiles_per_split = nullptr;   // ... and every sequence cut into `splits` equal ranges
+  a.items = 0;
   a.head_chunks = (a.nq / a.nkv + 15) / 16;
-  dim3 grid(a.splits, a.nkv * a.head_chunks, a.n_seqs);
-  if (grid.y > 65535) return ODI_ERR_UNSUPPORTED;
+  dim3 grid(a.n_seqs, a.nkv * a.head_chunks, a.splits);
+  if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;
   odi_rc = launch_pdl((attention_decode_kernel), dim3(grid), dim3(DC_WARPS * 32), dc_smem, stream, a);
   int rc = launch_status();
   if (rc != 0 || a.splits == 1) return rc;

@@ -86,7 +86,7 @@ class _DecodeContext(StepDescription):
         self._page_tables = [(page_start, ids) for ids in self._page_ids]
         self.slot_list: List[int] = []
         self._kv_lens: List[int] = [longest] * width         # host: the keys each row sees in the coming step
-        self._key_splits: Dict[int, list] = {}               # block rows -> [device int, its value, bound on the splits]
+        self._key_splits: Dict[int, list] = {}               # block rows -> [the list on the device, on the host, bound on the splits]
         self._planned_tiles: tuple = ()
         self._planned_bounds: tuple = ()
 
@@ -104,17 +104,20 @@ class _DecodeContext(StepDescription):
 
     def key_splits(self, block_rows: int):
         """``(tiles_per_split, splits)`` for a mixer whose decode kernel cuts each sequence's keys among
-        blocks.  The first is one int32 on the device that :meth:`plan_key_splits` refreshes before a
-        replay; the second, a power of two, is fixed in the graph being captured."""
+        blocks.  The first is the kernel's list of blocks on the device
+        (:func:`~ondeviceinfer_b200.kernels.ops.key_split_list`, as long as any plan for this width can make it),
+        which :meth:`plan_key_splits` refreshes before a replay; the second, a power of two, is fixed in the
+        graph being captured."""
         if block_rows not in self._key_splits:
             per, splits = ops.plan_key_splits(self.kv_lens, block_rows)
-            self._key_splits[block_rows] = [torch.tensor([per], dtype=torch.int32, device=self.token_ids.device), per,
+            blocks = ops.key_split_list(self.kv_lens, per, ops.key_split_capacity(self.width, block_rows))
+            self._key_splits[block_rows] = [torch.tensor(blocks, dtype=torch.int32, device=self.token_ids.device), blocks,
                                             _power_of_two(splits)]
         entry = self._key_splits[block_rows]
         return entry[0], entry[2]
 
     def plan_key_splits(self, kv_lens: Sequence[int], fix_bounds: bool = False) -> tuple:
-        """Refresh the block sizes for the coming step and return the bounds on the splits that it needs,
+        """Refresh the lists of blocks for the coming step and return the bounds on the splits that it needs,
         as a key for the graph to replay; ``fix_bounds`` makes them the bounds of the next capture."""
         tiles = tuple(-(-n // 64) for n in kv_lens)
         if tiles == self._planned_tiles and not fix_bounds and len(self._planned_bounds) == len(self._key_splits):
@@ -124,9 +127,12 @@ class _DecodeContext(StepDescription):
         for block_rows in sorted(self._key_splits):
             entry = self._key_splits[block_rows]
             per, splits = ops.plan_key_splits(self.kv_lens, block_rows)
-            if per != entry[1]:
-                entry[0].fill_(per)
-                entry[1] = per
+            blocks = ops.key_split_list(self.kv_lens, per, entry[0].numel() - 2)
+            if blocks != entry[1]:
+                # from pageable memory: the copy has left the host's list when the call returns, and is
+                # ordered on the stream before the replay that reads it
+                entry[0].copy_(torch.tensor(blocks, dtype=torch.int32))
+                entry[1] = blocks
             needed.append(_power_of_two(splits))
             if fix_bounds:
                 entry[2] = needed[-1]

@@ -129,10 +129,12 @@ class StepContext(StepDescription):
     def key_splits(self, block_rows: int) -> Tuple[Optional[torch.Tensor], int]:
         """For a mixer whose decode kernel cuts each sequence's keys among blocks (``block_rows`` blocks per
         cut): ``(tiles_per_split, splits)`` as :func:`ondeviceinfer_b200.kernels.ops.plan_key_splits` gives
-        them for this step's sequences, the first as one int32 on the device."""
+        them for this step's sequences, the first on the device as the kernel's list of blocks
+        (:func:`ondeviceinfer_b200.kernels.ops.key_split_list`)."""
         def make():
             per, splits = ops.plan_key_splits(self.kv_lens, block_rows)
-            return torch.tensor([per], dtype=torch.int32).to(self.past.device, non_blocking=True), splits
+            blocks = ops.key_split_list(self.kv_lens, per, ops.key_split_capacity(len(self.kv_lens), block_rows))
+            return torch.tensor(blocks, dtype=torch.int32).to(self.past.device, non_blocking=True), splits
         return self.memo(("key_splits", block_rows), make)
 
 

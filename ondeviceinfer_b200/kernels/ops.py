@@ -11,7 +11,7 @@ from __future__ import annotations
 import ctypes
 import os
 from ctypes import Structure, byref, c_float, c_int, c_long, c_ulonglong, c_void_p
-from typing import Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
@@ -304,9 +304,13 @@ def raise_on_kernel_fault() -> None:
                  21: "gemm_prefill_tcgen05: the TMA producer", 22: "gemm_prefill_tcgen05: the MMA issuer",
                  23: "gemm_prefill_tcgen05: the epilogue",
                  11: "attention_tcgen05: the TMA producer", 12: "attention_tcgen05: the MMA issuer",
-                 13: "attention_tcgen05: the softmax warps"}
+                 13: "attention_tcgen05: the softmax warps",
+                 31: "attention_mma (decode, TMA-fed): the TMA producer", 32: "attention_mma (decode, TMA-fed): a compute warp"}
         for state in _gemm_state.values():
             state["status"].zero_()
+        if code == 33:
+            raise KernelError("attention_mma (decode): the host's list of key blocks ends before a sequence's keys do "
+                              "(the lengths on the device are not those the list was made for); its result is invalid")
         raise KernelError(f"a kernel gave up waiting on a barrier ({names.get(code, code)}); its result is invalid")
 
 
@@ -558,7 +562,7 @@ class _MmaAttnArgs(Structure):
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("splits", c_int),
                 ("head_chunks", c_int), ("scale", c_float), ("clustered", c_int), ("tickets", c_void_p),
-                ("tiles_per_split", c_void_p)]
+                ("tiles_per_split", c_void_p), ("pool_rows", c_long), ("status", c_void_p), ("items", c_int)]
 
 
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -578,6 +582,7 @@ def _attention_tickets(device, count: int) -> torch.Tensor:
 
 
 DECODE_ATTENTION_BLOCKS = 296     # blocks of the split-key decode kernel that a B200 holds at once (148 SMs x 2)
+ROUND_FILL_CUTS = 6               # the most cuts per sequence when whole sequences already run in rounds
 
 
 def plan_key_splits(kv_lens: Sequence[int], block_rows: int, *, blocks: int = DECODE_ATTENTION_BLOCKS,
@@ -609,7 +614,7 @@ def plan_key_splits(kv_lens: Sequence[int], block_rows: int, *, blocks: int = DE
             count = sum(-(-t // size) for t in tiles) * block_rows
             return -(-count // blocks) * (size + 4) + (6 if size < longest else 0)
         best, best_cost = longest, estimate(longest)
-        for cuts in range(2, min(max_splits, 6) + 1):
+        for cuts in range(2, min(max_splits, ROUND_FILL_CUTS) + 1):
             size = -(-longest // cuts)
             if size < min_tiles:
                 break
@@ -620,6 +625,37 @@ def plan_key_splits(kv_lens: Sequence[int], block_rows: int, *, blocks: int = DE
     return per, -(-longest // per)
 
 
+def key_split_capacity(n_seqs: int, block_rows: int, *, blocks: int = DECODE_ATTENTION_BLOCKS, max_splits: int = 32) -> int:
+    """The most (sequence, split) pairs that :func:`plan_key_splits` gives ``n_seqs`` sequences, whatever their
+    lengths: what fills the GPU once, or every sequence whole; with more whole sequences than the GPU holds
+    blocks, every sequence may be cut ``ROUND_FILL_CUTS`` times."""
+    if n_seqs * block_rows > blocks:
+        return n_seqs * min(max_splits, ROUND_FILL_CUTS)
+    return min(n_seqs * max_splits, max(n_seqs, blocks // block_rows))
+
+
+def key_split_list(kv_lens: Sequence[int], tiles_per_split: int, capacity: int) -> List[int]:
+    """The decode attention's list of blocks for sequences of ``kv_lens`` keys cut every ``tiles_per_split`` tiles
+    of 64: ``[tiles_per_split, n, entry...]`` padded with zeros to ``2 + capacity``.  An entry is
+    ``sequence << 8 | 128 if it is the sequence's last | split``; blocks with the most tiles come first, so that
+    when the blocks run in more than one round the short ones fill the end.  The list holds for every bound on
+    the splits that the longest sequence fits (``splits * tiles_per_split`` tiles)."""
+    per = max(1, int(tiles_per_split))
+    entries = []
+    for seq, n in enumerate(kv_lens):
+        tiles = max(1, -(-int(n) // 64))
+        count = -(-tiles // per)
+        if count > 128:
+            raise KernelError(f"{count} blocks for one sequence; an entry of the list holds up to 128")
+        entries.extend((-per, seq, split, False) for split in range(count - 1))
+        entries.append((-(tiles - (count - 1) * per), seq, count - 1, True))
+    if len(entries) > capacity:
+        raise KernelError(f"{len(entries)} blocks of keys for a list of {capacity}: the plan and the graph disagree")
+    entries.sort()
+    packed = [(seq << 8) | (128 if last else 0) | split for _, seq, split, last in entries]
+    return [per, len(packed)] + packed + [0] * (capacity - len(packed))
+
+
 def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                   nq: int, nkv: int, d: int, page_size: int, scale: float, splits: int = 1,
                   partial: Optional[torch.Tensor] = None, cluster: bool = False, merge_in_kernel: bool = False,
@@ -627,10 +663,13 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
     """bf16 causal GQA on the tensor cores: the prefill kernel for any q_len, the split-key
     decode kernel when every sequence brings exactly one token.  No window.
 
-    Decode with ``tiles_per_split`` (one int32 on the device, written by the host; see
+    Decode with ``tiles_per_split`` (int32 on the device, written by the host; see
     :func:`plan_key_splits`): every block takes that many tiles of 64 keys and ``splits`` only bounds the
-    count per sequence; whatever the number says, ``splits`` blocks cover every sequence.  Without it every
-    sequence is cut into ``splits`` equal ranges.
+    count per sequence; whatever the number says, ``splits`` blocks cover every sequence.  With one element the
+    grid has ``splits`` blocks for every sequence and those without keys leave at once; with more it is a
+    :func:`key_split_list`, the grid is as long as the list's capacity (or ``n_seqs * splits`` if that is less),
+    and a list that does not cover the lengths on the device is reported through the kernels' status word.  Without it every sequence is cut into
+    ``splits`` equal ranges.
 
     Decode splits go through the fp32 ``partial`` buffer and a combine kernel.  ``merge_in_kernel=True``
     lets the block that finishes a (sequence, kv head) last merge them instead (an atomic ticket; the same
@@ -665,9 +704,18 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
         if not decode or clustered or tickets is not None:
             raise KernelError("tiles_per_split belongs to the decode kernel with the combine kernel")
         _require(tiles_per_split, "tiles_per_split", torch.int32)
+        if tiles_per_split.numel() == 2:
+            raise KernelError("tiles_per_split is one number or a list of 2 + capacity")
+    # the grid: as long as the list, but no longer than `splits` blocks for every sequence, which no list exceeds
+    # (blocks behind the list's end leave at once, yet each costs a place on an SM for a moment: 64 whole
+    # sequences on a grid for six cuts each measured 4 % more per step)
+    items = min(tiles_per_split.numel() - 2, n_seqs * splits) if tiles_per_split is not None and tiles_per_split.numel() > 1 else 0
+    # what the TMA-fed decode form needs besides: the pools' extent (rows of d) and the error word of its bounded waits
+    pool_rows = k_pool.numel() // d if k_pool.numel() == v_pool.numel() else 0
+    _, _, status = _gemm_buffers(q.device, 0)
     args = _MmaAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
                         _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale, 1 if clustered else 0,
-                        _ptr(tickets), _ptr(tiles_per_split if decode else None))
+                        _ptr(tickets), _ptr(tiles_per_split if decode else None), pool_rows, _ptr(status), items)
     lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(1 if decode else 0),
                                  _stream()), "attention_mma",

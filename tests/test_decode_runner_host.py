@@ -77,6 +77,11 @@ class ToyModel:
             if slot == cache.pad_slot:   # the runs of a capture: every row on the pad slot, results dropped
                 continue
             assert pos == int(ctx.past[row]) == cache.lengths[slot] + self.offset, (row, pos)
+            # the list of key blocks is the one for this step: the row's blocks cover its keys, the last one marked
+            per, count = int(per_tensor[0]), int(per_tensor[1])
+            mine = sorted(e & 255 for e in per_tensor[2:2 + count].tolist() if e >> 8 == row)
+            needed = -(-(pos // 64 + 1) // per)
+            assert mine == list(range(needed - 1)) + [128 | (needed - 1)] and needed <= bound, (row, pos, mine)
             for g, group in enumerate(cache.kv_groups):
                 start, ids = ctx.page_table(g)
                 pages = ids[int(start[row]):int(start[row]) + pos // 64 + 1].tolist()
@@ -150,7 +155,7 @@ def test_runner_follows_the_sequences_through_graphs_captures_and_dropped_rows(c
         # the logits of the replayed step stay readable: the token each live row chose is their argmax
         assert runner.last_logits().shape == (3, VOCAB) and runner.last_logits().argmax(-1).tolist() == tokens
         graph, _, _ = runner._graph_for(4, [n + 1 for n in lengths])
-        per = runner.ctx._key_splits[BLOCK_ROWS][1]
+        per = runner.ctx._key_splits[BLOCK_ROWS][1][0]
         assert math.ceil(max(-(-(n + 1) // 64) for n in lengths) / per) <= graph.bound
     assert any(key[1] == 512 for key in runner._graphs) and first_keys < set(runner._graphs)
     assert int(runner.ctx.active.sum()) == 3 and runner.ctx.slot_list[3] == cache.pad_slot   # restored after the capture

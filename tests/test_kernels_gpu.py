@@ -711,6 +711,52 @@ def test_attention_mma_blocks_of_equal_size(wanted):
                           tiles_per_split=torch.tensor([2], dtype=torch.int32, device=DEV))
 
 
+@pytest.mark.parametrize("d", [128, 64, 48])
+def test_attention_mma_with_the_hosts_list_of_blocks(d):
+    """The same decode with the host's list of (sequence, split) blocks instead of one block per sequence and
+    split: the same bits, whatever the order of the list and however much longer than the list the grid is; and
+    a list made for shorter sequences than the device holds is reported, not computed with."""
+    nq, nkv = 8, 2
+    lengths, past = [1, 1, 1, 1, 1], [1300, 10, 64, 700, 2100]
+    kv_lens = [p + 1 for p in past]
+    setup = paged_setup(lengths, past, nkv, d, "bfloat16", seed=25)
+    q = (torch.randn(5, nq, d) * 0.3).bfloat16().to(DEV)
+    scale = 1.0 / math.sqrt(d)
+    per, splits = ops.plan_key_splits(kv_lens, nkv, blocks=24, max_splits=8)
+    assert splits > 2
+
+    def run(plan):
+        out = torch.empty(5, nq * d, dtype=torch.bfloat16, device=DEV)
+        partial = torch.full((5 * nq * splits * (d + 2),), float("nan"), dtype=torch.float32, device=DEV)
+        ops.attention_mma(q, setup["k_pool"], setup["v_pool"], out, setup["cu_q"], setup["past"], setup["page_start"],
+                          setup["page_ids"], n_seqs=5, max_q_len=1, nq=nq, nkv=nkv, d=d, page_size=64, scale=scale,
+                          splits=splits, partial=partial, tiles_per_split=torch.tensor(plan, dtype=torch.int32, device=DEV))
+        return out
+
+    one_number = run([per])
+    blocks = ops.key_split_list(kv_lens, per, 40)
+    count = blocks[1]
+    assert count == sum(-(-(-(-n // 64)) // per) for n in kv_lens) and len(blocks) == 42
+    assert blocks[2] >> 8 in (0, 4) and blocks[2] & 128 == 0        # a full block of a long sequence comes first
+    assert torch.equal(run(blocks), one_number)
+    assert torch.equal(run(blocks[:2 + count]), one_number)                          # a grid exactly as long as the list
+    assert torch.equal(run(blocks[:2] + blocks[2:2 + count][::-1] + [0] * 7), one_number)    # any order
+    expected = plain_attention(q.float().cpu(), setup["dense"], lengths, past, nq, nkv, d, 0, scale, "bfloat16")
+    close(one_number, expected, "bfloat16")
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    stale = ops.key_split_list([n - 64 * per if n > 64 * per else n for n in kv_lens], per, 40)
+    assert stale[1] < count
+    run(stale)
+    with pytest.raises(ops.KernelError, match="list of key blocks"):
+        ops.raise_on_kernel_fault()
+    ops.raise_on_kernel_fault()                                                      # the word is clear again
+    with pytest.raises(ops.KernelError):
+        ops.key_split_list(kv_lens, per, count - 1)
+    with pytest.raises(ops.KernelError):
+        run([per, 0])
+
+
 TC_ATTN_CASES = [
     # d, nq, nkv, lengths, past
     (128, 4, 2, [128], [0]),                      # exactly one tile of queries, two pages of keys

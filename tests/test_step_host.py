@@ -91,6 +91,44 @@ def test_key_split_plan_covers_every_sequence_and_fills_the_gpu_once():
     assert plan_key_splits([131001], 8) == (64, 32)          # one long sequence: the most splits there are
 
 
+def test_the_list_of_key_blocks_covers_every_sequence_within_the_room_fixed_per_width():
+    """The decode kernel's grid is as long as the list's room, which depends on the number of sequences alone
+    (a graph fixes it): whatever the lengths, the planned blocks fit, every sequence has its blocks 0 .. n-1 with
+    the last one marked, and the blocks with the most tiles come first."""
+    import random
+
+    import pytest
+
+    from ondeviceinfer_b200.kernels.ops import KernelError, key_split_capacity, key_split_list, plan_key_splits
+
+    rng = random.Random(9)
+    for trial in range(300):
+        n = rng.choice([1, 2, 5, 8, 16, 37, 38, 40, 64, 200])
+        rows = rng.choice([1, 2, 4, 8, 16, 32])
+        top = rng.choice([64, 300, 5000, 200000])
+        kv_lens = [rng.randint(1, top) for _ in range(n)] if trial % 3 else [rng.randint(1, top)] * n
+        per, splits = plan_key_splits(kv_lens, rows)
+        room = key_split_capacity(n, rows)
+        blocks = key_split_list(kv_lens, per, room)
+        assert len(blocks) == 2 + room and blocks[0] == per and blocks[1] <= room
+        entries = blocks[2:2 + blocks[1]]
+        assert blocks[2 + blocks[1]:] == [0] * (room - blocks[1])
+        sizes = []
+        for seq, keys in enumerate(kv_lens):
+            tiles = -(-keys // 64)
+            count = -(-tiles // per)
+            assert sorted(e & 255 for e in entries if e >> 8 == seq) == list(range(count - 1)) + [128 | (count - 1)]
+            assert count <= splits
+        for e in entries:
+            tiles = -(-kv_lens[e >> 8] // 64)
+            sizes.append(min(per, tiles - (e & 127) * per))
+        assert sizes == sorted(sizes, reverse=True) and min(sizes) >= 1
+    assert key_split_capacity(8, 8) == 37 and key_split_capacity(64, 8) == 64 * 6 and key_split_capacity(1, 8) == 32
+    assert key_split_list([130, 64], 2, 4) == [2, 3, 0 << 8 | 0, 0 << 8 | 128 | 1, 1 << 8 | 128 | 0, 0]
+    with pytest.raises(KernelError):
+        key_split_list([130, 64], 2, 2)
+
+
 def test_a_kernel_that_gave_up_waiting_is_reported_once_by_name():
     """Every wait inside the tensor-core kernels is bounded; a kernel whose wait ran out writes a code into
     an error word and returns.  Here the word is set by hand (no GPU is made to wait): the host check names
