@@ -10,15 +10,19 @@
 //    results are merged in shared memory.  With several splits the block writes its merged
 //    (acc[d], max, sum) to global memory and the combine kernel below adds the splits of a
 //    (token, head) in order.  Either every sequence is cut into `splits` equal ranges, or every
-//    block takes the same number of tiles (read from the device), so that a long sequence has
-//    more blocks than a short one and all blocks end together.  Two other ways to merge are
-//    kept as options and measured slower on B200: 2..8 splits as a thread-block cluster that
-//    adds the partials in rank order through distributed shared memory, and the block that
-//    finishes a (sequence, kv head) last (an atomic ticket) merging them.
+//    block takes the same number of tiles (planned by the host), so that a long sequence has
+//    more blocks than a short one and all blocks end together; the host may then also list the
+//    (sequence, split) blocks that have keys, and the grid holds no others in front of them.  Two
+//    other ways to merge are kept as options and measured slower on B200: 2..8 splits as a
+//    thread-block cluster that adds the partials in rank order through distributed shared memory,
+//    and the block that finishes a (sequence, kv head) last (an atomic ticket) merging them.
 //
-// Key/value pages (64 positions x head_dim, contiguous) are copied to shared memory with
-// cp.async, double or triple buffered, one block barrier per tile; rows are padded by 16 bytes so that ldmatrix reads
-// are free of bank conflicts for every head size that is a multiple of 16.
+// Key/value pages (64 positions x head_dim, contiguous) reach shared memory in one of two ways.  For head
+// sizes 64 and 128 the decode block has a fifth warp whose one thread issues TMA copies into a ring of
+// six slots with full/empty mbarriers (attention_decode_tma_kernel: 128-byte swizzle, bounded waits).
+// Otherwise, and in the prefill form, the warps copy with cp.async, double or triple buffered, one block
+// barrier per tile, into rows padded by 16 bytes so that ldmatrix reads are free of bank conflicts for
+// every head size that is a multiple of 16.
 //
 // Compile with -DODI_HEAD_DIM=<d>, d a multiple of 16 up to 256.  No window, no ring:
 // layers that need those use attention_simt.cu.

@@ -13,8 +13,9 @@ What a graph fixes besides the width: how a mixer's decode kernel may cut a sequ
 among blocks.  That follows the sequences' lengths, so there is one graph per power of two of
 the longest sequence and per bound on the number of cuts (a power of two as well); all graphs of
 a width share its buffers, and a batch that outgrows its graph in the middle goes on with
-another.  The size of the cuts themselves is one number on the device that the host refreshes
-when a sequence enters another tile of 64 keys (:meth:`_DecodeContext.plan_key_splits`).
+another.  The size of the cuts and the list of (sequence, cut) blocks that follow from it live on
+the device in a buffer of the width; the host refreshes them when a sequence enters another tile of
+64 keys (:meth:`_DecodeContext.plan_key_splits`).
 
 Widths are powers of two up to 32, then multiples of 16; rows beyond the live sequences are padding: they run on a
 slot outside the cache's capacity with a constant length of zero and their results are dropped, so

@@ -113,24 +113,47 @@ def _cache_setup(batch: int, ctx: int, nkv: int, d: int, copies: int, in_order: 
     return pools, page_start, page_ids
 
 
+def _decode_lengths(args) -> list:
+    """``--lengths``: ``a,b,c`` (one sequence each) or ``LO-HI@SEED`` (``--batch`` random lengths); default ``--ctx`` each."""
+    if not args.lengths:
+        return [args.ctx] * args.batch
+    if "@" in args.lengths:
+        span, seed = args.lengths.split("@")
+        lo, hi = (int(v) for v in span.split("-"))
+        return torch.randint(lo, hi + 1, (args.batch,), generator=torch.Generator().manual_seed(int(seed))).tolist()
+    return [int(v) for v in args.lengths.split(",")]
+
+
 def attention_decode_case(args) -> dict:
     nq, nkv, d = args.heads, args.kv_heads, args.head_dim
-    kv_bytes = 2 * args.batch * args.ctx * nkv * d * 2
+    lengths = _decode_lengths(args)
+    batch = len(lengths)
+    kv_bytes = 2 * sum(lengths) * nkv * d * 2
     copies = max(1, int(math.ceil(3 * L2_BYTES / kv_bytes))) if args.rotate else 1
-    pools, page_start, page_ids = _cache_setup(args.batch, args.ctx, nkv, d, copies, args.pages_in_order)
-    q = torch.randn(args.batch, nq, d, device="cuda").bfloat16()
-    out = torch.empty(args.batch, nq * d, dtype=torch.bfloat16, device="cuda")
-    cu_q = torch.arange(args.batch + 1, dtype=torch.int32, device="cuda")
-    past = torch.full((args.batch,), args.ctx - 1, dtype=torch.int32, device="cuda")
-    splits = args.splits
-    partial = torch.empty(args.batch * nq * splits * (d + 2), dtype=torch.float32, device="cuda") if splits > 1 else None
+    pools, page_start, page_ids = _cache_setup(batch, max(lengths), nkv, d, copies, args.pages_in_order)
+    q = torch.randn(batch, nq, d, device="cuda").bfloat16()
+    out = torch.empty(batch, nq * d, dtype=torch.bfloat16, device="cuda")
+    cu_q = torch.arange(batch + 1, dtype=torch.int32, device="cuda")
+    past = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda")
+    splits, blocks, plan = args.splits, None, None
+    if args.planned:       # as a decode step does it: blocks of equal size from the plan, listed by the host
+        block_rows = nkv * -(-(nq // nkv) // 16)
+        per, needed = ops.plan_key_splits(lengths, block_rows)
+        splits = 1
+        while splits < needed:
+            splits *= 2
+        blocks = torch.tensor(ops.key_split_list(lengths, per, ops.key_split_capacity(batch, block_rows)),
+                              dtype=torch.int32, device="cuda")
+        plan = {"tiles_per_split": per, "splits": needed, "bound": splits, "blocks": int(blocks[1]) * block_rows}
+    partial = torch.empty(batch * nq * splits * (d + 2), dtype=torch.float32, device="cuda") if splits > 1 else None
     run = lambda i: ops.attention_mma(q, pools[i][0], pools[i][1], out, cu_q, past, page_start, page_ids,
-                                      n_seqs=args.batch, max_q_len=1, nq=nq, nkv=nkv, d=d, page_size=64,
-                                      scale=1 / math.sqrt(d), splits=splits, partial=partial,
+                                      n_seqs=batch, max_q_len=1, nq=nq, nkv=nkv, d=d, page_size=64,
+                                      scale=1 / math.sqrt(d), splits=splits, partial=partial, tiles_per_split=blocks,
                                       cluster=args.cluster_attention, merge_in_kernel=args.merge_in_kernel)
     us = time_kernel(run, copies, args.reps)
-    return {"case": "attention-decode", "batch": args.batch, "ctx": args.ctx, "splits": splits, "us": us,
-            "kv_GBps": kv_bytes / us / 1e3}
+    ops.raise_on_kernel_fault()
+    return {"case": "attention-decode", "batch": batch, "keys": sum(lengths), "longest": max(lengths), "splits": splits,
+            "plan": plan, "us": us, "kv_GBps": kv_bytes / us / 1e3}
 
 
 def attention_prefill_case(args) -> dict:
@@ -190,6 +213,9 @@ def main(argv=None) -> int:
     parser.add_argument("--heads-per-cta", type=int, default=0, help="attention-prefill on tcgen05: 1, 2 or 0 (default choice)")
     parser.add_argument("--pages-in-order", action="store_true",
                         help="attention-decode: every sequence's pages lie one after another in the pool, as a fresh cache hands them out")
+    parser.add_argument("--lengths", default="", help="attention-decode: a,b,c or LO-HI@SEED for --batch random lengths")
+    parser.add_argument("--planned", action="store_true",
+                        help="attention-decode: the cut that a decode step plans for these lengths, not --splits equal ranges")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--ctx", type=int, default=2048)
     parser.add_argument("--heads", type=int, default=32)
