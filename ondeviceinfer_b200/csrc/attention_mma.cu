@@ -68,6 +68,7 @@ struct MmaAttnArgs {
                           // tiles_per_split[2 .. 2 + n) the host's list of the blocks that have keys, one entry per
                           // (sequence, split): sequence << 8 | 128 if it is the sequence's last split | split.  The grid
                           // is then `items` wide and has no block without work among those with work.
+  int skip_combine;       // decode with global partials: leave them unmerged (the caller's next kernel merges them)
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -837,11 +838,7 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, 
   pdl_wait();
   const size_t row = blockIdx.x;
   int used = splits;
-  if (tiles_per_split != nullptr) {
-    const int n_tiles = past[row / nq] / KT + 1;
-    const int per_split = tiles_of_a_split(tiles_per_split, splits, n_tiles);
-    used = (n_tiles + per_split - 1) / per_split;
-  }
+  if (tiles_per_split != nullptr) used = merge_used_splits(tiles_per_split, splits, past[row / nq]);
   constexpr int RS = D + 2;
   const float* p = partial + row * splits * RS;
   if (used > 32) {
@@ -855,10 +852,12 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, 
     const float ms = s < used ? __ldcg(p + s * RS + D) : -INFINITY;
     const float ls = s < used ? __ldcg(p + s * RS + D + 1) : 0.f;
     const float M = warp_max(ms);
+    // every product and sum below is written as the one instruction it is, so that the output projection's
+    // merge prologue (gemm_tcgen05.cu), which does the same sums thread by thread, gives the same bits
     const float w = ms != -INFINITY ? expf(ms - M) : 0.f;       // an empty split (max -inf) adds nothing
-    const float wl = ms != -INFINITY ? w * ls : 0.f;
+    const float wl = ms != -INFINITY ? __fmul_rn(w, ls) : 0.f;
     float denom = 0.f;
-    for (int i = 0; i < used; ++i) denom += __shfl_sync(0xffffffffu, wl, i);     // in split order, as combine_row adds
+    for (int i = 0; i < used; ++i) denom = __fadd_rn(denom, __shfl_sync(0xffffffffu, wl, i));     // in split order
     weight[s] = w;
     if (s == 0) inv_denom = denom > 0.f ? 1.f / denom : 0.f;
   }
@@ -871,8 +870,8 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, 
     float v = 0.f;
 #pragma unroll
     for (int s = 0; s < 32; ++s)
-      if (s < used && weight[s] > 0.f) v += weight[s] * x[s];      // whatever an empty split's slot holds, it is not read into the sum
-    out[row * D + dd] = __float2bfloat16_rn(v * inv);
+      if (s < used && weight[s] > 0.f) v = __fmaf_rn(weight[s], x[s], v);      // whatever an empty split's slot holds, it is not read into the sum
+    out[row * D + dd] = __float2bfloat16_rn(__fmul_rn(v, inv));
   }
 }
 
@@ -995,10 +994,21 @@ extern "C" int odi_attention_mma(const MmaAttnArgs* args, int max_q_len, int n_t
 #endif
   odi_rc = launch_pdl((attention_decode_kernel), dim3(grid), dim3(DC_WARPS * 32), dc_smem, stream, a);
   int rc = launch_status();
-  if (rc != 0 || a.splits == 1 || a.tickets != nullptr) return rc;
+  if (rc != 0 || a.splits == 1 || a.tickets != nullptr || a.skip_combine) return rc;
   const int combine_threads = D >= 128 ? 128 : 64;
   odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * a.nq), dim3(combine_threads), 0, stream,
                       (const float*)a.partial, a.out, a.splits, a.past, a.nq, a.tiles_per_split);
+  return launch_status();
+}
+
+// The combine kernel alone, for partials that a decode launch with skip_combine left unmerged.
+extern "C" int odi_attention_mma_combine(const float* partial, bf16* out, int n_tokens, int nq, int splits,
+                                         const int* past, const int* tiles_per_split, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (partial == nullptr || out == nullptr || past == nullptr || nq < 1 || splits < 1) return ODI_ERR_ARGUMENT;
+  const int combine_threads = D >= 128 ? 128 : 64;
+  odi_rc = launch_pdl((attention_mma_combine_kernel), dim3(n_tokens * nq), dim3(combine_threads), 0, stream,
+                      partial, out, splits, past, nq, tiles_per_split);
   return launch_status();
 }
 
@@ -1082,6 +1092,7 @@ extern "C" int odi_attention_decode_noalloc(const MmaAttnArgs* args, int n_token
   a.tickets = nullptr;  // ... with the combine kernel
   a.tiles_per_split = nullptr;   // ... and every sequence cut into `splits` equal ranges
   a.items = 0;
+  a.skip_combine = 0;
   a.head_chunks = (a.nq / a.nkv + 15) / 16;
   dim3 grid(a.n_seqs, a.nkv * a.head_chunks, a.splits);
   if (grid.y > 65535 || grid.z > 65535) return ODI_ERR_UNSUPPORTED;

@@ -122,6 +122,26 @@ struct HeadPrepArgs {
   float eps;
 };
 
+// The output of a decode attention whose key splits have not been merged yet (attention_mma.cu leaves it when
+// asked to skip its combine kernel; the output projection's product can take it as its operand).
+struct MergeArgs {
+  const float* partial;   // [tokens, nq, splits, d + 2]: per split the weighted values, their maximum (natural-log
+                          // domain, -inf for a split without keys) and their sum
+  const int* past;        // [tokens]: the position of each token's query (one token per sequence)
+  const int* plan;        // null: every token uses all `splits`; else plan[0] = tiles of 64 keys per split
+  int splits, nq, d;
+};
+
+// How many of its `splits` partials a token at position `pos` has: all of them without a plan, else what its
+// tiles need at plan[0] tiles a split (never fewer tiles a split than `splits` blocks need to cover the sequence).
+__device__ __forceinline__ int merge_used_splits(const int* plan, int splits, int pos) {
+  if (plan == nullptr) return splits;
+  const int n_tiles = pos / 64 + 1;
+  const int even = (n_tiles + splits - 1) / splits;
+  const int per = max(plan[0], even);
+  return (n_tiles + per - 1) / per;
+}
+
 // Position of key `pos` inside a sequence's page list.  A group that keeps every key
 // has ring_pages == 0; a windowed group keeps a ring of ring_pages pages per sequence.
 __device__ __forceinline__ int page_slot_of(int pos, int page_size, int ring_pages) {

@@ -77,7 +77,15 @@ struct GemmArgs {
   // EPI_HEAD_PREP: a tile of 128 features is one head (query heads, then key heads, then value heads);
   // what the stand-alone head preparation would do with the bf16 projections happens in the epilogue.
   HeadPrepArgs hp;
+  // PRO_MERGE: the activation operand is the output of a decode attention whose key splits are still apart
+  // (K = mg.nq * mg.d); merge_kb_cap = the most k-blocks that one CTA of this launch takes.
+  MergeArgs mg;
+  int merge_kb_cap;
 };
+
+#define PRO_NONE 0
+#define PRO_NORM 1         // the operand is made from fp32 rows by RMSNorm
+#define PRO_MERGE 2        // the operand is made from the split partials of a decode attention
 
 // ------------------------------------------------------------------------------ PTX wrappers
 
@@ -267,11 +275,14 @@ __device__ __forceinline__ float emit(const GemmArgs& a, int token, int n, float
 
 
 // The 128 lanes of the accumulator are features (weight rows), its BN columns are tokens.
-// NORM: the four epilogue warps first serve as converters: for every k-block they
+// PRO_NORM: the four epilogue warps first serve as converters: for every k-block they
 // read the fp32 rows, scale them by the row's 1/rms and the norm weight with the roundings of the
 // stand-alone RMSNorm kernel, and write the bf16 operand tile in the swizzled layout that TMA would
 // have produced; the MMA thread waits for them (`ready`) as well as for the weight tile (`full`).
-template <int BN, bool DUAL, int EPI, int STAGES, bool CLUSTER, bool NORM>
+// PRO_MERGE: the converters build the operand tiles of all the CTA's k-blocks at once, behind the ring of
+// weight stages, from the split partials of the decode attention before (what its combine kernel would
+// have rounded to bf16, bit for bit); the MMA thread waits for all of them before its first product.
+template <int BN, bool DUAL, int EPI, int STAGES, bool CLUSTER, int PRO>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmArgs a) {
@@ -279,13 +290,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   constexpr int C_BYTES = BN * BK * 2;                    // columns operand tile
   constexpr int L_TILES = DUAL ? 2 : 1;                   // the gate and the up tile
   constexpr int C_TILES = 1;
-  constexpr int STAGE_BYTES = L_BYTES * L_TILES + C_BYTES * C_TILES;
+  constexpr bool NORM = PRO == PRO_NORM, MERGE = PRO == PRO_MERGE;
+  constexpr int STAGE_BYTES = L_BYTES * L_TILES + (MERGE ? 0 : C_BYTES * C_TILES);   // MERGE: the token tiles lie behind the ring
   constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
   constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   static_assert(!NORM || (BN % 16 == 0 && BN <= 64), "the norm prologue takes token tiles of 16, 32 or 64");
+  static_assert(!MERGE || (EPI == EPI_RESIDUAL && !DUAL && BN <= 32), "the merge prologue serves the output projection at decode widths");
   // EPI_HEAD_PREP stages the finished rows behind the split partials (which peers may still be reading)
   constexpr int HP_STAGE_OFFSET = BN * BM * 4;
   static_assert(EPI != EPI_HEAD_PREP || (!DUAL && BN <= 64 && 2 * BN * BM * 4 <= STAGES * STAGE_BYTES),
@@ -327,7 +340,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // Weights are never written by a kernel, so their first tiles are
       // requested before this grid waits for the kernels it depends on; only the activation
       // tiles (and everything the epilogue touches, which runs after them) come after the wait.
-      constexpr uint32_t TX_BYTES = NORM ? L_BYTES * L_TILES : STAGE_BYTES;   // NORM: the converters fill the rest
+      constexpr uint32_t TX_BYTES = PRO != PRO_NONE ? L_BYTES * L_TILES : STAGE_BYTES;   // else the converters make the token tile
       const int pre = min(STAGES, kb_count);
       for (int i = 0; i < pre; ++i) {
         const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
@@ -339,7 +352,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // (Asking the rest of this CTA's weights into L2 here as well, with cp.async.bulk.prefetch.tensor, measured
       // no gain for two k-blocks beyond the ring (3.46 against 3.49 ms a step at batch 8) and a loss beyond that:
       // 3.55 with four, 3.67 with eight, 4.16 with all.)
-      if (!NORM) {
+      if (PRO == PRO_NONE) {
         pdl_wait();
         for (int i = 0; i < pre; ++i) {
           const uint32_t dst = smem_u32(smem + (size_t)i * STAGE_BYTES);
@@ -355,14 +368,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         mbar_expect_tx(full0 + 8 * s, TX_BYTES);
         tma_load_2d(dst, map_l, k0, l_row, full0 + 8 * s);
         if (L_TILES == 2) tma_load_2d(dst + L_BYTES, map_l, k0, l_row + a.dual_offset, full0 + 8 * s);
-        if (!NORM) tma_load_2d(dst + L_BYTES * L_TILES, map_c, k0, c_row, full0 + 8 * s);
+        if (PRO == PRO_NONE) tma_load_2d(dst + L_BYTES * L_TILES, map_c, k0, c_row, full0 + 8 * s);
         if (C_TILES == 2) tma_load_2d(dst + L_BYTES * L_TILES + C_BYTES, map_c, k0, c_row + a.dual_offset, full0 + 8 * s);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc_bf16(BM, BN);
-      bool ok = true;
+      // MERGE: every token tile of this CTA is ready at once (the first `ready` barrier)
+      bool ok = !MERGE || mbar_wait(ready0, 0, abort_ptr, a.status, GEMM_ERR_TIMEOUT_MMA);
       for (int i = 0; i < kb_count && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
@@ -374,8 +388,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
         const uint64_t dl = smem_desc_k_sw128(sa);
         const uint64_t dl2 = smem_desc_k_sw128(sa + L_BYTES);
-        const uint64_t dc = smem_desc_k_sw128(sa + L_BYTES * L_TILES);
-        const uint64_t dc2 = smem_desc_k_sw128(sa + L_BYTES * L_TILES + C_BYTES);
+        const uint64_t dc = smem_desc_k_sw128(MERGE ? smem_u32(smem + (size_t)STAGES * STAGE_BYTES + (size_t)i * C_BYTES)
+                                                    : sa + L_BYTES * L_TILES);
 #pragma unroll
         for (int j = 0; j < BK / 16; ++j) {
           const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
@@ -472,6 +486,78 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           fetch_x(ring[j], i + DEPTH);
         }
       }
+    }
+    if (MERGE) {
+      const MergeArgs& mg = a.mg;
+      const int tid_c = threadIdx.x - 64;
+      const int RS = mg.d + 2, WS = mg.splits + 2;
+      const int k_begin = kb_begin * BK;                      // K is a multiple of 64 here: whole k-blocks
+      const int n_chunks = kb_count * (BK / 8);               // 16-byte pieces of a token's row in this CTA's range
+      const int head_begin = k_begin / mg.d;
+      const int n_heads = (k_begin + kb_count * BK - 1) / mg.d - head_begin + 1;
+      const int n_tok = min(BN, a.tokens - tok0);
+      uint8_t* c_region = smem + (size_t)STAGES * STAGE_BYTES;
+      float* wtab = (float*)(c_region + (size_t)a.merge_kb_cap * C_BYTES);   // per (token, head): weights, 1 / denominator, count
+      pdl_wait();                                             // the partials come from the kernel before
+      // a thread per (token, head): the weights of its splits, as the combine kernel makes them
+      for (int pair = tid_c; pair < n_tok * n_heads; pair += 128) {
+        const int token = tok0 + pair / n_heads, h = head_begin + pair % n_heads;
+        const int used = merge_used_splits(mg.plan, mg.splits, mg.past[token]);
+        const float* p = mg.partial + ((size_t)token * mg.nq + h) * mg.splits * RS + mg.d;
+        float* wrow = wtab + (size_t)pair * WS;
+        float M = -INFINITY;
+#pragma unroll 4
+        for (int s = 0; s < used; ++s) M = fmaxf(M, __ldcg(p + s * RS));
+        float denom = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < used; ++s) {
+          const float ms = __ldcg(p + s * RS), ls = __ldcg(p + s * RS + 1);
+          const float w = ms != -INFINITY ? expf(ms - M) : 0.f;       // an empty split (max -inf) adds nothing
+          denom = __fadd_rn(denom, ms != -INFINITY ? __fmul_rn(w, ls) : 0.f);
+          wrow[s] = w;
+        }
+        wrow[mg.splits] = denom > 0.f ? 1.f / denom : 0.f;
+        wrow[mg.splits + 1] = __int_as_float(used);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // the four converter warps
+      // a thread per (token row, 16-byte piece): the splits' values added in split order, rounded once
+      for (int item = tid_c; item < BN * n_chunks; item += 128) {
+        const int t = item / n_chunks, c = item % n_chunks;
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);            // rows beyond the tokens are zeros
+        if (t < n_tok) {
+          const int k = k_begin + c * 8, h = k / mg.d, dd = k % mg.d;
+          const float* wrow = wtab + (size_t)(t * n_heads + h - head_begin) * WS;
+          const int used = __float_as_int(wrow[mg.splits + 1]);
+          const float inv = wrow[mg.splits];
+          const float* p = mg.partial + ((size_t)(tok0 + t) * mg.nq + h) * mg.splits * RS + dd;
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = 0.f;
+#pragma unroll 4
+          for (int s = 0; s < used; ++s) {
+            // rows of d + 2 floats are 8-byte aligned; whatever an empty split's slot holds is loaded but not added
+            const float2* src = (const float2*)(p + (size_t)s * RS);
+            const float2 x0 = __ldcg(src), x1 = __ldcg(src + 1), x2 = __ldcg(src + 2), x3 = __ldcg(src + 3);
+            const float w = wrow[s];
+            if (w > 0.f) {
+              v[0] = __fmaf_rn(w, x0.x, v[0]); v[1] = __fmaf_rn(w, x0.y, v[1]);
+              v[2] = __fmaf_rn(w, x1.x, v[2]); v[3] = __fmaf_rn(w, x1.y, v[3]);
+              v[4] = __fmaf_rn(w, x2.x, v[4]); v[5] = __fmaf_rn(w, x2.y, v[5]);
+              v[6] = __fmaf_rn(w, x3.x, v[6]); v[7] = __fmaf_rn(w, x3.y, v[7]);
+            }
+          }
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv));
+          __nv_bfloat162 h1 = __floats2bfloat162_rn(__fmul_rn(v[2], inv), __fmul_rn(v[3], inv));
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(__fmul_rn(v[4], inv), __fmul_rn(v[5], inv));
+          __nv_bfloat162 h3 = __floats2bfloat162_rn(__fmul_rn(v[6], inv), __fmul_rn(v[7], inv));
+          packed = make_uint4(*(uint32_t*)&h0, *(uint32_t*)&h1, *(uint32_t*)&h2, *(uint32_t*)&h3);
+        }
+        uint8_t* tile = c_region + (size_t)(c >> 3) * C_BYTES;
+        *(uint4*)(tile + t * 128 + (((c & 7) ^ (t & 7)) << 4)) = packed;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ready0);
     }
     bool ok = mbar_wait(acc_bar, 0, abort_ptr, a.status, GEMM_ERR_TIMEOUT_EPILOGUE);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -702,9 +788,18 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   return r == CUDA_SUCCESS ? 0 : ODI_ERR_ARGUMENT;
 }
 
-template <int BN, bool DUAL, int EPI, bool CLUSTER, bool NORM = false>
+// Dynamic shared memory of the merge prologue's form beyond its ring of weight stages: the token tiles of
+// `kb_cap` k-blocks and the table of the splits' weights for the heads those k-blocks can touch.
+static inline int merge_extra_smem(int bn, int kb_cap, int splits, int d) {
+  const int heads = (kb_cap * BK + d - 1) / d + 1;
+  return kb_cap * bn * BK * 2 + bn * heads * (splits + 2) * 4;
+}
+#define MERGE_SMEM_LIMIT (96 * 1024)      // per CTA, so that two fit on an SM
+
+template <int BN, bool DUAL, int EPI, bool CLUSTER, int PRO = PRO_NONE>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, dim3 grid, cudaStream_t stream) {
-  constexpr int STAGE_BYTES = BM * BK * 2 * (DUAL ? 2 : 1) + BN * BK * 2;
+  constexpr bool MERGE = PRO == PRO_MERGE;
+  constexpr int STAGE_BYTES = BM * BK * 2 * (DUAL ? 2 : 1) + (MERGE ? 0 : BN * BK * 2);
   // A CTA takes about 72 KB (four stages of a 128 x 16 tile), so that three CTAs fit on an
   // SM: several short pipelines per SM hide each other's set-up, drain and split exchange, and the
   // CTAs of the next kernel of the stream find room to move in and request their first weight tiles
@@ -718,14 +813,16 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
   // projection 26.0 / 24.8 / 47.9 against 21.8, output projection 13.3 / 12.6 / 27.1 against 9.7, q/k/v 14.4 / 20.8 /
   // 34.2 against 11.3, gate/up with the SiLU gate 55 at every budget against 38.4 + 3.5: above 32 tokens the
   // projections go to the library, see parts/linear.py.)
-  constexpr int BUDGET = ODI_GEMM_DECODE_SMEM_KB * 1024;
+  // (MERGE: three weight stages, so that with the token tiles behind them a CTA still takes about 72 KB.)
+  constexpr int BUDGET = MERGE ? 48 * 1024 : ODI_GEMM_DECODE_SMEM_KB * 1024;
   constexpr int STAGES = BUDGET / STAGE_BYTES < 2 ? 2 : (BUDGET / STAGE_BYTES > 12 ? 12 : BUDGET / STAGE_BYTES);
-  constexpr int SMEM = STAGES * STAGE_BYTES + 1024;
+  const int SMEM = STAGES * STAGE_BYTES + 1024 + (MERGE ? merge_extra_smem(BN, a.merge_kb_cap, a.mg.splits, a.mg.d) : 0);
+  if (MERGE && SMEM > MERGE_SMEM_LIMIT) return ODI_ERR_UNSUPPORTED;
   static_assert(!CLUSTER || (DUAL ? 2 : 1) * BN * BM * 4 <= STAGES * STAGE_BYTES, "the split partial must fit the stage memory");
-  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, CLUSTER, NORM>;
+  auto kernel = gemm_tcgen05_kernel<BN, DUAL, EPI, STAGES, CLUSTER, PRO>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MERGE ? MERGE_SMEM_LIMIT : SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -757,9 +854,16 @@ static int dispatch_epi(int epi, const CUtensorMap& mw, const CUtensorMap& mx, c
   if (a.norm_x != nullptr) {
     // the norm prologue exists for the two products that follow a norm in a decoder layer, at decode widths
     if constexpr (BN <= 32) {
-      if (epi == EPI_STORE_BF16) return launch<BN, false, EPI_STORE_BF16, CLUSTER, true>(mw, mx, a, grid, stream);
-      if (epi == EPI_SWIGLU) return launch<BN, true, EPI_SWIGLU, CLUSTER, true>(mw, mx, a, grid, stream);
-      if (epi == EPI_HEAD_PREP) return launch<BN, false, EPI_HEAD_PREP, CLUSTER, true>(mw, mx, a, grid, stream);
+      if (epi == EPI_STORE_BF16) return launch<BN, false, EPI_STORE_BF16, CLUSTER, PRO_NORM>(mw, mx, a, grid, stream);
+      if (epi == EPI_SWIGLU) return launch<BN, true, EPI_SWIGLU, CLUSTER, PRO_NORM>(mw, mx, a, grid, stream);
+      if (epi == EPI_HEAD_PREP) return launch<BN, false, EPI_HEAD_PREP, CLUSTER, PRO_NORM>(mw, mx, a, grid, stream);
+    }
+    return ODI_ERR_UNSUPPORTED;
+  }
+  if (a.mg.partial != nullptr) {
+    // the merge prologue exists for the product that follows a decode attention: the output projection
+    if constexpr (BN <= 32) {
+      if (epi == EPI_RESIDUAL) return launch<BN, false, EPI_RESIDUAL, CLUSTER, PRO_MERGE>(mw, mx, a, grid, stream);
     }
     return ODI_ERR_UNSUPPORTED;
   }
@@ -795,10 +899,11 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
                              int ldo, int epi, int bn, int splits, int cluster, float* scratch,
                              int* tickets, int* status, const float* norm_x, const float* norm_w,
                              const float* norm_parts, int norm_n_parts, float norm_eps, float* sumsq_out,
-                             const HeadPrepArgs* head_prep, const float* bias, int no_loads, cudaStream_t stream) {
+                             const HeadPrepArgs* head_prep, const float* bias, int no_loads, const MergeArgs* merge,
+                             cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ODI_ERR_UNSUPPORTED;
-  if (x == nullptr && norm_x == nullptr) return ODI_ERR_ARGUMENT;
+  if ((x != nullptr) + (norm_x != nullptr) + (merge != nullptr) != 1) return ODI_ERR_ARGUMENT;
   const int total_kb = (K + BK - 1) / BK;
   if (splits < 1 || splits > total_kb) return ODI_ERR_ARGUMENT;
   const bool clustered = cluster && splits > 1 && splits <= 8 && bn <= 64;
@@ -809,7 +914,7 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   CUtensorMap mw, mx;
   int rc = make_map(&mw, w, w_rows, K, BM);
   if (rc != 0) return rc;
-  rc = make_map(&mx, norm_x != nullptr ? w : x, tokens, K, bn);    // with the norm prologue the map is not used
+  rc = make_map(&mx, x == nullptr ? w : x, tokens, K, bn);    // with a prologue the map is not used
   if (rc != 0) return rc;
   GemmArgs a;
   a.out = out; a.scratch = scratch; a.tickets = tickets; a.status = status;
@@ -824,7 +929,18 @@ extern "C" int odi_gemm_bf16(const void* x, const void* w, void* out, int tokens
   a.sumsq_out = sumsq_out;
   a.bias = bias;
   a.no_loads = no_loads;
-  if (no_loads && (norm_x != nullptr || splits != 1)) return ODI_ERR_ARGUMENT;     // the self-test is one plain tile
+  if (no_loads && (x == nullptr || splits != 1)) return ODI_ERR_ARGUMENT;     // the self-test is one plain tile
+  a.mg = MergeArgs{};
+  a.merge_kb_cap = 0;
+  if (merge != nullptr) {
+    // heads of a multiple of 64 (a k-block lies inside one head), K = all heads, one token per sequence, up to 32 splits
+    a.mg = *merge;
+    if (bn > 32 || epi != EPI_RESIDUAL || !(clustered || splits == 1)) return ODI_ERR_UNSUPPORTED;
+    if (a.mg.partial == nullptr || a.mg.past == nullptr || a.mg.splits < 1 || a.mg.splits > 32 || a.mg.d <= 0 ||
+        a.mg.d % BK != 0 || (long)a.mg.nq * a.mg.d != K || ((uintptr_t)a.mg.partial & 7))
+      return ODI_ERR_UNSUPPORTED;
+    a.merge_kb_cap = (total_kb + splits - 1) / splits;
+  }
   if (epi == EPI_HEAD_PREP) {
     // heads of 128 (a tile is a head), whole-head rotation or none, keys and values written, tokens in columns
     if (head_prep == nullptr) return ODI_ERR_ARGUMENT;

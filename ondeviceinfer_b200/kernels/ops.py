@@ -357,6 +357,27 @@ def gemm_bf16_fuses_head_prep(tokens: int, n_out: int, K: int, *, d: int, rot_di
             and (not rotated or rot_dim == d))
 
 
+MERGE_SMEM_LIMIT = 96 * 1024
+
+
+def gemm_bf16_fuses_merge(tokens: int, n_out: int, K: int, *, splits: int, nq: int, d: int) -> bool:
+    """Whether the planned form of this residual product can take the unmerged splits of a decode attention
+    (``splits`` partials per token and head, ``nq`` heads of ``d``) as its operand: decode widths, heads of a
+    multiple of 64, K all the heads, and shared memory for the token tiles of a CTA's share of K."""
+    bn, k_splits = gemm_bf16_plan(tokens, n_out, K, EPI_RESIDUAL)
+    if bn > 32 or tokens > 64 or k_splits > 8 or not 1 <= splits <= 32 or d % 64 or nq * d != K:
+        return False
+    kb_cap = -(-(K // 64) // k_splits)
+    heads = -(-kb_cap * 64 // d) + 1
+    smem = 3 * 128 * 64 * 2 + 1024 + kb_cap * bn * 64 * 2 + bn * heads * (splits + 2) * 4
+    return smem <= MERGE_SMEM_LIMIT
+
+
+class _MergeArgs(Structure):
+    _fields_ = [("partial", c_void_p), ("past", c_void_p), ("plan", c_void_p), ("splits", c_int), ("nq", c_int),
+                ("d", c_int)]
+
+
 def gemm_bf16_gives_sumsq(tokens: int, n_out: int, K: int) -> bool:
     """Whether the planned form of this residual product can leave the rows' sums of squares."""
     bn, splits = gemm_bf16_plan(tokens, n_out, K, EPI_RESIDUAL)
@@ -366,7 +387,7 @@ def gemm_bf16_gives_sumsq(tokens: int, n_out: int, K: int) -> bool:
 def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Tensor], epi: int, *,
               bn: Optional[int] = None, splits: Optional[int] = None, cluster: bool = True,
               norm: Optional[tuple] = None, sumsq_out: Optional[torch.Tensor] = None, head_prep=None,
-              bias: Optional[torch.Tensor] = None) -> None:
+              bias: Optional[torch.Tensor] = None, merge: Optional[tuple] = None) -> None:
     """Tensor-core product out = epilogue(x w^T): x [tokens, K] bf16, w [rows, K] bf16.
 
     ``EPI_STORE_BF16`` / ``EPI_STORE_F32``: out [tokens, rows]; ``EPI_RESIDUAL``: out (fp32) += product;
@@ -383,7 +404,27 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
     w holds query, key and value heads of 128 rows each; the epilogue rounds the projections to bf16 and
     does what :func:`head_prep` does with them (``gemm_bf16_fuses_head_prep`` says when).
     ``bias`` (fp32, one per row of w): added to the fp32 product before the epilogue's own work and rounding.
+    ``merge = (partial, past, plan, splits, nq, d)`` instead of ``x``, with ``EPI_RESIDUAL``: the operand is the
+    output of a decode attention whose ``splits`` partials per token and head are still apart in ``partial``
+    (:func:`attention_mma` with ``combine=False``; ``plan``: its ``tiles_per_split`` or None); the kernel merges
+    them as the combine kernel would, bit for bit (``gemm_bf16_fuses_merge`` says when it can).
     """
+    merge_args = None
+    if merge is not None:
+        if x is not None or norm is not None or epi != EPI_RESIDUAL:
+            raise KernelError("gemm_bf16 takes merge instead of x and norm, with EPI_RESIDUAL")
+        partial, past, plan, m_splits, m_nq, m_d = merge
+        _require(partial, "merge partial", torch.float32)
+        _require(past, "merge past", torch.int32, 1)
+        if plan is not None:
+            _require(plan, "merge plan", torch.int32, 1)
+        tokens = past.numel()
+        if partial.numel() < tokens * m_nq * m_splits * (m_d + 2):
+            raise KernelError("merge partial is smaller than tokens x heads x splits x (d + 2)")
+        if not gemm_bf16_fuses_merge(tokens, w.shape[0], m_nq * m_d, splits=m_splits, nq=m_nq, d=m_d):
+            raise KernelError("this product cannot take unmerged attention splits (see gemm_bf16_fuses_merge)")
+        merge_args = _MergeArgs(_ptr(partial), _ptr(past), _ptr(plan), m_splits, m_nq, m_d)
+        x_like = torch.empty((tokens, m_nq * m_d), dtype=torch.bfloat16, device="meta")
     if norm is not None:
         if x is not None:
             raise KernelError("gemm_bf16 takes either x or norm")
@@ -395,7 +436,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
             raise KernelError(f"norm operands disagree: rows {tuple(rows.shape)}, weight {tuple(norm_w.shape)}, "
                               f"parts {tuple(parts.shape)}")
         x_like = rows
-    else:
+    elif merge is None:
         _require(x, "x", torch.bfloat16, 2)
         x_like = x
     _require(w, "w", torch.bfloat16, 2)
@@ -415,7 +456,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
         _require(sumsq_out, "sumsq_out", torch.float32, 2)
         if epi != EPI_RESIDUAL or sumsq_out.shape != (gemm_bf16_sumsq_parts(n_out), tokens):
             raise KernelError("sumsq_out goes with EPI_RESIDUAL and has one row per tile of 128 features")
-    if not gemm_bf16_supported(x_like, w):
+    if not gemm_bf16_supported(w if merge is not None else x_like, w):
         raise KernelError(f"gemm_tcgen05 needs K a multiple of 8 and 16-byte aligned operands (K={K})")
     _require_bias(bias, w_rows)
     plan_bn, plan_splits = gemm_bf16_plan(tokens, n_out, K, epi)
@@ -436,7 +477,7 @@ def gemm_bf16(x: Optional[torch.Tensor], w: torch.Tensor, out: Optional[torch.Te
     _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(tokens), c_int(n_out), c_int(K), c_int(w_rows),
                              c_int(n_out), c_int(epi), c_int(bn), c_int(splits), c_int(1 if cluster else 0), _ptr(scratch), _ptr(tickets), _ptr(status), *norm_args,
                              _ptr(sumsq_out), byref(head_prep) if head_prep is not None else _ptr(None), _ptr(bias),
-                             c_int(0), _stream()),
+                             c_int(0), byref(merge_args) if merge_args is not None else _ptr(None), _stream()),
            "gemm_tcgen05")
 
 
@@ -462,7 +503,7 @@ def selftest_bounded_wait(device="cuda:0") -> int:
         _check(lib.odi_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(16), c_int(128), c_int(256), c_int(128), c_int(128),
                                  c_int(EPI_STORE_F32), c_int(16), c_int(1), c_int(0), _ptr(scratch), _ptr(tickets),
                                  _ptr(status), none, none, none, c_int(0), c_float(0.0), none, none, none, c_int(1),
-                                 _stream()), "gemm_tcgen05 (bounded-wait self-test)")
+                                 none, _stream()), "gemm_tcgen05 (bounded-wait self-test)")
         torch.cuda.synchronize(device)
     return int(status[0].item())
 
@@ -562,7 +603,8 @@ class _MmaAttnArgs(Structure):
                 ("partial", c_void_p), ("cu_q", c_void_p), ("past", c_void_p), ("page_start", c_void_p),
                 ("page_ids", c_void_p), ("n_seqs", c_int), ("nq", c_int), ("nkv", c_int), ("splits", c_int),
                 ("head_chunks", c_int), ("scale", c_float), ("clustered", c_int), ("tickets", c_void_p),
-                ("tiles_per_split", c_void_p), ("pool_rows", c_long), ("status", c_void_p), ("items", c_int)]
+                ("tiles_per_split", c_void_p), ("pool_rows", c_long), ("status", c_void_p), ("items", c_int),
+                ("skip_combine", c_int)]
 
 
 MMA_HEAD_DIMS = tuple(range(16, 257, 16))
@@ -659,7 +701,7 @@ def key_split_list(kv_lens: Sequence[int], tiles_per_split: int, capacity: int) 
 def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n_seqs: int, max_q_len: int,
                   nq: int, nkv: int, d: int, page_size: int, scale: float, splits: int = 1,
                   partial: Optional[torch.Tensor] = None, cluster: bool = False, merge_in_kernel: bool = False,
-                  tiles_per_split: Optional[torch.Tensor] = None) -> None:
+                  tiles_per_split: Optional[torch.Tensor] = None, combine: bool = True) -> None:
     """bf16 causal GQA on the tensor cores: the prefill kernel for any q_len, the split-key
     decode kernel when every sequence brings exactly one token.  No window.
 
@@ -671,7 +713,9 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
     and a list that does not cover the lengths on the device is reported through the kernels' status word.  Without it every sequence is cut into
     ``splits`` equal ranges.
 
-    Decode splits go through the fp32 ``partial`` buffer and a combine kernel.  ``merge_in_kernel=True``
+    Decode splits go through the fp32 ``partial`` buffer and a combine kernel; ``combine=False`` leaves them in
+    ``partial`` unmerged (``out`` may then be None) for a product that takes them as its operand
+    (:func:`gemm_bf16` with ``merge``).  ``merge_in_kernel=True``
     lets the block that finishes a (sequence, kv head) last merge them instead (an atomic ticket; the same
     bits); on B200 that measured slower (20.1 against 17.5 us at 8 x 2048 with 4 splits, 17.1 against 10.8 us
     at 1 x 2048 with 16: the fence, the ticket and the merge lengthen the slowest block).  ``cluster=True``
@@ -683,16 +727,19 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
     if page_size != 64:
         raise KernelError("the tensor-core attention works on pages of 64 positions")
     _require(q, "q", torch.bfloat16)
-    _require(out, "out", torch.bfloat16)
     _require(k_pool, "k_pool", torch.bfloat16)
     _require(v_pool, "v_pool", torch.bfloat16)
     n_tokens = q.numel() // (nq * d)
-    if out.numel() != q.numel():
-        raise KernelError("q and out disagree")
     decode = max_q_len == 1
     if not decode:
         splits = 1
     clustered = cluster and 1 < splits <= 8
+    if not combine and (not decode or splits == 1 or clustered or merge_in_kernel):
+        raise KernelError("combine=False belongs to the decode kernel with more than one split and global partials")
+    if combine or out is not None:
+        _require(out, "out", torch.bfloat16)
+        if out.numel() != q.numel():
+            raise KernelError("q and out disagree")
     if splits > 1 and not clustered:
         need = n_tokens * nq * splits * (d + 2)
         if partial is None or partial.numel() < need or partial.dtype != torch.float32:
@@ -715,11 +762,29 @@ def attention_mma(q, k_pool, v_pool, out, cu_q, past, page_start, page_ids, *, n
     _, _, status = _gemm_buffers(q.device, 0)
     args = _MmaAttnArgs(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(partial), _ptr(cu_q), _ptr(past),
                         _ptr(page_start), _ptr(page_ids), n_seqs, nq, nkv, splits, 0, scale, 1 if clustered else 0,
-                        _ptr(tickets), _ptr(tiles_per_split if decode else None), pool_rows, _ptr(status), items)
+                        _ptr(tickets), _ptr(tiles_per_split if decode else None), pool_rows, _ptr(status), items,
+                        0 if combine else 1)
     lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
     _check(lib.odi_attention_mma(byref(args), c_int(max_q_len), c_int(n_tokens), c_int(1 if decode else 0),
                                  _stream()), "attention_mma",
-           2 if (splits > 1 and not clustered and tickets is None) else 1)
+           2 if (splits > 1 and not clustered and tickets is None and combine) else 1)
+
+
+def attention_mma_combine(partial: torch.Tensor, out: torch.Tensor, past: torch.Tensor, *, nq: int, d: int, splits: int,
+                          tiles_per_split: Optional[torch.Tensor] = None) -> None:
+    """Merge the ``splits`` partials per token and head that :func:`attention_mma` left with ``combine=False``
+    into ``out`` [tokens, nq * d] (the kernel that the launch would have run itself)."""
+    _require(partial, "partial", torch.float32)
+    _require(out, "out", torch.bfloat16)
+    _require(past, "past", torch.int32, 1)
+    tokens = past.numel()
+    if d not in MMA_HEAD_DIMS or out.numel() != tokens * nq * d or partial.numel() < tokens * nq * splits * (d + 2):
+        raise KernelError("attention_mma_combine: sizes disagree")
+    if tiles_per_split is not None:
+        _require(tiles_per_split, "tiles_per_split", torch.int32)
+    lib = load_library("attention_mma", {"ODI_HEAD_DIM": d})
+    _check(lib.odi_attention_mma_combine(_ptr(partial), _ptr(out), c_int(tokens), c_int(nq), c_int(splits), _ptr(past),
+                                         _ptr(tiles_per_split), _stream()), "attention_mma_combine")
 
 
 class _TcAttnArgs(Structure):

@@ -20,7 +20,7 @@ from ..config.specs import AttentionSpec
 from ..kernels import ops
 from ..weights.tensors import TensorDecl
 from .base import Part, build_part, register_part
-from .linear import heads_in_epilogue, linear, project_heads
+from .linear import UnmergedSplits, heads_in_epilogue, linear, merge_in_product, project_heads
 
 
 TCGEN05_MIN_Q_LEN = 16     # shorter chunks fill too little of a 128-row tile
@@ -96,12 +96,14 @@ class Attention(Part):
                                  eps=s.qk_norm_eps if s.qk_norm_eps is not None else 0.0)
         if fused:
             project_heads(x, self.w_qkv, prepared, bias=self.b_qkv)
-        o = torch.empty_like(q)
-        self.attend(q, o, ctx, view, page_start, page_ids)
+        o = self.attend(q, ctx, view, page_start, page_ids)
         linear(o, self.w_o, bias=self.b_o, residual=residual, track=ctx)
 
-    def attend(self, q, o, ctx, view, page_start, page_ids) -> None:
-        """bf16 without a window: the tensor-core kernels -- tcgen05 flash attention for steps that
+    def attend(self, q, ctx, view, page_start, page_ids):
+        """The attention output [tokens, heads * head size], or, from a decode step whose key splits the output
+        projection can merge itself, those splits unmerged (:class:`~ondeviceinfer_b200.parts.linear.UnmergedSplits`).
+
+        bf16 without a window: the tensor-core kernels -- tcgen05 flash attention for steps that
         bring more than 16 tokens per sequence (head sizes 64 and 128), the mma.sync prefill form for
         short chunks and other head sizes, the split-key decode form when every sequence brings one
         token.  float32, windows, head sizes above 256: the CUDA-core kernel."""
@@ -119,21 +121,32 @@ class Attention(Part):
             if splits > 1:
                 partial = torch.empty((ctx.n_tokens * s.num_heads * splits * (s.head_dim + 2),),
                                       dtype=torch.float32, device=q.device)
+        if tensor_cores and ctx.max_q_len == 1 and splits > 1 and merge_in_product(
+                ctx.n_tokens, self.w_o, splits=splits, heads=s.num_heads, head_dim=s.head_dim, biased=self.b_o is not None):
+            # the output projection merges the splits in its prologue: no combine kernel, no bf16 round trip
+            ops.attention_mma(q, view.keys, view.values, None, ctx.cu_q, ctx.past, page_start, page_ids,
+                              n_seqs=ctx.n_seqs, max_q_len=1, nq=s.num_heads, nkv=s.num_kv_heads, d=s.head_dim,
+                              page_size=PAGE_SIZE, scale=self.scale, splits=splits, partial=partial,
+                              tiles_per_split=tiles_per_split, combine=False)
+            return UnmergedSplits(partial, ctx.past, tiles_per_split, splits=splits, heads=s.num_heads,
+                                  head_dim=s.head_dim)
+        o = torch.empty_like(q)
         if tensor_cores and ctx.max_q_len > TCGEN05_MIN_Q_LEN and s.head_dim in ops.TCGEN05_ATTENTION_HEAD_DIMS:
             ops.attention_tcgen05(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                                   n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
                                   d=s.head_dim, page_size=PAGE_SIZE, scale=self.scale)
-            return
+            return o
         if tensor_cores:
             ops.attention_mma(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                               n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
                               d=s.head_dim, page_size=PAGE_SIZE, scale=self.scale, splits=splits, partial=partial,
                               tiles_per_split=tiles_per_split if ctx.max_q_len == 1 else None)
-            return
+            return o
         ops.attention_simt(q, view.keys, view.values, o, ctx.cu_q, ctx.past, page_start, page_ids,
                            n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, nq=s.num_heads, nkv=s.num_kv_heads,
                            d=s.head_dim, page_size=PAGE_SIZE, ring_pages=view.kv_group.ring_pages,
                            window=s.window or 0, scale=self.scale, splits=splits, partial=partial)
+        return o
 
 
 register_part(AttentionSpec, Attention)

@@ -83,23 +83,76 @@ class NormedRows:
         return self._tensor
 
 
+class UnmergedSplits:
+    """The output of a decode attention whose key splits have not been merged yet: ``partial`` holds, per token,
+    head and split, the weighted values with their maximum and sum (what ``ops.attention_mma`` leaves with
+    ``combine=False``).  :func:`linear` with a residual merges them inside the tensor-core kernel of the
+    product (:func:`merge_in_product` says when), which saves the combine kernel and a round trip of the
+    activations; ``materialize()`` runs that kernel and gives the ordinary tensor to anybody else."""
+
+    def __init__(self, partial: torch.Tensor, past: torch.Tensor, plan: Optional[torch.Tensor], *, splits: int,
+                 heads: int, head_dim: int, dtype: torch.dtype = torch.bfloat16) -> None:
+        self.partial, self.past, self.plan = partial, past, plan
+        self.splits, self.heads, self.head_dim, self.dtype = splits, heads, head_dim, dtype
+        self._tensor: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return (self.past.numel(), self.heads * self.head_dim)
+
+    @property
+    def device(self):
+        return self.partial.device
+
+    def materialize(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = torch.empty(self.shape, dtype=self.dtype, device=self.partial.device)
+            ops.attention_mma_combine(self.partial, self._tensor, self.past, nq=self.heads, d=self.head_dim,
+                                      splits=self.splits, tiles_per_split=self.plan)
+        return self._tensor
+
+
+# Off by default: measured on B200 on whole captured decode steps it is slower than the combine kernel it saves
+# (Qwen3-8B sizes, 2,048-token context, merged in the product / combine kernel: batch 8 3.70 / 3.47 ms a step, batch 1
+# 3.54 / 3.02 ms; Qwen3-14B sizes, 16 unequal sequences 6.76 / 6.15 ms; 32B sizes, 8 x 8,192: 15.9 / 13.3 ms).  Every
+# CTA of the product merges all tokens over its share of K again, so the partials are read from L2 once per
+# tile of output features (32 times at these sizes) by 128 threads a CTA in several dependent round trips, where
+# the combine kernel spreads one pass over a block per (token, head).  ODI_MERGE_IN_PRODUCT=1 turns it on.
+MERGE_IN_PRODUCT = os.environ.get("ODI_MERGE_IN_PRODUCT", "0") == "1"
+
+
+def merge_in_product(tokens: int, weight: torch.Tensor, *, splits: int, heads: int, head_dim: int,
+                     biased: bool = False) -> bool:
+    """Whether :func:`linear` with a residual can take :class:`UnmergedSplits` of these sizes as they are
+    (bf16 weights; the few-token tensor-core kernel in a form whose prologue merges the splits)."""
+    if not MERGE_IN_PRODUCT or weight.dtype != torch.bfloat16 or weight.shape[1] != heads * head_dim or splits < 2:
+        return False
+    return (_own_tokens(tokens, weight, biased) and ops.gemm_bf16_supported(weight, weight)
+            and ops.gemm_bf16_fuses_merge(tokens, weight.shape[0], weight.shape[1], splits=splits, nq=heads, d=head_dim))
+
+
 # A product with this many output features (the logits) has tiles enough without K splits, and there the
 # own kernel stays ahead up to its widest token tile: 151,936 features x 4,096 at 64 tokens 192 us against
 # 208 us for the library's product, which leaves bf16 logits that a further kernel widens (41 us).
 TALL_PRODUCT_FEATURES, TALL_PRODUCT_MAX_TOKENS = 32768, 64
 
 
-def _own(x, weight: torch.Tensor, biased: bool = False) -> bool:
-    """Whether the few-token tensor-core kernel serves this product.  A product with a bias stays with this
-    library's kernels at every width (the bias joins the fp32 product before its one rounding, which a
-    library product that returns bf16 cannot offer): this kernel up to where the many-token one takes over."""
-    like = x.rows if isinstance(x, NormedRows) else x
+def _own_tokens(tokens: int, weight: torch.Tensor, biased: bool = False) -> bool:
+    """Whether the few-token tensor-core kernel serves a product of this many tokens.  A product with a bias
+    stays with this library's kernels at every width (the bias joins the fp32 product before its one rounding,
+    which a library product that returns bf16 cannot offer): this kernel up to where the many-token one takes over."""
     limit = OWN_KERNEL_MAX_TOKENS
     if weight.shape[0] >= TALL_PRODUCT_FEATURES and limit >= 32:
         limit = max(limit, TALL_PRODUCT_MAX_TOKENS)
     if biased and PREFILL_GEMM != "library":
         limit = max(limit, PERSISTENT_MIN_TOKENS_FUSED - 1)
-    return x.shape[0] <= limit and ops.gemm_bf16_supported(like, weight)
+    return tokens <= limit
+
+
+def _own(x, weight: torch.Tensor, biased: bool = False) -> bool:
+    """Whether the few-token tensor-core kernel serves this product: few enough tokens, operands it can map."""
+    like = x.rows if isinstance(x, NormedRows) else x
+    return _own_tokens(x.shape[0], weight, biased) and ops.gemm_bf16_supported(like, weight)
 
 
 def _operand(x, weight: torch.Tensor, n_out: int, epi: int):
@@ -113,7 +166,7 @@ def _operand(x, weight: torch.Tensor, n_out: int, epi: int):
 
 def linear(x, weight: torch.Tensor, *, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, track=None) -> Optional[torch.Tensor]:
-    """``x`` [tokens, in] (a tensor or :class:`NormedRows`), ``weight`` [out, in], ``bias`` None or fp32 [out]
+    """``x`` [tokens, in] (a tensor, :class:`NormedRows` or :class:`UnmergedSplits`), ``weight`` [out, in], ``bias`` None or fp32 [out]
     (added to the fp32 product before it is rounded or added to the residual).
 
     With ``residual`` (fp32 [tokens, out]) the product is added to it in place and
@@ -133,6 +186,18 @@ def linear(x, weight: torch.Tensor, *, bias: Optional[torch.Tensor] = None, resi
         track.residual_sumsq = None
     biased = bias is not None
     if isinstance(x, NormedRows) and not (x.dtype == torch.bfloat16 and _own(x, weight, biased)):
+        x = x.materialize()
+    if isinstance(x, UnmergedSplits):
+        if residual is not None and merge_in_product(n, weight, splits=x.splits, heads=x.heads, head_dim=x.head_dim,
+                                                     biased=biased):
+            parts = None
+            if track is not None and ops.gemm_bf16_gives_sumsq(n, N, weight.shape[1]):
+                parts = torch.empty((ops.gemm_bf16_sumsq_parts(N), n), dtype=torch.float32, device=residual.device)
+            ops.gemm_bf16(None, weight, residual, ops.EPI_RESIDUAL, sumsq_out=parts, bias=bias,
+                          merge=(x.partial, x.past, x.plan, x.splits, x.heads, x.head_dim))
+            if parts is not None:
+                track.residual_sumsq = (residual, parts)
+            return None
         x = x.materialize()
     if x.dtype == torch.float32:
         if residual is not None:

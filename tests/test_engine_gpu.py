@@ -361,3 +361,39 @@ def test_long_prompt_at_qwen3_8b_layer_sizes(dtype, tmp_path):
                         longest_sum=LARGE_PREFILL["intermediate_size"])
     cache.free(slot)
     cache.check()
+
+
+def test_decode_with_the_splits_merged_in_the_output_projection(monkeypatch, tmp_root):
+    """The optional form in which a decode attention leaves its key splits unmerged and the output projection
+    merges them in its prologue: the same logits, bit for bit, as with the combine kernel, on sequences long
+    enough for several splits (and one short one that uses a single split of the bound)."""
+    import importlib
+    linear_module = importlib.import_module("ondeviceinfer_b200.parts.linear")
+    from ondeviceinfer_b200.kernels import ops
+    model, weights, cfg = engine_model("Cb", "bfloat16", tmp_root)
+    prompts = plain.random_prompts(cfg, [700, 300, 70], 21)
+
+    def run(merge_in_product):
+        monkeypatch.setattr(linear_module, "MERGE_IN_PRODUCT", merge_in_product)
+        merged_calls = []
+        real = ops.gemm_bf16
+
+        def counting(*args, **kwargs):
+            merged_calls.append(kwargs.get("merge") is not None)
+            return real(*args, **kwargs)
+
+        monkeypatch.setattr(ops, "gemm_bf16", counting)
+        cache = model.make_cache(max_tokens=3 * 768, max_seqs=3)
+        slots = [cache.alloc() for _ in prompts]
+        rows = [model.step(cache, slots, prompts, "last")]
+        for t in range(3):
+            rows.append(model.step(cache, slots, [[5 + t], [9 + t], [11 + t]], "last"))
+        monkeypatch.setattr(ops, "gemm_bf16", real)
+        for slot in slots:
+            cache.free(slot)
+        return torch.cat(rows), sum(merged_calls)
+
+    plain_way, none = run(False)
+    fused_way, some = run(True)
+    assert none == 0 and some == 3 * cfg["num_hidden_layers"]
+    assert torch.equal(fused_way, plain_way)

@@ -757,6 +757,69 @@ def test_attention_mma_with_the_hosts_list_of_blocks(d):
         run([per, 0])
 
 
+MERGE_CASES = [
+    # tokens, heads, head size, splits, output features, with a plan, bias
+    (8, 32, 128, 4, 4096, True, False),        # the output projection of a decode step: clusters of 8 K splits
+    (1, 32, 128, 16, 4096, True, False),       # one sequence, many splits
+    (5, 6, 64, 3, 384, False, True),           # heads of 64, one K split, every token uses all splits, a bias
+    (20, 8, 128, 2, 1024, True, False),        # a token tile of 32
+    (16, 40, 128, 8, 5120, True, True),        # a width that is no power of two: 40 heads
+    (3, 4, 192, 32, 768, True, False),         # heads of 192 (three k-blocks each), the most splits
+]
+
+
+@pytest.mark.parametrize("tokens,heads,d,splits,n_out,planned,biased", MERGE_CASES)
+def test_gemm_bf16_merges_attention_splits_like_the_combine_kernel(tokens, heads, d, splits, n_out, planned, biased):
+    """The output projection fed with the unmerged splits of a decode attention against the combine kernel
+    followed by the same product: the same bits (the prologue rounds what the combine kernel would have
+    rounded), with splits that have no keys (maximum -inf, garbage values) and, with a plan, tokens that use
+    fewer splits than the bound; the sums of squares it leaves are the same too."""
+    gen = torch.Generator().manual_seed(tokens * 131 + splits)
+    K = heads * d
+    assert ops.gemm_bf16_fuses_merge(tokens, n_out, K, splits=splits, nq=heads, d=d)
+    partial = torch.randn(tokens, heads, splits, d + 2, generator=gen)
+    partial[..., d] = torch.randn(tokens, heads, splits, generator=gen) * 3.0           # maxima
+    partial[..., d + 1] = torch.rand(tokens, heads, splits, generator=gen) * 50 + 0.5   # sums
+    empty = torch.rand(tokens, heads, splits, generator=gen) < 0.15
+    empty[..., 0] = False
+    partial[..., d][empty] = float("-inf")
+    partial[..., :d][empty] = float("nan")                  # whatever an empty split holds must not matter
+    plan, past = None, torch.randint(0, 64 * splits * 3, (tokens,), generator=gen, dtype=torch.int32)
+    if planned:
+        plan = torch.tensor([3, 0, 0], dtype=torch.int32, device=DEV)          # 3 tiles a split (a list's first number)
+        past[0] = 64 * 3 * splits - 1                                          # one token uses every split
+        if tokens > 1:
+            past[1] = 5                                                        # and one a single split
+    partial, past = partial.to(DEV), past.to(DEV)
+    w = (torch.randn(n_out, K, generator=gen) / math.sqrt(K)).bfloat16().to(DEV)
+    bias = torch.randn(n_out, generator=gen).to(DEV) if biased else None
+    residual = torch.randn(tokens, n_out, generator=gen).to(DEV)
+
+    merged = torch.empty(tokens, K, dtype=torch.bfloat16, device=DEV)
+    ops.attention_mma_combine(partial, merged, past, nq=heads, d=d, splits=splits, tiles_per_split=plan)
+    assert bool(torch.isfinite(merged.float()).all())
+    expected, sums_expected = residual.clone(), torch.empty(ops.gemm_bf16_sumsq_parts(n_out), tokens, device=DEV)
+    ops.gemm_bf16(merged, w, expected, ops.EPI_RESIDUAL, bias=bias, sumsq_out=sums_expected)
+    got, sums = residual.clone(), torch.empty_like(sums_expected)
+    ops.gemm_bf16(None, w, got, ops.EPI_RESIDUAL, bias=bias, sumsq_out=sums,
+                  merge=(partial, past, plan, splits, heads, d))
+    torch.cuda.synchronize()
+    ops.raise_on_kernel_fault()
+    assert torch.equal(got, expected)
+    assert torch.equal(sums, sums_expected)
+    # and against plain arithmetic: softmax-weighted sum of the used splits, then the product
+    used = [splits if plan is None else -(-(int(p) // 64 + 1) // max(3, -(-(int(p) // 64 + 1) // splits))) for p in past.tolist()]
+    ref = torch.zeros(tokens, K, dtype=torch.float64)
+    host = partial.double().cpu()
+    for t in range(tokens):
+        m, l, acc = host[t, :, :used[t], d], host[t, :, :used[t], d + 1], host[t, :, :used[t], :d]
+        wgt = torch.exp(m - m.max(-1, keepdim=True).values)
+        acc = torch.where(torch.isfinite(m)[..., None], acc, torch.zeros_like(acc))
+        ref[t] = ((wgt[..., None] * acc).sum(1) / (wgt * l).sum(-1, keepdim=True)).reshape(-1)
+    product = ref.bfloat16().double() @ w.double().cpu().t() + (bias.double().cpu() if biased else 0.0)
+    close(got, (residual.double().cpu() + product).float(), "bfloat16")
+
+
 TC_ATTN_CASES = [
     # d, nq, nkv, lengths, past
     (128, 4, 2, [128], [0]),                      # exactly one tile of queries, two pages of keys
