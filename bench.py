@@ -549,7 +549,7 @@ def run_own_arm(args, parser) -> int:
                 n_layers = big["num_hidden_layers"]
                 longest = extra.get("prompt_len") or extra["prompt_range"][1]
                 steps = min(args.steps, extra["steps"])
-                room = -(-(longest + steps + 8) // 64) * 64
+                room = -(-(longest + max(3, SETTLE_STEPS) + steps + 8) // 64) * 64      # prompt, untimed and timed steps
                 _, w_bytes, kv_bytes = model_figures(big, n_layers)
                 if w_bytes + extra["batch"] * room * kv_bytes + (24 << 30) > free_bytes:
                     points[extra["name"] + "_skipped"] = "not enough free device memory"

@@ -17,6 +17,8 @@ host and uploaded in one copy.
 
 from __future__ import annotations
 
+import os
+
 from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 
 import numpy as np
@@ -175,17 +177,34 @@ def validate_step(cache, slots: Sequence[int], tokens: Sequence[Sequence[int]], 
             raise ValueError(f"sequence {i}: token id {lo if lo < 0 else hi} is outside the vocabulary of {vocab_size}")
 
 
+# The most tokens that one pass over the layers takes (ODI_STEP_TOKENS).  Longer steps run as several passes
+# over the same cache, which bounds the activations (a pass of 32,768 tokens of Qwen3-8B's width holds under
+# 2 GB of them) and keeps every index inside a kernel well below 2^31, and costs nothing: the many-token
+# kernels are at their full rate from a few thousand tokens on.
+STEP_TOKEN_LIMIT = int(os.environ.get("ODI_STEP_TOKENS", "32768"))
+
+
+def tokens_per_sequence_at_a_time(cache_limit: Optional[int], q_lens: Sequence[int]) -> Optional[int]:
+    """How many tokens of each sequence one pass takes, or None if the whole step is one pass.  A cache with
+    windowed groups takes at most ``cache_limit`` per sequence at a time (its rings are sized for that); a step of
+    more than ``STEP_TOKEN_LIMIT`` tokens is cut so that a pass holds about that many, in whole pages of 64."""
+    limit = cache_limit
+    if sum(q_lens) > STEP_TOKEN_LIMIT:
+        share = max(64, STEP_TOKEN_LIMIT // len(q_lens) // 64 * 64)
+        limit = share if limit is None else min(limit, share)
+    return None if limit is None or max(q_lens) <= limit else limit
+
+
 def run_step(model, cache, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Want = "last") -> torch.Tensor:
     """Run one step and return fp32 logits ``[n_wanted, vocab]`` on the device, ordered by
     sequence and then by place.  See the module text for the contract."""
     tokens = [list(run) for run in tokens]
     validate_step(cache, slots, tokens, model.vocab_size)
     places = resolve_want(want, [len(t) for t in tokens])
-    limit = cache.max_step_tokens
-    if limit is None or max(len(t) for t in tokens) <= limit:
+    limit = tokens_per_sequence_at_a_time(cache.max_step_tokens, [len(t) for t in tokens])
+    if limit is None:
         return _run_chunk(model, cache, slots, tokens, places)
-    # A cache with windowed groups takes at most `limit` tokens per sequence at a time:
-    # cut the step into sub-steps and put the wanted rows back in order.
+    # Cut the step into sub-steps of at most `limit` tokens per sequence and put the wanted rows back in order.
     outputs: List[List[Optional[torch.Tensor]]] = [[None] * len(p) for p in places]
     offset = 0
     while True:

@@ -397,3 +397,46 @@ def test_decode_with_the_splits_merged_in_the_output_projection(monkeypatch, tmp
     fused_way, some = run(True)
     assert none == 0 and some == 3 * cfg["num_hidden_layers"]
     assert torch.equal(fused_way, plain_way)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_longer_than_the_token_limit_runs_in_passes(dtype, monkeypatch, tmp_root):
+    """With the limit at 128 tokens a pass, prompts of 300, 70 and 129 tokens run as five passes of up to 64
+    tokens per sequence over the same cache: the logits at every place are those of the plain implementation,
+    and those of the step in one pass within rounding; decoding goes on from the cache they left."""
+    import importlib
+    step_module = importlib.import_module("ondeviceinfer_b200.engine.step")
+    model, weights, cfg = engine_model("B", dtype, tmp_root)
+    prompts = plain.random_prompts(cfg, [300, 70, 129], 33)
+    passes = []
+    real = step_module._run_chunk
+
+    def counting(model_, cache_, slots_, tokens_, places_):
+        passes.append([len(t) for t in tokens_])
+        return real(model_, cache_, slots_, tokens_, places_)
+
+    monkeypatch.setattr(step_module, "_run_chunk", counting)
+
+    def run(limit):
+        monkeypatch.setattr(step_module, "STEP_TOKEN_LIMIT", limit)
+        del passes[:]
+        cache = model.make_cache(max_tokens=3 * 384, max_seqs=3)
+        slots = [cache.alloc() for _ in prompts]
+        logits = model.step(cache, slots, prompts, "all")
+        shape = list(passes)
+        more = model.step(cache, slots, [[7], [8], [9]], "last")
+        return logits, more, shape
+
+    whole, whole_next, one = run(32768)
+    cut, cut_next, five = run(128)
+    assert one == [[300, 70, 129]]
+    assert five == [[64, 64, 64], [64, 6, 64], [64, 1], [64], [44]]
+    offset = 0
+    for r, prompt in enumerate(prompts):
+        expected = plain_logits("B", prompt, dtype)
+        assert_logits_close(cut[offset:offset + len(prompt)], expected, dtype, f"request {r} in passes")
+        offset += len(prompt)
+    if dtype == "float32":
+        assert float((cut - whole).abs().max()) < 2e-4 and float((cut_next - whole_next).abs().max()) < 2e-4
+    for r, (prompt, token) in enumerate(zip(prompts, (7, 8, 9))):
+        assert_logits_close(cut_next[r:r + 1], plain_logits("B", prompt + [token], dtype)[-1:], dtype, f"request {r} next")

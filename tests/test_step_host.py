@@ -129,6 +129,21 @@ def test_the_list_of_key_blocks_covers_every_sequence_within_the_room_fixed_per_
         key_split_list([130, 64], 2, 2)
 
 
+def test_a_long_step_is_cut_into_passes_of_about_the_token_limit(monkeypatch):
+    import importlib
+    step = importlib.import_module("ondeviceinfer_b200.engine.step")
+    cut = step.tokens_per_sequence_at_a_time
+    assert step.STEP_TOKEN_LIMIT == 32768
+    assert cut(None, [2048] * 8) is None                       # 16,384 tokens: one pass
+    assert cut(None, [8192] * 8) == 4096                       # 65,536 tokens: two passes of 32,768
+    assert cut(None, [100000]) == 32768
+    assert cut(None, [5000, 40000, 64]) == 10880               # 32,768 // 3 in whole pages
+    assert cut(256, [2048] * 8) == 256 and cut(256, [8192] * 8) == 256 and cut(256, [200]) is None
+    assert cut(None, [1] * 40000) is None                      # one token each: nothing to cut
+    monkeypatch.setattr(step, "STEP_TOKEN_LIMIT", 128)
+    assert cut(None, [300, 70, 129]) == 64 and cut(None, [100, 28]) is None and cut(None, [129]) == 128
+
+
 def test_a_kernel_that_gave_up_waiting_is_reported_once_by_name():
     """Every wait inside the tensor-core kernels is bounded; a kernel whose wait ran out writes a code into
     an error word and returns.  Here the word is set by hand (no GPU is made to wait): the host check names
