@@ -827,30 +827,43 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
 // One block per (token, head).  With `tiles_per_split` a row has the partials of its sequence's first
 // ceil(tiles / *tiles_per_split) splits only (one token per sequence: the token's index is the sequence's).
-// Up to 32 splits: the first warp reads every split's maximum and sum in one round trip and leaves the weights
-// in shared memory, then every thread requests its element of all splits at once and adds them in split order:
-// two round trips to L2 whatever the number of splits, and the arithmetic, its order and so its bits are those
-// of combine_row (which walks the splits three times, four loads at a time: with the 17 splits of one sequence
-// of 2,048 keys that kernel took as long as the attention itself).
+// Up to 32 splits: every thread requests its element of all splits, and the first warp every split's maximum and
+// sum, in the same round trip as the position that says how many splits count; the first warp leaves the weights
+// in shared memory and every thread adds its elements in split order: one round trip to L2 whatever the number
+// of splits (combine_row walks the splits three times, four loads at a time: with the 17 splits of one sequence
+// of 2,048 keys that took as long as the attention itself).
 __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int splits,
                                              const int* __restrict__ past, int nq, const int* __restrict__ tiles_per_split) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = blockIdx.x;
-  int used = splits;
-  if (tiles_per_split != nullptr) used = merge_used_splits(tiles_per_split, splits, past[row / nq]);
   constexpr int RS = D + 2;
   const float* p = partial + row * splits * RS;
-  if (used > 32) {
+  if (splits > 32) {
+    int used = splits;
+    if (tiles_per_split != nullptr) used = merge_used_splits(tiles_per_split, splits, past[row / nq]);
     combine_row(p, out + row * D, used, threadIdx.x, blockDim.x);
     return;
   }
+  // Everything the block reads is requested at once, before any of it is used: this thread's element of every
+  // split up to the bound, the splits' statistics (first warp), and the position that says how many splits count.
+  // Slots behind the count hold whatever the buffer held; they are loaded and never used.
+  float x[32];
+  const int dd0 = threadIdx.x;
+#pragma unroll
+  for (int s = 0; s < 32; ++s) x[s] = (s < splits && dd0 < D) ? __ldcg(p + s * RS + dd0) : 0.f;
+  float ms = -INFINITY, ls = 0.f;
+  if (threadIdx.x < 32 && (int)threadIdx.x < splits) {
+    ms = __ldcg(p + threadIdx.x * RS + D);
+    ls = __ldcg(p + threadIdx.x * RS + D + 1);
+  }
+  int used = splits;
+  if (tiles_per_split != nullptr) used = merge_used_splits(tiles_per_split, splits, past[row / nq]);
   __shared__ float weight[32];
   __shared__ float inv_denom;
   if (threadIdx.x < 32) {
     const int s = threadIdx.x;
-    const float ms = s < used ? __ldcg(p + s * RS + D) : -INFINITY;
-    const float ls = s < used ? __ldcg(p + s * RS + D + 1) : 0.f;
+    if (s >= used) ms = -INFINITY;
     const float M = warp_max(ms);
     // every product and sum below is written as the one instruction it is, so that the output projection's
     // merge prologue (gemm_tcgen05.cu), which does the same sums thread by thread, gives the same bits
@@ -863,10 +876,11 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ partial, 
   }
   __syncthreads();
   const float inv = inv_denom;
-  for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
-    float x[32];
+  for (int dd = dd0; dd < D; dd += blockDim.x) {
+    if (dd != dd0) {
 #pragma unroll
-    for (int s = 0; s < 32; ++s) x[s] = s < used ? __ldcg(p + s * RS + dd) : 0.f;
+      for (int s = 0; s < 32; ++s) x[s] = s < used ? __ldcg(p + s * RS + dd) : 0.f;
+    }
     float v = 0.f;
 #pragma unroll
     for (int s = 0; s < 32; ++s)
