@@ -598,16 +598,22 @@ attention_decode_kernel(MmaAttnArgs a) {
 // the compute warps: a fifth warp's one thread issues cp.async.bulk.tensor loads (boxes of 64 positions x 64 lanes
 // of the head, 128-byte swizzle, no multicast) into a ring of TD_SLOTS slots, a slot being the 64 x D keys or the
 // 64 x D values of one page; each slot has a `full` barrier (the copy's bytes) and an `empty` barrier (the four
-// compute warps, each when it has read the slot).  Against the cp.async form: up to TD_SLOTS - 1 slots of a
-// block are in flight instead of two stages (at head size 128: 80 KB instead of 64 KB, in 96 KB of shared memory
-// instead of 104 KB), a key slot is free again as soon as the scores exist, the warps meet at no block barrier per
-// tile, and the compute warps issue no copies.  Pages that earlier steps filled are requested before the
+// compute warps, each when it has read the slot).  Against the cp.async form: a key slot is free again as soon as
+// the scores exist, the warps meet at no block barrier per tile, and the compute warps issue no copies.  Four
+// slots (64 KB, three of them in flight) measured best on whole decode steps at Qwen3-8B sizes: 3 / 4 / 5 / 6 slots
+// gave 3.437 / 3.425 / 3.435 / 3.442 ms a step at 8 x 2,048 keys, 9.2 / 9.1 / - / 9.6 ms at 32 x 8,192 and 9.0 / 8.8 /
+// - / 9.0 ms at 8 x 32,768 (a smaller block leaves the kernels before and after it room on the SM to move in and
+// out), although the kernel alone streams a little faster with six.  Three blocks an SM (128 registers, no spills,
+// 65 KB each) were slower everywhere (batch 64: 8,616 against 9,112 tokens/s).  Pages that earlier steps filled are
+// requested before the
 // dependency wait; the page of the query's own position after it.  Every wait is bounded (about two seconds), after
 // which the block records who gave up in `status`, skips its work and leaves.  Head sizes 64 and 128.
 #if D == 64 || D == 128
 #include <cuda.h>
 
-#define TD_SLOTS 6
+#ifndef TD_SLOTS
+#define TD_SLOTS 4
+#endif
 #define TD_BOXES (D / 64)                 // boxes of 64 lanes (128 bytes) per row of the head
 #define TD_BOX_BYTES (KT * 128)           // 64 rows of 128 bytes
 #define TD_SLOT_BYTES (TD_BOXES * TD_BOX_BYTES)
