@@ -706,32 +706,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const uint32_t rank = cluster_rank();
       const bool sums = EPI == EPI_RESIDUAL && BN <= 64 && a.sumsq_out != nullptr;
       int slot = 0;
+      // The token columns this CTA owns, GROUP of them at a time: all peers' values of the whole group (and the
+      // residual values they will be added to) are requested before the first is used, so a group costs one round
+      // trip through the cluster's shared memory, not one per column; each column's values are then added in rank
+      // order, a fixed sum.  (One column at a time, a tile of 32 tokens in 8 splits paid four round trips here.)
+      constexpr int GROUP = (DUAL || BN <= 16) ? 2 : 4;
       if (live)
-        for (int c = (int)rank; c < BN && tok0 + c < a.tokens; c += a.splits, ++slot) {   // the token columns this CTA owns
-          // all peers' values are requested before the first is used (the loads do not wait on one
-          // another), then added in rank order: a fixed sum
-          float pv[8], pu[8];
-          const bool inside = tok0 + c < a.tokens && n < a.N;
-          float* res_at = (float*)a.out + (size_t)(tok0 + c) * a.ldo + n;
-          const float res = (EPI == EPI_RESIDUAL && inside) ? *res_at : 0.f;     // in flight with the peers' values
+        for (int c0 = (int)rank; c0 < BN && tok0 + c0 < a.tokens; c0 += GROUP * a.splits) {
+          float pv[GROUP][8], pu[DUAL ? GROUP : 1][8], res[GROUP];
 #pragma unroll
-          for (int p = 0; p < 8; ++p) {
-            pv[p] = p < a.splits ? ld_peer_f32(red + c * BM + row, (uint32_t)p) : 0.f;
-            if (DUAL) pu[p] = p < a.splits ? ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p) : 0.f;
-          }
-          float v = 0.f, u = 0.f;
+          for (int g = 0; g < GROUP; ++g) {
+            const int c = c0 + g * a.splits;
+            const bool owned = c < BN && tok0 + c < a.tokens;
+            const bool inside = owned && n < a.N;
+            res[g] = (EPI == EPI_RESIDUAL && inside) ? ((const float*)a.out)[(size_t)(tok0 + c) * a.ldo + n] : 0.f;
 #pragma unroll
-          for (int p = 0; p < 8; ++p) {
-            if (p < a.splits) { v += pv[p]; if (DUAL) u += pu[p]; }
+            for (int p = 0; p < 8; ++p) {
+              pv[g][p] = (owned && p < a.splits) ? ld_peer_f32(red + c * BM + row, (uint32_t)p) : 0.f;
+              if (DUAL) pu[g][p] = (owned && p < a.splits) ? ld_peer_f32(red + (BN + c) * BM + row, (uint32_t)p) : 0.f;
+            }
           }
-          if (a.bias != nullptr && n < a.N) { v += a.bias[n]; if (DUAL) u += a.bias[n + a.dual_offset]; }
-          if (EPI == EPI_HEAD_PREP) ((float*)(smem + HP_STAGE_OFFSET))[slot * BM + row] = round_to<bf16>(v);
-          float left = 0.f;
-          if (EPI == EPI_RESIDUAL) { left = inside ? res + v : 0.f; if (inside) *res_at = left; }
-          else emit<EPI>(a, tok0 + c, n, v, u);
-          if (sums) {
-            const float sq = warp_sum(left * left);
-            if (lane == 0) sumsq_part[warp & 3][BN <= 64 ? slot : 0] = sq;
+#pragma unroll
+          for (int g = 0; g < GROUP; ++g) {
+            const int c = c0 + g * a.splits;
+            if (c >= BN || tok0 + c >= a.tokens) break;       // the same for the whole warp
+            const bool inside = n < a.N;
+            float v = 0.f, u = 0.f;
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+              if (p < a.splits) { v += pv[g][p]; if (DUAL) u += pu[g][p]; }
+            }
+            if (a.bias != nullptr && n < a.N) { v += a.bias[n]; if (DUAL) u += a.bias[n + a.dual_offset]; }
+            if (EPI == EPI_HEAD_PREP) ((float*)(smem + HP_STAGE_OFFSET))[slot * BM + row] = round_to<bf16>(v);
+            float left = 0.f;
+            if (EPI == EPI_RESIDUAL) {
+              left = inside ? res[g] + v : 0.f;
+              if (inside) ((float*)a.out)[(size_t)(tok0 + c) * a.ldo + n] = left;
+            } else {
+              emit<EPI>(a, tok0 + c, n, v, u);
+            }
+            if (sums) {
+              const float sq = warp_sum(left * left);
+              if (lane == 0) sumsq_part[warp & 3][BN <= 64 ? slot : 0] = sq;
+            }
+            ++slot;
           }
         }
       if (EPI == EPI_HEAD_PREP) {
