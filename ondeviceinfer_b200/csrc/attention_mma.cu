@@ -19,7 +19,7 @@
 //
 // Key/value pages (64 positions x head_dim, contiguous) reach shared memory in one of two ways.  For head
 // sizes 64 and 128 the decode block has a fifth warp whose one thread issues TMA copies into a ring of
-// six slots with full/empty mbarriers (attention_decode_tma_kernel: 128-byte swizzle, bounded waits).
+// four slots with full/empty mbarriers (attention_decode_tma_kernel: 128-byte swizzle, bounded waits).
 // Otherwise, and in the prefill form, the warps copy with cp.async, double or triple buffered, one block
 // barrier per tile, into rows padded by 16 bytes so that ldmatrix reads are free of bank conflicts for
 // every head size that is a multiple of 16.
