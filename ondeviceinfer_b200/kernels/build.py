@@ -101,7 +101,7 @@ def compile_library(name: str, defines: Optional[Mapping[str, object]] = None, e
     if out.exists():
         return out
     source = CSRC / f"{name}.cu"
-    tmp = out.with_suffix(f".tmp{os.getpid()}.so")
+    tmp = out.with_suffix(f".tmp{os.getpid()}_{threading.get_ident()}.so")      # two builders of one library never share it
     cmd = [_nvcc(), *ARCH_FLAGS, *BASE_FLAGS, *extra, *[f"-D{k}={v}" for k, v in sorted(defines.items())],
            "-I", str(CSRC), str(source), "-o", str(tmp)]
     label = name + "".join(f" {k}={v}" for k, v in sorted(defines.items()))
