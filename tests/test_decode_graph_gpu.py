@@ -257,3 +257,41 @@ def test_graph_replay_of_a_windowed_layer_past_the_rings_wrap_and_across_a_bucke
     without = odi.generate(model, prompts, max_new_tokens=12, use_graphs=False)
     if dtype == "float32":
         assert with_graphs.generated_ids == without.generated_ids
+
+
+@pytest.mark.parametrize("case", ["C", "Cb"])
+def test_a_thousand_replayed_steps_are_the_step_paths_bit_for_bit(case, tmp_root):
+    """Three sequences of 40, 300 and 1,000 tokens decode 1,200 given tokens each: the longest passes 1,024 and 2,048
+    keys (other graphs take over), every sequence enters a new tile of keys every 64 steps (the host's list of key
+    blocks is renewed) and the cut of the keys changes as they grow.  bf16 with heads of 128 (the TMA-fed decode
+    attention).  The logits of every replayed step equal those of the generic step function bit for bit."""
+    model, _, cfg = engine_model(case, "bfloat16", tmp_root)
+    lengths, steps = [40, 300, 1000], 1200
+    streams = plain.random_prompts(cfg, [n + steps for n in lengths], 77)
+    room = -(-(max(lengths) + steps + 8) // 64) * 64
+
+    def run(graphs):
+        cache = model.make_cache(max_tokens=3 * room, max_seqs=3)
+        slots = [cache.alloc() for _ in lengths]
+        rows = [model.step(cache, slots, [s[:n] for s, n in zip(streams, lengths)], "last").clone()]
+        runner = None
+        if graphs:
+            runner = odi.api.decode_runner(model, cache)
+            runner.begin(slots, [s[n] for s, n in zip(streams, lengths)], [0, 1, 2], [1, 1, 1])
+        for t in range(steps):
+            feed = [s[n + t] for s, n in zip(streams, lengths)]
+            if graphs:
+                runner.step(feed)
+                rows.append(runner.last_logits().clone())
+            else:
+                rows.append(model.step(cache, slots, [[f] for f in feed], "last").clone())
+        cache.check()
+        assert [cache.length(slot) for slot in slots] == [n + steps for n in lengths]
+        return torch.stack(rows), (len(runner._graphs) if graphs else 0)
+
+    replayed, graphs = run(True)
+    stepped, _ = run(False)
+    assert graphs >= 3                                   # up to 2,048 keys, up to 4,096, and the splits' bounds
+    assert torch.isfinite(replayed).all()
+    differing = (replayed != stepped).flatten(1).any(1).nonzero().flatten().tolist()
+    assert not differing, f"steps whose logits differ: {differing[:10]}"
