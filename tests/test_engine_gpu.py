@@ -361,6 +361,40 @@ def test_long_prompt_at_qwen3_8b_layer_sizes(dtype, tmp_path):
                         longest_sum=LARGE_PREFILL["intermediate_size"])
     cache.free(slot)
     cache.check()
+    # An unequal batch at these sizes: five sequences that are the same tokens cut at different places (so one plain
+    # pass gives every expected row), decoded for four steps through graph replay and through the step function:
+    # 8 key/value heads with 33, 24, 11, 2 and 1 tiles of keys, cut into blocks by the host's list.
+    cuts = [2090, 1500, 700, 65, 3]
+    wide = model.make_cache(max_tokens=len(cuts) * 2112, max_seqs=len(cuts))
+
+    def decode(graphs):
+        slots = [wide.alloc() for _ in cuts]
+        rows = [model.step(wide, slots, [tokens[:c] for c in cuts], "last")]
+        runner = odi.api.decode_runner(model, wide) if graphs else None
+        if graphs:
+            runner.begin(slots, [tokens[c] for c in cuts], list(range(len(cuts))), [1] * len(cuts))
+        for t in range(4):
+            feed = [tokens[c + t] for c in cuts]
+            if graphs:
+                runner.step(feed)
+                rows.append(runner.last_logits().clone())
+            else:
+                rows.append(model.step(wide, slots, [[f] for f in feed], "last"))
+        for slot in slots:
+            wide.free(slot)
+        wide.check()
+        return torch.cat(rows)
+
+    replayed, stepped = decode(True), decode(False)
+    places = [c - 1 + t for t in range(5) for c in cuts]
+    assert_logits_close(replayed, expected[places], dtype, "unequal batch at 8B layer sizes, graph replay",
+                        longest_sum=LARGE_PREFILL["intermediate_size"])
+    assert_logits_close(stepped, expected[places], dtype, "unequal batch at 8B layer sizes, step function",
+                        longest_sum=LARGE_PREFILL["intermediate_size"])
+    # (the two need not agree bit for bit: the replayed graph is eight rows wide, and its three padding rows
+    # change how the host cuts the keys into blocks, so the splits' partial sums are grouped differently)
+    assert_logits_close(replayed, stepped, dtype, "graph replay against the step function at 8B layer sizes",
+                        longest_sum=LARGE_PREFILL["intermediate_size"])
 
 
 def test_decode_with_the_splits_merged_in_the_output_projection(monkeypatch, tmp_root):
