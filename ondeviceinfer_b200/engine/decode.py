@@ -291,6 +291,13 @@ class DecodeRunner:
         ctx.slot_list = [pad] * width
         for g, group in enumerate(self.cache.kv_groups):
             ctx._page_ids[g].fill_(group.slot_pages[pad][0])
+        # The rows' lengths as the plan has them: the list of key blocks on the device was made for these, and a
+        # kernel that finds longer sequences than its list covers reports it.  (The buffers may still hold the
+        # lengths of an earlier, longer batch.)  Wherever a position points, the run reads and writes the pad
+        # slot's one page.
+        planned = torch.tensor([max(int(n) - 1, 0) for n in ctx.kv_lens], dtype=torch.int32)
+        ctx.past.copy_(planned)
+        ctx.tok_pos.copy_(planned)
         # The run before the capture compiles, sizes scratch, sets function attributes and loads every kernel
         # that the graph will hold: a kernel's first launch is not allowed inside a capture, and a graph for
         # more key splits may be the first to use one (the merge of the splits).
@@ -300,6 +307,7 @@ class DecodeRunner:
             self._run_once(ctx)
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
+        ops.raise_on_kernel_fault()          # what this run reports belongs to it, not to the next step
         ctx.tok_pos.zero_(); ctx.past.zero_(); ctx.steps.zero_()
         counted = dict(ops.LAUNCHES)
         graph = torch.cuda.CUDAGraph()

@@ -295,3 +295,22 @@ def test_a_thousand_replayed_steps_are_the_step_paths_bit_for_bit(case, tmp_root
     assert torch.isfinite(replayed).all()
     differing = (replayed != stepped).flatten(1).any(1).nonzero().flatten().tolist()
     assert not differing, f"steps whose logits differ: {differing[:10]}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_shorter_batch_after_a_longer_one_captures_its_graph_on_the_same_buffers(dtype, tmp_root):
+    """Two sequences of about 1,500 keys, then, in the same slots and the same width, two of about 300: the second
+    batch needs a graph for shorter sequences (several key blocks each, but fewer than the first batch's), which
+    is captured while the buffers still hold the first batch's lengths.  The capture's own run must go by the
+    lengths its list of key blocks was planned for (a kernel that finds longer sequences than its list covers
+    reports it), and the logits must be those of the plain implementation."""
+    model, _, cfg = engine_model("C", dtype, tmp_root)
+    lengths = [1500, 1400, 300, 280]
+    requests = plain.random_prompts(cfg, lengths, 321)
+    tails = {r: 6 for r in range(4)}
+    cache = model.make_cache(max_tokens=2 * 1536, max_seqs=2)
+    got = replay_batches(model, cache, requests, [[0, 1], [2, 3]], tails)
+    runner = odi.api.decode_runner(model, cache)
+    assert {key[1] for key in runner._graphs} >= {512, 2048}
+    for r, tokens in enumerate(requests):
+        assert_logits_close(got[r], plain_logits("C", tokens)[len(tokens) - tails[r] - 1:], dtype, f"request {r}")
