@@ -191,3 +191,37 @@ def test_graph_replay_while_the_longest_sequence_passes_a_power_of_two(dtype, tm
     else:
         for p, g in zip(prompts, replayed.generated_ids):
             assert all(near_tie(weights, cfg, p + g[:t], g[t], dtype) for t in range(len(g)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_unequal_requests_that_stop_at_random_steps(dtype, tmp_root):
+    """Twenty-five requests of 1 to 700 tokens on a cache of four slots, a stop set of a fifth of the vocabulary, so
+    that sequences end at random steps: batches narrow (widths 4, 2, 1), slots and pages are reused, graphs for
+    shorter sequences are captured on buffers that held longer ones.  Every request ends for the reason its last
+    token gives, nothing is left held, no kernel reports a fault, and in 32-bit graph replay gives the tokens of the
+    step function."""
+    import random
+
+    from ondeviceinfer_b200.kernels import ops
+    model, _, cfg = engine_model("C", dtype, tmp_root)
+    rng = random.Random(3)
+    lengths = [rng.choice([1, 2, 63, 64, 65, 130, 300, 700]) for _ in range(25)]
+    prompts = plain.random_prompts(cfg, lengths, 55)
+    stop = list(range(0, cfg["vocab_size"], 5))
+    cache = model.make_cache(max_tokens=4 * 896, max_seqs=4)
+    runs = {}
+    for use_graphs in (True, False):
+        for temperature in (0.0, 0.9):
+            result = odi.generate(model, prompts, max_new_tokens=90, temperature=temperature, seed=7, cache=cache,
+                                  eos_token_id=stop, use_graphs=use_graphs)
+            torch.cuda.synchronize()
+            ops.raise_on_kernel_fault()
+            cache.check()
+            assert cache.slots.held_count == 0
+            for g, reason in zip(result.generated_ids, result.finish_reasons):
+                assert 1 <= len(g) <= 90 and all(t % 5 for t in g[:-1])
+                assert reason == ("stop" if g[-1] % 5 == 0 else "length") and (reason == "stop" or len(g) == 90)
+            assert result.finish_reasons.count("stop") >= 20
+            runs[use_graphs, temperature] = result.generated_ids
+    if dtype == "float32":
+        assert runs[True, 0.0] == runs[False, 0.0] and runs[True, 0.9] == runs[False, 0.9]
