@@ -474,3 +474,74 @@ def test_a_step_longer_than_the_token_limit_runs_in_passes(dtype, monkeypatch, t
         assert float((cut - whole).abs().max()) < 2e-4 and float((cut_next - whole_next).abs().max()) < 2e-4
     for r, (prompt, token) in enumerate(zip(prompts, (7, 8, 9))):
         assert_logits_close(cut_next[r:r + 1], plain_logits("B", prompt + [token], dtype)[-1:], dtype, f"request {r} next")
+
+
+def _drawn_config(rng):
+    nkv, group = rng.choice([1, 2, 3, 5]), rng.choice([1, 2, 3, 4, 7])
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+            "num_hidden_layers": rng.choice([1, 2, 3]), "hidden_size": rng.choice([36, 50, 72, 100, 104, 136, 250]),
+            "num_attention_heads": nkv * group, "num_key_value_heads": nkv,
+            "head_dim": rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 144, 192, 256]),
+            "intermediate_size": rng.choice([33, 64, 135, 136, 200, 264]), "vocab_size": rng.choice([50, 301, 1000, 2049]),
+            "rope_theta": rng.choice([10000.0, 1000000.0, 50000.0]), "rms_norm_eps": rng.choice([1e-6, 1e-5, 3e-6]),
+            "tie_word_embeddings": rng.random() < 0.5, "max_position_embeddings": 4096, "hidden_act": "silu",
+            "attention_bias": rng.random() < 0.4}
+
+
+@pytest.mark.parametrize("draw", [3, 12, 27, 41])
+def test_drawn_configurations(draw, tmp_path):
+    """Configurations drawn at random from sizes that are no powers of two (widths and feed-forward sizes that are
+    no multiples of 8, odd vocabularies, 1 to 35 query heads in groups of 1 to 7, head sizes from 16 to 256), with and
+    without biases and a tied head: a whole prompt, an unequal batch of four, and its tails one token at a time
+    through the step function and through graph replay, in both precisions, against the plain implementation."""
+    import random
+
+    import ondeviceinfer_b200 as odi
+    from helpers import write_model_folder
+    from ondeviceinfer_b200.kernels import ops
+
+    rng = random.Random(draw)
+    cfg = _drawn_config(rng)
+    weights = plain.random_weights(cfg, draw)
+    folder = write_model_folder(tmp_path / "drawn", cfg, weights)
+    lengths = [rng.choice([1, 5, 33, 64, 65, 100, 130, 257, 700]) for _ in range(4)]
+    requests = plain.random_prompts(cfg, lengths, draw + 1)
+    expected = [plain.forward_logits(weights, cfg, r) for r in requests]
+    room = -(-max(lengths) // 64) * 64 + 64
+    for dtype in DTYPES:
+        model = odi.load_resident_model(folder, device="cuda:0", dtype=dtype)
+        cache = model.make_cache(max_tokens=4 * room, max_seqs=4)
+        slot = cache.alloc()
+        assert_logits_close(model.step(cache, [slot], [requests[3]], "all"), expected[3], dtype, f"{cfg} whole")
+        cache.free(slot)
+        for graphs in (False, True):
+            slots = [cache.alloc() for _ in requests]
+            cut = [max(1, len(r) - 1 - 3 * (i % 3)) for i, r in enumerate(requests)]
+            logits = model.step(cache, slots, [r[:c] for r, c in zip(requests, cut)], "last")
+            assert_logits_close(logits, torch.stack([e[c - 1] for e, c in zip(expected, cut)]), dtype, f"{cfg} prompts")
+            live, fed, changed = list(range(4)), list(cut), True
+            runner = odi.api.decode_runner(model, cache) if graphs else None
+            while True:
+                done = [i for i in live if fed[i] == len(requests[i])]
+                for i in done:
+                    cache.free(slots[i])
+                changed = changed or bool(done)
+                live = [i for i in live if i not in done]
+                if not live:
+                    break
+                feed = [requests[i][fed[i]] for i in live]
+                if graphs:
+                    if changed:
+                        runner.begin([slots[i] for i in live], feed, live, [fed[i] for i in live])
+                        changed = False
+                    runner.step(feed)
+                    rows = runner.last_logits()
+                else:
+                    rows = model.step(cache, [slots[i] for i in live], [[f] for f in feed], "last")
+                assert_logits_close(rows, torch.stack([expected[i][fed[i]] for i in live]), dtype,
+                                    f"{cfg} one token each, graphs={graphs}")
+                for i in live:
+                    fed[i] += 1
+            cache.check()
+        torch.cuda.synchronize()
+        ops.raise_on_kernel_fault()
