@@ -150,21 +150,26 @@ def load_library(name: str, defines: Optional[Mapping[str, object]] = None) -> c
 
 
 # Every source with the defines its default build uses.
+# Every library that build_all() makes: the sources without a head size, and the attention kernels for the head
+# sizes that the Qwen3 sizes use (128) and that the tests use; any other head size in steps of 16 is compiled
+# when a model first needs it.
+_HEAD_SIZES_MMA = (16, 32, 48, 64, 80, 96, 112, 128, 192, 256)
 ALL_SOURCES = {
     "elementwise": [{}],
     "gemm_f32": [{}],
     "sampling": [{}],
     "gemm_tcgen05": [{}, {"ODI_WAIT_CYCLES": 20_000_000}],      # the second: ops.selftest_bounded_wait
     "gemm_prefill_tcgen05": [{}],
-    "attention_simt": [{"ODI_HEAD_DIM": 128}],
-    "attention_mma": [{"ODI_HEAD_DIM": 128}],
-    "attention_tcgen05": [{"ODI_HEAD_DIM": 128}],
+    "attention_simt": [{"ODI_HEAD_DIM": d} for d in _HEAD_SIZES_MMA + (512,)],
+    "attention_mma": [{"ODI_HEAD_DIM": d} for d in _HEAD_SIZES_MMA],
+    "attention_tcgen05": [{"ODI_HEAD_DIM": 64}, {"ODI_HEAD_DIM": 128}],
 }
 
 
-def build_all(verbose: bool = True) -> list:
-    built = []
-    for name, variants in ALL_SOURCES.items():
-        for defines in variants:
-            built.append(compile_library(name, defines, EXTRA_FLAGS.get(name), verbose=verbose))
-    return built
+def build_all(verbose: bool = True, jobs: Optional[int] = None) -> list:
+    """Compile every library of ALL_SOURCES that has no up-to-date build, several at a time."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    work = [(name, defines) for name, variants in ALL_SOURCES.items() for defines in variants]
+    with ThreadPoolExecutor(jobs or min(8, os.cpu_count() or 1)) as pool:
+        return list(pool.map(lambda w: compile_library(w[0], w[1], EXTRA_FLAGS.get(w[0]), verbose=verbose), work))
