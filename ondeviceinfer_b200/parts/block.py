@@ -4,7 +4,6 @@ from __future__ import annotations
 
 from ..config.specs import PreNormBlockSpec
 from .base import Part, build_part, register_part
-from .linear import flush_residual_add
 
 
 def ops_residual_add(residual, product) -> None:
