@@ -88,6 +88,8 @@ EXTRA_POINTS = (
      "steps": 64, "temperature": 0.0},
     {"name": "qwen3_8b_b8_32768", "sizes": "8B", "batch": 8, "prompt_len": 32768, "seed": 0,
      "steps": 64, "temperature": 0.0},
+    {"name": "qwen3_8b_b16_32768", "sizes": "8B", "batch": 16, "prompt_len": 32768, "seed": 0,
+     "steps": 64, "temperature": 0.0},
 )
 
 
